@@ -1,0 +1,12 @@
+// Convenience include of every op class this backend executes
+// (reference: include/tim/vx/ops.h lists ~110 headers; the quantized CNN path
+// needs these six).
+#ifndef TIM_VX_OPS_H_
+#define TIM_VX_OPS_H_
+#include "tim/vx/ops/activations.h"
+#include "tim/vx/ops/conv2d.h"
+#include "tim/vx/ops/elementwise.h"
+#include "tim/vx/ops/fullyconnected.h"
+#include "tim/vx/ops/pool2d.h"
+#include "tim/vx/ops/softmax.h"
+#endif  // TIM_VX_OPS_H_

@@ -1,0 +1,756 @@
+// Implementation of the tim::vx classes on top of the b2vx C ABI.
+//
+// Behaviour follows the reference's C++ layer: Context (src/tim/vx/context.cc),
+// Graph (src/tim/vx/graph.cc:91-394), Tensor (src/tim/vx/tensor.cc:105-592),
+// Operation (src/tim/vx/operation.cc:43-97) and the op constructors under
+// src/tim/vx/ops/.  Failures are reported as `false` plus one line on stderr,
+// never as exceptions.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "impl.h"
+#include "tim/vx/builtin_op.h"
+#include "tim/vx/ops/activations.h"
+#include "tim/vx/ops/conv2d.h"
+#include "tim/vx/ops/elementwise.h"
+#include "tim/vx/ops/fullyconnected.h"
+#include "tim/vx/ops/pool2d.h"
+#include "tim/vx/ops/softmax.h"
+
+namespace tim {
+namespace vx {
+
+namespace {
+
+int log_level() {
+  // Same variable and levels as the reference's logger
+  // (src/tim/vx/internal/src/vsi_nn_log.c:32-76): 0 none .. 4 debug, default 2.
+  static int lvl = [] {
+    const char* e = std::getenv("VSI_NN_LOG_LEVEL");
+    return e ? std::atoi(e) : 2;
+  }();
+  return lvl;
+}
+
+#define TVX_LOGE(...)                                   \
+  do {                                                  \
+    if (log_level() >= 1) {                             \
+      std::fprintf(stderr, "E [tim-vx/b200] ");         \
+      std::fprintf(stderr, __VA_ARGS__);                \
+      std::fprintf(stderr, "\n");                       \
+    }                                                   \
+  } while (0)
+#define TVX_LOGW(...)                                   \
+  do {                                                  \
+    if (log_level() >= 2) {                             \
+      std::fprintf(stderr, "W [tim-vx/b200] ");         \
+      std::fprintf(stderr, __VA_ARGS__);                \
+      std::fprintf(stderr, "\n");                       \
+    }                                                   \
+  } while (0)
+
+int64_t element_bytes(DataType t) {
+  switch (t) {
+    case DataType::INT8: case DataType::UINT8: case DataType::BOOL8: return 1;
+    case DataType::INT16: case DataType::UINT16: case DataType::FLOAT16: return 2;
+    case DataType::INT32: case DataType::UINT32: case DataType::FLOAT32: return 4;
+    case DataType::INT64: return 8;
+    default: return 0;
+  }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- Quantization / TensorSpec
+
+bool Quantization::operator==(const Quantization& o) const {
+  if (type_ != o.type_) return false;
+  if (type_ == QuantType::NONE) return true;
+  if (type_ == QuantType::DYNAMIC_FIXED_POINT) return fl_ == o.fl_;
+  return channel_dim_ == o.channel_dim_ && scales_ == o.scales_ && zero_points_ == o.zero_points_;
+}
+
+TensorSpec::TensorSpec(const TensorSpec& other)
+    : datatype_(other.datatype_), shape_(other.shape_), attr_(other.attr_),
+      quantization_(other.quantization_) {}
+
+TensorSpec& TensorSpec::operator=(const TensorSpec& other) {
+  datatype_ = other.datatype_;
+  shape_ = other.shape_;
+  attr_ = other.attr_;
+  quantization_ = other.quantization_;
+  return *this;
+}
+
+bool TensorSpec::operator==(const TensorSpec& o) const {
+  return datatype_ == o.datatype_ && shape_ == o.shape_ && attr_ == o.attr_ &&
+         quantization_ == o.quantization_;
+}
+
+TensorSpec& TensorSpec::SetDataType(DataType d) { datatype_ = d; return *this; }
+TensorSpec& TensorSpec::SetShape(const ShapeType& s) { shape_ = s; return *this; }
+TensorSpec& TensorSpec::SetAttribute(TensorAttribute a) { attr_ = a; return *this; }
+TensorSpec& TensorSpec::SetQuantization(Quantization& q) { quantization_ = q; return *this; }
+
+TensorSpec TensorSpec::AsTransientSpec() const {
+  return TensorSpec(datatype_, ShapeType({}), TensorAttribute::TRANSIENT, quantization_);
+}
+
+int64_t TensorSpec::GetElementNum() const {
+  int64_t n = 1;
+  for (uint32_t d : shape_) n *= d;
+  return n;
+}
+int64_t TensorSpec::GetElementByteSize() const { return element_bytes(datatype_); }
+int64_t TensorSpec::GetByteSize() const { return GetElementNum() * GetElementByteSize(); }
+
+// ---------------------------------------------------------------- CompileOption
+
+CompileOption CompileOption::DefaultOptions;
+
+CompileOption::CompileOption() : impl_(new CompileOptionImpl()) {}
+bool CompileOption::isRelaxMode() const { return impl_->relax_mode; }
+bool CompileOption::setRelaxMode(bool enable) { impl_->relax_mode = enable; return true; }
+void CompileOption::setDeviceId(uint32_t device) { impl_->device_id = device; }
+uint32_t CompileOption::getDeviceId() const { return impl_->device_id; }
+
+// ---------------------------------------------------------------- Context
+
+std::shared_ptr<Context> Context::Create() { return std::make_shared<ContextImpl>(); }
+
+ContextImpl::ContextImpl() {
+  if (b2vx_context_create(&ctx_) != B2VX_OK) {
+    TVX_LOGE("b2vx_context_create failed");
+    ctx_ = nullptr;
+  }
+}
+ContextImpl::~ContextImpl() {
+  if (ctx_) b2vx_context_destroy(ctx_);
+}
+std::shared_ptr<Graph> ContextImpl::CreateGraph() {
+  return std::make_shared<GraphImpl>(this, CompileOption::DefaultOptions);
+}
+std::shared_ptr<Graph> ContextImpl::CreateGraph(const CompileOption& options) {
+  return std::make_shared<GraphImpl>(this, options);
+}
+
+// ---------------------------------------------------------------- Tensor
+
+TensorImpl::TensorImpl(GraphImpl* graph, const TensorSpec& spec, const void* data, void* io_handle)
+    : graph_(graph), spec_(spec) {
+  if (!graph_->EnsureHandle()) return;
+  const Quantization& q = spec_.quantization_;
+  b2vx_tensor_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.dtype = static_cast<int32_t>(spec_.datatype_);
+  d.rank = static_cast<uint32_t>(spec_.shape_.size());
+  if (d.rank > B2VX_MAX_RANK) {
+    TVX_LOGE("tensor rank %u exceeds %u", d.rank, B2VX_MAX_RANK);
+    return;
+  }
+  for (uint32_t i = 0; i < d.rank; ++i) d.dims[i] = spec_.shape_[i];
+  d.attr = static_cast<int32_t>(spec_.attr_);
+  d.channel_dim = q.ChannelDim();
+  switch (q.Type()) {
+    case QuantType::NONE:
+      d.quant_type = B2VX_QUANT_NONE;
+      break;
+    case QuantType::ASYMMETRIC:
+      d.quant_type = B2VX_QUANT_ASYMMETRIC;
+      d.scale = q.Scales().empty() ? 1.0f : q.Scales()[0];
+      d.zero_point = q.ZeroPoints().empty() ? 0 : q.ZeroPoints()[0];
+      break;
+    case QuantType::SYMMETRIC_PER_CHANNEL:
+      d.quant_type = B2VX_QUANT_SYMMETRIC_PER_CHANNEL;
+      d.n_channel = static_cast<uint32_t>(q.Scales().size());
+      d.scales = q.Scales().data();
+      d.zero_points = q.ZeroPoints().size() == q.Scales().size() ? q.ZeroPoints().data() : nullptr;
+      break;
+    default:
+      TVX_LOGE("quantization type %d is not supported by this backend", static_cast<int>(q.Type()));
+      return;
+  }
+  uint32_t id = B2VX_NO_TENSOR;
+  if (b2vx_tensor_create(graph_->handle(), &d, data, &id) != B2VX_OK) {
+    graph_->LogBackendError("CreateTensor");
+    return;
+  }
+  id_ = id;
+  host_ = io_handle;
+}
+
+TensorImpl::~TensorImpl() {
+  if (host_ && host_owned_) b2vx_host_free(host_);
+}
+
+void TensorImpl::RefreshShape() {
+  if (!valid()) return;
+  b2vx_tensor_desc d;
+  if (b2vx_tensor_get_desc(graph_->handle(), id_, &d) != B2VX_OK) return;
+  spec_.shape_.assign(d.dims, d.dims + d.rank);
+}
+
+const ShapeType& TensorImpl::GetShape() { return spec_.shape_; }
+
+bool TensorImpl::CopyDataToTensor(const void* data, uint32_t /*size_in_bytes*/) {
+  if (!valid() || data == nullptr) return false;
+  if (spec_.attr_ & TensorAttribute::TRANSIENT) return false;
+  size_t bytes = static_cast<size_t>(spec_.GetByteSize());
+  if (host_ && host_ != data) std::memcpy(host_, data, bytes);
+  if (b2vx_tensor_write(graph_->handle(), id_, data, bytes) != B2VX_OK) {
+    graph_->LogBackendError("CopyDataToTensor");
+    return false;
+  }
+  return true;
+}
+
+bool TensorImpl::CopyDataFromTensor(void* data) {
+  if (!valid() || data == nullptr) return false;
+  size_t bytes = static_cast<size_t>(spec_.GetByteSize());
+  if (b2vx_tensor_read(graph_->handle(), id_, data, bytes) != B2VX_OK) {
+    graph_->LogBackendError("CopyDataFromTensor");
+    return false;
+  }
+  return true;
+}
+
+bool TensorImpl::EnsureHostBuffer() {
+  if (host_) return true;
+  size_t bytes = static_cast<size_t>(spec_.GetByteSize());
+  if (bytes == 0) return false;
+  if (b2vx_host_alloc(&host_, bytes) != B2VX_OK) {
+    host_ = nullptr;
+    return false;
+  }
+  host_owned_ = true;
+  return true;
+}
+
+// Handle semantics of the reference (src/tim/vx/tensor.cc:243-389): an
+// INPUT/OUTPUT tensor has a host side that the caller may own.  Here the host
+// side is a plain buffer; unmap()/Flush push it to the GPU, map(true)/
+// Invalidate pull the GPU copy into it.
+bool TensorImpl::SwapHandle(void* new_ptr, bool /*is_new_ptr_malloc_by_ovxlib*/, void** old_ptr) {
+  if (!valid() || !(spec_.attr_ & (TensorAttribute::INPUT | TensorAttribute::OUTPUT))) return false;
+  if (old_ptr) *old_ptr = host_owned_ ? nullptr : host_;
+  if (host_ && host_owned_) b2vx_host_free(host_);
+  host_ = new_ptr;
+  host_owned_ = false;
+  if (host_ && (spec_.attr_ & TensorAttribute::INPUT)) return FlushCacheForHandle();
+  return true;
+}
+
+bool TensorImpl::SwapHandle(std::shared_ptr<tim::vx::Tensor> tensor) {
+  auto other = std::dynamic_pointer_cast<TensorImpl>(tensor);
+  if (!other || other->spec_.GetByteSize() != spec_.GetByteSize()) return false;
+  std::swap(host_, other->host_);
+  std::swap(host_owned_, other->host_owned_);
+  return true;
+}
+
+bool TensorImpl::SwapHandleWithCache(std::shared_ptr<tim::vx::Tensor> tensor) {
+  if (!SwapHandle(tensor)) return false;
+  if (spec_.attr_ & TensorAttribute::INPUT) return host_ ? FlushCacheForHandle() : true;
+  return true;
+}
+
+bool TensorImpl::FlushCacheForHandle() {
+  if (!valid() || !host_) return false;
+  return b2vx_tensor_write(graph_->handle(), id_, host_, static_cast<size_t>(spec_.GetByteSize())) == B2VX_OK;
+}
+
+bool TensorImpl::InvalidateCacheForHandle() {
+  if (!valid() || !host_) return false;
+  return b2vx_tensor_read(graph_->handle(), id_, host_, static_cast<size_t>(spec_.GetByteSize())) == B2VX_OK;
+}
+
+void* TensorImpl::map(bool invalidate_cpu_cache) {
+  if (!valid() || !(spec_.attr_ & (TensorAttribute::INPUT | TensorAttribute::OUTPUT))) return nullptr;
+  if (!EnsureHostBuffer()) return nullptr;
+  if (invalidate_cpu_cache || (spec_.attr_ & TensorAttribute::OUTPUT)) InvalidateCacheForHandle();
+  return host_;
+}
+
+void TensorImpl::unmap() {
+  if (valid() && host_ && (spec_.attr_ & TensorAttribute::INPUT)) FlushCacheForHandle();
+}
+
+float* TensorImpl::ConvertTensorToFloat32Data() {
+  // Caller frees with free(), as with vsi_nn_ConvertTensorToFloat32Data.
+  if (!valid()) return nullptr;
+  size_t n = static_cast<size_t>(spec_.GetElementNum());
+  std::vector<uint8_t> raw(static_cast<size_t>(spec_.GetByteSize()));
+  if (!CopyDataFromTensor(raw.data())) return nullptr;
+  float* out = static_cast<float*>(std::malloc(n * sizeof(float)));
+  if (!out) return nullptr;
+  std::shared_ptr<Tensor> self(this, [](Tensor*) {});
+  if (!utils::DtypeToFloat32(self, raw.data(), out)) {
+    std::free(out);
+    return nullptr;
+  }
+  return out;
+}
+
+void* TensorImpl::ConvertTensorToData(uint8_t* tensorData) {
+  if (!valid()) return nullptr;
+  size_t bytes = static_cast<size_t>(spec_.GetByteSize());
+  if (tensorData == nullptr) tensorData = static_cast<uint8_t*>(std::malloc(bytes));
+  if (tensorData && !CopyDataFromTensor(tensorData)) return nullptr;
+  return tensorData;
+}
+
+bool TensorImpl::SaveTensorToTextByFp32(std::string filename) {
+  float* f = ConvertTensorToFloat32Data();
+  if (!f) return false;
+  FILE* fp = std::fopen(filename.c_str(), "w");
+  if (!fp) {
+    std::free(f);
+    return false;
+  }
+  for (int64_t i = 0; i < spec_.GetElementNum(); ++i) std::fprintf(fp, "%f\n", f[i]);
+  std::fclose(fp);
+  std::free(f);
+  return true;
+}
+
+namespace utils {
+
+// Element-wise conversions with the tensor's quantization
+// (reference: vsi_nn_Float32ToDtype / vsi_nn_DtypeToFloat32 via
+// src/tim/vx/tensor.cc:571-587).  Quantization uses f/scale rounded to nearest
+// even plus zero point, saturated to the type's range.
+bool Float32ToDtype(std::shared_ptr<tim::vx::Tensor> tensor, std::vector<float> fval,
+                    uint8_t* tensorData) {
+  if (!tensor || !tensorData) return false;
+  const Quantization& q = tensor->GetQuantization();
+  float scale = q.Scales().empty() ? 1.0f : q.Scales()[0];
+  int32_t zp = q.ZeroPoints().empty() ? 0 : q.ZeroPoints()[0];
+  for (size_t i = 0; i < fval.size(); ++i) {
+    switch (tensor->GetDataType()) {
+      case DataType::FLOAT32:
+        reinterpret_cast<float*>(tensorData)[i] = fval[i];
+        break;
+      case DataType::UINT8: {
+        double v = std::nearbyint(static_cast<double>(fval[i] / scale)) + zp;
+        tensorData[i] = static_cast<uint8_t>(std::min(255.0, std::max(0.0, v)));
+        break;
+      }
+      case DataType::INT8: {
+        double v = std::nearbyint(static_cast<double>(fval[i] / scale)) + zp;
+        reinterpret_cast<int8_t*>(tensorData)[i] =
+            static_cast<int8_t>(std::min(127.0, std::max(-128.0, v)));
+        break;
+      }
+      case DataType::INT32: {
+        double v = std::nearbyint(static_cast<double>(fval[i] / scale)) + zp;
+        reinterpret_cast<int32_t*>(tensorData)[i] =
+            static_cast<int32_t>(std::min(2147483647.0, std::max(-2147483648.0, v)));
+        break;
+      }
+      default:
+        return false;
+    }
+  }
+  return true;
+}
+
+bool DtypeToFloat32(std::shared_ptr<tim::vx::Tensor> tensor, uint8_t* tensorData, float* data) {
+  if (!tensor || !tensorData || !data) return false;
+  const Quantization& q = tensor->GetQuantization();
+  float scale = q.Scales().empty() ? 1.0f : q.Scales()[0];
+  int32_t zp = q.ZeroPoints().empty() ? 0 : q.ZeroPoints()[0];
+  int64_t n = tensor->GetSpec().GetElementNum();
+  for (int64_t i = 0; i < n; ++i) {
+    switch (tensor->GetDataType()) {
+      case DataType::FLOAT32: data[i] = reinterpret_cast<float*>(tensorData)[i]; break;
+      case DataType::UINT8: data[i] = (static_cast<float>(tensorData[i]) - zp) * scale; break;
+      case DataType::INT8:
+        data[i] = (static_cast<float>(reinterpret_cast<int8_t*>(tensorData)[i]) - zp) * scale;
+        break;
+      case DataType::INT32:
+        data[i] = (static_cast<float>(reinterpret_cast<int32_t*>(tensorData)[i]) - zp) * scale;
+        break;
+      default: return false;
+    }
+  }
+  return true;
+}
+
+}  // namespace utils
+
+// ---------------------------------------------------------------- Graph
+
+GraphImpl::GraphImpl(ContextImpl* context, const CompileOption& options)
+    : context_(context), options_(options) {}
+
+GraphImpl::~GraphImpl() {
+  // Ops and tensors hold raw pointers to this graph; release them first.
+  op_vector_.clear();
+  tensor_consumers_.clear();
+  tensor_producer_.clear();
+  inputs_tensor_.clear();
+  outputs_tensor_.clear();
+  if (graph_) b2vx_graph_destroy(graph_);
+}
+
+bool GraphImpl::EnsureHandle() {
+  if (graph_) return true;
+  if (!context_ || !context_->handle()) return false;
+  int32_t dev = static_cast<int32_t>(options_.getDeviceId());
+  if (const char* e = std::getenv("B2VX_DEVICE")) dev = std::atoi(e);
+  if (b2vx_graph_create(context_->handle(), dev, &graph_) != B2VX_OK) {
+    LogBackendError("CreateGraph");
+    graph_ = nullptr;
+    return false;
+  }
+  return true;
+}
+
+void GraphImpl::LogBackendError(const char* where) const {
+  TVX_LOGE("%s: %s", where, context_ && context_->handle() ? b2vx_last_error(context_->handle()) : "no context");
+}
+
+std::shared_ptr<Tensor> GraphImpl::CreateTensor(const TensorSpec& spec, const void* data) {
+  auto t = std::make_shared<TensorImpl>(this, spec, data, nullptr);
+  if (!t->valid()) return nullptr;
+  if (spec.attr_ & TensorAttribute::INPUT) inputs_tensor_.push_back(t);
+  if (spec.attr_ & TensorAttribute::OUTPUT) outputs_tensor_.push_back(t);
+  all_tensors_.push_back(t);
+  return t;
+}
+
+std::shared_ptr<Tensor> GraphImpl::CreateTensor(const TensorSpec& /*spec*/, const DmaBufferDesc& /*dmafd*/) {
+  TVX_LOGE("dma-buf backed tensors are not supported");
+  return nullptr;
+}
+
+std::shared_ptr<Tensor> GraphImpl::CreateIOTensor(const TensorSpec& spec, void* data) {
+  if (!(spec.attr_ & (TensorAttribute::INPUT | TensorAttribute::OUTPUT))) {
+    TVX_LOGE("CreateIOTensor needs an INPUT or OUTPUT spec");
+    return nullptr;
+  }
+  auto t = std::make_shared<TensorImpl>(this, spec, nullptr, data);
+  if (!t->valid()) return nullptr;
+  // As in the reference (src/tim/vx/tensor.cc:126-137) IO tensors made here
+  // are not appended to the graph's input/output lists.
+  all_tensors_.push_back(t);
+  return t;
+}
+
+std::shared_ptr<Tensor> GraphImpl::CreateTensorPlaceHolder() {
+  return std::make_shared<TensorPlaceholder>();
+}
+
+void GraphImpl::UpdateTensorConsumersMap(const std::shared_ptr<Tensor>& tensor, const Operation* op) {
+  for (const auto& sp : op_vector_) {
+    if (sp.get() == op) {
+      tensor_consumers_[tensor].push_back(sp);
+      return;
+    }
+  }
+}
+
+void GraphImpl::RenewTensorConsumersMap(const std::shared_ptr<Tensor>& org_tensor,
+                                        const std::shared_ptr<Tensor>& dst_tensor,
+                                        const Operation* op) {
+  auto it = tensor_consumers_.find(org_tensor);
+  if (it != tensor_consumers_.end()) {
+    auto& v = it->second;
+    v.erase(std::remove_if(v.begin(), v.end(), [op](const std::shared_ptr<Operation>& p) { return p.get() == op; }),
+            v.end());
+    if (v.empty()) tensor_consumers_.erase(it);
+  }
+  UpdateTensorConsumersMap(dst_tensor, op);
+}
+
+void GraphImpl::UpdateTensorProducerMap(const std::shared_ptr<Tensor>& tensor, const Operation* op) {
+  for (const auto& sp : op_vector_) {
+    if (sp.get() == op) {
+      tensor_producer_[tensor] = sp;
+      return;
+    }
+  }
+}
+
+const std::vector<std::shared_ptr<Operation>> GraphImpl::GetConsumersOp(std::shared_ptr<Tensor> tensor) const {
+  auto it = tensor_consumers_.find(tensor);
+  if (it == tensor_consumers_.end()) return {};
+  return it->second;
+}
+
+std::shared_ptr<Operation> GraphImpl::GetProducerOp(std::shared_ptr<Tensor> tensor) {
+  auto it = tensor_producer_.find(tensor);
+  return it == tensor_producer_.end() ? nullptr : it->second;
+}
+
+const std::vector<std::shared_ptr<Tensor>> Graph::GetConstantInputs() const {
+  std::vector<std::shared_ptr<Tensor>> out;
+  for (const auto& op : op_vector_) {
+    auto c = op->ConstantInputsTensor();
+    out.insert(out.end(), c.begin(), c.end());
+  }
+  return out;
+}
+
+bool GraphImpl::EmitNodes() {
+  for (const auto& op : op_vector_) {
+    OpImpl* p = op->impl().get();
+    auto in = [&](size_t i) -> uint32_t {
+      return i < p->inputs_tensor_.size() && p->inputs_tensor_[i] ? p->inputs_tensor_[i]->GetId() : B2VX_NO_TENSOR;
+    };
+    auto out = [&](size_t i) -> uint32_t {
+      return i < p->outputs_tensor_.size() && p->outputs_tensor_[i] ? p->outputs_tensor_[i]->GetId() : B2VX_NO_TENSOR;
+    };
+    b2vx_status st = B2VX_UNSUPPORTED;
+    switch (p->kind_) {
+      case B2VX_NODE_CONV2D: st = b2vx_node_conv2d(graph_, in(0), in(1), in(2), out(0), &p->desc_.conv2d); break;
+      case B2VX_NODE_FULLY_CONNECTED:
+        st = b2vx_node_fully_connected(graph_, in(0), in(1), in(2), out(0), &p->desc_.fc);
+        break;
+      case B2VX_NODE_POOL2D: st = b2vx_node_pool2d(graph_, in(0), out(0), &p->desc_.pool2d); break;
+      case B2VX_NODE_ADD: st = b2vx_node_add(graph_, in(0), in(1), out(0)); break;
+      case B2VX_NODE_RELU: st = b2vx_node_relu(graph_, in(0), out(0)); break;
+      case B2VX_NODE_RELU6: st = b2vx_node_relu6(graph_, in(0), out(0)); break;
+      case B2VX_NODE_SOFTMAX: st = b2vx_node_softmax(graph_, in(0), out(0), &p->desc_.softmax); break;
+      default: break;
+    }
+    if (st != B2VX_OK) {
+      LogBackendError("AddNode");
+      return false;
+    }
+  }
+  return true;
+}
+
+bool GraphImpl::Compile() {
+  std::call_once(compile_once_, [this] {
+    if (!EnsureHandle()) return;
+    if (!EmitNodes()) return;
+    if (b2vx_graph_compile(graph_) != B2VX_OK) {
+      LogBackendError("Compile");
+      return;
+    }
+    for (auto& w : all_tensors_) {
+      if (auto t = w.lock()) t->RefreshShape();
+    }
+    compiled_ok_ = true;
+  });
+  return compiled_ok_;
+}
+
+bool GraphImpl::CompileToBinary(void* /*buf*/, size_t* /*size*/) {
+  TVX_LOGE("CompileToBinary: serialised graphs are not provided by this backend");
+  return false;
+}
+
+bool GraphImpl::Run() {
+  if (!Compile()) return false;
+  if (b2vx_graph_run(graph_) != B2VX_OK) {
+    LogBackendError("Run");
+    return false;
+  }
+  return true;
+}
+
+void GraphImpl::PrintGraph() const {
+  if (graph_) b2vx_graph_print(graph_);
+}
+
+// ---------------------------------------------------------------- Operation
+
+OpImpl::OpImpl(Graph* graph, uint32_t kind, int in_cnt, int out_cnt, DataLayout layout)
+    : graph_(graph), kind_(kind), input_cnt_(in_cnt), output_cnt_(out_cnt), layout_(layout),
+      uid_(static_cast<GraphImpl*>(graph)->NextOpUid()) {
+  std::memset(&desc_, 0, sizeof(desc_));
+}
+
+Operation::Operation() {}
+Operation::~Operation() {}
+
+std::unique_ptr<OpImpl>& Operation::impl() { return impl_; }
+const std::unique_ptr<OpImpl>& Operation::impl() const { return impl_; }
+const uint32_t& Operation::uid() const { return impl_->uid_; }
+
+Operation& Operation::BindInput(const std::shared_ptr<Tensor>& tensor) {
+  impl_->inputs_tensor_.push_back(tensor);
+  if (tensor && !tensor->IsPlaceHolder()) impl_->graph_->UpdateTensorConsumersMap(tensor, this);
+  OnBindInputPostProc(tensor, static_cast<int32_t>(impl_->inputs_tensor_.size()) - 1);
+  return *this;
+}
+
+Operation& Operation::BindOutput(const std::shared_ptr<Tensor>& tensor) {
+  impl_->outputs_tensor_.push_back(tensor);
+  if (tensor) impl_->graph_->UpdateTensorProducerMap(tensor, this);
+  return *this;
+}
+
+Operation& Operation::BindInputs(const std::vector<std::shared_ptr<Tensor>>& tensors) {
+  for (const auto& t : tensors) BindInput(t);
+  return *this;
+}
+
+Operation& Operation::BindOutputs(const std::vector<std::shared_ptr<Tensor>>& tensors) {
+  for (const auto& t : tensors) BindOutput(t);
+  return *this;
+}
+
+Operation& Operation::SetRoundingPolicy(OverflowPolicy, RoundingPolicy, RoundType, uint32_t) { return *this; }
+
+const std::vector<std::shared_ptr<Tensor>> Operation::ConstantInputsTensor() const {
+  if (IsAllInputsConst()) return impl_->inputs_tensor_;
+  return {};
+}
+
+bool Operation::IsAllInputsConst() const {
+  for (const auto& t : impl_->inputs_tensor_) {
+    if (!t || !t->IsConstTensor()) return false;
+  }
+  return true;
+}
+
+void Operation::OnBindInputPostProc(const std::shared_ptr<Tensor>&, int32_t) {}
+
+BuiltinOp::BuiltinOp(Graph* graph, uint32_t kind, int in_cnt, int out_cnt, DataLayout layout) {
+  impl_.reset(new OpImpl(graph, kind, in_cnt, out_cnt, layout));
+}
+
+// ---------------------------------------------------------------- ops
+
+namespace ops {
+
+Conv2d::Conv2d(Graph* graph, PadType padding, const std::array<uint32_t, 2>& stride,
+               const std::array<uint32_t, 2>& dilation, int32_t multiplier, DataLayout input_layout,
+               DataLayout kernel_layout)
+    : Conv2d(graph, 0, padding, {0, 0}, stride, dilation, {0, 0, 0, 0}, multiplier, input_layout, kernel_layout) {}
+
+Conv2d::Conv2d(Graph* graph, const std::array<uint32_t, 4> pad, const std::array<uint32_t, 2>& stride,
+               const std::array<uint32_t, 2>& dilation, int32_t multiplier, DataLayout input_layout,
+               DataLayout kernel_layout)
+    : Conv2d(graph, 0, PadType::AUTO, {0, 0}, stride, dilation, pad, multiplier, input_layout, kernel_layout) {}
+
+Conv2d::Conv2d(Graph* graph, int32_t weights, PadType padding, const std::array<uint32_t, 2>& ksize,
+               const std::array<uint32_t, 2>& stride, const std::array<uint32_t, 2>& dilation,
+               int32_t multiplier, DataLayout input_layout, DataLayout kernel_layout)
+    : Conv2d(graph, weights, padding, ksize, stride, dilation, {0, 0, 0, 0}, multiplier, input_layout,
+             kernel_layout) {}
+
+Conv2d::Conv2d(Graph* graph, int32_t weights, PadType padding, const std::array<uint32_t, 2>& ksize,
+               const std::array<uint32_t, 2>& stride, const std::array<uint32_t, 2>& dilation,
+               const std::array<uint32_t, 4>& pad, int32_t multiplier, DataLayout input_layout,
+               DataLayout kernel_layout)
+    : BuiltinOp(graph, B2VX_NODE_CONV2D, 0, 0, input_layout),
+      weights_(weights), padding_(padding), ksize_(ksize), stride_(stride), dilation_(dilation),
+      pad_(pad), multiplier_(multiplier), kernel_layout_(kernel_layout) {
+  b2vx_conv2d_desc& d = impl_->desc_.conv2d;
+  d.weights = weights_;
+  d.pad_type = static_cast<int32_t>(padding_);
+  for (int i = 0; i < 2; ++i) {
+    d.ksize[i] = ksize_[i];
+    d.stride[i] = stride_[i];
+    d.dilation[i] = dilation_[i];
+  }
+  for (int i = 0; i < 4; ++i) d.pad[i] = pad_[i];
+  d.multiplier = multiplier_;
+  if (input_layout != DataLayout::WHCN && input_layout != DataLayout::ANY)
+    TVX_LOGW("Conv2d: only WHCN input layout is executed; run layout inference first");
+  if (kernel_layout != DataLayout::WHIcOc && kernel_layout != DataLayout::ANY)
+    TVX_LOGW("Conv2d: only WHIcOc kernel layout is executed");
+}
+
+std::shared_ptr<Operation> Conv2d::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<Conv2d>(static_cast<int32_t>(weights_), padding_, ksize_, stride_, dilation_, pad_,
+                                        multiplier_, impl_->layout_, kernel_layout_);
+}
+
+const std::vector<std::shared_ptr<Tensor>> Conv2d::ConstantInputsTensor() const {
+  if (IsAllInputsConst()) return {impl_->inputs_tensor_[0]};
+  return {};
+}
+
+FullyConnected::FullyConnected(Graph* graph, uint32_t axis) : FullyConnected(graph, axis, 0) {}
+
+FullyConnected::FullyConnected(Graph* graph, uint32_t axis, uint32_t weights)
+    : BuiltinOp(graph, B2VX_NODE_FULLY_CONNECTED), axis_(axis), weights_(weights) {
+  impl_->desc_.fc.axis = axis;
+  impl_->desc_.fc.weights = weights;
+}
+
+std::shared_ptr<Operation> FullyConnected::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<FullyConnected>(axis_, weights_);
+}
+
+Pool2d::Pool2d(Graph* graph, PoolType type, PadType padding, const std::array<uint32_t, 2>& ksize,
+               const std::array<uint32_t, 2>& stride, RoundType round_type, DataLayout layout)
+    : BuiltinOp(graph, B2VX_NODE_POOL2D, 1, 1, layout),
+      type_(type), padding_(padding), ksize_(ksize), stride_(stride), round_type_(round_type),
+      pad_({0, 0, 0, 0}) {
+  Init();
+}
+
+Pool2d::Pool2d(Graph* graph, PoolType type, const std::array<uint32_t, 4>& pad,
+               const std::array<uint32_t, 2>& ksize, const std::array<uint32_t, 2>& stride,
+               RoundType round_type, DataLayout layout)
+    : BuiltinOp(graph, B2VX_NODE_POOL2D, 1, 1, layout),
+      type_(type), padding_(PadType::AUTO), ksize_(ksize), stride_(stride), round_type_(round_type), pad_(pad) {
+  Init();
+}
+
+Pool2d::Pool2d(Graph* graph, PoolType type, const std::array<uint32_t, 2>& input_size, RoundType round_type,
+               DataLayout layout)
+    : BuiltinOp(graph, B2VX_NODE_POOL2D, 1, 1, layout),
+      type_(type), padding_(PadType::AUTO), ksize_(input_size), stride_(input_size), round_type_(round_type),
+      pad_({0, 0, 0, 0}) {
+  Init();
+}
+
+Pool2d::Pool2d(Graph* graph, PoolType type, const std::array<uint32_t, 2>& input_size,
+               const std::array<uint32_t, 2>& output_size, RoundType round_type, DataLayout layout)
+    : BuiltinOp(graph, B2VX_NODE_POOL2D, 1, 1, layout),
+      type_(type), padding_(PadType::AUTO), round_type_(round_type), pad_({0, 0, 0, 0}) {
+  for (int i = 0; i < 2; ++i) {
+    stride_[i] = static_cast<uint32_t>(std::floor(input_size[i] / static_cast<float>(output_size[i])));
+    ksize_[i] = input_size[i] - (output_size[i] - 1) * stride_[i];
+  }
+  Init();
+}
+
+void Pool2d::Init() {
+  b2vx_pool2d_desc& d = impl_->desc_.pool2d;
+  d.type = static_cast<int32_t>(type_);
+  d.pad_type = static_cast<int32_t>(padding_);
+  d.round_type = static_cast<int32_t>(round_type_);
+  for (int i = 0; i < 2; ++i) {
+    d.ksize[i] = ksize_[i];
+    d.stride[i] = stride_[i];
+  }
+  for (int i = 0; i < 4; ++i) d.pad[i] = pad_[i];
+}
+
+std::shared_ptr<Operation> Pool2d::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<Pool2d>(type_, pad_, ksize_, stride_, round_type_, impl_->layout_);
+}
+
+Add::Add(Graph* graph) : BuiltinOp(graph, B2VX_NODE_ADD, 2, 1) {}
+std::shared_ptr<Operation> Add::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Add>(); }
+
+Relu::Relu(Graph* graph) : BuiltinOp(graph, B2VX_NODE_RELU, 1, 1) {}
+std::shared_ptr<Operation> Relu::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Relu>(); }
+
+Relu6::Relu6(Graph* graph) : BuiltinOp(graph, B2VX_NODE_RELU6, 1, 1) {}
+std::shared_ptr<Operation> Relu6::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Relu6>(); }
+
+Softmax::Softmax(Graph* graph, float beta, int32_t axis)
+    : BuiltinOp(graph, B2VX_NODE_SOFTMAX, 1, 1), beta_(beta), axis_(axis) {
+  impl_->desc_.softmax.beta = beta;
+  impl_->desc_.softmax.axis = axis;
+}
+std::shared_ptr<Operation> Softmax::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<Softmax>(beta_, axis_);
+}
+
+}  // namespace ops
+}  // namespace vx
+}  // namespace tim
