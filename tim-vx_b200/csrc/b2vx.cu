@@ -1,0 +1,1244 @@
+// b2vx C ABI on CUDA: graph bookkeeping, validation, shape inference, weight
+// packing and the launch plan.  (Entry points are documented in b2vx.h.)
+//
+// What Compile does — the part the reference spreads over vsi_nn_SetupGraph /
+// vsi_nn_VerifyGraph (src/tim/vx/internal/src/vsi_nn_graph.c:1450-1603) and
+// the closed driver's vxVerifyGraph:
+//   1. order nodes by data dependency;
+//   2. per node: dtype/quantization checks, padding and output-shape rules
+//      (vsi_nn_op_conv2d.c:199-287, vsi_nn_op_pool.c:324-427,
+//      vsi_nn_op_fullconnect2.c:154-196, vsi_nn_util.c:483-588);
+//   3. give every activation tensor channels-last device storage (kernels.h);
+//   4. pack constants for the kernel chosen per node: int8-shifted weight
+//      matrix [rows][Kp], folded bias (bias - zx*sum(w) + K*zx*dz), per-tap
+//      border corrections, per-channel accumulator scales;
+//   5. record one launch closure per kernel.
+// Run replays the closures on the graph's stream.
+//
+// There is no CPU execution path: without a CUDA device graph creation fails.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "b2vx.h"
+#include "kernels.h"
+
+using namespace b2vx;
+
+namespace {
+
+size_t dtype_size(int32_t dt) {
+  switch (dt) {
+    case B2VX_DT_INT8: case B2VX_DT_UINT8: case B2VX_DT_BOOL8: return 1;
+    case B2VX_DT_INT16: case B2VX_DT_UINT16: case B2VX_DT_FLOAT16: return 2;
+    case B2VX_DT_INT32: case B2VX_DT_UINT32: case B2VX_DT_FLOAT32: return 4;
+    case B2VX_DT_INT64: return 8;
+    default: return 0;
+  }
+}
+bool is_q8(int32_t dt) { return dt == B2VX_DT_INT8 || dt == B2VX_DT_UINT8; }
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+struct TensorRec {
+  b2vx_tensor_desc d;
+  std::vector<float> scales;
+  std::vector<int32_t> zps;
+  bool has_shape = false;
+  std::vector<uint8_t> host;   // constants, and data written before compile (WHCN order)
+  bool host_valid = false;
+  // device side
+  int W = 1, H = 1, C = 1, N = 1, Cp = 0;
+  void* d_cl = nullptr;        // channels-last storage
+  void* d_io = nullptr;        // WHCN copy for graph inputs/outputs (== d_cl when both layouts coincide)
+  size_t cl_bytes = 0, io_bytes = 0;
+  bool is_activation = false;
+
+  size_t elems() const {
+    size_t n = 1;
+    for (uint32_t i = 0; i < d.rank; ++i) n *= d.dims[i];
+    return n;
+  }
+  size_t bytes() const { return elems() * dtype_size(d.dtype); }
+  float scale() const { return d.quant_type == B2VX_QUANT_ASYMMETRIC ? d.scale : 1.0f; }
+  int32_t zp() const { return d.quant_type == B2VX_QUANT_ASYMMETRIC ? d.zero_point : 0; }
+  bool same_layouts() const { return H == 1 && W == 1 && Cp == C; }
+};
+
+struct NodeRec {
+  int32_t kind;
+  uint32_t in[3];
+  uint32_t out;
+  union {
+    b2vx_conv2d_desc conv;
+    b2vx_fc_desc fc;
+    b2vx_pool2d_desc pool;
+    b2vx_softmax_desc softmax;
+  } p;
+  uint32_t pad[4];
+};
+
+struct Step {
+  b2vx_kernel_info info;
+  std::function<cudaError_t(cudaStream_t)> fn;
+};
+
+}  // namespace
+
+struct b2vx_context {
+  std::string err;
+};
+
+struct b2vx_graph {
+  b2vx_context* ctx = nullptr;
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  std::vector<TensorRec> tensors;
+  std::vector<NodeRec> nodes;
+  std::vector<uint32_t> order;
+  std::vector<Step> steps;
+  std::vector<void*> allocs;
+  std::vector<GemmTcPlan*> gemm_plans;
+  std::vector<std::function<b2vx_status()>> finalizers;   // run once device scratch exists
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int* d_status = nullptr;
+  int* h_status = nullptr;
+  bool compiled = false;
+  bool use_tc = false;
+};
+
+namespace {
+
+b2vx_status fail(b2vx_graph* g, b2vx_status st, const std::string& msg) {
+  if (g && g->ctx) g->ctx->err = msg;
+  return st;
+}
+
+#define CUDA_TRY(g, expr)                                                                         \
+  do {                                                                                            \
+    cudaError_t _e = (expr);                                                                      \
+    if (_e != cudaSuccess)                                                                        \
+      return fail((g), B2VX_CUDA_ERROR, std::string(#expr) + ": " + cudaGetErrorString(_e));      \
+  } while (0)
+
+bool valid_id(const b2vx_graph* g, uint32_t id) { return id < g->tensors.size(); }
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+    else prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+b2vx_status dev_alloc(b2vx_graph* g, void** out, size_t bytes) {
+  *out = nullptr;
+  if (bytes == 0) bytes = 16;
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e != cudaSuccess) return fail(g, B2VX_OOM, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+  g->allocs.push_back(*out);
+  return B2VX_OK;
+}
+
+template <typename T>
+b2vx_status upload(b2vx_graph* g, const std::vector<T>& v, T** out) {
+  void* p = nullptr;
+  b2vx_status st = dev_alloc(g, &p, v.size() * sizeof(T));
+  if (st != B2VX_OK) return st;
+  if (!v.empty()) CUDA_TRY(g, cudaMemcpy(p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+  *out = static_cast<T*>(p);
+  return B2VX_OK;
+}
+
+// ---------------------------------------------------------------- shapes
+
+// vsi_nn_ComputeFilterSize (src/tim/vx/internal/src/utils/vsi_nn_util.c:483-511)
+uint32_t filter_size(uint32_t in, uint32_t k, uint32_t pad0, uint32_t pad1, uint32_t stride, uint32_t dilation, int32_t round_type) {
+  if (stride == 0) {
+    if (in != k) return 0;
+    stride = 1;
+  }
+  if (dilation > 1) k = dilation * (k - 1) + 1;
+  const int64_t span = static_cast<int64_t>(in) + pad0 + pad1 - k;
+  if (span < 0) return 0;
+  const uint32_t steps = round_type == B2VX_ROUND_CEILING ? static_cast<uint32_t>((span + stride - 1) / stride)
+                                                          : static_cast<uint32_t>(span / stride);
+  return steps + 1;
+}
+
+// vsi_nn_compute_padding (vsi_nn_util.c:535-588): SAME -> out = ceil(in/stride),
+// odd padding goes to the end; VALID -> none; AUTO/NONE -> the explicit values.
+void resolve_pads(int32_t pad_type, const uint32_t in[2], const uint32_t k[2], const uint32_t stride[2],
+                  const uint32_t dil[2], const uint32_t explicit_pad[4], uint32_t out[4]) {
+  for (int i = 0; i < 4; ++i) out[i] = explicit_pad[i];
+  if (pad_type != B2VX_PAD_SAME && pad_type != B2VX_PAD_VALID) return;
+  uint32_t d[2] = {dil[0], dil[1]};
+  if (d[0] == 0 && d[1] == 0) d[0] = d[1] = 1;
+  for (int a = 0; a < 2; ++a) {
+    const uint32_t dl = d[a] ? d[a] : 1, st = stride[a] ? stride[a] : 1;
+    const int64_t eff = static_cast<int64_t>(k[a] - 1) * dl + 1;
+    const int64_t o = pad_type == B2VX_PAD_SAME ? (static_cast<int64_t>(in[a]) + st - 1) / st
+                                                : (static_cast<int64_t>(in[a]) + st - eff) / st;
+    int64_t total = (o - 1) * st + eff - in[a];
+    if (total < 0) total = 0;
+    out[2 * a] = static_cast<uint32_t>(total / 2);
+    out[2 * a + 1] = static_cast<uint32_t>(total - total / 2);
+  }
+}
+
+// A declared output shape wins over the inferred one; for conv/pool it may be
+// smaller in W/H (the reference's own depthwise padding test relies on that:
+// src/tim/vx/ops/depthwiseConv_test.cc:268-330).
+b2vx_status set_shape(b2vx_graph* g, uint32_t id, const std::vector<uint32_t>& dims, const char* what, bool spatial_may_shrink) {
+  TensorRec& t = g->tensors[id];
+  if (t.has_shape) {
+    bool ok = t.d.rank == dims.size();
+    for (size_t i = 0; ok && i < dims.size(); ++i) {
+      if (spatial_may_shrink && i < 2) ok = t.d.dims[i] >= 1 && t.d.dims[i] <= dims[i];
+      else ok = t.d.dims[i] == dims[i];
+    }
+    if (!ok) return fail(g, B2VX_SHAPE_MISMATCH, std::string(what) + ": declared output shape differs from the inferred one");
+    return B2VX_OK;
+  }
+  t.d.rank = static_cast<uint32_t>(dims.size());
+  for (size_t i = 0; i < dims.size(); ++i) t.d.dims[i] = dims[i];
+  t.has_shape = true;
+  return B2VX_OK;
+}
+
+b2vx_status infer_node(b2vx_graph* g, NodeRec& n) {
+  const TensorRec& x = g->tensors[n.in[0]];
+  if (!x.has_shape) return fail(g, B2VX_SHAPE_MISMATCH, "node input has no shape");
+  switch (n.kind) {
+    case B2VX_NODE_CONV2D: {
+      const TensorRec& w = g->tensors[n.in[1]];
+      if (x.d.rank < 3 || x.d.rank > 4 || w.d.rank != 4) return fail(g, B2VX_SHAPE_MISMATCH, "conv2d: input must be rank 3/4 and kernel rank 4");
+      const b2vx_conv2d_desc& c = n.p.conv;
+      const uint32_t in2[2] = {x.d.dims[0], x.d.dims[1]}, k2[2] = {w.d.dims[0], w.d.dims[1]};
+      resolve_pads(c.pad_type, in2, k2, c.stride, c.dilation, c.pad, n.pad);
+      const uint32_t wo = filter_size(in2[0], k2[0], n.pad[0], n.pad[1], c.stride[0], c.dilation[0], B2VX_ROUND_FLOOR);
+      const uint32_t ho = filter_size(in2[1], k2[1], n.pad[2], n.pad[3], c.stride[1], c.dilation[1], B2VX_ROUND_FLOOR);
+      if (wo == 0 || ho == 0) return fail(g, B2VX_SHAPE_MISMATCH, "conv2d: kernel larger than padded input");
+      const uint32_t oc = c.weights > 0 ? c.weights : (c.multiplier > 0 ? x.d.dims[2] * c.multiplier : w.d.dims[3]);
+      std::vector<uint32_t> dims = {wo, ho, oc};
+      if (x.d.rank == 4) dims.push_back(x.d.dims[3]);
+      return set_shape(g, n.out, dims, "conv2d", true);
+    }
+    case B2VX_NODE_FULLY_CONNECTED: {
+      const TensorRec& w = g->tensors[n.in[1]];
+      if (w.d.rank != 2 || n.p.fc.axis >= x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "fully_connected: weights must be rank 2 and axis inside the input rank");
+      std::vector<uint32_t> dims = {n.p.fc.weights ? n.p.fc.weights : w.d.dims[1]};
+      for (uint32_t i = n.p.fc.axis + 1; i < x.d.rank; ++i) dims.push_back(x.d.dims[i]);
+      if (dims.size() == 1) dims.push_back(1);
+      TensorRec& y = g->tensors[n.out];
+      if (y.has_shape) {
+        size_t want = 1;
+        for (uint32_t v : dims) want *= v;
+        if (y.elems() != want || y.d.dims[0] != dims[0]) return fail(g, B2VX_SHAPE_MISMATCH, "fully_connected: declared output shape");
+        return B2VX_OK;
+      }
+      return set_shape(g, n.out, dims, "fully_connected", false);
+    }
+    case B2VX_NODE_POOL2D: {
+      if (x.d.rank < 3 || x.d.rank > 4) return fail(g, B2VX_SHAPE_MISMATCH, "pool2d: input must be rank 3 or 4");
+      const b2vx_pool2d_desc& c = n.p.pool;
+      const uint32_t in2[2] = {x.d.dims[0], x.d.dims[1]}, dil[2] = {1, 1};
+      resolve_pads(c.pad_type, in2, c.ksize, c.stride, dil, c.pad, n.pad);
+      const uint32_t wo = filter_size(in2[0], c.ksize[0], n.pad[0], n.pad[1], c.stride[0], 1, c.round_type);
+      const uint32_t ho = filter_size(in2[1], c.ksize[1], n.pad[2], n.pad[3], c.stride[1], 1, c.round_type);
+      if (wo == 0 || ho == 0) return fail(g, B2VX_SHAPE_MISMATCH, "pool2d: window larger than padded input");
+      std::vector<uint32_t> dims = {wo, ho};
+      for (uint32_t i = 2; i < x.d.rank; ++i) dims.push_back(x.d.dims[i]);
+      return set_shape(g, n.out, dims, "pool2d", true);
+    }
+    case B2VX_NODE_ADD: {
+      const TensorRec& b = g->tensors[n.in[1]];
+      if (!b.has_shape) return fail(g, B2VX_SHAPE_MISMATCH, "add: input has no shape");
+      if (b.d.rank != x.d.rank || !std::equal(x.d.dims, x.d.dims + x.d.rank, b.d.dims))
+        return fail(g, B2VX_UNSUPPORTED, "add: broadcasting is not supported, operands must have equal shapes");
+      return set_shape(g, n.out, std::vector<uint32_t>(x.d.dims, x.d.dims + x.d.rank), "add", false);
+    }
+    default:
+      return set_shape(g, n.out, std::vector<uint32_t>(x.d.dims, x.d.dims + x.d.rank), "unary", false);
+  }
+}
+
+// tim::vx dims -> (W,H,C,N): rank 4 as is, rank 3 = [W,H,C], rank 2 = [C,N], rank 1 = [C].
+void map_dims(TensorRec& t) {
+  t.W = t.H = t.C = t.N = 1;
+  const uint32_t* d = t.d.dims;
+  switch (t.d.rank) {
+    case 4: t.W = d[0]; t.H = d[1]; t.C = d[2]; t.N = d[3]; break;
+    case 3: t.W = d[0]; t.H = d[1]; t.C = d[2]; break;
+    case 2: t.C = d[0]; t.N = d[1]; break;
+    case 1: t.C = d[0]; break;
+    default: break;
+  }
+  const int per16 = static_cast<int>(16 / dtype_size(t.d.dtype));
+  t.Cp = round_up(t.C, per16);
+  t.cl_bytes = static_cast<size_t>(t.N) * t.H * t.W * t.Cp * dtype_size(t.d.dtype);
+  t.io_bytes = t.bytes();
+}
+
+OutQuant out_quant(const TensorRec& t) {
+  OutQuant q;
+  q.scale = t.scale();
+  q.zp = t.zp();
+  if (t.d.dtype == B2VX_DT_INT8) { q.lo = -128; q.hi = 127; }
+  else if (t.d.dtype == B2VX_DT_UINT8) { q.lo = 0; q.hi = 255; }
+  else { q.lo = INT32_MIN; q.hi = INT32_MAX; }
+  return q;
+}
+
+b2vx_kernel_info make_info(const char* name, uint32_t node, uint64_t ops, uint64_t bytes) {
+  b2vx_kernel_info i;
+  std::memset(&i, 0, sizeof(i));
+  std::snprintf(i.name, sizeof(i.name), "%s", name);
+  i.node_index = node;
+  i.ops = ops;
+  i.bytes = bytes;
+  return i;
+}
+
+ConvGeom conv_geom(const TensorRec& x, const TensorRec& y, int kw, int kh, const uint32_t stride[2], const uint32_t dil[2], const uint32_t pad[4]) {
+  ConvGeom g;
+  g.N = x.N; g.H = x.H; g.W = x.W; g.C = x.C; g.Cp = x.Cp;
+  g.Ho = y.H; g.Wo = y.W; g.Oc = y.C; g.Ocp = y.Cp;
+  g.kh = kh; g.kw = kw;
+  g.sx = stride[0] ? stride[0] : 1; g.sy = stride[1] ? stride[1] : 1;
+  g.dx = dil[0] ? dil[0] : 1; g.dy = dil[1] ? dil[1] : 1;
+  g.pl = pad[0]; g.pt = pad[2];
+  return g;
+}
+
+// vsi_nn_QuantCheck (src/tim/vx/internal/src/utils/vsi_nn_dtype_util.c:368-441):
+// only same-dtype, same-quantization-kind triples are checked; the bias scale
+// has to equal s_in*s_w within max(min(.)*1e-5, 1e-8)
+// (src/tim/vx/internal/src/quantization/vsi_nn_asymmetric_affine.c:59-112).
+bool quant_check(const TensorRec& x, const TensorRec& w, const TensorRec* b) {
+  if (x.d.dtype != w.d.dtype || x.d.quant_type != w.d.quant_type) return true;
+  if (b && b->d.quant_type != x.d.quant_type) return true;
+  if (!is_q8(x.d.dtype) || x.d.quant_type != B2VX_QUANT_ASYMMETRIC) return true;
+  if (!b || b->d.scale == 0.0f) return true;
+  const double prod = static_cast<double>(x.d.scale) * static_cast<double>(w.d.scale), bs = b->d.scale;
+  return std::fabs(prod - bs) <= std::max(std::min(prod, bs) * 1e-5, 1e-8);
+}
+
+// ---------------------------------------------------------------- contraction planning (conv2d dense, fully connected)
+
+struct PackedContraction {
+  std::vector<int8_t> w8;          // [rows][Kp]
+  std::vector<int32_t> bias_full;  // [Ocp]
+  std::vector<float> acc_scale;    // [Ocp]
+  std::vector<int32_t> dz;         // [Ocp]
+  std::vector<int32_t> tapc;       // [taps][Ocp]
+  bool need_s = false;
+  int rows = 0, Kp = 0;
+};
+
+// Weight element (kx,ky,ic,oc) of a WHIcOc kernel as a signed value together
+// with the zero point that still has to be subtracted from it: u8 weights are
+// shifted by 128 into int8 (dz = zw-128), s8 weights are kept (dz = zw).
+// K index = tap*Cs + ic; rows are output channels (+ the all-ones row at index
+// rows_before_ones when some dz != 0 and with_ones_row is set).
+void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* bias, int kw, int kh, int C, int Cs,
+                      int Kp, int Oc, int Ocp, int rows, bool zero_fill_semantics, bool with_ones_row,
+                      PackedContraction* out) {
+  const int taps = kw * kh;
+  const bool w_u8 = w.d.dtype == B2VX_DT_UINT8;
+  const bool per_ch = w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL;
+  out->rows = rows;
+  out->Kp = Kp;
+  out->bias_full.assign(Ocp, 0);
+  out->acc_scale.assign(Ocp, 0.0f);
+  out->dz.assign(Ocp, 0);
+  out->tapc.assign(static_cast<size_t>(taps) * Ocp, 0);
+  out->need_s = false;
+  const int zx = x.zp();
+  const float sx = x.scale();
+  std::vector<int64_t> tapsum(taps);
+  const int32_t* b = bias ? reinterpret_cast<const int32_t*>(bias->host.data()) : nullptr;
+  for (int oc = 0; oc < Oc; ++oc) {
+    const int zw = per_ch ? (w.zps.empty() ? 0 : w.zps[oc]) : w.zp();
+    const float sw = per_ch ? w.scales[oc] : w.scale();
+    const int dz = w_u8 ? zw - 128 : zw;
+    out->dz[oc] = dz;
+    if (dz != 0) out->need_s = true;
+    out->acc_scale[oc] = sx * sw;
+  }
+  const int total_rows = rows + ((with_ones_row && out->need_s) ? 1 : 0);
+  out->w8.assign(static_cast<size_t>(total_rows) * Kp, 0);
+  for (int oc = 0; oc < Oc; ++oc) {
+    std::fill(tapsum.begin(), tapsum.end(), 0);
+    int8_t* row = out->w8.data() + static_cast<size_t>(oc) * Kp;
+    for (int ic = 0; ic < C; ++ic) {
+      for (int t = 0; t < taps; ++t) {
+        const size_t src = (static_cast<size_t>(oc) * C + ic) * taps + t;   // WHIcOc, W fastest: tap = ky*kw + kx
+        const int v = w_u8 ? static_cast<int>(w.host[src]) - 128 : static_cast<int>(reinterpret_cast<const int8_t*>(w.host.data())[src]);
+        row[static_cast<size_t>(t) * Cs + ic] = static_cast<int8_t>(v);
+        tapsum[t] += v;
+      }
+    }
+    int64_t all = 0;
+    for (int t = 0; t < taps; ++t) {
+      // contribution of one fully in-bounds tap beyond the raw products:
+      //   -zx*sum_c(w8) + C*zx*dz
+      const int64_t tc = -static_cast<int64_t>(zx) * tapsum[t] + static_cast<int64_t>(C) * zx * out->dz[oc];
+      out->tapc[static_cast<size_t>(t) * Ocp + oc] = static_cast<int32_t>(tc);
+      all += tc;
+    }
+    out->bias_full[oc] = static_cast<int32_t>((b ? b[oc] : 0) + all);
+  }
+  if (with_ones_row && out->need_s) {
+    int8_t* ones = out->w8.data() + static_cast<size_t>(rows) * Kp;
+    for (int t = 0; t < taps; ++t)
+      for (int ic = 0; ic < C; ++ic) ones[static_cast<size_t>(t) * Cs + ic] = 1;
+  }
+  (void)zero_fill_semantics;
+}
+
+b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* label, TensorRec& x, TensorRec& w,
+                             TensorRec* bias, TensorRec& y, int kw, int kh, const uint32_t stride[2],
+                             const uint32_t dil[2], const uint32_t pad[4]) {
+  if (!w.host_valid) return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": weights must be a CONSTANT tensor with data");
+  if (bias && !bias->host_valid) return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": bias must be a CONSTANT tensor with data");
+  const ConvGeom geo = conv_geom(x, y, kw, kh, stride, dil, pad);
+  const uint64_t P = static_cast<uint64_t>(y.N) * y.H * y.W;
+  const uint64_t macs = P * y.C * static_cast<uint64_t>(kw) * kh * x.C;
+  const uint64_t abytes = x.elems() * dtype_size(x.d.dtype) + y.elems() * dtype_size(y.d.dtype) + w.bytes() +
+                          (bias ? bias->bytes() : 0);
+
+  // ---- float32
+  if (x.d.dtype == B2VX_DT_FLOAT32) {
+    if (w.d.dtype != B2VX_DT_FLOAT32 || y.d.dtype != B2VX_DT_FLOAT32 || (bias && bias->d.dtype != B2VX_DT_FLOAT32))
+      return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": float32 input needs float32 weights, bias and output");
+    float *dw = nullptr, *db = nullptr;
+    std::vector<float> wv(reinterpret_cast<const float*>(w.host.data()), reinterpret_cast<const float*>(w.host.data()) + w.elems());
+    b2vx_status st = upload(g, wv, &dw);
+    if (st != B2VX_OK) return st;
+    if (bias) {
+      std::vector<float> bv(reinterpret_cast<const float*>(bias->host.data()), reinterpret_cast<const float*>(bias->host.data()) + bias->elems());
+      st = upload(g, bv, &db);
+      if (st != B2VX_OK) return st;
+    }
+    const float* xp = static_cast<const float*>(x.d_cl);
+    float* yp = static_cast<float*>(y.d_cl);
+    const int w_ic = x.C;
+    Step s;
+    s.info = make_info("conv_f32", node_index, 2 * macs, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_conv_f32(xp, dw, db, 0, w_ic, geo, yp, st2); return cudaGetLastError(); };
+    g->steps.push_back(std::move(s));
+    return B2VX_OK;
+  }
+
+  // ---- quantized
+  if (!is_q8(x.d.dtype) || !is_q8(w.d.dtype) || !is_q8(y.d.dtype))
+    return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": supported types are int8/uint8 activations and weights, or all float32");
+  if (bias && bias->d.dtype != B2VX_DT_INT32) return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": bias of a quantized op must be int32");
+  if (x.d.quant_type != B2VX_QUANT_ASYMMETRIC || y.d.quant_type != B2VX_QUANT_ASYMMETRIC)
+    return fail(g, B2VX_QUANT_MISMATCH, std::string(label) + ": activations must use ASYMMETRIC quantization");
+  if (w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL) {
+    if (static_cast<int>(w.scales.size()) != y.C) return fail(g, B2VX_QUANT_MISMATCH, std::string(label) + ": per-channel scale count != output channels");
+  } else if (w.d.quant_type != B2VX_QUANT_ASYMMETRIC) {
+    return fail(g, B2VX_QUANT_MISMATCH, std::string(label) + ": weights need ASYMMETRIC or SYMMETRIC_PER_CHANNEL quantization");
+  }
+  if (!quant_check(x, w, bias)) return fail(g, B2VX_QUANT_MISMATCH, std::string(label) + ": bias scale != input scale * weight scale");
+
+  const int taps = kw * kh;
+  const bool x_signed = x.d.dtype == B2VX_DT_INT8;
+  const bool has_pad = pad[0] || pad[1] || pad[2] || pad[3];
+  bool any_dz = false;
+  {
+    const bool w_u8 = w.d.dtype == B2VX_DT_UINT8;
+    if (w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL) {
+      for (int32_t z : w.zps) any_dz = any_dz || z != 0;
+    } else {
+      any_dz = (w_u8 ? w.zp() - 128 : w.zp()) != 0;
+    }
+  }
+  // The im2col matrix is the input itself when the window is 1x1/stride 1/no
+  // padding, or when the window covers the whole (unpadded) input.
+  const bool identity_1x1 = kw == 1 && kh == 1 && geo.sx == 1 && geo.sy == 1 && !has_pad;
+  const bool identity_full = kw == x.W && kh == x.H && !has_pad && y.W == 1 && y.H == 1 && geo.dx == 1 && geo.dy == 1;
+  const bool tc_ok = g->use_tc && !any_dz;
+
+  ContractEpilogue ep;
+  std::memset(&ep, 0, sizeof(ep));
+  ep.out = out_quant(y);
+  PackedContraction pk;
+
+  if (tc_ok) {
+    int Cs, Kp, M;
+    const void* A;
+    bool need_im2col = false;
+    if (identity_1x1) { Cs = x.Cp; Kp = x.Cp; M = static_cast<int>(P); A = x.d_cl; }
+    else if (identity_full) { Cs = x.Cp; Kp = taps * x.Cp; M = y.N; A = x.d_cl; }
+    else {
+      Cs = x.C < 16 ? x.C : x.Cp;
+      Kp = round_up(taps * Cs, 16);
+      M = static_cast<int>(P);
+      need_im2col = true;
+      A = nullptr;
+    }
+    const int n_tiles = (y.Cp + 255) / 256;
+    const int BN = round_up((y.Cp + n_tiles - 1) / n_tiles, 16);
+    const int Np = n_tiles * BN;
+    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, Np, false, false, &pk);
+    int8_t* dw8 = nullptr; int32_t* dbias = nullptr; float* dscale = nullptr;
+    b2vx_status st = upload(g, pk.w8, &dw8);
+    if (st == B2VX_OK) st = upload(g, pk.bias_full, &dbias);
+    if (st == B2VX_OK) st = upload(g, pk.acc_scale, &dscale);
+    if (st != B2VX_OK) return st;
+    ep.bias_full = dbias;
+    ep.acc_scale = dscale;
+    if (need_im2col) {
+      const size_t need = static_cast<size_t>(M) * Kp;
+      g->scratch_bytes = std::max(g->scratch_bytes, need);
+    }
+    // The GEMM plan bakes the A address into a TMA tensor map; for the im2col
+    // form that address is the graph's scratch buffer, which is sized over all
+    // nodes and allocated after planning, so plan creation is deferred to a
+    // finalizer that Compile runs at its end.
+    const int zx = x.zp();
+    const std::string lbl = label;
+    const void* xcl = x.d_cl;
+    void* ycl = y.d_cl;
+    const int ldd = y.Cp, Oc = y.C, y_signed = y.d.dtype == B2VX_DT_INT8;
+    if (need_im2col) {
+      Step s_col;
+      s_col.info = make_info("im2col", node_index, 0, x.elems() + static_cast<uint64_t>(M) * Kp);
+      s_col.fn = [=](cudaStream_t st2) {
+        launch_im2col(xcl, Cs, Kp, zx, geo, g->scratch, st2);
+        return cudaGetLastError();
+      };
+      g->steps.push_back(std::move(s_col));
+    }
+    auto plan_holder = std::make_shared<GemmTcPlan*>(nullptr);
+    g->finalizers.push_back([=]() -> b2vx_status {
+      char err[160] = {0};
+      const void* Aptr = need_im2col ? g->scratch : A;
+      GemmTcPlan* pl = gemm_tc_plan_create(Aptr, x_signed, dw8, M, Np, Kp, Oc, ycl, ldd, y_signed, ep, g->d_status, err, sizeof(err));
+      if (!pl) return fail(g, B2VX_UNSUPPORTED, lbl + ": " + err);
+      g->gemm_plans.push_back(pl);
+      *plan_holder = pl;
+      return B2VX_OK;
+    });
+    Step s_gemm;
+    s_gemm.info = make_info(need_im2col ? "gemm_i8_tc(im2col)" : "gemm_i8_tc", node_index, 2 * macs, abytes);
+    s_gemm.fn = [=](cudaStream_t st2) -> cudaError_t { return gemm_tc_launch(*plan_holder, st2); };
+    g->steps.push_back(std::move(s_gemm));
+    return B2VX_OK;
+  }
+
+  // CUDA-core path: K = tap*Cp + c, out-of-bounds taps are skipped and corrected per tap.
+  const int Kp = taps * x.Cp;
+  pack_contraction(x, w, bias, kw, kh, x.C, x.Cp, Kp, y.C, y.Cp, y.Cp, true, true, &pk);
+  int8_t* dw8 = nullptr; int32_t *dbias = nullptr, *ddz = nullptr, *dtapc = nullptr; float* dscale = nullptr;
+  b2vx_status st = upload(g, pk.w8, &dw8);
+  if (st == B2VX_OK) st = upload(g, pk.bias_full, &dbias);
+  if (st == B2VX_OK) st = upload(g, pk.acc_scale, &dscale);
+  if (st == B2VX_OK && pk.need_s) st = upload(g, pk.dz, &ddz);
+  if (st == B2VX_OK && has_pad && x.zp() != 0) st = upload(g, pk.tapc, &dtapc);
+  if (st != B2VX_OK) return st;
+  ep.bias_full = dbias;
+  ep.acc_scale = dscale;
+  ep.dz = ddz;
+  ep.tapc = dtapc;
+  const void* xcl = x.d_cl;
+  void* ycl = y.d_cl;
+  Step s;
+  s.info = make_info("conv_simt", node_index, 2 * macs, abytes);
+  s.fn = [=](cudaStream_t st2) { launch_conv_simt(xcl, x_signed, dw8, Kp, geo, ep, ycl, st2); return cudaGetLastError(); };
+  g->steps.push_back(std::move(s));
+  return B2VX_OK;
+}
+
+// ---------------------------------------------------------------- per-node planning
+
+b2vx_status plan_conv(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& x = g->tensors[n.in[0]];
+  TensorRec& w = g->tensors[n.in[1]];
+  TensorRec* bias = n.in[2] != B2VX_NO_TENSOR ? &g->tensors[n.in[2]] : nullptr;
+  TensorRec& y = g->tensors[n.out];
+  const b2vx_conv2d_desc& c = n.p.conv;
+  const int kw = w.d.dims[0], kh = w.d.dims[1];
+  if (c.multiplier < 1) {
+    if (static_cast<int>(w.d.dims[2]) != x.C || static_cast<int>(w.d.dims[3]) != y.C)
+      return fail(g, B2VX_SHAPE_MISMATCH, "conv2d: kernel shape does not match input/output channels");
+    if (w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL && w.d.channel_dim != 3)
+      return fail(g, B2VX_QUANT_MISMATCH, "conv2d: per-channel weights must use channel_dim 3");
+    return plan_contraction(g, idx, "conv2d", x, w, bias, y, kw, kh, c.stride, c.dilation, n.pad);
+  }
+  // depthwise
+  if (static_cast<int>(w.d.dims[2]) != x.C * c.multiplier || y.C != x.C * c.multiplier)
+    return fail(g, B2VX_SHAPE_MISMATCH, "depthwise conv2d: kernel channels != input channels * multiplier");
+  if (!w.host_valid || (bias && !bias->host_valid)) return fail(g, B2VX_UNSUPPORTED, "depthwise conv2d: weights and bias must be constants");
+  const ConvGeom geo = conv_geom(x, y, kw, kh, c.stride, c.dilation, n.pad);
+  const uint64_t macs = static_cast<uint64_t>(y.N) * y.H * y.W * y.C * kw * kh;
+  const uint64_t abytes = x.bytes() + y.bytes() + w.bytes() + (bias ? bias->bytes() : 0);
+  if (x.d.dtype == B2VX_DT_FLOAT32) {
+    if (w.d.dtype != B2VX_DT_FLOAT32 || y.d.dtype != B2VX_DT_FLOAT32 || (bias && bias->d.dtype != B2VX_DT_FLOAT32))
+      return fail(g, B2VX_UNSUPPORTED, "depthwise conv2d: float32 input needs float32 weights, bias and output");
+    float *dw = nullptr, *db = nullptr;
+    std::vector<float> wv(reinterpret_cast<const float*>(w.host.data()), reinterpret_cast<const float*>(w.host.data()) + w.elems());
+    b2vx_status st = upload(g, wv, &dw);
+    if (st != B2VX_OK) return st;
+    if (bias) {
+      std::vector<float> bv(reinterpret_cast<const float*>(bias->host.data()), reinterpret_cast<const float*>(bias->host.data()) + bias->elems());
+      st = upload(g, bv, &db);
+      if (st != B2VX_OK) return st;
+    }
+    const float* xp = static_cast<const float*>(x.d_cl);
+    float* yp = static_cast<float*>(y.d_cl);
+    const int mult = c.multiplier;
+    Step s;
+    s.info = make_info("depthwise_f32", idx, 2 * macs, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_conv_f32(xp, dw, db, mult, 0, geo, yp, st2); return cudaGetLastError(); };
+    g->steps.push_back(std::move(s));
+    return B2VX_OK;
+  }
+  if (!is_q8(x.d.dtype) || !is_q8(w.d.dtype) || !is_q8(y.d.dtype) || (bias && bias->d.dtype != B2VX_DT_INT32))
+    return fail(g, B2VX_UNSUPPORTED, "depthwise conv2d: unsupported dtype combination");
+  const bool per_ch = w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL;
+  if (per_ch && static_cast<int>(w.scales.size()) != y.C) return fail(g, B2VX_QUANT_MISMATCH, "depthwise conv2d: per-channel scale count != channels");
+  if (per_ch && w.d.channel_dim != 2) return fail(g, B2VX_QUANT_MISMATCH, "depthwise conv2d: per-channel weights must use channel_dim 2");
+  if (!quant_check(x, w, bias)) return fail(g, B2VX_QUANT_MISMATCH, "depthwise conv2d: bias scale != input scale * weight scale");
+  const int taps = kw * kh;
+  std::vector<int16_t> wd(static_cast<size_t>(taps) * y.Cp, 0);
+  std::vector<int32_t> bv(y.Cp, 0);
+  std::vector<float> sc(y.Cp, 0.0f);
+  const bool w_u8 = w.d.dtype == B2VX_DT_UINT8;
+  for (int oc = 0; oc < y.C; ++oc) {
+    const int zw = per_ch ? (w.zps.empty() ? 0 : w.zps[oc]) : w.zp();
+    for (int t = 0; t < taps; ++t) {
+      const size_t src = static_cast<size_t>(oc) * taps + t;
+      const int v = w_u8 ? static_cast<int>(w.host[src]) : static_cast<int>(reinterpret_cast<const int8_t*>(w.host.data())[src]);
+      wd[static_cast<size_t>(t) * y.Cp + oc] = static_cast<int16_t>(v - zw);
+    }
+    bv[oc] = bias ? reinterpret_cast<const int32_t*>(bias->host.data())[oc] : 0;
+    sc[oc] = x.scale() * (per_ch ? w.scales[oc] : w.scale());
+  }
+  int16_t* dwd = nullptr; int32_t* db = nullptr; float* dsc = nullptr;
+  b2vx_status st = upload(g, wd, &dwd);
+  if (st == B2VX_OK) st = upload(g, bv, &db);
+  if (st == B2VX_OK) st = upload(g, sc, &dsc);
+  if (st != B2VX_OK) return st;
+  const void* xcl = x.d_cl;
+  void* ycl = y.d_cl;
+  const int xs = x.d.dtype == B2VX_DT_INT8, zx = x.zp(), mult = c.multiplier;
+  const OutQuant oq = out_quant(y);
+  Step s;
+  s.info = make_info("depthwise_q", idx, 2 * macs, abytes);
+  s.fn = [=](cudaStream_t st2) { launch_depthwise_q(xcl, xs, zx, dwd, db, dsc, mult, geo, oq, ycl, st2); return cudaGetLastError(); };
+  g->steps.push_back(std::move(s));
+  return B2VX_OK;
+}
+
+b2vx_status plan_fc(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& x = g->tensors[n.in[0]];
+  TensorRec& w = g->tensors[n.in[1]];
+  TensorRec* bias = n.in[2] != B2VX_NO_TENSOR ? &g->tensors[n.in[2]] : nullptr;
+  TensorRec& y = g->tensors[n.out];
+  // dims [0..axis] flatten into K; everything after must be the batch (N) axis.
+  size_t K = 1;
+  for (uint32_t i = 0; i <= n.p.fc.axis; ++i) K *= x.d.dims[i];
+  const size_t batch = x.elems() / K;
+  if (K != static_cast<size_t>(x.W) * x.H * x.C || static_cast<int>(batch) != x.N)
+    return fail(g, B2VX_UNSUPPORTED, "fully_connected: axis must flatten every non-batch dimension");
+  if (w.d.dims[0] != K) return fail(g, B2VX_SHAPE_MISMATCH, "fully_connected: weight K != flattened input size");
+  if (w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL && w.d.channel_dim != 1)
+    return fail(g, B2VX_QUANT_MISMATCH, "fully_connected: per-channel weights must use channel_dim 1");
+  // A weight [K,N] with k = x + W*(y + H*c) is a WHIcOc kernel [W,H,C,N]: the
+  // op is a convolution whose window is the whole input.
+  TensorRec yv = y;   // view of the output as [1,1,N_out,batch]
+  yv.W = 1; yv.H = 1; yv.C = static_cast<int>(w.d.dims[1]); yv.N = x.N;
+  if (static_cast<size_t>(yv.C) * yv.N != y.elems() || y.C != yv.C || y.N != yv.N)
+    return fail(g, B2VX_SHAPE_MISMATCH, "fully_connected: output must be [weights, batch]");
+  const uint32_t one[2] = {1, 1}, nopad[4] = {0, 0, 0, 0};
+  return plan_contraction(g, idx, "fully_connected", x, w, bias, y, x.W, x.H, one, one, nopad);
+}
+
+b2vx_status plan_pool(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& x = g->tensors[n.in[0]];
+  TensorRec& y = g->tensors[n.out];
+  const b2vx_pool2d_desc& c = n.p.pool;
+  if (c.type != B2VX_POOL_MAX && c.type != B2VX_POOL_AVG && c.type != B2VX_POOL_AVG_ANDROID)
+    return fail(g, B2VX_UNSUPPORTED, "pool2d: only MAX, AVG and AVG_ANDROID are supported");
+  if (x.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "pool2d: input and output dtype must match");
+  const uint32_t one[2] = {1, 1};
+  const ConvGeom geo = conv_geom(x, y, c.ksize[0], c.ksize[1], c.stride, one, n.pad);
+  const uint64_t abytes = x.bytes() + y.bytes();
+  const int type = c.type;
+  Step s;
+  if (x.d.dtype == B2VX_DT_FLOAT32) {
+    const float* xp = static_cast<const float*>(x.d_cl);
+    float* yp = static_cast<float*>(y.d_cl);
+    s.info = make_info("pool_f32", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_pool_f32(xp, type, geo, yp, st2); return cudaGetLastError(); };
+  } else if (is_q8(x.d.dtype)) {
+    const void* xp = x.d_cl;
+    void* yp = y.d_cl;
+    const int sg = x.d.dtype == B2VX_DT_INT8, zx = x.zp(), same = x.scale() == y.scale() && x.zp() == y.zp();
+    const float sx = x.scale();
+    const OutQuant oq = out_quant(y);
+    s.info = make_info("pool_q", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_pool_q(xp, sg, type, sx, zx, same, geo, oq, yp, st2); return cudaGetLastError(); };
+  } else {
+    return fail(g, B2VX_UNSUPPORTED, "pool2d: unsupported dtype");
+  }
+  g->steps.push_back(std::move(s));
+  return B2VX_OK;
+}
+
+b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& a = g->tensors[n.in[0]];
+  TensorRec& b = g->tensors[n.in[1]];
+  TensorRec& y = g->tensors[n.out];
+  const uint64_t abytes = a.bytes() + b.bytes() + y.bytes();
+  Step s;
+  if (a.d.dtype == B2VX_DT_FLOAT32 && b.d.dtype == B2VX_DT_FLOAT32 && y.d.dtype == B2VX_DT_FLOAT32) {
+    const float *ap = static_cast<const float*>(a.d_cl), *bp = static_cast<const float*>(b.d_cl);
+    float* yp = static_cast<float*>(y.d_cl);
+    const size_t nel = y.cl_bytes / 4;
+    s.info = make_info("add_f32", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_add_f32(ap, bp, yp, nel, st2); return cudaGetLastError(); };
+  } else if (is_q8(a.d.dtype) && is_q8(b.d.dtype) && is_q8(y.d.dtype)) {
+    const void *ap = a.d_cl, *bp = b.d_cl;
+    void* yp = y.d_cl;
+    const int as = a.d.dtype == B2VX_DT_INT8, bs = b.d.dtype == B2VX_DT_INT8, ys = y.d.dtype == B2VX_DT_INT8;
+    const float sa = a.scale(), sb = b.scale();
+    const int za = a.zp(), zb = b.zp();
+    const OutQuant oq = out_quant(y);
+    const size_t nel = y.cl_bytes;
+    s.info = make_info("add_q", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_add_q(ap, as, sa, za, bp, bs, sb, zb, oq, ys, yp, nel, st2); return cudaGetLastError(); };
+  } else {
+    return fail(g, B2VX_UNSUPPORTED, "add: operands must be all int8/uint8 or all float32");
+  }
+  g->steps.push_back(std::move(s));
+  return B2VX_OK;
+}
+
+b2vx_status plan_relu(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& x = g->tensors[n.in[0]];
+  TensorRec& y = g->tensors[n.out];
+  const float upper = n.kind == B2VX_NODE_RELU6 ? 6.0f : -1.0f;
+  const uint64_t abytes = x.bytes() + y.bytes();
+  Step s;
+  if (x.d.dtype == B2VX_DT_FLOAT32 && y.d.dtype == B2VX_DT_FLOAT32) {
+    const float* xp = static_cast<const float*>(x.d_cl);
+    float* yp = static_cast<float*>(y.d_cl);
+    const size_t nel = y.cl_bytes / 4;
+    s.info = make_info("relu_f32", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_relu_f32(xp, upper, yp, nel, st2); return cudaGetLastError(); };
+  } else if (is_q8(x.d.dtype) && is_q8(y.d.dtype)) {
+    const void* xp = x.d_cl;
+    void* yp = y.d_cl;
+    const int xs = x.d.dtype == B2VX_DT_INT8, ys = y.d.dtype == B2VX_DT_INT8, zx = x.zp();
+    const float sx = x.scale();
+    const OutQuant oq = out_quant(y);
+    const size_t nel = y.cl_bytes;
+    s.info = make_info("relu_q", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_relu_q(xp, xs, sx, zx, upper, oq, ys, yp, nel, st2); return cudaGetLastError(); };
+  } else {
+    return fail(g, B2VX_UNSUPPORTED, "relu: input and output must be both int8/uint8 or both float32");
+  }
+  g->steps.push_back(std::move(s));
+  return B2VX_OK;
+}
+
+b2vx_status plan_softmax(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& x = g->tensors[n.in[0]];
+  TensorRec& y = g->tensors[n.out];
+  int axis = n.p.softmax.axis;
+  if (axis < 0) axis += static_cast<int>(x.d.rank);
+  if (axis < 0 || axis >= static_cast<int>(x.d.rank)) return fail(g, B2VX_INVALID_ARG, "softmax: axis out of range");
+  auto kind_of = [](int32_t dt) { return dt == B2VX_DT_UINT8 ? 0 : dt == B2VX_DT_INT8 ? 1 : dt == B2VX_DT_FLOAT32 ? 2 : -1; };
+  const int xk = kind_of(x.d.dtype), yk = kind_of(y.d.dtype);
+  if (xk < 0 || yk < 0) return fail(g, B2VX_UNSUPPORTED, "softmax: unsupported dtype");
+  // which of (W,H,C,N) the axis is
+  static const int map4[4] = {0, 1, 2, 3}, map3[3] = {0, 1, 2}, map2[2] = {2, 3}, map1[1] = {2};
+  const int* mp = x.d.rank == 4 ? map4 : x.d.rank == 3 ? map3 : x.d.rank == 2 ? map2 : map1;
+  const int which = mp[axis];
+  const long long ext[4] = {x.W, x.H, x.C, x.N};
+  const long long xst[4] = {x.Cp, static_cast<long long>(x.W) * x.Cp, 1, static_cast<long long>(x.H) * x.W * x.Cp};
+  const long long yst[4] = {y.Cp, static_cast<long long>(y.W) * y.Cp, 1, static_cast<long long>(y.H) * y.W * y.Cp};
+  SoftmaxGeom sg;
+  sg.len = static_cast<int>(ext[which]);
+  sg.x_stride = xst[which];
+  sg.y_stride = yst[which];
+  for (int i = 0, k = 0; i < 4; ++i) {
+    if (i == which) continue;
+    sg.o[k] = static_cast<int>(ext[i]);
+    sg.xs[k] = xst[i];
+    sg.ys[k] = yst[i];
+    ++k;
+  }
+  const void* xp = x.d_cl;
+  void* yp = y.d_cl;
+  const float sx = x.scale(), beta = n.p.softmax.beta;
+  const int zx = x.zp();
+  const OutQuant oq = out_quant(y);
+  Step st;
+  st.info = make_info("softmax", idx, 0, x.bytes() + y.bytes());
+  st.fn = [=](cudaStream_t st2) { launch_softmax(xp, xk, sx, zx, yp, yk, oq, beta, sg, st2); return cudaGetLastError(); };
+  g->steps.push_back(std::move(st));
+  return B2VX_OK;
+}
+
+b2vx_status add_node(b2vx_graph* g, int32_t kind, uint32_t i0, uint32_t i1, uint32_t i2, uint32_t out, const NodeRec* proto) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (g->compiled) return fail(g, B2VX_BAD_STATE, "graph is already compiled");
+  if (!valid_id(g, i0) || !valid_id(g, out)) return fail(g, B2VX_INVALID_ARG, "node: bad tensor id");
+  if (i1 != B2VX_NO_TENSOR && !valid_id(g, i1)) return fail(g, B2VX_INVALID_ARG, "node: bad tensor id");
+  if (i2 != B2VX_NO_TENSOR && !valid_id(g, i2)) return fail(g, B2VX_INVALID_ARG, "node: bad tensor id");
+  NodeRec n;
+  if (proto) n = *proto;
+  else std::memset(&n, 0, sizeof(n));
+  n.kind = kind;
+  n.in[0] = i0; n.in[1] = i1; n.in[2] = i2; n.out = out;
+  g->nodes.push_back(n);
+  return B2VX_OK;
+}
+
+}  // namespace
+
+// ================================================================== C ABI
+
+extern "C" {
+
+b2vx_status b2vx_context_create(b2vx_context** out) {
+  if (!out) return B2VX_INVALID_ARG;
+  *out = new b2vx_context();
+  return B2VX_OK;
+}
+void b2vx_context_destroy(b2vx_context* ctx) { delete ctx; }
+const char* b2vx_last_error(const b2vx_context* ctx) { return ctx ? ctx->err.c_str() : ""; }
+
+int32_t b2vx_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+b2vx_status b2vx_graph_create(b2vx_context* ctx, int32_t device_id, b2vx_graph** out) {
+  if (!ctx || !out) return B2VX_INVALID_ARG;
+  const int n = b2vx_device_count();
+  if (n <= 0) {
+    ctx->err = "no CUDA device: this backend has no CPU execution path";
+    return B2VX_CUDA_ERROR;
+  }
+  if (device_id < 0 || device_id >= n) {
+    ctx->err = "device id out of range";
+    return B2VX_INVALID_ARG;
+  }
+  b2vx_graph* g = new b2vx_graph();
+  g->ctx = ctx;
+  g->device = device_id;
+  DeviceGuard guard(device_id);
+  if (cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void**>(&g->d_status), sizeof(int)) != cudaSuccess ||
+      cudaMemset(g->d_status, 0, sizeof(int)) != cudaSuccess ||
+      cudaHostAlloc(reinterpret_cast<void**>(&g->h_status), sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
+    ctx->err = std::string("graph_create: ") + cudaGetErrorString(cudaGetLastError());
+    delete g;
+    return B2VX_CUDA_ERROR;
+  }
+  *g->h_status = 0;
+  g->stream = g->own_stream;
+  const char* k = std::getenv("B2VX_CONV_KERNEL");
+  g->use_tc = gemm_tc_available() && !(k && std::strcmp(k, "simt") == 0);
+  *out = g;
+  return B2VX_OK;
+}
+
+void b2vx_graph_destroy(b2vx_graph* g) {
+  if (!g) return;
+  DeviceGuard guard(g->device);
+  cudaStreamSynchronize(g->stream);
+  for (GemmTcPlan* p : g->gemm_plans) gemm_tc_plan_destroy(p);
+  for (void* p : g->allocs) cudaFree(p);
+  if (g->d_status) cudaFree(g->d_status);
+  if (g->h_status) cudaFreeHost(g->h_status);
+  if (g->own_stream) cudaStreamDestroy(g->own_stream);
+  delete g;
+}
+
+b2vx_status b2vx_tensor_create(b2vx_graph* g, const b2vx_tensor_desc* desc, const void* const_data, uint32_t* out_id) {
+  if (!g || !desc || !out_id) return B2VX_INVALID_ARG;
+  if (g->compiled) return fail(g, B2VX_BAD_STATE, "graph is already compiled");
+  if (desc->rank > 4) return fail(g, B2VX_UNSUPPORTED, "tensor: rank above 4 is not supported on this path");
+  if (desc->dtype != B2VX_DT_INT8 && desc->dtype != B2VX_DT_UINT8 && desc->dtype != B2VX_DT_INT32 && desc->dtype != B2VX_DT_FLOAT32)
+    return fail(g, B2VX_UNSUPPORTED, "tensor: dtype must be int8, uint8, int32 or float32");
+  if (desc->quant_type != B2VX_QUANT_NONE && desc->quant_type != B2VX_QUANT_ASYMMETRIC &&
+      desc->quant_type != B2VX_QUANT_SYMMETRIC_PER_CHANNEL)
+    return fail(g, B2VX_UNSUPPORTED, "tensor: quantization type not supported");
+  TensorRec t;
+  t.d = *desc;
+  if (desc->quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL) {
+    if (!desc->scales || desc->n_channel == 0) return fail(g, B2VX_INVALID_ARG, "tensor: per-channel scales missing");
+    t.scales.assign(desc->scales, desc->scales + desc->n_channel);
+    if (desc->zero_points) t.zps.assign(desc->zero_points, desc->zero_points + desc->n_channel);
+  }
+  if (desc->quant_type == B2VX_QUANT_ASYMMETRIC && is_q8(desc->dtype) && !(desc->scale > 0.0f))
+    return fail(g, B2VX_QUANT_MISMATCH, "tensor: scale must be positive");
+  t.d.scales = nullptr;
+  t.d.zero_points = nullptr;
+  t.has_shape = desc->rank > 0;
+  for (uint32_t i = 0; i < desc->rank; ++i)
+    if (desc->dims[i] == 0) return fail(g, B2VX_INVALID_ARG, "tensor: zero-sized dimension");
+  if (const_data) {
+    if (!t.has_shape) return fail(g, B2VX_INVALID_ARG, "tensor: data given without a shape");
+    t.host.assign(static_cast<const uint8_t*>(const_data), static_cast<const uint8_t*>(const_data) + t.bytes());
+    t.host_valid = true;
+  }
+  g->tensors.push_back(std::move(t));
+  *out_id = static_cast<uint32_t>(g->tensors.size() - 1);
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_tensor_get_desc(b2vx_graph* g, uint32_t id, b2vx_tensor_desc* out) {
+  if (!g || !out || !valid_id(g, id)) return B2VX_INVALID_ARG;
+  TensorRec& t = g->tensors[id];
+  *out = t.d;
+  if (!t.has_shape) out->rank = 0;
+  out->n_channel = static_cast<uint32_t>(t.scales.size());
+  out->scales = t.scales.empty() ? nullptr : t.scales.data();
+  out->zero_points = t.zps.empty() ? nullptr : t.zps.data();
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_tensor_write(b2vx_graph* g, uint32_t id, const void* src, size_t bytes) {
+  if (!g || !src || !valid_id(g, id)) return B2VX_INVALID_ARG;
+  TensorRec& t = g->tensors[id];
+  if (t.d.attr & B2VX_ATTR_TRANSIENT) return fail(g, B2VX_BAD_STATE, "tensor_write: transient tensors cannot be written");
+  if (!t.has_shape || bytes != t.bytes()) return fail(g, B2VX_INVALID_ARG, "tensor_write: byte size does not match the tensor");
+  if (!g->compiled) {
+    t.host.assign(static_cast<const uint8_t*>(src), static_cast<const uint8_t*>(src) + bytes);
+    t.host_valid = true;
+    return B2VX_OK;
+  }
+  if (t.d.attr & B2VX_ATTR_CONSTANT) return fail(g, B2VX_BAD_STATE, "tensor_write: constants are frozen at compile");
+  if (!t.d_io) return fail(g, B2VX_BAD_STATE, "tensor_write: tensor has no device storage");
+  DeviceGuard guard(g->device);
+  CUDA_TRY(g, cudaMemcpyAsync(t.d_io, src, bytes, cudaMemcpyHostToDevice, g->stream));
+  CUDA_TRY(g, cudaStreamSynchronize(g->stream));
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_tensor_read(b2vx_graph* g, uint32_t id, void* dst, size_t bytes) {
+  if (!g || !dst || !valid_id(g, id)) return B2VX_INVALID_ARG;
+  TensorRec& t = g->tensors[id];
+  if (!t.has_shape || bytes != t.bytes()) return fail(g, B2VX_INVALID_ARG, "tensor_read: byte size does not match the tensor");
+  if (!g->compiled) {
+    if (!t.host_valid) return fail(g, B2VX_BAD_STATE, "tensor_read: tensor holds no data yet");
+    std::memcpy(dst, t.host.data(), bytes);
+    return B2VX_OK;
+  }
+  if (!t.is_activation) {
+    if (!t.host_valid) return fail(g, B2VX_BAD_STATE, "tensor_read: tensor holds no data");
+    std::memcpy(dst, t.host.data(), bytes);
+    return B2VX_OK;
+  }
+  DeviceGuard guard(g->device);
+  if (t.d_io) {
+    CUDA_TRY(g, cudaMemcpyAsync(dst, t.d_io, bytes, cudaMemcpyDeviceToHost, g->stream));
+    CUDA_TRY(g, cudaStreamSynchronize(g->stream));
+    return B2VX_OK;
+  }
+  // intermediate tensor: convert on the fly (debugging / per-layer checks)
+  void* tmp = nullptr;
+  CUDA_TRY(g, cudaMalloc(&tmp, bytes));
+  launch_cl_to_whcn(t.d_cl, tmp, t.N, t.C, t.H, t.W, t.Cp, static_cast<int>(dtype_size(t.d.dtype)), g->stream);
+  cudaError_t e = cudaMemcpyAsync(dst, tmp, bytes, cudaMemcpyDeviceToHost, g->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+  cudaFree(tmp);
+  if (e != cudaSuccess) return fail(g, B2VX_CUDA_ERROR, std::string("tensor_read: ") + cudaGetErrorString(e));
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_node_conv2d(b2vx_graph* g, uint32_t x, uint32_t w, uint32_t bias, uint32_t y, const b2vx_conv2d_desc* d) {
+  if (!g || !d) return B2VX_INVALID_ARG;
+  if (!valid_id(g, w)) return fail(g, B2VX_INVALID_ARG, "conv2d: weight tensor missing");
+  NodeRec n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.conv = *d;
+  return add_node(g, B2VX_NODE_CONV2D, x, w, bias, y, &n);
+}
+
+b2vx_status b2vx_node_fully_connected(b2vx_graph* g, uint32_t x, uint32_t w, uint32_t bias, uint32_t y, const b2vx_fc_desc* d) {
+  if (!g || !d) return B2VX_INVALID_ARG;
+  if (!valid_id(g, w)) return fail(g, B2VX_INVALID_ARG, "fully_connected: weight tensor missing");
+  NodeRec n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.fc = *d;
+  return add_node(g, B2VX_NODE_FULLY_CONNECTED, x, w, bias, y, &n);
+}
+
+b2vx_status b2vx_node_pool2d(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_pool2d_desc* d) {
+  if (!g || !d) return B2VX_INVALID_ARG;
+  NodeRec n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.pool = *d;
+  return add_node(g, B2VX_NODE_POOL2D, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+}
+
+b2vx_status b2vx_node_add(b2vx_graph* g, uint32_t a, uint32_t b, uint32_t y) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (!valid_id(g, b)) return fail(g, B2VX_INVALID_ARG, "add: second input missing");
+  return add_node(g, B2VX_NODE_ADD, a, b, B2VX_NO_TENSOR, y, nullptr);
+}
+b2vx_status b2vx_node_relu(b2vx_graph* g, uint32_t x, uint32_t y) {
+  return add_node(g, B2VX_NODE_RELU, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
+}
+b2vx_status b2vx_node_relu6(b2vx_graph* g, uint32_t x, uint32_t y) {
+  return add_node(g, B2VX_NODE_RELU6, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
+}
+b2vx_status b2vx_node_softmax(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_softmax_desc* d) {
+  if (!g || !d) return B2VX_INVALID_ARG;
+  NodeRec n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.softmax = *d;
+  return add_node(g, B2VX_NODE_SOFTMAX, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+}
+
+b2vx_status b2vx_graph_compile(b2vx_graph* g) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (g->compiled) return B2VX_OK;
+  DeviceGuard guard(g->device);
+  // 1. order
+  std::vector<char> ready(g->tensors.size(), 0), done(g->nodes.size(), 0);
+  for (size_t i = 0; i < g->tensors.size(); ++i)
+    ready[i] = (g->tensors[i].d.attr & (B2VX_ATTR_CONSTANT | B2VX_ATTR_INPUT | B2VX_ATTR_VARIABLE)) != 0;
+  for (const NodeRec& n : g->nodes) ready[n.out] = 0;
+  g->order.clear();
+  for (bool progress = true; progress;) {
+    progress = false;
+    for (size_t i = 0; i < g->nodes.size(); ++i) {
+      if (done[i]) continue;
+      NodeRec& n = g->nodes[i];
+      bool ok = true;
+      for (uint32_t id : n.in) ok = ok && (id == B2VX_NO_TENSOR || ready[id]);
+      if (!ok) continue;
+      b2vx_status st = infer_node(g, n);
+      if (st != B2VX_OK) return st;
+      ready[n.out] = 1;
+      done[i] = 1;
+      g->order.push_back(static_cast<uint32_t>(i));
+      progress = true;
+    }
+  }
+  if (g->order.size() != g->nodes.size()) return fail(g, B2VX_BAD_STATE, "graph has a cycle or a node whose input is never produced");
+
+  // 2. which tensors are activations (touched by a node as data, not as weights/bias)
+  for (const NodeRec& n : g->nodes) {
+    g->tensors[n.in[0]].is_activation = true;
+    g->tensors[n.out].is_activation = true;
+    if (n.kind == B2VX_NODE_ADD) g->tensors[n.in[1]].is_activation = true;
+  }
+  for (TensorRec& t : g->tensors) {
+    if (!t.is_activation) continue;
+    if (!t.has_shape) return fail(g, B2VX_SHAPE_MISMATCH, "an activation tensor has no shape");
+    if (t.d.dtype == B2VX_DT_INT32) return fail(g, B2VX_UNSUPPORTED, "int32 activations are not supported");
+    map_dims(t);
+    b2vx_status st = dev_alloc(g, &t.d_cl, t.cl_bytes);
+    if (st != B2VX_OK) return st;
+    CUDA_TRY(g, cudaMemsetAsync(t.d_cl, 0, t.cl_bytes, g->stream));
+    const bool io = (t.d.attr & (B2VX_ATTR_INPUT | B2VX_ATTR_OUTPUT | B2VX_ATTR_CONSTANT | B2VX_ATTR_VARIABLE)) != 0;
+    if (io) {
+      if (t.same_layouts()) t.d_io = t.d_cl;
+      else {
+        st = dev_alloc(g, &t.d_io, t.io_bytes);
+        if (st != B2VX_OK) return st;
+      }
+    }
+  }
+
+  // 3. plan: inputs -> channels-last, nodes, outputs -> WHCN
+  g->steps.clear();
+  for (size_t i = 0; i < g->tensors.size(); ++i) {
+    TensorRec& t = g->tensors[i];
+    if (!t.is_activation || !(t.d.attr & (B2VX_ATTR_INPUT | B2VX_ATTR_VARIABLE))) continue;
+    if (t.d_io == t.d_cl) continue;
+    const void* src = t.d_io;
+    void* dst = t.d_cl;
+    const int N = t.N, C = t.C, H = t.H, W = t.W, Cp = t.Cp, el = static_cast<int>(dtype_size(t.d.dtype));
+    Step s;
+    s.info = make_info("whcn_to_cl", B2VX_NO_TENSOR, 0, t.io_bytes + t.cl_bytes);
+    s.fn = [=](cudaStream_t st2) { launch_whcn_to_cl(src, dst, N, C, H, W, Cp, el, st2); return cudaGetLastError(); };
+    g->steps.push_back(std::move(s));
+  }
+  for (uint32_t idx : g->order) {
+    NodeRec& n = g->nodes[idx];
+    b2vx_status st = B2VX_UNSUPPORTED;
+    switch (n.kind) {
+      case B2VX_NODE_CONV2D: st = plan_conv(g, idx, n); break;
+      case B2VX_NODE_FULLY_CONNECTED: st = plan_fc(g, idx, n); break;
+      case B2VX_NODE_POOL2D: st = plan_pool(g, idx, n); break;
+      case B2VX_NODE_ADD: st = plan_add(g, idx, n); break;
+      case B2VX_NODE_RELU:
+      case B2VX_NODE_RELU6: st = plan_relu(g, idx, n); break;
+      case B2VX_NODE_SOFTMAX: st = plan_softmax(g, idx, n); break;
+      default: return fail(g, B2VX_UNSUPPORTED, "unknown node kind");
+    }
+    if (st != B2VX_OK) return st;
+  }
+  for (size_t i = 0; i < g->tensors.size(); ++i) {
+    TensorRec& t = g->tensors[i];
+    if (!t.is_activation || !(t.d.attr & B2VX_ATTR_OUTPUT)) continue;
+    if (t.d_io == t.d_cl) continue;
+    const void* src = t.d_cl;
+    void* dst = t.d_io;
+    const int N = t.N, C = t.C, H = t.H, W = t.W, Cp = t.Cp, el = static_cast<int>(dtype_size(t.d.dtype));
+    Step s;
+    s.info = make_info("cl_to_whcn", B2VX_NO_TENSOR, 0, t.io_bytes + t.cl_bytes);
+    s.fn = [=](cudaStream_t st2) { launch_cl_to_whcn(src, dst, N, C, H, W, Cp, el, st2); return cudaGetLastError(); };
+    g->steps.push_back(std::move(s));
+  }
+  if (g->scratch_bytes) {
+    b2vx_status st = dev_alloc(g, &g->scratch, g->scratch_bytes);
+    if (st != B2VX_OK) return st;
+  }
+  for (auto& f : g->finalizers) {
+    b2vx_status st = f();
+    if (st != B2VX_OK) return st;
+  }
+  g->finalizers.clear();
+
+  // 4. data that was supplied before compile: inputs written early, constant activations
+  for (TensorRec& t : g->tensors) {
+    if (!t.is_activation || !t.host_valid || !t.d_io) continue;
+    CUDA_TRY(g, cudaMemcpyAsync(t.d_io, t.host.data(), t.io_bytes, cudaMemcpyHostToDevice, g->stream));
+    if ((t.d.attr & B2VX_ATTR_CONSTANT) && t.d_io != t.d_cl)
+      launch_whcn_to_cl(t.d_io, t.d_cl, t.N, t.C, t.H, t.W, t.Cp, static_cast<int>(dtype_size(t.d.dtype)), g->stream);
+  }
+  CUDA_TRY(g, cudaStreamSynchronize(g->stream));
+  CUDA_TRY(g, cudaGetLastError());
+  g->compiled = true;
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_graph_run_async(b2vx_graph* g) {
+  if (!g) return B2VX_INVALID_ARG;
+  b2vx_status st = b2vx_graph_compile(g);
+  if (st != B2VX_OK) return st;
+  DeviceGuard guard(g->device);
+  for (Step& s : g->steps) {
+    cudaError_t e = s.fn(g->stream);
+    if (e != cudaSuccess) {
+      return fail(g, B2VX_CUDA_ERROR, std::string(s.info.name) + ": " + cudaGetErrorString(e));
+    }
+  }
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_graph_sync(b2vx_graph* g) {
+  if (!g) return B2VX_INVALID_ARG;
+  DeviceGuard guard(g->device);
+  CUDA_TRY(g, cudaMemcpyAsync(g->h_status, g->d_status, sizeof(int), cudaMemcpyDeviceToHost, g->stream));
+  CUDA_TRY(g, cudaStreamSynchronize(g->stream));
+  if (*g->h_status != 0) {
+    const int code = *g->h_status;
+    cudaMemsetAsync(g->d_status, 0, sizeof(int), g->stream);
+    return fail(g, B2VX_DEVICE_TIMEOUT, "a tensor-core kernel gave up waiting on a barrier (code " + std::to_string(code) + ")");
+  }
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_graph_run(b2vx_graph* g) {
+  b2vx_status st = b2vx_graph_run_async(g);
+  if (st != B2VX_OK) return st;
+  return b2vx_graph_sync(g);
+}
+
+b2vx_status b2vx_graph_set_stream(b2vx_graph* g, void* cuda_stream) {
+  if (!g) return B2VX_INVALID_ARG;
+  DeviceGuard guard(g->device);
+  cudaStreamSynchronize(g->stream);
+  g->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : g->own_stream;
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_graph_kernel_count(b2vx_graph* g, uint32_t* out) {
+  if (!g || !out) return B2VX_INVALID_ARG;
+  *out = static_cast<uint32_t>(g->steps.size());
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_graph_kernel_info(b2vx_graph* g, uint32_t index, b2vx_kernel_info* out) {
+  if (!g || !out || index >= g->steps.size()) return B2VX_INVALID_ARG;
+  *out = g->steps[index].info;
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_graph_print(b2vx_graph* g) {
+  if (!g) return B2VX_INVALID_ARG;
+  std::fprintf(stderr, "b2vx graph: %zu tensors, %zu nodes, %zu kernels, device %d, tensor cores %s\n", g->tensors.size(),
+               g->nodes.size(), g->steps.size(), g->device, g->use_tc ? "on" : "off");
+  for (size_t i = 0; i < g->steps.size(); ++i) {
+    const b2vx_kernel_info& k = g->steps[i].info;
+    std::fprintf(stderr, "  [%3zu] %-22s node %-4d ops %-12llu bytes %-12llu %8.3f ms\n", i, k.name,
+                 k.node_index == B2VX_NO_TENSOR ? -1 : static_cast<int>(k.node_index),
+                 static_cast<unsigned long long>(k.ops), static_cast<unsigned long long>(k.bytes), k.last_ms);
+  }
+  return B2VX_OK;
+}
+
+b2vx_status b2vx_graph_profile(b2vx_graph* g, uint32_t iters) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (iters == 0) iters = 1;
+  b2vx_status st = b2vx_graph_run(g);   // warm-up
+  if (st != B2VX_OK) return st;
+  DeviceGuard guard(g->device);
+  std::vector<cudaEvent_t> ev(g->steps.size() + 1);
+  for (auto& e : ev) CUDA_TRY(g, cudaEventCreate(&e));
+  std::vector<double> total(g->steps.size(), 0.0);
+  for (uint32_t it = 0; it < iters; ++it) {
+    CUDA_TRY(g, cudaEventRecord(ev[0], g->stream));
+    for (size_t i = 0; i < g->steps.size(); ++i) {
+      cudaError_t e = g->steps[i].fn(g->stream);
+      if (e != cudaSuccess) return fail(g, B2VX_CUDA_ERROR, std::string(g->steps[i].info.name) + ": " + cudaGetErrorString(e));
+      CUDA_TRY(g, cudaEventRecord(ev[i + 1], g->stream));
+    }
+    CUDA_TRY(g, cudaStreamSynchronize(g->stream));
+    for (size_t i = 0; i < g->steps.size(); ++i) {
+      float ms = 0.0f;
+      CUDA_TRY(g, cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
+      total[i] += ms;
+    }
+  }
+  for (size_t i = 0; i < g->steps.size(); ++i) g->steps[i].info.last_ms = static_cast<float>(total[i] / iters);
+  for (auto& e : ev) cudaEventDestroy(e);
+  return b2vx_graph_sync(g);
+}
+
+b2vx_status b2vx_host_alloc(void** out, size_t bytes) {
+  if (!out) return B2VX_INVALID_ARG;
+  if (cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    *out = nullptr;
+    return B2VX_OOM;
+  }
+  return B2VX_OK;
+}
+void b2vx_host_free(void* p) {
+  if (p) cudaFreeHost(p);
+}
+
+}  // extern "C"

@@ -1,0 +1,452 @@
+// int8 GEMM with fused requantization on Blackwell tensor cores (sm_100a).
+//
+//   D[m][oc] = requant( sum_k A[m][k] * B[oc][k]  + epilogue terms )
+//
+// A: activations, u8 or s8, [M][Kp] K-contiguous (a channels-last tensor viewed
+//    as pixels x channels, or an im2col matrix);  B: weights shifted into int8,
+//    [Np][Kp] K-contiguous.  Both are "K-major" operands, which is what TMA
+//    tiled loads with a 32/64/128-byte swizzle and tcgen05.mma.kind::i8 consume
+//    directly; accumulation is int32 in tensor memory.
+//
+// One persistent CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer: per k-block one A box (128 rows x BK bytes) and
+//               one B box (BN rows x BK bytes) into a ring of smem stages;
+//   warp 1      allocates tensor memory, then one lane issues the MMAs
+//               (M=128, N=BN, K=32 per instruction) and commits them to
+//               mbarriers: stage-free after each k-block, accumulator-ready
+//               after the last one;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp owns the 32
+//               TMEM lanes its warp id maps to), add the folded bias, replay
+//               the float requantization, pack to bytes and store 16-byte
+//               runs.  Two accumulator buffers let the MMAs of tile i+1
+//               overlap the epilogue of tile i.
+// Tiles are visited n-fastest so the CTAs that share an A row-block run at the
+// same time and the second and later reads of it hit L2.
+//
+// Every mbarrier wait is bounded: after kWaitLimitCycles the waiting thread
+// records a code in *status, raises a CTA-wide abort flag that all other waits
+// poll, and the CTA falls through to its common exit where tensor memory is
+// released.  No cluster launch, no multicast.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "kernels.h"
+#include "requant.cuh"
+
+namespace b2vx {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kThreadsTc = 192;
+constexpr int kMaxStages = 8;
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+constexpr int kMinDynSmem = 120 * 1024;               // keeps two CTAs from sharing an SM (and its TMEM)
+
+struct GemmParams {
+  int M, Ocp, ldd;
+  int BN, BK, n_tiles, m_tiles, num_kb, stages;
+  int tmem_cols;
+  int acc_stride;          // TMEM columns between the two accumulator buffers (BN rounded up to 32)
+  uint32_t idesc;
+  uint32_t layout_type;   // UMMA smem descriptor swizzle code
+  uint32_t sbo;           // bytes between 8-row groups
+  ContractEpilogue ep;
+  uint8_t* D;
+  int* status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - start > kWaitLimitCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, int (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are one
+// swizzle span wide: start address, LBO = 1 (unused for swizzled K-major),
+// SBO = 8 rows, descriptor version 1, swizzle code in bits 61-63.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t sbo_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(layout_type & 7) << 61;
+  return d;
+}
+
+struct SmemHeader {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long tmem_full[2];
+  unsigned long long tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreadsTc, 1)
+gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // tiles first (1024-byte aligned for the 128-byte swizzle), header after them
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
+  const uint32_t a_bytes = kBlockM * p.BK;
+  const uint32_t b_bytes = static_cast<uint32_t>(p.BN) * p.BK;
+  const uint32_t stage_bytes = a_bytes + b_bytes;   // whole swizzle atoms, see the host-side plan
+  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(tiles + static_cast<size_t>(p.stages) * stage_bytes);
+  volatile int* abort_flag = &hdr->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&hdr->full[s]), 1);
+      mbar_init(smem_u32(&hdr->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&hdr->tmem_full[a]), 1);
+      mbar_init(smem_u32(&hdr->tmem_empty[a]), 4);
+    }
+    hdr->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hdr->tmem_base)),
+                 "r"(static_cast<uint32_t>(p.tmem_cols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = hdr->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m_tile = tile / p.n_tiles, n_tile = tile - m_tile * p.n_tiles;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
+          if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          const uint32_t full = smem_u32(&hdr->full[s]);
+          const uint32_t dst = tiles_addr + s * stage_bytes;
+          mbar_arrive_expect_tx(full, stage_bytes);
+          tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
+          tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      int j = 0;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
+        const uint32_t a = j & 1, aph = (j >> 1) & 1;
+        if (!mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + a * p.acc_stride;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
+          if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = tiles_addr + s * stage_bytes;
+          const uint64_t da = make_smem_desc(a_addr, p.sbo, p.layout_type);
+          const uint64_t db = make_smem_desc(a_addr + a_bytes, p.sbo, p.layout_type);
+          const int ksteps = p.BK >> 5;
+          for (int k = 0; k < ksteps; ++k) {
+            // advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
+            tc_mma_i8(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc,
+                      (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&hdr->empty[s]));
+        }
+        if (ok) tc_commit(smem_u32(&hdr->tmem_full[a]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;                 // TMEM lanes [32*quarter, +32) belong to this warp
+    const int row_in_tile = quarter * 32 + lane;
+    const ContractEpilogue& e = p.ep;
+    int j = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
+      const int m_tile = tile / p.n_tiles, n_tile = tile - m_tile * p.n_tiles;
+      const uint32_t a = j & 1, aph = (j >> 1) & 1;
+      if (!mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4)) break;
+      tc_fence_after();
+      const long long row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
+      const uint32_t taddr = tmem_base + a * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
+      for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        int acc[32];
+        tc_ld_32x32(taddr + c0, acc);
+        tc_ld_wait();
+        const int col0 = n_tile * p.BN + c0;
+        if (row < p.M) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int cbase = col0 + h * 16;
+            if (cbase + 16 <= p.Ocp) {
+              uint32_t w4[4] = {0, 0, 0, 0};
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const int oc = cbase + i;
+                const int v = acc[h * 16 + i] + __ldg(e.bias_full + oc);
+                const float real = __fmul_rn(__int2float_rn(v), __ldg(e.acc_scale + oc));
+                w4[i >> 2] |= static_cast<uint32_t>(requant(real, e.out) & 0xFF) << ((i & 3) * 8);
+              }
+              *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&hdr->tmem_empty[a]));
+    }
+  }
+
+  // ---------------------------------------------------------------- common exit
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(p.tmem_cols))
+                 : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+bool encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+               uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+struct GemmTcPlan {
+  CUtensorMap map_a;
+  CUtensorMap map_b;
+  GemmParams params;
+  int grid;
+  size_t smem;
+};
+
+int gemm_tc_available(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return 0;
+  return prop.major == 10 && get_encode_fn() != nullptr;
+}
+
+GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, int M, int Np, int Kp, int Oc, void* D,
+                                int ldd, int d_signed, const ContractEpilogue& e, int* status, char* err,
+                                size_t err_len) {
+  (void)Oc;
+  (void)d_signed;
+  auto fail = [&](const char* msg) -> GemmTcPlan* {
+    if (err && err_len) std::snprintf(err, err_len, "%s", msg);
+    return nullptr;
+  };
+  if (M <= 0 || Np <= 0 || Kp <= 0 || (Kp & 15) || (ldd & 15) || (Np & 15)) return fail("gemm_tc: sizes must be positive multiples of 16");
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(D) & 15))
+    return fail("gemm_tc: operands must be 16-byte aligned");
+  if (e.dz != nullptr || e.tapc != nullptr || e.out_is_float) return fail("gemm_tc: epilogue form not supported");
+
+  GemmTcPlan* plan = new GemmTcPlan();
+  GemmParams& p = plan->params;
+  std::memset(&p, 0, sizeof(p));
+  p.M = M;
+  p.Ocp = ldd;
+  p.ldd = ldd;
+  // N tiling: as few tiles of at most 256 columns as cover Np, width a multiple of 16.
+  p.n_tiles = (Np + 255) / 256;
+  p.BN = (((Np + p.n_tiles - 1) / p.n_tiles) + 15) & ~15;
+  if (p.n_tiles * p.BN != Np) {
+    delete plan;
+    return fail("gemm_tc: weight rows must be packed to n_tiles*BN");
+  }
+  // K block: the swizzle span (32/64/128 bytes) that wastes the least tail.
+  int best_bk = 32;
+  long long best_cost = -1;
+  for (int bk : {128, 64, 32}) {
+    long long cost = static_cast<long long>((Kp + bk - 1) / bk) * bk;
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best_bk = bk;
+    }
+  }
+  p.BK = best_bk;
+  p.num_kb = (Kp + p.BK - 1) / p.BK;
+  p.m_tiles = (M + kBlockM - 1) / kBlockM;
+  p.layout_type = p.BK == 128 ? 2u : (p.BK == 64 ? 4u : 6u);
+  p.sbo = 8u * p.BK;
+  const size_t stage_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
+  // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
+  // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
+  // aligned start of the ring.
+  int stages = static_cast<int>((200 * 1024) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) {
+    delete plan;
+    return fail("gemm_tc: tile does not fit shared memory");
+  }
+  p.stages = stages;
+  // the epilogue reads 32 columns at a time, so each accumulator buffer spans BN rounded up to 32
+  p.acc_stride = (p.BN + 31) & ~31;
+  int cols = 32;
+  while (cols < 2 * p.acc_stride) cols <<= 1;
+  p.tmem_cols = cols;
+  p.idesc = (2u << 4) | (static_cast<uint32_t>(a_signed ? 1 : 0) << 7) | (1u << 10) |
+            (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+  p.ep = e;
+  p.D = static_cast<uint8_t*>(D);
+  p.status = status;
+
+  const CUtensorMapSwizzle swz = p.BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                             : (p.BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  if (!encode_2d(&plan->map_a, A, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M), static_cast<uint64_t>(Kp),
+                 static_cast<uint32_t>(p.BK), kBlockM, swz) ||
+      !encode_2d(&plan->map_b, B, static_cast<uint64_t>(Kp), static_cast<uint64_t>(Np), static_cast<uint64_t>(Kp),
+                 static_cast<uint32_t>(p.BK), static_cast<uint32_t>(p.BN), swz)) {
+    delete plan;
+    return fail("gemm_tc: cuTensorMapEncodeTiled failed");
+  }
+
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = p.m_tiles * p.n_tiles;
+  plan->grid = tiles < sms ? tiles : sms;
+  size_t smem = static_cast<size_t>(stages) * stage_bytes + sizeof(SmemHeader) + 1024;
+  if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
+  plan->smem = smem;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      delete plan;
+      return fail("gemm_tc: cannot raise the dynamic shared memory limit");
+    }
+    attr_set = true;
+  }
+  return plan;
+}
+
+void gemm_tc_plan_destroy(GemmTcPlan* p) { delete p; }
+
+cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
+  gemm_i8_tc_kernel<<<plan->grid, kThreadsTc, plan->smem, s>>>(plan->map_a, plan->map_b, plan->params);
+  return cudaGetLastError();
+}
+
+}  // namespace b2vx

@@ -1,0 +1,121 @@
+// Launch wrappers of the sm_100a kernels behind the b2vx C ABI.
+//
+// Device layout of an activation tensor with tim::vx shape [W,H,C,N] (lower
+// ranks are padded with ones: [K,B] is C=K, N=B): channels-last, dense,
+//     addr(n,h,w,c) = ((n*H + h)*W + w)*Cp + c,   Cp = C rounded up to 16 bytes,
+// so a pixel's channels are one contiguous, 16-byte aligned run — the unit of
+// every 128-bit load below and the K-contiguous ("K-major") operand layout the
+// tensor-core GEMM wants.  Bytes in the channel padding are don't-care: packed
+// weights are zero there, and per-channel kernels carry them along untouched.
+//
+// Quantized outputs are produced by replaying the reference's float sequence
+// (affine_to_fp32 then fp32_to_affine,
+// src/tim/vx/internal/include/utils/vsi_nn_dtype_util_prv.h:228-266, with the
+// vsi_rint tie rule of include/utils/vsi_nn_math.h:191-210) with explicit
+// round-to-nearest intrinsics, never a fused multiply-add.
+#ifndef B2VX_KERNELS_H_
+#define B2VX_KERNELS_H_
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b2vx {
+
+// Output quantization of a kernel: q = clamp(rint(real / scale) + zp, lo, hi).
+struct OutQuant {
+  float scale;
+  int32_t zp;
+  int32_t lo;
+  int32_t hi;
+};
+
+// Geometry of one convolution / pooling window sweep over channels-last data.
+struct ConvGeom {
+  int N, H, W, C, Cp;        // input
+  int Ho, Wo, Oc, Ocp;       // output
+  int kh, kw, sy, sx, dy, dx, pt, pl;
+};
+
+// Per-output-channel epilogue tables of a quantized contraction (device
+// pointers, Ocp entries each; tapc is [kh*kw][Ocp] or null).
+//   acc = A - dz[oc]*S + bias_full[oc] - sum over out-of-bounds taps of tapc[tap][oc]
+//   real = float(acc) * acc_scale[oc]
+// A is the raw sum of x*w8 over in-bounds taps (w8 = weight shifted into int8),
+// S the raw sum of x over the same taps (needed only when some dz != 0).
+struct ContractEpilogue {
+  const int32_t* bias_full;
+  const float* acc_scale;
+  const int32_t* dz;         // null when all zero
+  const int32_t* tapc;       // null when the input zero point is 0 or there is no padding
+  OutQuant out;
+  int out_is_float;          // write float(acc)*acc_scale instead of quantizing
+};
+
+// ---- layout converters (elem = 1 or 4 bytes) -------------------------------
+void launch_whcn_to_cl(const void* src, void* dst, int N, int C, int H, int W, int Cp, int elem, cudaStream_t s);
+void launch_cl_to_whcn(const void* src, void* dst, int N, int C, int H, int W, int Cp, int elem, cudaStream_t s);
+
+// ---- quantized contraction on CUDA cores (any shape; the fallback path) ----
+// w8: [rows][Kp] int8, row oc holds K = (tap*Cp + c), Ocp rows; when e.dz != null
+// one more row (index Ocp) follows: the all-ones row whose dot product is S.
+void launch_conv_simt(const void* x, int x_signed, const int8_t* w8, int Kp, const ConvGeom& g,
+                      const ContractEpilogue& e, void* y, cudaStream_t s);
+
+// ---- depthwise convolution, quantized: wd [kh*kw][Ocp] int16 = w - zw -------
+void launch_depthwise_q(const void* x, int x_signed, int zx, const int16_t* wd, const int32_t* bias,
+                        const float* acc_scale, int multiplier, const ConvGeom& g, OutQuant out,
+                        void* y, cudaStream_t s);
+
+// ---- float32 convolution (dense or depthwise), accumulation order ic,ky,kx --
+// w: original WHIcOc layout; bias may be null.
+void launch_conv_f32(const float* x, const float* w, const float* bias, int multiplier, int w_ic,
+                     const ConvGeom& g, float* y, cudaStream_t s);
+
+// ---- pooling: type 0 max, 1 avg (divide by kw*kh), 3 avg over valid taps ----
+void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int in_zp, int same_quant,
+                   const ConvGeom& g, OutQuant out, void* y, cudaStream_t s);
+void launch_pool_f32(const float* x, int type, const ConvGeom& g, float* y, cudaStream_t s);
+
+// ---- elementwise over n elements of channels-last storage -------------------
+void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, int b_signed, float sb, int zb,
+                  OutQuant out, int out_signed, void* y, size_t n, cudaStream_t s);
+void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s);
+// upper < 0: relu, else clamp to [0, upper]
+void launch_relu_q(const void* x, int x_signed, float sx, int zx, float upper, OutQuant out, int out_signed,
+                   void* y, size_t n, cudaStream_t s);
+void launch_relu_f32(const float* x, float upper, float* y, size_t n, cudaStream_t s);
+
+// ---- softmax along one axis of a channels-last tensor ----------------------
+// Input and output may differ in element size (u8 in, f32 out), hence in
+// channel padding, so each side has its own element strides.  The reduced axis
+// is (len, x_stride/y_stride); the other three axes enumerate the slices.
+struct SoftmaxGeom {
+  int len; long long x_stride, y_stride;
+  int o[3]; long long xs[3], ys[3];
+};
+// x_kind: 0 u8, 1 s8, 2 f32.  y_kind likewise.
+void launch_softmax(const void* x, int x_kind, float sx, int zx, void* y, int y_kind, OutQuant out, float beta,
+                    const SoftmaxGeom& g, cudaStream_t s);
+
+// ---- explicit im2col for the tensor-core GEMM -------------------------------
+// col [M][Kp] bytes, M = N*Ho*Wo, K index = tap*Cs + c with Cs = g.C (dense) or
+// g.Cp; out-of-bounds taps are filled with the input zero point, the K tail
+// (and the channel padding when Cs = Cp) with zero.
+void launch_im2col(const void* x, int Cs, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s);
+
+// ---- int8 GEMM on tcgen05 tensor cores --------------------------------------
+// D[M][ldd] (u8/s8) = requant(A[M][Kp] (u8 or s8) * B[Np][Kp]^T (s8)), K-major
+// operands fed by TMA, int32 accumulation in tensor memory.  Returns a CUDA
+// error code; the kernel's bounded waits report through *status (device int,
+// 0 = ok).
+struct GemmTcPlan;   // opaque: tensor maps + launch geometry, built once at compile
+GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, int M, int Np, int Kp, int Oc,
+                                void* D, int ldd, int d_signed, const ContractEpilogue& e, int* status,
+                                char* err, size_t err_len);
+void gemm_tc_plan_destroy(GemmTcPlan* p);
+cudaError_t gemm_tc_launch(const GemmTcPlan* p, cudaStream_t s);
+// 1 when this build and device can run the tensor-core path.
+int gemm_tc_available(void);
+
+}  // namespace b2vx
+#endif  // B2VX_KERNELS_H_
