@@ -1,0 +1,206 @@
+"""GPU parity: the CUDA library against the reference's vectors and the CPU oracle.
+
+All calls go through the C ABI (pyb2vx).  Integer outputs must be bit-exact;
+float32 softmax is compared within 1e-5 (device expf vs libm expf); float32
+convolution/pooling/FC replay the oracle's operation order without fused
+multiply-add and must be bit-exact too.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import graph_cases as G
+import pyb2vx as B
+
+pytestmark = pytest.mark.gpu
+
+SOFTMAX_TOL = 1e-5
+
+
+@pytest.fixture(params=["tensorcore", "cudacore"])
+def conv_kernel(request):
+    """Run a test once with the tensor-core GEMM path and once with the CUDA-core path."""
+    old = os.environ.get("B2VX_CONV_KERNEL")
+    os.environ["B2VX_CONV_KERNEL"] = "tc" if request.param == "tensorcore" else "simt"
+    yield request.param
+    if old is None:
+        os.environ.pop("B2VX_CONV_KERNEL", None)
+    else:
+        os.environ["B2VX_CONV_KERNEL"] = old
+
+
+def test_device_present(product_lib):
+    assert product_lib.b2vx_device_count() >= 1
+
+
+def test_reference_vectors(product_lib, reference_cases, conv_kernel):
+    """Every graph of the reference's unit tests: GPU vs the test's own expected vector,
+    and GPU vs the oracle output recorded in the fixture (bit for bit for integers)."""
+    failures = []
+    for case in reference_cases:
+        g, inputs, expects, recorded = B.graph_from_case(product_lib, case)
+        try:
+            g.compile()
+            for tid, arr in inputs:
+                g.write(tid, arr)
+            g.run()
+            is_softmax = any(n["kind"] == B.NODE_SOFTMAX for n in case["nodes"])
+            for tid, want, tol in expects:
+                got = g.read(tid).reshape(-1)
+                if want.dtype == np.float32:
+                    if not np.allclose(got, want, rtol=0, atol=max(tol, 1e-5)):
+                        failures.append("%s: float mismatch vs reference vector %g" % (case["name"], np.abs(got - want).max()))
+                else:
+                    d = np.abs(got.astype(np.int64) - want.astype(np.int64)).max()
+                    if d > tol:
+                        failures.append("%s: |gpu - reference vector| = %d > %g" % (case["name"], d, tol))
+            for tid, want in recorded.items():
+                got = g.read(tid).reshape(-1)
+                if is_softmax:
+                    ok = np.allclose(got, want, rtol=0, atol=SOFTMAX_TOL)
+                else:
+                    ok = np.array_equal(got.view(np.uint8), want.view(np.uint8))
+                if not ok:
+                    failures.append("%s: gpu differs from oracle output" % case["name"])
+        except B.B2vxError as e:
+            failures.append("%s: %s" % (case["name"], e))
+        finally:
+            g.close()
+    assert not failures, "\n".join(failures[:40])
+
+
+CONV_CASES = {
+    # the single-conv sweep of the benchmark configuration at small batch, plus its 1x1 and stride-2 variants
+    "cfg2_3x3_n1": G.conv2d_q(56, 56, 64, 1, 3, 3, 64, relu=True),
+    "cfg2_3x3_n3": G.conv2d_q(56, 56, 64, 3, 3, 3, 64, relu=True),
+    "cfg2_1x1": G.conv2d_q(56, 56, 64, 2, 1, 1, 64, relu=True),
+    "cfg2_3x3_s2": G.conv2d_q(56, 56, 64, 2, 3, 3, 64, stride=(2, 2), relu=True),
+    # channel counts that need padding, odd sizes, ragged tiles
+    "c24_oc40": G.conv2d_q(13, 11, 24, 2, 3, 3, 40),
+    "c3_stem7x7": G.conv2d_q(32, 32, 3, 2, 7, 7, 64, stride=(2, 2), pad_type=B.PAD_AUTO, pad=(3, 3, 3, 3)),
+    "c1_5x5_valid": G.conv2d_q(28, 28, 1, 2, 5, 5, 20, pad_type=B.PAD_VALID, w_kind="u8z128", in_q=(1 / 255.0, 0), out_q=(0.05, 128)),
+    "u8_weights_zp": G.conv2d_q(10, 9, 20, 2, 3, 3, 50, w_kind="u8", out_q=(0.3, 121)),
+    "u8_weights_1x1": G.conv2d_q(7, 7, 96, 3, 1, 1, 24, w_kind="u8", out_q=(0.2, 130)),
+    "s8_act_s8_w": G.conv2d_q(9, 9, 16, 1, 3, 3, 32, x_dtype=B.DT_INT8, w_kind="s8", in_q=(0.5, -1), out_q=(1.5, -3), out_dtype=B.DT_INT8),
+    "dilated": G.conv2d_q(17, 15, 32, 1, 3, 3, 32, dilation=(2, 2)),
+    "oc_320_two_n_tiles": G.conv2d_q(7, 7, 64, 4, 1, 1, 320),
+    "oc_1024_k_2048": G.conv2d_q(4, 4, 2048, 2, 1, 1, 1024, in_q=(0.02, 128), out_q=(0.6, 0)),
+    "explicit_pad_asym": G.conv2d_q(12, 12, 16, 1, 3, 3, 16, stride=(2, 2), pad_type=B.PAD_AUTO, pad=(0, 1, 0, 1)),
+    "no_bias": G.conv2d_q(8, 8, 16, 1, 3, 3, 16, bias=False),
+    "single_pixel": G.conv2d_q(1, 1, 64, 1, 1, 1, 16),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CONV_CASES))
+def test_conv2d_matches_oracle(oracle_lib, product_lib, conv_kernel, name):
+    want, _ = G.run_case(oracle_lib, CONV_CASES[name], seed=11)
+    got, kernels = G.run_case(product_lib, CONV_CASES[name], seed=11)
+    G.assert_same(want, got)
+    names = [k["name"] for k in kernels]
+    if conv_kernel == "cudacore":
+        assert not any(n.startswith("gemm_i8_tc") for n in names)
+
+
+def test_tensor_core_path_is_taken(product_lib):
+    """With the default setting a plain int8 convolution runs on the tcgen05 GEMM."""
+    os.environ.pop("B2VX_CONV_KERNEL", None)
+    _, kernels = G.run_case(product_lib, CONV_CASES["cfg2_1x1"], seed=1)
+    assert any(k["name"].startswith("gemm_i8_tc") for k in kernels), [k["name"] for k in kernels]
+
+
+DEPTHWISE_CASES = {
+    "dw3x3_s1": G.depthwise_q(28, 28, 32, 2, 3, 3),
+    "dw3x3_s2": G.depthwise_q(28, 28, 96, 2, 3, 3, stride=(2, 2)),
+    "dw_c24": G.depthwise_q(15, 15, 24, 1, 3, 3),
+    "dw_mult2": G.depthwise_q(9, 9, 6, 2, 3, 3, multiplier=2),
+    "dw_s8pc": G.depthwise_q(14, 14, 64, 2, 3, 3, w_kind="s8pc"),
+    "dw5x5": G.depthwise_q(11, 13, 16, 1, 5, 5, relu6=False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(DEPTHWISE_CASES))
+def test_depthwise_matches_oracle(oracle_lib, product_lib, name):
+    want, _ = G.run_case(oracle_lib, DEPTHWISE_CASES[name], seed=5)
+    got, _ = G.run_case(product_lib, DEPTHWISE_CASES[name], seed=5)
+    G.assert_same(want, got)
+
+
+FC_CASES = {
+    "fc_1024_m16": G.fc_q(1024, 1024, 16),
+    "fc_1024_m1": G.fc_q(1024, 1024, 1),
+    "fc_1024_m130": G.fc_q(1024, 1024, 130),
+    "fc_k500_n10": G.fc_q(500, 10, 5, w_kind="u8z128"),
+    "fc_k800_from4d": G.fc_q(800, 500, 3, from_4d=(4, 4, 50), w_kind="u8z128"),
+    "fc_u8_zp": G.fc_q(1280, 1000, 2, w_kind="u8"),
+    "fc_2048_1000": G.fc_q(2048, 1000, 4),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FC_CASES))
+def test_fully_connected_matches_oracle(oracle_lib, product_lib, conv_kernel, name):
+    want, _ = G.run_case(oracle_lib, FC_CASES[name], seed=3)
+    got, _ = G.run_case(product_lib, FC_CASES[name], seed=3)
+    G.assert_same(want, got)
+
+
+POOL_CASES = {
+    "max2x2": G.pool_q(24, 24, 20, 2, B.POOL_MAX, (2, 2), (2, 2)),
+    "max3x3s2_ceil": G.pool_q(112, 112, 64, 1, B.POOL_MAX, (3, 3), (2, 2), pad=(0, 1, 0, 1), round_type=B.ROUND_CEILING),
+    "max_requant": G.pool_q(9, 9, 16, 1, B.POOL_MAX, (3, 3), (1, 1), pad=(1, 1, 1, 1), out_q=(0.07, 10)),
+    "avg7x7_global": G.pool_q(7, 7, 2048, 2, B.POOL_AVG, (7, 7), (7, 7), out_q=(0.04, 7)),
+    "avg_pad": G.pool_q(10, 10, 32, 1, B.POOL_AVG, (3, 3), (2, 2), pad=(1, 1, 1, 1)),
+    "avg_android_pad": G.pool_q(10, 10, 32, 1, B.POOL_AVG_ANDROID, (3, 3), (2, 2), pad=(1, 1, 1, 1)),
+    "avg_s8": G.pool_q(8, 8, 16, 1, B.POOL_AVG, (2, 2), (2, 2), in_q=(0.1, -5), dtype=B.DT_INT8),
+}
+
+
+@pytest.mark.parametrize("name", sorted(POOL_CASES))
+def test_pool_matches_oracle(oracle_lib, product_lib, name):
+    want, _ = G.run_case(oracle_lib, POOL_CASES[name], seed=9)
+    got, _ = G.run_case(product_lib, POOL_CASES[name], seed=9)
+    G.assert_same(want, got)
+
+
+ELTWISE_CASES = {
+    "add_resnet": G.add_q([56, 56, 256, 1], relu=True),
+    "add_c24": G.add_q([14, 14, 24, 2]),
+    "add_1m": G.add_q([1 << 20]),
+    "relu": G.relu_q([14, 14, 40, 2]),
+    "relu6": G.relu_q([14, 14, 40, 2], six=True, qi=(0.05, 100), qo=(0.0235, 0)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ELTWISE_CASES))
+def test_elementwise_matches_oracle(oracle_lib, product_lib, name):
+    want, _ = G.run_case(oracle_lib, ELTWISE_CASES[name], seed=21)
+    got, _ = G.run_case(product_lib, ELTWISE_CASES[name], seed=21)
+    G.assert_same(want, got)
+
+
+def test_softmax_matches_oracle(oracle_lib, product_lib):
+    for build in (G.softmax_q(10, 7), G.softmax_q(1000, 3, beta=0.5)):
+        want, _ = G.run_case(oracle_lib, build, seed=2)
+        got, _ = G.run_case(product_lib, build, seed=2)
+        G.assert_same(want, got, float_tol=SOFTMAX_TOL)
+
+
+@pytest.mark.parametrize("batch", [1, 16])
+def test_lenet_matches_oracle(oracle_lib, product_lib, conv_kernel, batch):
+    want, _ = G.run_case(oracle_lib, G.lenet_synthetic(batch), seed=77)
+    got, _ = G.run_case(product_lib, G.lenet_synthetic(batch), seed=77)
+    G.assert_same(want[:1], got[:1])                       # uint8 logits: bit-exact
+    G.assert_same(want[1:], got[1:], float_tol=SOFTMAX_TOL)  # float32 probabilities
+
+
+def test_errors_are_reported_not_swallowed(product_lib):
+    g = B.Graph(product_lib)
+    x = g.tensor(B.DT_UINT8, [4, 4, 8, 1], B.ATTR_INPUT, scale=0.1, zero_point=0)
+    w = g.tensor(B.DT_UINT8, [3, 3, 4, 8], B.ATTR_CONSTANT, scale=0.1, zero_point=0,
+                 data=np.zeros((8, 4, 3, 3), np.uint8))   # Ic 4 != C 8
+    y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.1, zero_point=0)
+    g.conv2d(x, w, None, y, pad_type=B.PAD_SAME)
+    with pytest.raises(B.B2vxError) as e:
+        g.compile()
+    assert e.value.status == 3  # SHAPE_MISMATCH
+    g.close()

@@ -754,3 +754,11 @@ std::shared_ptr<Operation> Softmax::Clone(std::shared_ptr<Graph>& graph) const {
 }  // namespace ops
 }  // namespace vx
 }  // namespace tim
+
+// The b2vx_graph behind a tim::vx::Graph, for tools that read back the launch
+// plan or time it (creates the backend graph if it does not exist yet).
+extern "C" void* timvx_graph_backend_handle(tim::vx::Graph* graph) {
+  auto* impl = static_cast<tim::vx::GraphImpl*>(graph);
+  if (!impl || !impl->EnsureHandle()) return nullptr;
+  return impl->handle();
+}

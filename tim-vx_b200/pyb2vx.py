@@ -1,0 +1,333 @@
+"""ctypes binding of the b2vx C ABI (include/b2vx.h) for tests and benchmarks.
+
+The same binding drives two libraries that export the identical ABI:
+``tim-vx_b200/csrc/libb2vx.so`` (the CUDA product) and
+``oracle/_build/libb2vx_oracle.so`` (the CPU oracle, test infrastructure).
+Nothing here computes anything: tensors go in and out as numpy arrays in
+tim::vx order (shape listed fastest dimension first, i.e. the reversed numpy
+shape of a C-contiguous array).
+"""
+import base64
+import ctypes as C
+import os
+import zlib
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PRODUCT_LIB = os.path.join(ROOT, "tim-vx_b200", "csrc", "libb2vx.so")
+ORACLE_LIB = os.path.join(ROOT, "oracle", "_build", "libb2vx_oracle.so")
+ORACLE_OPS_LIB = os.path.join(ROOT, "oracle", "_build", "liboracle_ops.so")
+
+NO_TENSOR = 0xFFFFFFFF
+DT_INT8, DT_UINT8, DT_INT32, DT_FLOAT32 = 1, 2, 5, 9
+NP_DTYPE = {DT_INT8: np.int8, DT_UINT8: np.uint8, DT_INT32: np.int32, DT_FLOAT32: np.float32}
+Q_NONE, Q_ASYM, Q_PER_CHANNEL = 0, 1, 2
+ATTR_CONSTANT, ATTR_TRANSIENT, ATTR_VARIABLE, ATTR_INPUT, ATTR_OUTPUT = 1, 2, 4, 8, 16
+PAD_NONE, PAD_AUTO, PAD_VALID, PAD_SAME = -1, 0, 1, 2
+POOL_MAX, POOL_AVG, POOL_AVG_ANDROID = 0, 1, 3
+ROUND_CEILING, ROUND_FLOOR = 0, 1
+NODE_CONV2D, NODE_FC, NODE_POOL2D, NODE_ADD, NODE_RELU, NODE_RELU6, NODE_SOFTMAX = 1, 2, 3, 4, 5, 6, 7
+STATUS_NAMES = ["OK", "INVALID_ARG", "UNSUPPORTED", "SHAPE_MISMATCH", "QUANT_MISMATCH", "OOM", "CUDA_ERROR",
+                "DEVICE_TIMEOUT", "BAD_STATE"]
+
+
+class TensorDesc(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("rank", C.c_uint32), ("dims", C.c_uint32 * 8), ("attr", C.c_int32),
+                ("quant_type", C.c_int32), ("scale", C.c_float), ("zero_point", C.c_int32),
+                ("channel_dim", C.c_int32), ("n_channel", C.c_uint32), ("scales", C.POINTER(C.c_float)),
+                ("zero_points", C.POINTER(C.c_int32))]
+
+
+class Conv2dDesc(C.Structure):
+    _fields_ = [("weights", C.c_uint32), ("pad_type", C.c_int32), ("ksize", C.c_uint32 * 2),
+                ("stride", C.c_uint32 * 2), ("dilation", C.c_uint32 * 2), ("pad", C.c_uint32 * 4),
+                ("multiplier", C.c_int32)]
+
+
+class FcDesc(C.Structure):
+    _fields_ = [("axis", C.c_uint32), ("weights", C.c_uint32)]
+
+
+class Pool2dDesc(C.Structure):
+    _fields_ = [("type", C.c_int32), ("pad_type", C.c_int32), ("ksize", C.c_uint32 * 2), ("stride", C.c_uint32 * 2),
+                ("pad", C.c_uint32 * 4), ("round_type", C.c_int32)]
+
+
+class SoftmaxDesc(C.Structure):
+    _fields_ = [("beta", C.c_float), ("axis", C.c_int32)]
+
+
+class KernelInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("node_index", C.c_uint32), ("ops", C.c_uint64), ("bytes", C.c_uint64),
+                ("last_ms", C.c_float)]
+
+
+class B2vxError(RuntimeError):
+    def __init__(self, status, message):
+        self.status = status
+        name = STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else str(status)
+        super().__init__("%s: %s" % (name, message))
+
+
+def load(path):
+    """Load one library exporting the b2vx ABI and declare its signatures."""
+    lib = C.CDLL(path)
+    vp, u32, st = C.c_void_p, C.c_uint32, C.c_int32
+    sigs = {
+        "b2vx_context_create": (st, [C.POINTER(vp)]),
+        "b2vx_context_destroy": (None, [vp]),
+        "b2vx_last_error": (C.c_char_p, [vp]),
+        "b2vx_device_count": (C.c_int32, []),
+        "b2vx_graph_create": (st, [vp, C.c_int32, C.POINTER(vp)]),
+        "b2vx_graph_destroy": (None, [vp]),
+        "b2vx_tensor_create": (st, [vp, C.POINTER(TensorDesc), vp, C.POINTER(u32)]),
+        "b2vx_tensor_get_desc": (st, [vp, u32, C.POINTER(TensorDesc)]),
+        "b2vx_tensor_write": (st, [vp, u32, vp, C.c_size_t]),
+        "b2vx_tensor_read": (st, [vp, u32, vp, C.c_size_t]),
+        "b2vx_node_conv2d": (st, [vp, u32, u32, u32, u32, C.POINTER(Conv2dDesc)]),
+        "b2vx_node_fully_connected": (st, [vp, u32, u32, u32, u32, C.POINTER(FcDesc)]),
+        "b2vx_node_pool2d": (st, [vp, u32, u32, C.POINTER(Pool2dDesc)]),
+        "b2vx_node_add": (st, [vp, u32, u32, u32]),
+        "b2vx_node_relu": (st, [vp, u32, u32]),
+        "b2vx_node_relu6": (st, [vp, u32, u32]),
+        "b2vx_node_softmax": (st, [vp, u32, u32, C.POINTER(SoftmaxDesc)]),
+        "b2vx_graph_compile": (st, [vp]),
+        "b2vx_graph_run": (st, [vp]),
+        "b2vx_graph_run_async": (st, [vp]),
+        "b2vx_graph_sync": (st, [vp]),
+        "b2vx_graph_set_stream": (st, [vp, vp]),
+        "b2vx_graph_print": (st, [vp]),
+        "b2vx_graph_kernel_count": (st, [vp, C.POINTER(u32)]),
+        "b2vx_graph_kernel_info": (st, [vp, u32, C.POINTER(KernelInfo)]),
+        "b2vx_graph_profile": (st, [vp, u32]),
+        "b2vx_host_alloc": (st, [C.POINTER(vp), C.c_size_t]),
+        "b2vx_host_free": (None, [vp]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+class Graph:
+    """One b2vx context + graph."""
+
+    def __init__(self, lib, device=0):
+        self.lib = lib
+        self.ctx = C.c_void_p()
+        self.g = C.c_void_p()
+        st = lib.b2vx_context_create(C.byref(self.ctx))
+        if st != 0:
+            raise B2vxError(st, "context_create")
+        st = lib.b2vx_graph_create(self.ctx, device, C.byref(self.g))
+        if st != 0:
+            msg = lib.b2vx_last_error(self.ctx).decode()
+            lib.b2vx_context_destroy(self.ctx)
+            self.ctx = None
+            raise B2vxError(st, msg)
+        self._keep = []
+
+    def close(self):
+        if self.g:
+            self.lib.b2vx_graph_destroy(self.g)
+            self.g = None
+        if self.ctx:
+            self.lib.b2vx_context_destroy(self.ctx)
+            self.ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st):
+        if st != 0:
+            raise B2vxError(st, self.lib.b2vx_last_error(self.ctx).decode())
+
+    def tensor(self, dtype, dims, attr, scale=None, zero_point=0, scales=None, zero_points=None, channel_dim=-1,
+               data=None):
+        d = TensorDesc()
+        d.dtype = dtype
+        d.rank = len(dims)
+        for i, v in enumerate(dims):
+            d.dims[i] = int(v)
+        d.attr = attr
+        d.channel_dim = channel_dim
+        if scales is not None:
+            d.quant_type = Q_PER_CHANNEL
+            sc = (C.c_float * len(scales))(*[float(s) for s in scales])
+            zps = zero_points if zero_points is not None else [0] * len(scales)
+            zp = (C.c_int32 * len(zps))(*[int(z) for z in zps])
+            d.n_channel = len(scales)
+            d.scales = C.cast(sc, C.POINTER(C.c_float))
+            d.zero_points = C.cast(zp, C.POINTER(C.c_int32))
+            self._keep += [sc, zp]
+        elif scale is not None:
+            d.quant_type = Q_ASYM
+            d.scale = float(scale)
+            d.zero_point = int(zero_point)
+        else:
+            d.quant_type = Q_NONE
+        ptr = None
+        if data is not None:
+            data = np.ascontiguousarray(data, dtype=NP_DTYPE[dtype])
+            self._keep.append(data)
+            ptr = data.ctypes.data_as(C.c_void_p)
+        tid = C.c_uint32()
+        self._check(self.lib.b2vx_tensor_create(self.g, C.byref(d), ptr, C.byref(tid)))
+        return tid.value
+
+    def conv2d(self, x, w, bias, y, stride=(1, 1), dilation=(1, 1), pad_type=PAD_AUTO, pad=(0, 0, 0, 0), multiplier=0,
+               weights=0, ksize=(0, 0)):
+        d = Conv2dDesc()
+        d.weights = weights
+        d.pad_type = pad_type
+        d.ksize[:] = ksize
+        d.stride[:] = stride
+        d.dilation[:] = dilation
+        d.pad[:] = pad
+        d.multiplier = multiplier
+        self._check(self.lib.b2vx_node_conv2d(self.g, x, w, NO_TENSOR if bias is None else bias, y, C.byref(d)))
+
+    def fully_connected(self, x, w, bias, y, axis=0, weights=0):
+        d = FcDesc(axis, weights)
+        self._check(self.lib.b2vx_node_fully_connected(self.g, x, w, NO_TENSOR if bias is None else bias, y, C.byref(d)))
+
+    def pool2d(self, x, y, type, ksize, stride, pad_type=PAD_AUTO, pad=(0, 0, 0, 0), round_type=ROUND_FLOOR):
+        d = Pool2dDesc()
+        d.type = type
+        d.pad_type = pad_type
+        d.ksize[:] = ksize
+        d.stride[:] = stride
+        d.pad[:] = pad
+        d.round_type = round_type
+        self._check(self.lib.b2vx_node_pool2d(self.g, x, y, C.byref(d)))
+
+    def add(self, a, b, y):
+        self._check(self.lib.b2vx_node_add(self.g, a, b, y))
+
+    def relu(self, x, y):
+        self._check(self.lib.b2vx_node_relu(self.g, x, y))
+
+    def relu6(self, x, y):
+        self._check(self.lib.b2vx_node_relu6(self.g, x, y))
+
+    def softmax(self, x, y, beta=1.0, axis=0):
+        d = SoftmaxDesc(beta, axis)
+        self._check(self.lib.b2vx_node_softmax(self.g, x, y, C.byref(d)))
+
+    def compile(self):
+        self._check(self.lib.b2vx_graph_compile(self.g))
+
+    def run(self):
+        self._check(self.lib.b2vx_graph_run(self.g))
+
+    def run_async(self):
+        self._check(self.lib.b2vx_graph_run_async(self.g))
+
+    def sync(self):
+        self._check(self.lib.b2vx_graph_sync(self.g))
+
+    def set_stream(self, stream_ptr):
+        self._check(self.lib.b2vx_graph_set_stream(self.g, C.c_void_p(stream_ptr)))
+
+    def desc(self, tid):
+        d = TensorDesc()
+        self._check(self.lib.b2vx_tensor_get_desc(self.g, tid, C.byref(d)))
+        return d
+
+    def shape(self, tid):
+        d = self.desc(tid)
+        return [int(d.dims[i]) for i in range(d.rank)]
+
+    def write(self, tid, array):
+        d = self.desc(tid)
+        a = np.ascontiguousarray(array, dtype=NP_DTYPE[d.dtype])
+        self._check(self.lib.b2vx_tensor_write(self.g, tid, a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def write_ptr(self, tid, ptr, nbytes):
+        self._check(self.lib.b2vx_tensor_write(self.g, tid, C.c_void_p(ptr), nbytes))
+
+    def read_ptr(self, tid, ptr, nbytes):
+        self._check(self.lib.b2vx_tensor_read(self.g, tid, C.c_void_p(ptr), nbytes))
+
+    def read(self, tid):
+        d = self.desc(tid)
+        dims = [int(d.dims[i]) for i in range(d.rank)]
+        out = np.empty(dims[::-1], dtype=NP_DTYPE[d.dtype])
+        self._check(self.lib.b2vx_tensor_read(self.g, tid, out.ctypes.data_as(C.c_void_p), out.nbytes))
+        return out
+
+    def kernels(self):
+        n = C.c_uint32()
+        self._check(self.lib.b2vx_graph_kernel_count(self.g, C.byref(n)))
+        out = []
+        for i in range(n.value):
+            k = KernelInfo()
+            self._check(self.lib.b2vx_graph_kernel_info(self.g, i, C.byref(k)))
+            out.append({"name": k.name.decode(), "node": k.node_index, "ops": k.ops, "bytes": k.bytes, "ms": k.last_ms})
+        return out
+
+    def profile(self, iters=5):
+        self._check(self.lib.b2vx_graph_profile(self.g, iters))
+        return self.kernels()
+
+
+# ----------------------------------------------------------------------------
+# Fixture cases (tests/golden/reference_cases.json)
+
+def unpack(b64, dtype):
+    return np.frombuffer(zlib.decompress(base64.b64decode(b64)), dtype=NP_DTYPE[dtype])
+
+
+def graph_from_case(lib, case, device=0):
+    """Rebuild the graph of one fixture case.  Returns (graph, inputs, expectations):
+    inputs is a list of (tensor id, array) to write before running, expectations a
+    list of (tensor id, expected array, tolerance)."""
+    g = Graph(lib, device)
+    ids = []
+    inputs = []
+    for t in case["tensors"]:
+        declared = t["declared_rank"] > 0
+        dims = t["dims"] if declared else []
+        kw = {}
+        if t["quant_type"] == Q_PER_CHANNEL:
+            kw = dict(scales=t["scales"], zero_points=t["zero_points"] or None, channel_dim=t["channel_dim"])
+        elif t["quant_type"] == Q_ASYM:
+            kw = dict(scale=t["scale"], zero_point=t["zero_point"], channel_dim=t["channel_dim"])
+        data = None
+        if t["data"] is not None and (t["attr"] & ATTR_CONSTANT):
+            data = unpack(t["data"], t["dtype"])
+        tid = g.tensor(t["dtype"], dims, t["attr"], data=data, **kw)
+        ids.append(tid)
+        if t["data"] is not None and (t["attr"] & ATTR_INPUT):
+            inputs.append((tid, unpack(t["data"], t["dtype"])))
+    for n in case["nodes"]:
+        i = [ids[v] if v != NO_TENSOR else None for v in n["in"]]
+        o = ids[n["out"]]
+        k = n["kind"]
+        if k == NODE_CONV2D:
+            g.conv2d(i[0], i[1], i[2], o, stride=n["stride"], dilation=n["dilation"], pad_type=n["pad_type"],
+                     pad=n["pad"], multiplier=n["multiplier"], weights=n["weights"], ksize=n["ksize"])
+        elif k == NODE_FC:
+            g.fully_connected(i[0], i[1], i[2], o, axis=n["axis"], weights=n["weights"])
+        elif k == NODE_POOL2D:
+            g.pool2d(i[0], o, n["type"], n["ksize"], n["stride"], pad_type=n["pad_type"], pad=n["pad"],
+                     round_type=n["round_type"])
+        elif k == NODE_ADD:
+            g.add(i[0], i[1], o)
+        elif k == NODE_RELU:
+            g.relu(i[0], o)
+        elif k == NODE_RELU6:
+            g.relu6(i[0], o)
+        elif k == NODE_SOFTMAX:
+            g.softmax(i[0], o, beta=n["beta"], axis=n["axis"])
+        else:
+            raise ValueError("unknown node kind %r" % k)
+    expects = [(ids[e["tensor"]], unpack(e["data"], e["dtype"]), e["tol"]) for e in case["expect"]]
+    oracle_out = {ids[t["id"]]: unpack(t["data"], t["dtype"]) for t in case["tensors"]
+                  if t["data"] is not None and (t["attr"] & ATTR_OUTPUT)}
+    return g, inputs, expects, oracle_out
