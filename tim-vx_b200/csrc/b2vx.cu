@@ -83,6 +83,7 @@ struct NodeRec {
     b2vx_softmax_desc softmax;
   } p;
   uint32_t pad[4];
+  bool removed = false;   // folded into its producer at compile
 };
 
 struct Step {
@@ -301,6 +302,39 @@ OutQuant out_quant(const TensorRec& t) {
   else if (t.d.dtype == B2VX_DT_UINT8) { q.lo = 0; q.hi = 255; }
   else { q.lo = INT32_MIN; q.hi = INT32_MAX; }
   return q;
+}
+
+// Host copy of the device requantization (requant.cuh): fp32_to_affine of the
+// reference with its vsi_rint tie rule, in plain IEEE float operations.
+int host_requant(float real, const OutQuant& q) {
+  if (std::isinf(real)) return real < 0.0f ? q.lo : q.hi;
+  const float x = real / q.scale;
+  const float ax = std::fabs(x);
+  const float fl = std::floor(ax);
+  float r;
+  if (ax - fl == 0.5f) r = fl + static_cast<float>(static_cast<long long>(fl) & 1);
+  else r = std::floor(ax + 0.5f);
+  r = std::copysign(r, x);
+  double v = static_cast<double>(r) + q.zp;
+  if (!(v == v)) v = 0;
+  v = std::max(static_cast<double>(q.lo), std::min(static_cast<double>(q.hi), v));
+  return static_cast<int>(v);
+}
+
+// Relu / Relu6 from one 8-bit quantization to another as a byte table:
+// quantize(clamp(dequantize(q), 0, upper)).
+std::vector<uint8_t> relu_table(const TensorRec& x, const TensorRec& y, float upper) {
+  std::vector<uint8_t> lut(256);
+  const OutQuant oq = out_quant(y);
+  const bool xs = x.d.dtype == B2VX_DT_INT8;
+  for (int i = 0; i < 256; ++i) {
+    const int q = xs ? static_cast<int>(static_cast<int8_t>(i)) : i;
+    float r = (static_cast<float>(q) - static_cast<float>(x.zp())) * x.scale();
+    r = r < 0.0f ? 0.0f : r;
+    if (upper >= 0.0f && r > upper) r = upper;
+    lut[i] = static_cast<uint8_t>(host_requant(r, oq) & 0xFF);
+  }
+  return lut;
 }
 
 b2vx_kernel_info make_info(const char* name, uint32_t node, uint64_t ops, uint64_t bytes) {
@@ -747,12 +781,12 @@ b2vx_status plan_relu(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   } else if (is_q8(x.d.dtype) && is_q8(y.d.dtype)) {
     const void* xp = x.d_cl;
     void* yp = y.d_cl;
-    const int xs = x.d.dtype == B2VX_DT_INT8, ys = y.d.dtype == B2VX_DT_INT8, zx = x.zp();
-    const float sx = x.scale();
-    const OutQuant oq = out_quant(y);
+    uint8_t* dlut = nullptr;
+    b2vx_status st = upload(g, relu_table(x, y, upper), &dlut);
+    if (st != B2VX_OK) return st;
     const size_t nel = y.cl_bytes;
-    s.info = make_info("relu_q", idx, 0, abytes);
-    s.fn = [=](cudaStream_t st2) { launch_relu_q(xp, xs, sx, zx, upper, oq, ys, yp, nel, st2); return cudaGetLastError(); };
+    s.info = make_info("relu_lut_q", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_lut_q(xp, dlut, yp, nel, st2); return cudaGetLastError(); };
   } else {
     return fail(g, B2VX_UNSUPPORTED, "relu: input and output must be both int8/uint8 or both float32");
   }
@@ -1046,8 +1080,36 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
   }
   if (g->order.size() != g->nodes.size()) return fail(g, B2VX_BAD_STATE, "graph has a cycle or a node whose input is never produced");
 
+  // 1b. A Relu/Relu6 between identical 8-bit quantizations whose byte table is the
+  // identity (zero point at the bottom of the range, nothing to clamp) changes no
+  // byte: its producer writes straight into the Relu's output tensor.
+  for (NodeRec& r : g->nodes) {
+    if (r.kind != B2VX_NODE_RELU && r.kind != B2VX_NODE_RELU6) continue;
+    TensorRec& tin = g->tensors[r.in[0]];
+    TensorRec& tout = g->tensors[r.out];
+    if (!is_q8(tin.d.dtype) || tin.d.dtype != tout.d.dtype) continue;
+    if (tin.d.quant_type != B2VX_QUANT_ASYMMETRIC || tout.d.quant_type != B2VX_QUANT_ASYMMETRIC) continue;
+    if (tin.scale() != tout.scale() || tin.zp() != tout.zp()) continue;
+    if (tin.d.attr != B2VX_ATTR_TRANSIENT) continue;
+    int consumers = 0;
+    NodeRec* producer = nullptr;
+    for (NodeRec& n : g->nodes) {
+      if (n.removed) continue;
+      for (uint32_t id : n.in) consumers += id == r.in[0];
+      if (n.out == r.in[0]) producer = &n;
+    }
+    if (consumers != 1 || !producer) continue;
+    const std::vector<uint8_t> lut = relu_table(tin, tout, r.kind == B2VX_NODE_RELU6 ? 6.0f : -1.0f);
+    bool identity = true;
+    for (int i = 0; i < 256; ++i) identity = identity && lut[i] == i;
+    if (!identity) continue;
+    producer->out = r.out;
+    r.removed = true;
+  }
+
   // 2. which tensors are activations (touched by a node as data, not as weights/bias)
   for (const NodeRec& n : g->nodes) {
+    if (n.removed) continue;
     g->tensors[n.in[0]].is_activation = true;
     g->tensors[n.out].is_activation = true;
     if (n.kind == B2VX_NODE_ADD) g->tensors[n.in[1]].is_activation = true;
@@ -1086,6 +1148,7 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
   }
   for (uint32_t idx : g->order) {
     NodeRec& n = g->nodes[idx];
+    if (n.removed) continue;
     b2vx_status st = B2VX_UNSUPPORTED;
     switch (n.kind) {
       case B2VX_NODE_CONV2D: st = plan_conv(g, idx, n); break;

@@ -8,20 +8,23 @@
 //    tiled loads with a 32/64/128-byte swizzle and tcgen05.mma.kind::i8 consume
 //    directly; accumulation is int32 in tensor memory.
 //
-// One persistent CTA per SM, 192 threads, warp-specialised:
+// One persistent CTA per SM, 576 threads, warp-specialised:
 //   warp 0      TMA producer: per k-block one A box (128 rows x BK bytes) and
 //               one B box (BN rows x BK bytes) into a ring of smem stages;
 //   warp 1      allocates tensor memory, then one lane issues the MMAs
 //               (M=128, N=BN, K=32 per instruction) and commits them to
 //               mbarriers: stage-free after each k-block, accumulator-ready
 //               after the last one;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp owns the 32
-//               TMEM lanes its warp id maps to), add the folded bias, replay
-//               the float requantization, pack to bytes and store 16-byte
-//               runs.  Two accumulator buffers let the MMAs of tile i+1
-//               overlap the epilogue of tile i.
-// Tiles are visited n-fastest so the CTAs that share an A row-block run at the
-// same time and the second and later reads of it hit L2.
+//   warps 2-17  epilogue, 16 warps so that each SM scheduler has four of them
+//               to hide latency: a warp owns the 32 TMEM lanes (rows) its warp
+//               id maps to and every fourth 16-column chunk; it tcgen05.ld's
+//               the chunk, adds the folded bias, requantizes (requant_fast:
+//               same integers as the reference's float sequence), packs 16
+//               bytes and stores them.  Two accumulator buffers let the MMAs
+//               of tile i+1 overlap the epilogue of tile i.
+// The grid is a multiple of the number of N tiles, so a CTA keeps one N tile
+// for its whole life (bias and scales are staged in shared memory once) and
+// neighbouring CTAs share an A row-block, whose second and later reads hit L2.
 //
 // Every mbarrier wait is bounded: after kWaitLimitCycles the waiting thread
 // records a code in *status, raises a CTA-wide abort flag that all other waits
@@ -41,7 +44,8 @@ namespace b2vx {
 namespace {
 
 constexpr int kBlockM = 128;
-constexpr int kThreadsTc = 192;
+constexpr int kEpilogueWarps = 16;
+constexpr int kThreadsTc = (2 + kEpilogueWarps) * 32;
 constexpr int kMaxStages = 8;
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 constexpr int kMinDynSmem = 120 * 1024;               // keeps two CTAs from sharing an SM (and its TMEM)
@@ -134,6 +138,15 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, int (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, int (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are one
@@ -156,6 +169,9 @@ struct SmemHeader {
   unsigned long long tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  // this CTA's N tile: folded bias and accumulator scale per column; read as 128-bit vectors
+  alignas(16) int bias[256];
+  alignas(16) float scale[256];
 };
 
 __global__ void __launch_bounds__(kThreadsTc, 1)
@@ -182,10 +198,16 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&hdr->tmem_full[a]), 1);
-      mbar_init(smem_u32(&hdr->tmem_empty[a]), 4);
+      mbar_init(smem_u32(&hdr->tmem_empty[a]), kEpilogueWarps);
     }
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  const int n_tile = blockIdx.x % p.n_tiles;   // fixed per CTA: gridDim.x is a multiple of n_tiles
+  for (int i = threadIdx.x; i < p.BN; i += kThreadsTc) {
+    const int oc = n_tile * p.BN + i;
+    hdr->bias[i] = oc < p.Ocp ? p.ep.bias_full[oc] : 0;
+    hdr->scale[i] = oc < p.Ocp ? p.ep.acc_scale[oc] : 0.0f;
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hdr->tmem_base)),
@@ -204,7 +226,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m_tile = tile / p.n_tiles, n_tile = tile - m_tile * p.n_tiles;
+        const int m_tile = tile / p.n_tiles;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
           if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
@@ -247,38 +269,42 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    const int ew = warp - 2;                      // 0..15
     const int quarter = warp & 3;                 // TMEM lanes [32*quarter, +32) belong to this warp
+    const int col_group = ew >> 2;                // this warp takes 16-column chunks col_group, col_group+4, ...
     const int row_in_tile = quarter * 32 + lane;
-    const ContractEpilogue& e = p.ep;
+    const OutQuant oq = p.ep.out;
+    const float inv_scale = __frcp_rn(oq.scale);
+    const int span = oq.hi - oq.lo;
+    const int addc = oq.zp - oq.lo - 0x4B400000;
+    const uint32_t sign_fix = oq.lo < 0 ? 0x80808080u : 0u;   // u + lo as a byte == u ^ 0x80 when lo == -128
     int j = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
-      const int m_tile = tile / p.n_tiles, n_tile = tile - m_tile * p.n_tiles;
+      const int m_tile = tile / p.n_tiles;
       const uint32_t a = j & 1, aph = (j >> 1) & 1;
       if (!mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4)) break;
       tc_fence_after();
       const long long row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
       const uint32_t taddr = tmem_base + a * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
-      for (int c0 = 0; c0 < p.BN; c0 += 32) {
-        int acc[32];
-        tc_ld_32x32(taddr + c0, acc);
+      for (int c0 = col_group * 16; c0 < p.BN; c0 += 64) {
+        int acc[16];
+        tc_ld_32x16(taddr + c0, acc);
         tc_ld_wait();
-        const int col0 = n_tile * p.BN + c0;
-        if (row < p.M) {
+        const int cbase = n_tile * p.BN + c0;
+        if (row < p.M && cbase + 16 <= p.Ocp) {
+          uint32_t w4[4];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int cbase = col0 + h * 16;
-            if (cbase + 16 <= p.Ocp) {
-              uint32_t w4[4] = {0, 0, 0, 0};
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int oc = cbase + i;
-                const int v = acc[h * 16 + i] + __ldg(e.bias_full + oc);
-                const float real = __fmul_rn(__int2float_rn(v), __ldg(e.acc_scale + oc));
-                w4[i >> 2] |= static_cast<uint32_t>(requant(real, e.out) & 0xFF) << ((i & 3) * 8);
-              }
-              *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-            }
+          for (int g4 = 0; g4 < 4; ++g4) {
+            const int4 b4 = *reinterpret_cast<const int4*>(&hdr->bias[c0 + g4 * 4]);
+            const float4 s4 = *reinterpret_cast<const float4*>(&hdr->scale[c0 + g4 * 4]);
+            const int u0 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 0] + b4.x), s4.x), oq, inv_scale, addc, span);
+            const int u1 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 1] + b4.y), s4.y), oq, inv_scale, addc, span);
+            const int u2 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 2] + b4.z), s4.z), oq, inv_scale, addc, span);
+            const int u3 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 3] + b4.w), s4.w), oq, inv_scale, addc, span);
+            w4[g4] = (static_cast<uint32_t>(u0) | (static_cast<uint32_t>(u1) << 8) | (static_cast<uint32_t>(u2) << 16) |
+                      (static_cast<uint32_t>(u3) << 24)) ^ sign_fix;
           }
+          *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
         }
       }
       tc_fence_before();
@@ -402,7 +428,7 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
     return fail("gemm_tc: tile does not fit shared memory");
   }
   p.stages = stages;
-  // the epilogue reads 32 columns at a time, so each accumulator buffer spans BN rounded up to 32
+  // the epilogue reads 16 columns at a time; buffers start on 32-column boundaries
   p.acc_stride = (p.BN + 31) & ~31;
   int cols = 32;
   while (cols < 2 * p.acc_stride) cols <<= 1;
@@ -426,8 +452,12 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // a multiple of n_tiles, so that every CTA works on one N tile only
   const int tiles = p.m_tiles * p.n_tiles;
-  plan->grid = tiles < sms ? tiles : sms;
+  int grid = (sms / p.n_tiles) * p.n_tiles;
+  if (grid < p.n_tiles) grid = p.n_tiles;
+  if (grid > tiles) grid = tiles;
+  plan->grid = grid;
   size_t smem = static_cast<size_t>(stages) * stage_bytes + sizeof(SmemHeader) + 1024;
   if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
   plan->smem = smem;

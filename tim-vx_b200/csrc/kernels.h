@@ -80,9 +80,10 @@ void launch_pool_f32(const float* x, int type, const ConvGeom& g, float* y, cuda
 void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, int b_signed, float sb, int zb,
                   OutQuant out, int out_signed, void* y, size_t n, cudaStream_t s);
 void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s);
+// y[i] = lut[x[i]] over n bytes: Relu/Relu6 between any two 8-bit quantizations,
+// the 256-entry device table being built on the host with the reference's float sequence
+void launch_lut_q(const void* x, const uint8_t* lut, void* y, size_t n, cudaStream_t s);
 // upper < 0: relu, else clamp to [0, upper]
-void launch_relu_q(const void* x, int x_signed, float sx, int zx, float upper, OutQuant out, int out_signed,
-                   void* y, size_t n, cudaStream_t s);
 void launch_relu_f32(const float* x, float upper, float* y, size_t n, cudaStream_t s);
 
 // ---- softmax along one axis of a channels-last tensor ----------------------

@@ -309,28 +309,40 @@ __device__ __forceinline__ int byte_at(uint32_t word, int j) {
   return S ? static_cast<int>(static_cast<int8_t>(b)) : static_cast<int>(b);
 }
 
-// 16 elements per thread, 128-bit loads and stores.
+// 16 elements per thread, 128-bit loads and stores.  The two dequantizations
+// ((q - zp) * scale, 256 possible values each) are tabulated in shared memory
+// by the block; the sum is requantized with requant_fast.
 template <bool AS, bool BS>
 __global__ void add_q_kernel(const uint4* __restrict__ a, float sa, int za, const uint4* __restrict__ b, float sb, int zb,
                              OutQuant out, uint4* __restrict__ y, size_t n16) {
-  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  if (i >= n16) return;
-  const uint4 av = a[i], bv = b[i];
-  const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-  uint32_t ow[4];
-  const float zaf = __int2float_rn(za), zbf = __int2float_rn(zb);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float fa = __fmul_rn(__fsub_rn(__int2float_rn(byte_at<AS>(aw[k], j)), zaf), sa);
-      const float fb = __fmul_rn(__fsub_rn(__int2float_rn(byte_at<BS>(bw[k], j)), zbf), sb);
-      word |= static_cast<uint32_t>(requant(__fadd_rn(fa, fb), out) & 0xFF) << (8 * j);
-    }
-    ow[k] = word;
+  __shared__ float fa[256], fb[256];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    const int qa = AS ? static_cast<int>(static_cast<int8_t>(i)) : i;
+    const int qb = BS ? static_cast<int>(static_cast<int8_t>(i)) : i;
+    fa[i] = __fmul_rn(__fsub_rn(__int2float_rn(qa), __int2float_rn(za)), sa);
+    fb[i] = __fmul_rn(__fsub_rn(__int2float_rn(qb), __int2float_rn(zb)), sb);
   }
-  y[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  __syncthreads();
+  const float inv_scale = __frcp_rn(out.scale);
+  const int span = out.hi - out.lo, addc = out.zp - out.lo - 0x4B400000;
+  const uint32_t sign_fix = out.lo < 0 ? 0x80808080u : 0u;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
+    const uint4 av = a[i], bv = b[i];
+    const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float r = __fadd_rn(fa[(aw[k] >> (8 * j)) & 0xFF], fb[(bw[k] >> (8 * j)) & 0xFF]);
+        word |= static_cast<uint32_t>(requant_fast(r, out, inv_scale, addc, span)) << (8 * j);
+      }
+      ow[k] = word ^ sign_fix;
+    }
+    y[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
 }
 
 __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y, size_t n) {
@@ -338,28 +350,25 @@ __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restr
   if (i < n) y[i] = __fadd_rn(a[i], b[i]);
 }
 
-template <bool XS>
-__global__ void relu_q_kernel(const uint4* __restrict__ x, float sx, int zx, float upper, OutQuant out,
-                              uint4* __restrict__ y, size_t n16) {
-  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  if (i >= n16) return;
-  const uint4 xv = x[i];
-  const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-  uint32_t ow[4];
-  const float zf = __int2float_rn(zx);
+// Any 8-bit -> 8-bit pointwise map (Relu, Relu6 with arbitrary input/output
+// quantization) as a 256-entry table built on the host with the reference's
+// float sequence; 16 elements per thread.
+__global__ void lut_q_kernel(const uint4* __restrict__ x, const uint8_t* __restrict__ lut, uint4* __restrict__ y, size_t n16) {
+  __shared__ uint8_t t[256];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) t[i] = lut[i];
+  __syncthreads();
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
+    const uint4 xv = x[i];
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    uint32_t ow[4];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float r = __fmul_rn(__fsub_rn(__int2float_rn(byte_at<XS>(xw[k], j)), zf), sx);
-      r = r < 0.0f ? 0.0f : r;
-      if (upper >= 0.0f && r > upper) r = upper;
-      word |= static_cast<uint32_t>(requant(r, out) & 0xFF) << (8 * j);
+    for (int k = 0; k < 4; ++k) {
+      ow[k] = static_cast<uint32_t>(t[xw[k] & 0xFF]) | (static_cast<uint32_t>(t[(xw[k] >> 8) & 0xFF]) << 8) |
+              (static_cast<uint32_t>(t[(xw[k] >> 16) & 0xFF]) << 16) | (static_cast<uint32_t>(t[xw[k] >> 24]) << 24);
     }
-    ow[k] = word;
+    y[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
   }
-  y[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
 }
 
 __global__ void relu_f32_kernel(const float* __restrict__ x, float upper, float* __restrict__ y, size_t n) {
@@ -534,7 +543,8 @@ void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, 
                   OutQuant out, int /*out_signed*/, void* y, size_t n, cudaStream_t s) {
   const size_t n16 = n / 16;
   if (n16 == 0) return;
-  const unsigned grid = grid_for(static_cast<long long>(n16), kThreads);
+  unsigned grid = grid_for(static_cast<long long>(n16), kThreads);
+  if (grid > 148u * 16u) grid = 148u * 16u;
   const uint4* pa = static_cast<const uint4*>(a);
   const uint4* pb = static_cast<const uint4*>(b);
   uint4* py = static_cast<uint4*>(y);
@@ -549,15 +559,12 @@ void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStre
   add_f32_kernel<<<grid_for(static_cast<long long>(n), kThreads), kThreads, 0, s>>>(a, b, y, n);
 }
 
-void launch_relu_q(const void* x, int x_signed, float sx, int zx, float upper, OutQuant out, int /*out_signed*/, void* y,
-                   size_t n, cudaStream_t s) {
+void launch_lut_q(const void* x, const uint8_t* lut, void* y, size_t n, cudaStream_t s) {
   const size_t n16 = n / 16;
   if (n16 == 0) return;
-  const unsigned grid = grid_for(static_cast<long long>(n16), kThreads);
-  if (x_signed)
-    relu_q_kernel<true><<<grid, kThreads, 0, s>>>(static_cast<const uint4*>(x), sx, zx, upper, out, static_cast<uint4*>(y), n16);
-  else
-    relu_q_kernel<false><<<grid, kThreads, 0, s>>>(static_cast<const uint4*>(x), sx, zx, upper, out, static_cast<uint4*>(y), n16);
+  unsigned grid = grid_for(static_cast<long long>(n16), kThreads);
+  if (grid > 148u * 16u) grid = 148u * 16u;
+  lut_q_kernel<<<grid, kThreads, 0, s>>>(static_cast<const uint4*>(x), lut, static_cast<uint4*>(y), n16);
 }
 
 void launch_relu_f32(const float* x, float upper, float* y, size_t n, cudaStream_t s) {

@@ -36,5 +36,28 @@ __device__ __forceinline__ int requant(float real, const OutQuant& q) {
   return static_cast<int>(v);
 }
 
+// Fast form of the same conversion for hot epilogues.  Returns q - lo, in
+// [0, span] with span = hi - lo.  inv_scale = 1/scale (rounded), addc =
+// zp - lo - 0x4B400000.
+//
+// t = real*inv_scale differs from the reference's real/scale by at most a
+// couple of ulps, and the reference's rounding differs from round-to-nearest-
+// even only within one ulp of a .5 fraction.  So whenever t is farther than
+// |t|*2^-20 from every .5 fraction, RTNE(t) is the reference's result; RTNE
+// comes from adding 1.5*2^23, which leaves the integer in the low mantissa
+// bits.  The rare near-tie element (about |t|*2e-6 of them) takes the exact
+// sequence.  |t| is clamped to 2^16 first: beyond that the output saturates
+// whatever the rounding (|zp| and the output range are at most 8 bits).
+__device__ __forceinline__ int requant_fast(float real, const OutQuant& q, float inv_scale, int addc, int span) {
+  float t = __fmul_rn(real, inv_scale);
+  t = fminf(fmaxf(t, -65536.0f), 65536.0f);
+  const float r = __fadd_rn(t, 12582912.0f);
+  const float d = __fsub_rn(t, __fsub_rn(r, 12582912.0f));
+  const float thr = fmaf(fabsf(t), -9.5367431640625e-7f, 0.5f);
+  int u = __vimin_s32_relu(__float_as_int(r) + addc, span);
+  if (fabsf(d) > thr) u = requant(real, q) - q.lo;
+  return u;
+}
+
 }  // namespace b2vx
 #endif  // B2VX_REQUANT_CUH_
