@@ -60,6 +60,7 @@ struct TensorRec {
   void* d_io = nullptr;        // WHCN copy for graph inputs/outputs (== d_cl when both layouts coincide)
   size_t cl_bytes = 0, io_bytes = 0;
   bool is_activation = false;
+  bool cl_used = false;        // some kernel reads the channels-last copy (decides whether a graph input is converted)
 
   size_t elems() const {
     size_t n = 1;
@@ -294,6 +295,12 @@ void map_dims(TensorRec& t) {
   t.io_bytes = t.bytes();
 }
 
+// Channels-last storage of a tensor a kernel is about to read.
+const void* cl_in(TensorRec& t) {
+  t.cl_used = true;
+  return t.d_cl;
+}
+
 OutQuant out_quant(const TensorRec& t) {
   OutQuant q;
   q.scale = t.scale();
@@ -386,10 +393,11 @@ struct PackedContraction {
 // Weight element (kx,ky,ic,oc) of a WHIcOc kernel as a signed value together
 // with the zero point that still has to be subtracted from it: u8 weights are
 // shifted by 128 into int8 (dz = zw-128), s8 weights are kept (dz = zw).
-// K index = tap*Cs + ic; rows are output channels (+ the all-ones row at index
+// K index = tap*Cs + ic, or ic*taps + tap when channel_major (the kernel tensor's own order,
+// used with the WHCN im2col); rows are output channels (+ the all-ones row at index
 // rows_before_ones when some dz != 0 and with_ones_row is set).
 void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* bias, int kw, int kh, int C, int Cs,
-                      int Kp, int Oc, int Ocp, int rows, bool zero_fill_semantics, bool with_ones_row,
+                      int Kp, int Oc, int Ocp, int rows, bool channel_major, bool with_ones_row,
                       PackedContraction* out) {
   const int taps = kw * kh;
   const bool w_u8 = w.d.dtype == B2VX_DT_UINT8;
@@ -422,7 +430,7 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
       for (int t = 0; t < taps; ++t) {
         const size_t src = (static_cast<size_t>(oc) * C + ic) * taps + t;   // WHIcOc, W fastest: tap = ky*kw + kx
         const int v = w_u8 ? static_cast<int>(w.host[src]) - 128 : static_cast<int>(reinterpret_cast<const int8_t*>(w.host.data())[src]);
-        row[static_cast<size_t>(t) * Cs + ic] = static_cast<int8_t>(v);
+        row[channel_major ? static_cast<size_t>(ic) * taps + t : static_cast<size_t>(t) * Cs + ic] = static_cast<int8_t>(v);
         tapsum[t] += v;
       }
     }
@@ -439,9 +447,8 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
   if (with_ones_row && out->need_s) {
     int8_t* ones = out->w8.data() + static_cast<size_t>(rows) * Kp;
     for (int t = 0; t < taps; ++t)
-      for (int ic = 0; ic < C; ++ic) ones[static_cast<size_t>(t) * Cs + ic] = 1;
+      for (int ic = 0; ic < C; ++ic) ones[channel_major ? static_cast<size_t>(ic) * taps + t : static_cast<size_t>(t) * Cs + ic] = 1;
   }
-  (void)zero_fill_semantics;
 }
 
 b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* label, TensorRec& x, TensorRec& w,
@@ -468,7 +475,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       st = upload(g, bv, &db);
       if (st != B2VX_OK) return st;
     }
-    const float* xp = static_cast<const float*>(x.d_cl);
+    const float* xp = static_cast<const float*>(cl_in(x));
     float* yp = static_cast<float*>(y.d_cl);
     const int w_ic = x.C;
     Step s;
@@ -515,22 +522,32 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
   PackedContraction pk;
 
   if (tc_ok) {
+    // Four ways to present the input to the GEMM kernel:
+    //   identity  the channels-last input already is the A matrix (1x1/s1, or a window = whole input);
+    //   implicit  filter taps fetched as shifted 4-D TMA boxes, zero fill as padding (needs zx == 0 or no pad);
+    //   whcn      first layers with < 16 channels: im2col straight from the WHCN graph input, K = (c,ky,kx);
+    //   im2col    everything else: explicit matrix in scratch memory, padding filled with zx.
+    enum { IDENTITY, IMPLICIT, WHCN, IM2COL } mode;
+    static const bool allow_strided = [] { const char* e = std::getenv("B2VX_IMPLICIT_STRIDED"); return !(e && e[0] == '0'); }();
+    const bool strided = geo.sx != 1 || geo.sy != 1;
+    if (identity_1x1 || identity_full) mode = IDENTITY;
+    else if (x.C >= 16 && (x.zp() == 0 || !has_pad) && (!strided || allow_strided)) mode = IMPLICIT;
+    else if (x.C < 16 && (x.d.attr & B2VX_ATTR_INPUT) && x.d_io != nullptr &&
+             static_cast<size_t>(x.C) * kh * ((geo.Wo - 1) * geo.sx + (kw - 1) * geo.dx + 1) + 4u * round_up(taps * x.C, 16) <= 40u * 1024u)
+      mode = WHCN;   // the staging rows of one output row fit in shared memory
+    else mode = IM2COL;
     int Cs, Kp, M;
-    const void* A;
-    bool need_im2col = false;
-    if (identity_1x1) { Cs = x.Cp; Kp = x.Cp; M = static_cast<int>(P); A = x.d_cl; }
-    else if (identity_full) { Cs = x.Cp; Kp = taps * x.Cp; M = y.N; A = x.d_cl; }
-    else {
-      Cs = x.C < 16 ? x.C : x.Cp;
-      Kp = round_up(taps * Cs, 16);
-      M = static_cast<int>(P);
-      need_im2col = true;
-      A = nullptr;
-    }
+    const void* A = nullptr;
+    const bool need_im2col = mode == WHCN || mode == IM2COL;
+    if (mode == IDENTITY && identity_1x1) { Cs = x.Cp; Kp = x.Cp; M = static_cast<int>(P); A = cl_in(x); }
+    else if (mode == IDENTITY) { Cs = x.Cp; Kp = taps * x.Cp; M = y.N; A = cl_in(x); }
+    else if (mode == IMPLICIT) { Cs = x.Cp; Kp = taps * x.Cp; M = static_cast<int>(P); A = cl_in(x); }
+    else if (mode == WHCN) { Cs = x.C; Kp = round_up(taps * x.C, 16); M = static_cast<int>(P); }
+    else { Cs = x.C < 16 ? x.C : x.Cp; Kp = round_up(taps * Cs, 16); M = static_cast<int>(P); }
     const int n_tiles = (y.Cp + 255) / 256;
     const int BN = round_up((y.Cp + n_tiles - 1) / n_tiles, 16);
     const int Np = n_tiles * BN;
-    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, Np, false, false, &pk);
+    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, Np, mode == WHCN, false, &pk);
     int8_t* dw8 = nullptr; int32_t* dbias = nullptr; float* dscale = nullptr;
     b2vx_status st = upload(g, pk.w8, &dw8);
     if (st == B2VX_OK) st = upload(g, pk.bias_full, &dbias);
@@ -548,10 +565,19 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     // finalizer that Compile runs at its end.
     const int zx = x.zp();
     const std::string lbl = label;
-    const void* xcl = x.d_cl;
     void* ycl = y.d_cl;
     const int ldd = y.Cp, Oc = y.C, y_signed = y.d.dtype == B2VX_DT_INT8;
-    if (need_im2col) {
+    if (mode == WHCN) {
+      const void* xio = x.d_io;
+      Step s_col;
+      s_col.info = make_info("im2col_whcn", node_index, 0, x.elems() + static_cast<uint64_t>(M) * Kp);
+      s_col.fn = [=](cudaStream_t st2) {
+        launch_im2col_whcn(xio, Kp, zx, geo, g->scratch, st2);
+        return cudaGetLastError();
+      };
+      g->steps.push_back(std::move(s_col));
+    } else if (mode == IM2COL) {
+      const void* xcl = cl_in(x);
       Step s_col;
       s_col.info = make_info("im2col", node_index, 0, x.elems() + static_cast<uint64_t>(M) * Kp);
       s_col.fn = [=](cudaStream_t st2) {
@@ -561,17 +587,24 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       g->steps.push_back(std::move(s_col));
     }
     auto plan_holder = std::make_shared<GemmTcPlan*>(nullptr);
+    const bool implicit = mode == IMPLICIT;
     g->finalizers.push_back([=]() -> b2vx_status {
       char err[160] = {0};
-      const void* Aptr = need_im2col ? g->scratch : A;
-      GemmTcPlan* pl = gemm_tc_plan_create(Aptr, x_signed, dw8, M, Np, Kp, Oc, ycl, ldd, y_signed, ep, g->d_status, err, sizeof(err));
+      GemmTcPlan* pl;
+      if (implicit) {
+        pl = gemm_tc_conv_plan_create(A, x_signed, dw8, geo, Np, ycl, ep, g->d_status, err, sizeof(err));
+      } else {
+        const void* Aptr = need_im2col ? g->scratch : A;
+        pl = gemm_tc_plan_create(Aptr, x_signed, dw8, M, Np, Kp, Oc, ycl, ldd, y_signed, ep, g->d_status, err, sizeof(err));
+      }
       if (!pl) return fail(g, B2VX_UNSUPPORTED, lbl + ": " + err);
       g->gemm_plans.push_back(pl);
       *plan_holder = pl;
       return B2VX_OK;
     });
     Step s_gemm;
-    s_gemm.info = make_info(need_im2col ? "gemm_i8_tc(im2col)" : "gemm_i8_tc", node_index, 2 * macs, abytes);
+    s_gemm.info = make_info(implicit ? "gemm_i8_tc(implicit)" : (need_im2col ? "gemm_i8_tc(im2col)" : "gemm_i8_tc"), node_index,
+                            2 * macs, abytes);
     s_gemm.fn = [=](cudaStream_t st2) -> cudaError_t { return gemm_tc_launch(*plan_holder, st2); };
     g->steps.push_back(std::move(s_gemm));
     return B2VX_OK;
@@ -579,7 +612,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
 
   // CUDA-core path: K = tap*Cp + c, out-of-bounds taps are skipped and corrected per tap.
   const int Kp = taps * x.Cp;
-  pack_contraction(x, w, bias, kw, kh, x.C, x.Cp, Kp, y.C, y.Cp, y.Cp, true, true, &pk);
+  pack_contraction(x, w, bias, kw, kh, x.C, x.Cp, Kp, y.C, y.Cp, y.Cp, false, true, &pk);
   int8_t* dw8 = nullptr; int32_t *dbias = nullptr, *ddz = nullptr, *dtapc = nullptr; float* dscale = nullptr;
   b2vx_status st = upload(g, pk.w8, &dw8);
   if (st == B2VX_OK) st = upload(g, pk.bias_full, &dbias);
@@ -591,7 +624,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
   ep.acc_scale = dscale;
   ep.dz = ddz;
   ep.tapc = dtapc;
-  const void* xcl = x.d_cl;
+  const void* xcl = cl_in(x);
   void* ycl = y.d_cl;
   Step s;
   s.info = make_info("conv_simt", node_index, 2 * macs, abytes);
@@ -635,7 +668,7 @@ b2vx_status plan_conv(b2vx_graph* g, uint32_t idx, NodeRec& n) {
       st = upload(g, bv, &db);
       if (st != B2VX_OK) return st;
     }
-    const float* xp = static_cast<const float*>(x.d_cl);
+    const float* xp = static_cast<const float*>(cl_in(x));
     float* yp = static_cast<float*>(y.d_cl);
     const int mult = c.multiplier;
     Step s;
@@ -670,7 +703,7 @@ b2vx_status plan_conv(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   if (st == B2VX_OK) st = upload(g, bv, &db);
   if (st == B2VX_OK) st = upload(g, sc, &dsc);
   if (st != B2VX_OK) return st;
-  const void* xcl = x.d_cl;
+  const void* xcl = cl_in(x);
   void* ycl = y.d_cl;
   const int xs = x.d.dtype == B2VX_DT_INT8, zx = x.zp(), mult = c.multiplier;
   const OutQuant oq = out_quant(y);
@@ -718,12 +751,12 @@ b2vx_status plan_pool(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   const int type = c.type;
   Step s;
   if (x.d.dtype == B2VX_DT_FLOAT32) {
-    const float* xp = static_cast<const float*>(x.d_cl);
+    const float* xp = static_cast<const float*>(cl_in(x));
     float* yp = static_cast<float*>(y.d_cl);
     s.info = make_info("pool_f32", idx, 0, abytes);
     s.fn = [=](cudaStream_t st2) { launch_pool_f32(xp, type, geo, yp, st2); return cudaGetLastError(); };
   } else if (is_q8(x.d.dtype)) {
-    const void* xp = x.d_cl;
+    const void* xp = cl_in(x);
     void* yp = y.d_cl;
     const int sg = x.d.dtype == B2VX_DT_INT8, zx = x.zp(), same = x.scale() == y.scale() && x.zp() == y.zp();
     const float sx = x.scale();
@@ -744,13 +777,13 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   const uint64_t abytes = a.bytes() + b.bytes() + y.bytes();
   Step s;
   if (a.d.dtype == B2VX_DT_FLOAT32 && b.d.dtype == B2VX_DT_FLOAT32 && y.d.dtype == B2VX_DT_FLOAT32) {
-    const float *ap = static_cast<const float*>(a.d_cl), *bp = static_cast<const float*>(b.d_cl);
+    const float *ap = static_cast<const float*>(cl_in(a)), *bp = static_cast<const float*>(cl_in(b));
     float* yp = static_cast<float*>(y.d_cl);
     const size_t nel = y.cl_bytes / 4;
     s.info = make_info("add_f32", idx, 0, abytes);
     s.fn = [=](cudaStream_t st2) { launch_add_f32(ap, bp, yp, nel, st2); return cudaGetLastError(); };
   } else if (is_q8(a.d.dtype) && is_q8(b.d.dtype) && is_q8(y.d.dtype)) {
-    const void *ap = a.d_cl, *bp = b.d_cl;
+    const void *ap = cl_in(a), *bp = cl_in(b);
     void* yp = y.d_cl;
     const int as = a.d.dtype == B2VX_DT_INT8, bs = b.d.dtype == B2VX_DT_INT8, ys = y.d.dtype == B2VX_DT_INT8;
     const float sa = a.scale(), sb = b.scale();
@@ -773,13 +806,13 @@ b2vx_status plan_relu(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   const uint64_t abytes = x.bytes() + y.bytes();
   Step s;
   if (x.d.dtype == B2VX_DT_FLOAT32 && y.d.dtype == B2VX_DT_FLOAT32) {
-    const float* xp = static_cast<const float*>(x.d_cl);
+    const float* xp = static_cast<const float*>(cl_in(x));
     float* yp = static_cast<float*>(y.d_cl);
     const size_t nel = y.cl_bytes / 4;
     s.info = make_info("relu_f32", idx, 0, abytes);
     s.fn = [=](cudaStream_t st2) { launch_relu_f32(xp, upper, yp, nel, st2); return cudaGetLastError(); };
   } else if (is_q8(x.d.dtype) && is_q8(y.d.dtype)) {
-    const void* xp = x.d_cl;
+    const void* xp = cl_in(x);
     void* yp = y.d_cl;
     uint8_t* dlut = nullptr;
     b2vx_status st = upload(g, relu_table(x, y, upper), &dlut);
@@ -821,7 +854,7 @@ b2vx_status plan_softmax(b2vx_graph* g, uint32_t idx, NodeRec& n) {
     sg.ys[k] = yst[i];
     ++k;
   }
-  const void* xp = x.d_cl;
+  const void* xp = cl_in(x);
   void* yp = y.d_cl;
   const float sx = x.scale(), beta = n.p.softmax.beta;
   const int zx = x.zp();
@@ -1132,20 +1165,9 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
     }
   }
 
-  // 3. plan: inputs -> channels-last, nodes, outputs -> WHCN
+  // 3. plan: nodes first (they record which inputs they read in channels-last form), then the
+  //    input conversions are put in front and the output conversions behind
   g->steps.clear();
-  for (size_t i = 0; i < g->tensors.size(); ++i) {
-    TensorRec& t = g->tensors[i];
-    if (!t.is_activation || !(t.d.attr & (B2VX_ATTR_INPUT | B2VX_ATTR_VARIABLE))) continue;
-    if (t.d_io == t.d_cl) continue;
-    const void* src = t.d_io;
-    void* dst = t.d_cl;
-    const int N = t.N, C = t.C, H = t.H, W = t.W, Cp = t.Cp, el = static_cast<int>(dtype_size(t.d.dtype));
-    Step s;
-    s.info = make_info("whcn_to_cl", B2VX_NO_TENSOR, 0, t.io_bytes + t.cl_bytes);
-    s.fn = [=](cudaStream_t st2) { launch_whcn_to_cl(src, dst, N, C, H, W, Cp, el, st2); return cudaGetLastError(); };
-    g->steps.push_back(std::move(s));
-  }
   for (uint32_t idx : g->order) {
     NodeRec& n = g->nodes[idx];
     if (n.removed) continue;
@@ -1161,6 +1183,22 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
       default: return fail(g, B2VX_UNSUPPORTED, "unknown node kind");
     }
     if (st != B2VX_OK) return st;
+  }
+  {
+    std::vector<Step> head;
+    for (size_t i = 0; i < g->tensors.size(); ++i) {
+      TensorRec& t = g->tensors[i];
+      if (!t.is_activation || !t.cl_used || !(t.d.attr & (B2VX_ATTR_INPUT | B2VX_ATTR_VARIABLE))) continue;
+      if (t.d_io == t.d_cl) continue;
+      const void* src = t.d_io;
+      void* dst = t.d_cl;
+      const int N = t.N, C = t.C, H = t.H, W = t.W, Cp = t.Cp, el = static_cast<int>(dtype_size(t.d.dtype));
+      Step s;
+      s.info = make_info("whcn_to_cl", B2VX_NO_TENSOR, 0, t.io_bytes + t.cl_bytes);
+      s.fn = [=](cudaStream_t st2) { launch_whcn_to_cl(src, dst, N, C, H, W, Cp, el, st2); return cudaGetLastError(); };
+      head.push_back(std::move(s));
+    }
+    g->steps.insert(g->steps.begin(), std::make_move_iterator(head.begin()), std::make_move_iterator(head.end()));
   }
   for (size_t i = 0; i < g->tensors.size(); ++i) {
     TensorRec& t = g->tensors[i];

@@ -61,6 +61,15 @@ struct GemmParams {
   ContractEpilogue ep;
   uint8_t* D;
   int* status;
+  // implicit-GEMM convolution (conv != 0): A is the channels-last input seen
+  // as a 4-D tensor (C, W, H, N); one M tile is TW x TH x TN output pixels and
+  // one k-block is (filter tap, channel block).
+  int conv;
+  int TW, TH, TN, tiles_w, tiles_h;
+  int Wo, Ho, Nimg;
+  int kw, sx, sy, dx, dy, pl, pt;
+  int cblocks, Cp;
+  uint32_t a_tx_bytes;     // bytes one A box delivers (rows in the box x BK)
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -107,6 +116,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
 }
 
@@ -232,9 +248,21 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           const uint32_t full = smem_u32(&hdr->full[s]);
           const uint32_t dst = tiles_addr + s * stage_bytes;
-          mbar_arrive_expect_tx(full, stage_bytes);
-          tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
-          tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
+          mbar_arrive_expect_tx(full, p.a_tx_bytes + b_bytes);
+          if (p.conv) {
+            // tile -> (tw, th, tn); k-block -> (tap, channel block).  Coordinates left of / above the
+            // image are negative and read as zero (the padding), as do channels beyond Cp.
+            const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
+            const int th = rest % p.tiles_h, tn = rest / p.tiles_h;
+            const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+            const int ky = tap / p.kw, kx = tap - ky * p.kw;
+            tma_load_4d(dst, &map_a, cb * p.BK, tw * p.TW * p.sx - p.pl + kx * p.dx, th * p.TH * p.sy - p.pt + ky * p.dy,
+                        tn * p.TN, full);
+            tma_load_2d(dst + a_bytes, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
+          } else {
+            tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
+            tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
+          }
         }
       }
     }
@@ -284,14 +312,27 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t a = j & 1, aph = (j >> 1) & 1;
       if (!mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4)) break;
       tc_fence_after();
-      const long long row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
+      // output row (pixel index into D) of this thread, or -1 when the tile row is outside the tensor
+      long long row;
+      if (p.conv) {
+        const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
+        const int th = rest % p.tiles_h, tn = rest / p.tiles_h;
+        const int i = row_in_tile % p.TW, r2 = row_in_tile / p.TW;
+        const int jh = r2 % p.TH, l = r2 / p.TH;
+        const int wo = tw * p.TW + i, ho = th * p.TH + jh, n = tn * p.TN + l;
+        row = (l < p.TN && wo < p.Wo && ho < p.Ho && n < p.Nimg)
+                  ? (static_cast<long long>(n) * p.Ho + ho) * p.Wo + wo : -1;
+      } else {
+        row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
+        if (row >= p.M) row = -1;
+      }
       const uint32_t taddr = tmem_base + a * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
       for (int c0 = col_group * 16; c0 < p.BN; c0 += 64) {
         int acc[16];
         tc_ld_32x16(taddr + c0, acc);
         tc_ld_wait();
         const int cbase = n_tile * p.BN + c0;
-        if (row < p.M && cbase + 16 <= p.Ocp) {
+        if (row >= 0 && cbase + 16 <= p.Ocp) {
           uint32_t w4[4];
 #pragma unroll
           for (int g4 = 0; g4 < 4; ++g4) {
@@ -357,6 +398,20 @@ bool encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t oute
   return r == CUDA_SUCCESS;
 }
 
+bool encode_4d(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint32_t box[4], const uint32_t estr[4],
+               CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t strides[3] = {dims[0], dims[0] * dims[1], dims[0] * dims[1] * dims[2]};   // bytes: uint8 elements
+  cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t e[4] = {estr[0], estr[1], estr[2], estr[3]};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), d, strides, b, e,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 struct GemmTcPlan {
@@ -375,6 +430,87 @@ int gemm_tc_available(void) {
   return prop.major == 10 && get_encode_fn() != nullptr;
 }
 
+namespace {
+
+// Everything of a plan that does not depend on how A is addressed: N tiling, K block / swizzle mode,
+// stage count, TMEM columns, instruction descriptor, the B tensor map and the launch geometry.
+// Kspan is the K extent one tap (or the whole GEMM) covers, used to pick BK.
+bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int ldd,
+                 const ContractEpilogue& e, void* D, int* status, const char** why) {
+  GemmParams& p = plan->params;
+  p.Ocp = ldd;
+  p.ldd = ldd;
+  p.n_tiles = (Np + 255) / 256;
+  p.BN = (((Np + p.n_tiles - 1) / p.n_tiles) + 15) & ~15;
+  if (p.n_tiles * p.BN != Np) { *why = "gemm_tc: weight rows must be packed to n_tiles*BN"; return false; }
+  // K block: the swizzle span (32/64/128 bytes) that wastes the least tail.
+  int best_bk = 32;
+  long long best_cost = -1;
+  for (int bk : {128, 64, 32}) {
+    const long long cost = static_cast<long long>((Kspan + bk - 1) / bk) * bk;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bk = bk; }
+  }
+  p.BK = best_bk;
+  p.layout_type = p.BK == 128 ? 2u : (p.BK == 64 ? 4u : 6u);
+  p.sbo = 8u * p.BK;
+  // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
+  // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
+  // aligned start of the ring.
+  const size_t stage_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
+  int stages = static_cast<int>((200 * 1024) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) { *why = "gemm_tc: tile does not fit shared memory"; return false; }
+  p.stages = stages;
+  // the epilogue reads 16 columns at a time; buffers start on 32-column boundaries
+  p.acc_stride = (p.BN + 31) & ~31;
+  int cols = 32;
+  while (cols < 2 * p.acc_stride) cols <<= 1;
+  p.tmem_cols = cols;
+  p.idesc = (2u << 4) | (static_cast<uint32_t>(a_signed ? 1 : 0) << 7) | (1u << 10) |
+            (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+  p.ep = e;
+  p.D = static_cast<uint8_t*>(D);
+  p.status = status;
+  const CUtensorMapSwizzle swz = p.BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                             : (p.BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  if (!encode_2d(&plan->map_b, B, static_cast<uint64_t>(Kp), static_cast<uint64_t>(Np), static_cast<uint64_t>(Kp),
+                 static_cast<uint32_t>(p.BK), static_cast<uint32_t>(p.BN), swz)) {
+    *why = "gemm_tc: cuTensorMapEncodeTiled failed for the weights";
+    return false;
+  }
+  size_t smem = static_cast<size_t>(stages) * stage_bytes + sizeof(SmemHeader) + 1024;
+  if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
+  plan->smem = smem;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      *why = "gemm_tc: cannot raise the dynamic shared memory limit";
+      return false;
+    }
+    attr_set = true;
+  }
+  return true;
+}
+
+void set_grid(GemmTcPlan* plan) {
+  GemmParams& p = plan->params;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // a multiple of n_tiles, so that every CTA works on one N tile only
+  const int tiles = p.m_tiles * p.n_tiles;
+  int grid = (sms / p.n_tiles) * p.n_tiles;
+  if (grid < p.n_tiles) grid = p.n_tiles;
+  if (grid > tiles) grid = tiles;
+  plan->grid = grid;
+}
+
+CUtensorMapSwizzle swizzle_of(int bk) {
+  return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+}  // namespace
+
 GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, int M, int Np, int Kp, int Oc, void* D,
                                 int ldd, int d_signed, const ContractEpilogue& e, int* status, char* err,
                                 size_t err_len) {
@@ -392,83 +528,82 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   GemmTcPlan* plan = new GemmTcPlan();
   GemmParams& p = plan->params;
   std::memset(&p, 0, sizeof(p));
-  p.M = M;
-  p.Ocp = ldd;
-  p.ldd = ldd;
-  // N tiling: as few tiles of at most 256 columns as cover Np, width a multiple of 16.
-  p.n_tiles = (Np + 255) / 256;
-  p.BN = (((Np + p.n_tiles - 1) / p.n_tiles) + 15) & ~15;
-  if (p.n_tiles * p.BN != Np) {
+  const char* why = "";
+  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, ldd, e, D, status, &why)) {
     delete plan;
-    return fail("gemm_tc: weight rows must be packed to n_tiles*BN");
+    return fail(why);
   }
-  // K block: the swizzle span (32/64/128 bytes) that wastes the least tail.
-  int best_bk = 32;
-  long long best_cost = -1;
-  for (int bk : {128, 64, 32}) {
-    long long cost = static_cast<long long>((Kp + bk - 1) / bk) * bk;
-    if (best_cost < 0 || cost < best_cost) {
-      best_cost = cost;
-      best_bk = bk;
-    }
-  }
-  p.BK = best_bk;
+  p.M = M;
   p.num_kb = (Kp + p.BK - 1) / p.BK;
   p.m_tiles = (M + kBlockM - 1) / kBlockM;
-  p.layout_type = p.BK == 128 ? 2u : (p.BK == 64 ? 4u : 6u);
-  p.sbo = 8u * p.BK;
-  const size_t stage_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
-  // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
-  // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
-  // aligned start of the ring.
-  int stages = static_cast<int>((200 * 1024) / stage_bytes);
-  if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) {
-    delete plan;
-    return fail("gemm_tc: tile does not fit shared memory");
-  }
-  p.stages = stages;
-  // the epilogue reads 16 columns at a time; buffers start on 32-column boundaries
-  p.acc_stride = (p.BN + 31) & ~31;
-  int cols = 32;
-  while (cols < 2 * p.acc_stride) cols <<= 1;
-  p.tmem_cols = cols;
-  p.idesc = (2u << 4) | (static_cast<uint32_t>(a_signed ? 1 : 0) << 7) | (1u << 10) |
-            (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
-  p.ep = e;
-  p.D = static_cast<uint8_t*>(D);
-  p.status = status;
-
-  const CUtensorMapSwizzle swz = p.BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                             : (p.BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  p.a_tx_bytes = static_cast<uint32_t>(kBlockM) * p.BK;
   if (!encode_2d(&plan->map_a, A, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M), static_cast<uint64_t>(Kp),
-                 static_cast<uint32_t>(p.BK), kBlockM, swz) ||
-      !encode_2d(&plan->map_b, B, static_cast<uint64_t>(Kp), static_cast<uint64_t>(Np), static_cast<uint64_t>(Kp),
-                 static_cast<uint32_t>(p.BK), static_cast<uint32_t>(p.BN), swz)) {
+                 static_cast<uint32_t>(p.BK), kBlockM, swizzle_of(p.BK))) {
     delete plan;
     return fail("gemm_tc: cuTensorMapEncodeTiled failed");
   }
+  set_grid(plan);
+  return plan;
+}
 
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // a multiple of n_tiles, so that every CTA works on one N tile only
-  const int tiles = p.m_tiles * p.n_tiles;
-  int grid = (sms / p.n_tiles) * p.n_tiles;
-  if (grid < p.n_tiles) grid = p.n_tiles;
-  if (grid > tiles) grid = tiles;
-  plan->grid = grid;
-  size_t smem = static_cast<size_t>(stages) * stage_bytes + sizeof(SmemHeader) + 1024;
-  if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
-  plan->smem = smem;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
-      delete plan;
-      return fail("gemm_tc: cannot raise the dynamic shared memory limit");
-    }
-    attr_set = true;
+GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* B, const ConvGeom& g, int Np, void* D,
+                                     const ContractEpilogue& e, int* status, char* err, size_t err_len) {
+  auto fail = [&](const char* msg) -> GemmTcPlan* {
+    if (err && err_len) std::snprintf(err, err_len, "%s", msg);
+    return nullptr;
+  };
+  if ((g.Cp & 15) || (g.Ocp & 15) || (Np & 15)) return fail("gemm_tc conv: channel counts must be padded to 16");
+  if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(D) & 15))
+    return fail("gemm_tc conv: operands must be 16-byte aligned");
+  if (e.dz != nullptr || e.tapc != nullptr || e.out_is_float) return fail("gemm_tc conv: epilogue form not supported");
+
+  GemmTcPlan* plan = new GemmTcPlan();
+  GemmParams& p = plan->params;
+  std::memset(&p, 0, sizeof(p));
+  const char* why = "";
+  const int Kp = g.kh * g.kw * g.Cp;
+  if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.Ocp, e, D, status, &why)) {
+    delete plan;
+    return fail(why);
   }
+  // M tile = TW x TH x TN output pixels, at most 128: the shape that leaves the fewest tile rows unused.
+  int bw = 1, bh = 1, bn = 1;
+  double best = -1.0;
+  for (int tw = 1; tw <= g.Wo && tw <= kBlockM; ++tw) {
+    for (int th = 1; th <= g.Ho && tw * th <= kBlockM; ++th) {
+      int tn = kBlockM / (tw * th);
+      if (tn > g.N) tn = g.N;
+      if (tn < 1) continue;
+      // the box extent along a strided axis is (T-1)*stride+1 elements and may not exceed 256
+      if ((tw - 1) * g.sx + 1 > 256 || (th - 1) * g.sy + 1 > 256) continue;
+      const long long tiles = static_cast<long long>((g.Wo + tw - 1) / tw) * ((g.Ho + th - 1) / th) * ((g.N + tn - 1) / tn);
+      const double eff = static_cast<double>(g.Wo) * g.Ho * g.N / (static_cast<double>(tiles) * kBlockM);
+      // prefer wider rows at equal efficiency: longer contiguous runs per TMA box
+      if (eff > best + 1e-9 || (eff > best - 1e-9 && tw > bw)) { best = eff; bw = tw; bh = th; bn = tn; }
+    }
+  }
+  p.conv = 1;
+  p.TW = bw; p.TH = bh; p.TN = bn;
+  p.tiles_w = (g.Wo + bw - 1) / bw;
+  p.tiles_h = (g.Ho + bh - 1) / bh;
+  const int tiles_n = (g.N + bn - 1) / bn;
+  p.m_tiles = p.tiles_w * p.tiles_h * tiles_n;
+  p.M = g.N * g.Ho * g.Wo;
+  p.Wo = g.Wo; p.Ho = g.Ho; p.Nimg = g.N;
+  p.kw = g.kw; p.sx = g.sx; p.sy = g.sy; p.dx = g.dx; p.dy = g.dy; p.pl = g.pl; p.pt = g.pt;
+  p.Cp = g.Cp;
+  p.cblocks = (g.Cp + p.BK - 1) / p.BK;
+  p.num_kb = g.kh * g.kw * p.cblocks;
+  p.a_tx_bytes = static_cast<uint32_t>(bw * bh * bn) * p.BK;
+  const uint64_t dims[4] = {static_cast<uint64_t>(g.Cp), static_cast<uint64_t>(g.W), static_cast<uint64_t>(g.H), static_cast<uint64_t>(g.N)};
+  const uint32_t box[4] = {static_cast<uint32_t>(p.BK), static_cast<uint32_t>((bw - 1) * g.sx + 1),
+                           static_cast<uint32_t>((bh - 1) * g.sy + 1), static_cast<uint32_t>(bn)};
+  const uint32_t estr[4] = {1, static_cast<uint32_t>(g.sx), static_cast<uint32_t>(g.sy), 1};
+  if (!encode_4d(&plan->map_a, X, dims, box, estr, swizzle_of(p.BK))) {
+    delete plan;
+    return fail("gemm_tc conv: cuTensorMapEncodeTiled failed for the input");
+  }
+  set_grid(plan);
   return plan;
 }
 

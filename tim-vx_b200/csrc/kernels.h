@@ -104,6 +104,10 @@ void launch_softmax(const void* x, int x_kind, float sx, int zx, void* y, int y_
 // (and the channel padding when Cs = Cp) with zero.
 void launch_im2col(const void* x, int Cs, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s);
 
+// The same matrix straight from a WHCN tensor [N][C][H][W] with few channels (network inputs):
+// K index = (c*kh + ky)*kw + kx, the kernel tensor's own element order.
+void launch_im2col_whcn(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s);
+
 // ---- int8 GEMM on tcgen05 tensor cores --------------------------------------
 // D[M][ldd] (u8/s8) = requant(A[M][Kp] (u8 or s8) * B[Np][Kp]^T (s8)), K-major
 // operands fed by TMA, int32 accumulation in tensor memory.  Returns a CUDA
@@ -113,6 +117,12 @@ struct GemmTcPlan;   // opaque: tensor maps + launch geometry, built once at com
 GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, int M, int Np, int Kp, int Oc,
                                 void* D, int ldd, int d_signed, const ContractEpilogue& e, int* status,
                                 char* err, size_t err_len);
+// Implicit-GEMM convolution on the same kernel: X is the channels-last input [N][H][W][Cp], B is
+// [Np][kh*kw*Cp] with K = tap*Cp + c, D the channels-last output.  Filter taps are fetched as
+// shifted 4-D TMA boxes; positions in the padding read as zero, so this form requires an input
+// zero point of 0 or no padding (no border correction in the epilogue).
+GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* B, const ConvGeom& g, int Np, void* D,
+                                     const ContractEpilogue& e, int* status, char* err, size_t err_len);
 void gemm_tc_plan_destroy(GemmTcPlan* p);
 cudaError_t gemm_tc_launch(const GemmTcPlan* p, cudaStream_t s);
 // 1 when this build and device can run the tensor-core path.

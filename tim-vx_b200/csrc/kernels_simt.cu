@@ -462,6 +462,51 @@ __global__ void im2col_kernel(const uint8_t* __restrict__ x, int Cs, int Kp, int
   *reinterpret_cast<uint4*>(col + static_cast<size_t>(p) * Kp + k0) = v;
 }
 
+// im2col from a WHCN input: one block per (image, output row).  The input rows the
+// block needs (C*kh of them, padding materialised with the zero point) are staged
+// in shared memory with coalesced loads; every thread then assembles 16-byte
+// pieces of im2col rows from a per-k offset table.
+__global__ void im2col_whcn_kernel(const uint8_t* __restrict__ x, int Kp, int zx, ConvGeom g, int rowlen,
+                                   uint8_t* __restrict__ col) {
+  extern __shared__ uint8_t sm[];
+  const int n = blockIdx.y, ho = blockIdx.x;
+  const int rows = g.C * g.kh;
+  const int K = rows * g.kw;
+  int* koff = reinterpret_cast<int*>(sm);                    // [Kp]
+  uint8_t* img = sm + static_cast<size_t>(Kp) * sizeof(int);   // [rows][rowlen]
+  for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
+    int off = -1;
+    if (k < K) {
+      const int r = k / g.kw, kx = k - r * g.kw;
+      off = r * rowlen + kx * g.dx;
+    }
+    koff[k] = off;
+  }
+  for (int idx = threadIdx.x; idx < rows * rowlen; idx += blockDim.x) {
+    const int r = idx / rowlen, j = idx - r * rowlen;
+    const int c = r / g.kh, ky = r - c * g.kh;
+    const int hi = ho * g.sy - g.pt + ky * g.dy, wi = j - g.pl;
+    uint8_t v = static_cast<uint8_t>(zx);
+    if (hi >= 0 && hi < g.H && wi >= 0 && wi < g.W) v = x[((static_cast<size_t>(n) * g.C + c) * g.H + hi) * g.W + wi];
+    img[idx] = v;
+  }
+  __syncthreads();
+  const int chunks = Kp >> 4;
+  uint8_t* out = col + (static_cast<size_t>(n) * g.Ho + ho) * g.Wo * Kp;
+  for (int q = threadIdx.x; q < g.Wo * chunks; q += blockDim.x) {
+    const int wo = q / chunks, ch = q - wo * chunks;
+    const int base = wo * g.sx;
+    uint32_t w4[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int off = koff[ch * 16 + j];
+      const uint32_t b = off >= 0 ? img[off + base] : 0u;
+      w4[j >> 2] |= b << ((j & 3) * 8);
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(wo) * Kp + ch * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+  }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------- wrappers
@@ -584,6 +629,15 @@ void launch_im2col(const void* x, int Cs, int Kp, int zx, const ConvGeom& g, voi
   if (total == 0) return;
   im2col_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(x), Cs, Kp, zx, g,
                                                              static_cast<uint8_t*>(col));
+}
+
+void launch_im2col_whcn(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s) {
+  if (g.N == 0 || g.Ho == 0 || g.Wo == 0) return;
+  // input columns a row of outputs touches, counted from -pad_left
+  const int rowlen = (g.Wo - 1) * g.sx + (g.kw - 1) * g.dx + 1;
+  const size_t smem = static_cast<size_t>(Kp) * sizeof(int) + static_cast<size_t>(g.C) * g.kh * rowlen;
+  dim3 grid(g.Ho, g.N);
+  im2col_whcn_kernel<<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(x), Kp, zx, g, rowlen, static_cast<uint8_t*>(col));
 }
 
 }  // namespace b2vx
