@@ -70,6 +70,7 @@ struct GemmParams {
   int kw, sx, sy, dx, dy, pl, pt;
   int cblocks, Cp;
   uint32_t a_tx_bytes;     // bytes one A box delivers (rows in the box x BK)
+  int group;               // k-blocks per pipeline stage
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -199,7 +200,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
   const uint32_t a_bytes = kBlockM * p.BK;
   const uint32_t b_bytes = static_cast<uint32_t>(p.BN) * p.BK;
-  const uint32_t stage_bytes = a_bytes + b_bytes;   // whole swizzle atoms, see the host-side plan
+  const uint32_t sub_bytes = a_bytes + b_bytes;     // one k-block: whole swizzle atoms, see the host-side plan
+  const uint32_t stage_bytes = sub_bytes * p.group;
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(tiles + static_cast<size_t>(p.stages) * stage_bytes);
   volatile int* abort_flag = &hdr->abort_flag;
 
@@ -238,30 +240,40 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // One stage = up to `group` consecutive k-blocks of one tile under a single barrier, so that the
+    // wait / expect_tx / commit round trip is paid once per stage, not once per (small) k-block.
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const int m_tile = tile / p.n_tiles;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        int w0 = 0, h0 = 0, n0 = 0;
+        if (p.conv) {
+          // tile -> first output pixel (tw, th, tn), turned into input coordinates of tap (0,0).
+          // Coordinates left of / above the image are negative and read as zero (the padding).
+          const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
+          w0 = tw * p.TW * p.sx - p.pl;
+          h0 = (rest % p.tiles_h) * p.TH * p.sy - p.pt;
+          n0 = (rest / p.tiles_h) * p.TN;
+        }
+        for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
           const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
           if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          const int cnt = min(p.group, p.num_kb - kb0);
           const uint32_t full = smem_u32(&hdr->full[s]);
-          const uint32_t dst = tiles_addr + s * stage_bytes;
-          mbar_arrive_expect_tx(full, p.a_tx_bytes + b_bytes);
-          if (p.conv) {
-            // tile -> (tw, th, tn); k-block -> (tap, channel block).  Coordinates left of / above the
-            // image are negative and read as zero (the padding), as do channels beyond Cp.
-            const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
-            const int th = rest % p.tiles_h, tn = rest / p.tiles_h;
-            const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
-            const int ky = tap / p.kw, kx = tap - ky * p.kw;
-            tma_load_4d(dst, &map_a, cb * p.BK, tw * p.TW * p.sx - p.pl + kx * p.dx, th * p.TH * p.sy - p.pt + ky * p.dy,
-                        tn * p.TN, full);
-            tma_load_2d(dst + a_bytes, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
-          } else {
-            tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
-            tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
+          uint32_t dst = tiles_addr + s * stage_bytes;
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (p.a_tx_bytes + b_bytes));
+          for (int gi = 0; gi < cnt; ++gi, dst += sub_bytes) {
+            const int kb = kb0 + gi;
+            if (p.conv) {
+              const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+              const int ky = tap / p.kw, kx = tap - ky * p.kw;
+              tma_load_4d(dst, &map_a, cb * p.BK, w0 + kx * p.dx, h0 + ky * p.dy, n0, full);
+              tma_load_2d(dst + a_bytes, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
+            } else {
+              tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
+              tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
+            }
           }
         }
       }
@@ -272,23 +284,27 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       int j = 0;
+      const int ksteps = p.BK >> 5;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
         const uint32_t a = j & 1, aph = (j >> 1) & 1;
         if (!mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + a * p.acc_stride;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        uint32_t accumulate = 0;
+        for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
           const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
           if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = tiles_addr + s * stage_bytes;
-          const uint64_t da = make_smem_desc(a_addr, p.sbo, p.layout_type);
-          const uint64_t db = make_smem_desc(a_addr + a_bytes, p.sbo, p.layout_type);
-          const int ksteps = p.BK >> 5;
-          for (int k = 0; k < ksteps; ++k) {
-            // advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
-            tc_mma_i8(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc,
-                      (kb | k) != 0 ? 1u : 0u);
+          const int cnt = min(p.group, p.num_kb - kb0);
+          uint32_t a_addr = tiles_addr + s * stage_bytes;
+          for (int gi = 0; gi < cnt; ++gi, a_addr += sub_bytes) {
+            const uint64_t da = make_smem_desc(a_addr, p.sbo, p.layout_type);
+            const uint64_t db = make_smem_desc(a_addr + a_bytes, p.sbo, p.layout_type);
+            for (int k = 0; k < ksteps; ++k) {
+              // advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
+              tc_mma_i8(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc, accumulate);
+              accumulate = 1;
+            }
           }
           tc_commit(smem_u32(&hdr->empty[s]));
         }
@@ -302,7 +318,15 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int col_group = ew >> 2;                // this warp takes 16-column chunks col_group, col_group+4, ...
     const int row_in_tile = quarter * 32 + lane;
     const OutQuant oq = p.ep.out;
-    const float inv_scale = __frcp_rn(oq.scale);
+    // Requantization, fast form (see requant.cuh for the exact sequence it must reproduce).
+    // The reference computes q = R(real / scale) with R = round-half-even except within an ulp of
+    // a .5 fraction.  r_hi and r_lo round real*(1/scale)*(1 +- 2^-20) to the nearest integer in one
+    // fused multiply-add each (adding 1.5*2^23 leaves the integer in the low mantissa bits; beyond
+    // 2^22 the bit pattern is still monotone, so saturation below stays right).  The reference's
+    // quotient lies between the two products; when both round to the same integer, that integer is
+    // the reference's result.  Chunks where any element disagrees are redone with the exact code.
+    const float inv = __frcp_rn(oq.scale);
+    const float inv_hi = __fmul_rn(inv, 1.00000095367431640625f), inv_lo = __fmul_rn(inv, 0.99999904632568359375f);
     const int span = oq.hi - oq.lo;
     const int addc = oq.zp - oq.lo - 0x4B400000;
     const uint32_t sign_fix = oq.lo < 0 ? 0x80808080u : 0u;   // u + lo as a byte == u ^ 0x80 when lo == -128
@@ -332,21 +356,36 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         tc_ld_32x16(taddr + c0, acc);
         tc_ld_wait();
         const int cbase = n_tile * p.BN + c0;
-        if (row >= 0 && cbase + 16 <= p.Ocp) {
-          uint32_t w4[4];
+        if (row < 0 || cbase + 16 > p.Ocp) continue;
+        float real[16];
+        int u[16];
+        int disagree = 0;
 #pragma unroll
-          for (int g4 = 0; g4 < 4; ++g4) {
-            const int4 b4 = *reinterpret_cast<const int4*>(&hdr->bias[c0 + g4 * 4]);
-            const float4 s4 = *reinterpret_cast<const float4*>(&hdr->scale[c0 + g4 * 4]);
-            const int u0 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 0] + b4.x), s4.x), oq, inv_scale, addc, span);
-            const int u1 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 1] + b4.y), s4.y), oq, inv_scale, addc, span);
-            const int u2 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 2] + b4.z), s4.z), oq, inv_scale, addc, span);
-            const int u3 = requant_fast(__fmul_rn(__int2float_rn(acc[g4 * 4 + 3] + b4.w), s4.w), oq, inv_scale, addc, span);
-            w4[g4] = (static_cast<uint32_t>(u0) | (static_cast<uint32_t>(u1) << 8) | (static_cast<uint32_t>(u2) << 16) |
-                      (static_cast<uint32_t>(u3) << 24)) ^ sign_fix;
-          }
-          *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        for (int g4 = 0; g4 < 4; ++g4) {
+          const int4 b4 = *reinterpret_cast<const int4*>(&hdr->bias[c0 + g4 * 4]);
+          const float4 s4 = *reinterpret_cast<const float4*>(&hdr->scale[c0 + g4 * 4]);
+          real[g4 * 4 + 0] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 0] + b4.x), s4.x);
+          real[g4 * 4 + 1] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 1] + b4.y), s4.y);
+          real[g4 * 4 + 2] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 2] + b4.z), s4.z);
+          real[g4 * 4 + 3] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 3] + b4.w), s4.w);
         }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int r_hi = __float_as_int(__fmaf_rn(real[i], inv_hi, 12582912.0f));
+          const int r_lo = __float_as_int(__fmaf_rn(real[i], inv_lo, 12582912.0f));
+          disagree |= r_hi ^ r_lo;
+          u[i] = __vimin_s32_relu(r_hi + addc, span);
+        }
+        if (disagree) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) u[i] = requant(real[i], oq) - oq.lo;
+        }
+        uint32_t w4[4];
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4)
+          w4[g4] = (static_cast<uint32_t>(u[g4 * 4]) | (static_cast<uint32_t>(u[g4 * 4 + 1]) << 8) |
+                    (static_cast<uint32_t>(u[g4 * 4 + 2]) << 16) | (static_cast<uint32_t>(u[g4 * 4 + 3]) << 24)) ^ sign_fix;
+        *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
       }
       tc_fence_before();
       __syncwarp();
@@ -435,7 +474,7 @@ namespace {
 // Everything of a plan that does not depend on how A is addressed: N tiling, K block / swizzle mode,
 // stage count, TMEM columns, instruction descriptor, the B tensor map and the launch geometry.
 // Kspan is the K extent one tap (or the whole GEMM) covers, used to pick BK.
-bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int ldd,
+bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int taps, int ldd,
                  const ContractEpilogue& e, void* D, int* status, const char** why) {
   GemmParams& p = plan->params;
   p.Ocp = ldd;
@@ -451,12 +490,20 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bk = bk; }
   }
   p.BK = best_bk;
+  const int Kblocks_per_tile = taps * ((Kspan + p.BK - 1) / p.BK);
   p.layout_type = p.BK == 128 ? 2u : (p.BK == 64 ? 4u : 6u);
   p.sbo = 8u * p.BK;
   // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
   // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
   // aligned start of the ring.
-  const size_t stage_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
+  // Several k-blocks share a stage (one barrier round trip) when they are small: up to 64 KiB per stage.
+  const size_t sub_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
+  int group = static_cast<int>((64 * 1024) / sub_bytes);
+  const int total_kb = Kblocks_per_tile > 0 ? Kblocks_per_tile : 1;
+  if (group > total_kb) group = total_kb;
+  if (group < 1) group = 1;
+  p.group = group;
+  const size_t stage_bytes = sub_bytes * group;
   int stages = static_cast<int>((200 * 1024) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) { *why = "gemm_tc: tile does not fit shared memory"; return false; }
@@ -529,7 +576,7 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   GemmParams& p = plan->params;
   std::memset(&p, 0, sizeof(p));
   const char* why = "";
-  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, ldd, e, D, status, &why)) {
+  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why)) {
     delete plan;
     return fail(why);
   }
@@ -562,7 +609,7 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   std::memset(&p, 0, sizeof(p));
   const char* why = "";
   const int Kp = g.kh * g.kw * g.Cp;
-  if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.Ocp, e, D, status, &why)) {
+  if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.kh * g.kw, g.Ocp, e, D, status, &why)) {
     delete plan;
     return fail(why);
   }
