@@ -1,35 +1,45 @@
-// int8 GEMM with fused requantization on Blackwell tensor cores (sm_100a).
+// int8 GEMM / implicit-GEMM convolution with fused requantization on Blackwell
+// tensor cores (sm_100a).
 //
-//   D[m][oc] = requant( sum_k A[m][k] * B[oc][k]  + epilogue terms )
+//   D[m][oc] = requant( sum_k A[m][k] * B[oc][k] + bias_full[oc] )
 //
-// A: activations, u8 or s8, [M][Kp] K-contiguous (a channels-last tensor viewed
-//    as pixels x channels, or an im2col matrix);  B: weights shifted into int8,
-//    [Np][Kp] K-contiguous.  Both are "K-major" operands, which is what TMA
-//    tiled loads with a 32/64/128-byte swizzle and tcgen05.mma.kind::i8 consume
-//    directly; accumulation is int32 in tensor memory.
+// A: activations, u8 or s8, K-contiguous: either a matrix [M][Kp] (a
+//    channels-last tensor seen as pixels x channels, or an im2col matrix), or —
+//    convolution mode — the channels-last input itself as a 4-D tensor
+//    (C, W, H, N), one filter tap per k-block fetched as a shifted TMA box.
+// B: weights shifted into int8, [Np][Kp] K-contiguous.
+// Both are "K-major" operands, which is what TMA tiled loads with a 32/64/128
+// byte swizzle and tcgen05.mma.kind::i8 consume directly; accumulation is int32
+// in tensor memory (TMEM).
 //
-// One persistent CTA per SM, 576 threads, warp-specialised:
-//   warp 0      TMA producer: per k-block one A box (128 rows x BK bytes) and
-//               one B box (BN rows x BK bytes) into a ring of smem stages;
-//   warp 1      allocates tensor memory, then one lane issues the MMAs
-//               (M=128, N=BN, K=32 per instruction) and commits them to
-//               mbarriers: stage-free after each k-block, accumulator-ready
-//               after the last one;
-//   warps 2-17  epilogue, 16 warps so that each SM scheduler has four of them
-//               to hide latency: a warp owns the 32 TMEM lanes (rows) its warp
-//               id maps to and every fourth 16-column chunk; it tcgen05.ld's
-//               the chunk, adds the folded bias, requantizes (requant_fast:
-//               same integers as the reference's float sequence), packs 16
-//               bytes and stores them.  Two accumulator buffers let the MMAs
-//               of tile i+1 overlap the epilogue of tile i.
-// The grid is a multiple of the number of N tiles, so a CTA keeps one N tile
-// for its whole life (bias and scales are staged in shared memory once) and
-// neighbouring CTAs share an A row-block, whose second and later reads hit L2.
+// One persistent CTA per SM, 640 threads, warp-specialised:
+//   warp 0      A producer   per stage: wait slot free, expect_tx, one TMA box
+//   warp 2      B producer   per k-block (lanes issue the boxes of a stage in
+//                            one instruction).  Two warps because a single
+//                            thread's wait/expect/issue sequence, not memory,
+//                            bounded the load rate.
+//   warp 1      MMA issuer   allocates TMEM; one lane issues M=128,N=BN,K=32
+//                            MMAs and commits them to mbarriers: slot-free
+//                            after each stage, accumulator-ready after a tile.
+//   warps 4-19  epilogue     16 warps (four per SM scheduler, to hide latency).
+//                            A warp owns the 32 TMEM lanes (tile rows) its id
+//                            maps to and every fourth 16-column chunk:
+//                            tcgen05.ld, folded bias, requantize, pack 16
+//                            bytes, write them swizzled into a staging tile in
+//                            shared memory; one thread then stores the tile
+//                            with TMA (clipped at the tensor edge).  Two
+//                            accumulator buffers and two staging tiles overlap
+//                            tile i's epilogue with tile i+1's MMAs.
+// A stage holds up to `group` k-blocks so that small k-blocks share one
+// barrier round trip.  The grid is a multiple of the number of N tiles: a CTA
+// keeps one N tile for life (bias and scales staged in shared memory once) and
+// neighbouring CTAs share an A row-block, whose repeated reads hit L2.
 //
 // Every mbarrier wait is bounded: after kWaitLimitCycles the waiting thread
 // records a code in *status, raises a CTA-wide abort flag that all other waits
-// poll, and the CTA falls through to its common exit where tensor memory is
-// released.  No cluster launch, no multicast.
+// poll, and the CTA falls through to its common exit where outstanding TMA
+// stores are drained and tensor memory is released.  No cluster launch, no
+// multicast.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -39,38 +49,57 @@
 #include "kernels.h"
 #include "requant.cuh"
 
+// Build with -DB2VX_TC_TRACE to record, for CTA 0, when each role passed its waits (a debugging aid
+// for pipeline stalls; the normal build contains none of it).
+#ifdef B2VX_TC_TRACE
+#define TC_TRACE(role, idx, slot) \
+  do { if (p.trace && blockIdx.x == 0 && (idx) < 64) p.trace[((role) * 64 + (idx)) * 2 + (slot)] = clock64(); } while (0)
+#else
+#define TC_TRACE(role, idx, slot) do { } while (0)
+#endif
+
 namespace b2vx {
 
 namespace {
 
 constexpr int kBlockM = 128;
+constexpr int kFirstEpilogueWarp = 4;
 constexpr int kEpilogueWarps = 16;
-constexpr int kThreadsTc = (2 + kEpilogueWarps) * 32;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kThreadsTc = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
 constexpr int kMaxStages = 8;
+constexpr int kMaxGroup = 8;
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+constexpr int kSmemBudget = 226 * 1024;               // dynamic shared memory requested at most
 constexpr int kMinDynSmem = 120 * 1024;               // keeps two CTAs from sharing an SM (and its TMEM)
 
 struct GemmParams {
   int M, Ocp, ldd;
   int BN, BK, n_tiles, m_tiles, num_kb, stages;
+  int group;               // k-blocks per pipeline stage
   int tmem_cols;
   int acc_stride;          // TMEM columns between the two accumulator buffers (BN rounded up to 32)
   uint32_t idesc;
-  uint32_t layout_type;   // UMMA smem descriptor swizzle code
-  uint32_t sbo;           // bytes between 8-row groups
+  uint32_t layout_type;    // UMMA smem descriptor swizzle code
+  uint32_t sbo;            // bytes between 8-row groups
   ContractEpilogue ep;
   uint8_t* D;
   int* status;
-  // implicit-GEMM convolution (conv != 0): A is the channels-last input seen
-  // as a 4-D tensor (C, W, H, N); one M tile is TW x TH x TN output pixels and
-  // one k-block is (filter tap, channel block).
+  // implicit-GEMM convolution (conv != 0): one M tile is TW x TH x TN output pixels and one k-block is
+  // (filter tap, channel block).
   int conv;
   int TW, TH, TN, tiles_w, tiles_h;
   int Wo, Ho, Nimg;
   int kw, sx, sy, dx, dy, pl, pt;
   int cblocks, Cp;
   uint32_t a_tx_bytes;     // bytes one A box delivers (rows in the box x BK)
-  int group;               // k-blocks per pipeline stage
+  // output through shared memory + TMA store: the tile is staged as BN/store_span column blocks of
+  // [128 rows][store_span bytes], 16-byte chunks XOR-swizzled the way the store's tensor map expects.
+  // store_span == 0: BN is not a multiple of 32, threads store their 16-byte pieces directly.
+  int store_span;
+#ifdef B2VX_TC_TRACE
+  long long* trace;        // clock64 stamps of CTA 0, [3 roles][64 iterations][2]
+#endif
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -119,13 +148,33 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
 }
-
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's store groups still have to read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Makes this thread's shared-memory writes visible to the TMA engine (async proxy).
+__device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Barrier among the epilogue warps only.
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -143,18 +192,6 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
-__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, int (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, int (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -192,9 +229,10 @@ struct SmemHeader {
 };
 
 __global__ void __launch_bounds__(kThreadsTc, 1)
-gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  // tiles first (1024-byte aligned for the 128-byte swizzle), header after them
+  // [ring of stages | two staging tiles | header], the first two 1024-byte aligned (128-byte swizzle)
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
@@ -202,7 +240,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t b_bytes = static_cast<uint32_t>(p.BN) * p.BK;
   const uint32_t sub_bytes = a_bytes + b_bytes;     // one k-block: whole swizzle atoms, see the host-side plan
   const uint32_t stage_bytes = sub_bytes * p.group;
-  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(tiles + static_cast<size_t>(p.stages) * stage_bytes);
+  const uint32_t ring_bytes = (p.stages * stage_bytes + 1023u) & ~1023u;
+  const uint32_t staging_bytes = p.store_span ? static_cast<uint32_t>(kBlockM) * p.BN : 0u;   // per buffer, multiple of 4096
+  uint8_t* staging = tiles + ring_bytes;
+  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(staging + 2 * staging_bytes);
   volatile int* abort_flag = &hdr->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -211,7 +252,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&hdr->full[s]), 1);
+      mbar_init(smem_u32(&hdr->full[s]), 2);     // A producer + B producer
       mbar_init(smem_u32(&hdr->empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -238,44 +279,53 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = hdr->tmem_base;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    // One stage = up to `group` consecutive k-blocks of one tile under a single barrier, so that the
-    // wait / expect_tx / commit round trip is paid once per stage, not once per (small) k-block.
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m_tile = tile / p.n_tiles;
-        int w0 = 0, h0 = 0, n0 = 0;
-        if (p.conv) {
-          // tile -> first output pixel (tw, th, tn), turned into input coordinates of tap (0,0).
-          // Coordinates left of / above the image are negative and read as zero (the padding).
-          const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
-          w0 = tw * p.TW * p.sx - p.pl;
-          h0 = (rest % p.tiles_h) * p.TH * p.sy - p.pt;
-          n0 = (rest / p.tiles_h) * p.TN;
+  if (warp == 0 || warp == 2) {
+    // ------------------------------------------------------------ TMA producers (warp 0: A, warp 2: B)
+    // Lane 0 waits for the slot and announces the bytes; lanes 0..cnt-1 then issue the boxes of the
+    // stage's k-blocks in one instruction.
+    const bool is_a = warp == 0;
+    uint32_t it = 0;
+    int ok = 1;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      const int m_tile = tile / p.n_tiles;
+      int w0 = 0, h0 = 0, n0 = 0;
+      if (p.conv) {
+        // tile -> first output pixel (tw, th, tn), turned into input coordinates of tap (0,0).
+        // Coordinates left of / above the image are negative and read as zero (the padding).
+        const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
+        w0 = tw * p.TW * p.sx - p.pl;
+        h0 = (rest % p.tiles_h) * p.TH * p.sy - p.pt;
+        n0 = (rest / p.tiles_h) * p.TN;
+      }
+      for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
+        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
+        const int cnt = min(p.group, p.num_kb - kb0);
+        const uint32_t full = smem_u32(&hdr->full[s]);
+        if (lane == 0) {
+          ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, is_a ? 1 : 5) ? 1 : 0;
+          if (is_a) TC_TRACE(0, it, 0);
+          if (ok) mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (is_a ? p.a_tx_bytes : b_bytes));
         }
-        for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
-          const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
-          if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-          const int cnt = min(p.group, p.num_kb - kb0);
-          const uint32_t full = smem_u32(&hdr->full[s]);
-          uint32_t dst = tiles_addr + s * stage_bytes;
-          mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (p.a_tx_bytes + b_bytes));
-          for (int gi = 0; gi < cnt; ++gi, dst += sub_bytes) {
-            const int kb = kb0 + gi;
-            if (p.conv) {
-              const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (lane < cnt) {
+          const int kb = kb0 + lane;
+          const uint32_t dst = tiles_addr + s * stage_bytes + lane * sub_bytes;
+          if (p.conv) {
+            const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+            if (is_a) {
               const int ky = tap / p.kw, kx = tap - ky * p.kw;
               tma_load_4d(dst, &map_a, cb * p.BK, w0 + kx * p.dx, h0 + ky * p.dy, n0, full);
-              tma_load_2d(dst + a_bytes, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
             } else {
-              tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
-              tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
+              tma_load_2d(dst + a_bytes, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
             }
+          } else if (is_a) {
+            tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
+          } else {
+            tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
           }
         }
+        if (is_a && lane == 0) TC_TRACE(0, it, 1);
       }
     }
   } else if (warp == 1) {
@@ -294,6 +344,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
           const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
           if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3)) { ok = false; break; }
+          TC_TRACE(1, it, 0);
           tc_fence_after();
           const int cnt = min(p.group, p.num_kb - kb0);
           uint32_t a_addr = tiles_addr + s * stage_bytes;
@@ -307,46 +358,69 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
           }
           tc_commit(smem_u32(&hdr->empty[s]));
+          TC_TRACE(1, it, 1);
         }
         if (ok) tc_commit(smem_u32(&hdr->tmem_full[a]));
       }
     }
-  } else {
+  } else if (warp >= kFirstEpilogueWarp) {
     // ------------------------------------------------------------ epilogue
-    const int ew = warp - 2;                      // 0..15
+    const int ew = warp - kFirstEpilogueWarp;     // 0..15
     const int quarter = warp & 3;                 // TMEM lanes [32*quarter, +32) belong to this warp
     const int col_group = ew >> 2;                // this warp takes 16-column chunks col_group, col_group+4, ...
     const int row_in_tile = quarter * 32 + lane;
+    const bool store_issuer = threadIdx.x == kFirstEpilogueWarp * 32;
     const OutQuant oq = p.ep.out;
     // Requantization, fast form (see requant.cuh for the exact sequence it must reproduce).
     // The reference computes q = R(real / scale) with R = round-half-even except within an ulp of
-    // a .5 fraction.  r_hi and r_lo round real*(1/scale)*(1 +- 2^-20) to the nearest integer in one
+    // a .5 fraction.  r_hi and r_lo round real*(1/scale)*(1 +- 2^-22) to the nearest integer in one
     // fused multiply-add each (adding 1.5*2^23 leaves the integer in the low mantissa bits; beyond
     // 2^22 the bit pattern is still monotone, so saturation below stays right).  The reference's
-    // quotient lies between the two products; when both round to the same integer, that integer is
-    // the reference's result.  Chunks where any element disagrees are redone with the exact code.
+    // quotient real/scale (one rounding, of a divisor within half an ulp of 1/scale) lies between the
+    // two products; when both round to the same integer, that integer is the reference's result.  Chunks where any element disagrees are redone with the exact code.
     const float inv = __frcp_rn(oq.scale);
-    const float inv_hi = __fmul_rn(inv, 1.00000095367431640625f), inv_lo = __fmul_rn(inv, 0.99999904632568359375f);
+    const float inv_hi = __fmul_rn(inv, 1.0000002384185791015625f), inv_lo = __fmul_rn(inv, 0.9999997615814208984375f);
     const int span = oq.hi - oq.lo;
     const int addc = oq.zp - oq.lo - 0x4B400000;
     const uint32_t sign_fix = oq.lo < 0 ? 0x80808080u : 0u;   // u + lo as a byte == u ^ 0x80 when lo == -128
+    // position of this thread's 16-byte chunks inside a staging column block
+    const int span_b = p.store_span;
+    const int swz = span_b == 128 ? (row_in_tile & 7) : span_b == 64 ? ((row_in_tile >> 1) & 3) : ((row_in_tile >> 2) & 1);
     int j = 0;
+    // Once a wait has given up (alive == false) a thread does no more work, but it keeps running the
+    // loop and both barriers of every tile, so the other epilogue threads never wait for it.
+    bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
       const int m_tile = tile / p.n_tiles;
       const uint32_t a = j & 1, aph = (j >> 1) & 1;
-      if (!mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4)) break;
+      uint8_t* stage_out = staging + a * staging_bytes;
+      if (span_b) {
+        // the staging tile written two tiles ago must have been read by its TMA store
+        if (store_issuer) tma_store_wait_read<1>();
+        epilogue_barrier();
+      }
+      if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
+      alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
+      if (!alive) {
+        if (span_b) epilogue_barrier();
+        continue;
+      }
+      if (warp == kFirstEpilogueWarp && lane == 0) TC_TRACE(2, j, 0);
       tc_fence_after();
-      // output row (pixel index into D) of this thread, or -1 when the tile row is outside the tensor
-      long long row;
+      int tw = 0, th = 0, tn = 0;
+      long long row = -1;   // direct-store path: output row (pixel index into D), -1 outside the tensor
       if (p.conv) {
-        const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
-        const int th = rest % p.tiles_h, tn = rest / p.tiles_h;
-        const int i = row_in_tile % p.TW, r2 = row_in_tile / p.TW;
-        const int jh = r2 % p.TH, l = r2 / p.TH;
-        const int wo = tw * p.TW + i, ho = th * p.TH + jh, n = tn * p.TN + l;
-        row = (l < p.TN && wo < p.Wo && ho < p.Ho && n < p.Nimg)
-                  ? (static_cast<long long>(n) * p.Ho + ho) * p.Wo + wo : -1;
-      } else {
+        tw = m_tile % p.tiles_w;
+        const int rest = m_tile / p.tiles_w;
+        th = rest % p.tiles_h;
+        tn = rest / p.tiles_h;
+        if (!span_b) {
+          const int i = row_in_tile % p.TW, r2 = row_in_tile / p.TW;
+          const int jh = r2 % p.TH, l = r2 / p.TH;
+          const int wo = tw * p.TW + i, ho = th * p.TH + jh, n = tn * p.TN + l;
+          if (l < p.TN && wo < p.Wo && ho < p.Ho && n < p.Nimg) row = (static_cast<long long>(n) * p.Ho + ho) * p.Wo + wo;
+        }
+      } else if (!span_b) {
         row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
         if (row >= p.M) row = -1;
       }
@@ -356,7 +430,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         tc_ld_32x16(taddr + c0, acc);
         tc_ld_wait();
         const int cbase = n_tile * p.BN + c0;
-        if (row < 0 || cbase + 16 > p.Ocp) continue;
+        if (!span_b && (row < 0 || cbase + 16 > p.Ocp)) continue;
         float real[16];
         int u[16];
         int disagree = 0;
@@ -373,8 +447,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int i = 0; i < 16; ++i) {
           const int r_hi = __float_as_int(__fmaf_rn(real[i], inv_hi, 12582912.0f));
           const int r_lo = __float_as_int(__fmaf_rn(real[i], inv_lo, 12582912.0f));
-          disagree |= r_hi ^ r_lo;
           u[i] = __vimin_s32_relu(r_hi + addc, span);
+          // compared after saturation: values far outside the output range (half of them under a
+          // ReLU) agree however wide their band is
+          disagree |= u[i] ^ __vimin_s32_relu(r_lo + addc, span);
         }
         if (disagree) {
 #pragma unroll
@@ -385,12 +461,37 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int g4 = 0; g4 < 4; ++g4)
           w4[g4] = (static_cast<uint32_t>(u[g4 * 4]) | (static_cast<uint32_t>(u[g4 * 4 + 1]) << 8) |
                     (static_cast<uint32_t>(u[g4 * 4 + 2]) << 16) | (static_cast<uint32_t>(u[g4 * 4 + 3]) << 24)) ^ sign_fix;
-        *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        const uint4 out16 = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        if (span_b) {
+          const int blk = c0 / span_b, chunk = (c0 - blk * span_b) >> 4;
+          *reinterpret_cast<uint4*>(stage_out + static_cast<size_t>(blk) * kBlockM * span_b + row_in_tile * span_b +
+                                    ((chunk ^ swz) << 4)) = out16;
+        } else {
+          *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = out16;
+        }
       }
+      // accumulator buffer free again
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&hdr->tmem_empty[a]));
+      if (span_b) {
+        fence_smem_to_async();
+        epilogue_barrier();
+        if (store_issuer) {
+          const int nblk = p.BN / span_b;
+          for (int blk = 0; blk < nblk; ++blk) {
+            const int col = n_tile * p.BN + blk * span_b;
+            if (col >= p.Ocp) break;
+            const uint32_t src = smem_u32(stage_out + static_cast<size_t>(blk) * kBlockM * span_b);
+            if (p.conv) tma_store_4d(&map_d, src, col, tw * p.TW, th * p.TH, tn * p.TN);
+            else tma_store_2d(&map_d, src, col, m_tile * kBlockM);
+          }
+          tma_store_commit();
+        }
+      }
+      if (warp == kFirstEpilogueWarp && lane == 0) TC_TRACE(2, j, 1);
     }
+    if (store_issuer) tma_store_wait_all();
   }
 
   // ---------------------------------------------------------------- common exit
@@ -423,29 +524,26 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-bool encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
-               uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {row_stride_bytes};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+CUtensorMapSwizzle swizzle_of(int span) {
+  return span == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (span == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-bool encode_4d(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint32_t box[4], const uint32_t estr[4],
+// uint8 tensor of rank 2 or 4, dense (stride of dim i+1 = stride of dim i * dims[i])
+bool encode_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint32_t* box, const uint32_t* estr,
                CUtensorMapSwizzle swz) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
-  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
-  cuuint64_t strides[3] = {dims[0], dims[0] * dims[1], dims[0] * dims[1] * dims[2]};   // bytes: uint8 elements
-  cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
-  cuuint32_t e[4] = {estr[0], estr[1], estr[2], estr[3]};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), d, strides, b, e,
+  cuuint64_t d[4], strides[3];
+  cuuint32_t b[4], e[4];
+  uint64_t pitch = 1;
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    e[i] = estr ? estr[i] : 1;
+    pitch *= dims[i];
+    if (i + 1 < rank) strides[i] = pitch;
+  }
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, strides, b, e,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -456,6 +554,7 @@ bool encode_4d(CUtensorMap* map, const void* base, const uint64_t dims[4], const
 struct GemmTcPlan {
   CUtensorMap map_a;
   CUtensorMap map_b;
+  CUtensorMap map_d;
   GemmParams params;
   int grid;
   size_t smem;
@@ -472,7 +571,7 @@ int gemm_tc_available(void) {
 namespace {
 
 // Everything of a plan that does not depend on how A is addressed: N tiling, K block / swizzle mode,
-// stage count, TMEM columns, instruction descriptor, the B tensor map and the launch geometry.
+// output staging, stage count, TMEM columns, instruction descriptor, the B tensor map.
 // Kspan is the K extent one tap (or the whole GEMM) covers, used to pick BK.
 bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int taps, int ldd,
                  const ContractEpilogue& e, void* D, int* status, const char** why) {
@@ -490,21 +589,26 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bk = bk; }
   }
   p.BK = best_bk;
-  const int Kblocks_per_tile = taps * ((Kspan + p.BK - 1) / p.BK);
+  const int kblocks_per_tile = taps * ((Kspan + p.BK - 1) / p.BK);
   p.layout_type = p.BK == 128 ? 2u : (p.BK == 64 ? 4u : 6u);
   p.sbo = 8u * p.BK;
+  // Output staging for the TMA store: column blocks as wide as the widest swizzle span dividing BN.
+  p.store_span = p.BN % 128 == 0 ? 128 : (p.BN % 64 == 0 ? 64 : (p.BN % 32 == 0 ? 32 : 0));
+  const size_t staging = p.store_span ? 2 * static_cast<size_t>(kBlockM) * p.BN : 0;
   // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
   // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
-  // aligned start of the ring.
-  // Several k-blocks share a stage (one barrier round trip) when they are small: up to 64 KiB per stage.
+  // aligned start of the ring.  Several k-blocks share a stage (one barrier round trip) when they are
+  // small: up to 64 KiB per stage.
   const size_t sub_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
+  const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging;
   int group = static_cast<int>((64 * 1024) / sub_bytes);
-  const int total_kb = Kblocks_per_tile > 0 ? Kblocks_per_tile : 1;
-  if (group > total_kb) group = total_kb;
+  if (group > kblocks_per_tile) group = kblocks_per_tile;
+  if (group > kMaxGroup) group = kMaxGroup;
   if (group < 1) group = 1;
+  while (group > 1 && ring_budget / (sub_bytes * group) < 3) --group;
   p.group = group;
   const size_t stage_bytes = sub_bytes * group;
-  int stages = static_cast<int>((200 * 1024) / stage_bytes);
+  int stages = static_cast<int>(ring_budget / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) { *why = "gemm_tc: tile does not fit shared memory"; return false; }
   p.stages = stages;
@@ -518,14 +622,13 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.ep = e;
   p.D = static_cast<uint8_t*>(D);
   p.status = status;
-  const CUtensorMapSwizzle swz = p.BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                             : (p.BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
-  if (!encode_2d(&plan->map_b, B, static_cast<uint64_t>(Kp), static_cast<uint64_t>(Np), static_cast<uint64_t>(Kp),
-                 static_cast<uint32_t>(p.BK), static_cast<uint32_t>(p.BN), swz)) {
+  const uint64_t bdims[2] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(Np)};
+  const uint32_t bbox[2] = {static_cast<uint32_t>(p.BK), static_cast<uint32_t>(p.BN)};
+  if (!encode_u8(&plan->map_b, B, 2, bdims, bbox, nullptr, swizzle_of(p.BK))) {
     *why = "gemm_tc: cuTensorMapEncodeTiled failed for the weights";
     return false;
   }
-  size_t smem = static_cast<size_t>(stages) * stage_bytes + sizeof(SmemHeader) + 1024;
+  size_t smem = ((static_cast<size_t>(stages) * stage_bytes + 1023) & ~static_cast<size_t>(1023)) + staging + sizeof(SmemHeader) + 1024;
   if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
   plan->smem = smem;
   static bool attr_set = false;
@@ -552,10 +655,6 @@ void set_grid(GemmTcPlan* plan) {
   plan->grid = grid;
 }
 
-CUtensorMapSwizzle swizzle_of(int bk) {
-  return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
-}
-
 }  // namespace
 
 GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, int M, int Np, int Kp, int Oc, void* D,
@@ -575,6 +674,7 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   GemmTcPlan* plan = new GemmTcPlan();
   GemmParams& p = plan->params;
   std::memset(&p, 0, sizeof(p));
+  std::memset(&plan->map_d, 0, sizeof(plan->map_d));
   const char* why = "";
   if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why)) {
     delete plan;
@@ -584,8 +684,15 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   p.num_kb = (Kp + p.BK - 1) / p.BK;
   p.m_tiles = (M + kBlockM - 1) / kBlockM;
   p.a_tx_bytes = static_cast<uint32_t>(kBlockM) * p.BK;
-  if (!encode_2d(&plan->map_a, A, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M), static_cast<uint64_t>(Kp),
-                 static_cast<uint32_t>(p.BK), kBlockM, swizzle_of(p.BK))) {
+  const uint64_t adims[2] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(M)};
+  const uint32_t abox[2] = {static_cast<uint32_t>(p.BK), kBlockM};
+  bool ok = encode_u8(&plan->map_a, A, 2, adims, abox, nullptr, swizzle_of(p.BK));
+  if (ok && p.store_span) {
+    const uint64_t ddims[2] = {static_cast<uint64_t>(ldd), static_cast<uint64_t>(M)};
+    const uint32_t dbox[2] = {static_cast<uint32_t>(p.store_span), kBlockM};
+    ok = encode_u8(&plan->map_d, D, 2, ddims, dbox, nullptr, swizzle_of(p.store_span));
+  }
+  if (!ok) {
     delete plan;
     return fail("gemm_tc: cuTensorMapEncodeTiled failed");
   }
@@ -607,6 +714,7 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   GemmTcPlan* plan = new GemmTcPlan();
   GemmParams& p = plan->params;
   std::memset(&p, 0, sizeof(p));
+  std::memset(&plan->map_d, 0, sizeof(plan->map_d));
   const char* why = "";
   const int Kp = g.kh * g.kw * g.Cp;
   if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.kh * g.kw, g.Ocp, e, D, status, &why)) {
@@ -646,9 +754,15 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   const uint32_t box[4] = {static_cast<uint32_t>(p.BK), static_cast<uint32_t>((bw - 1) * g.sx + 1),
                            static_cast<uint32_t>((bh - 1) * g.sy + 1), static_cast<uint32_t>(bn)};
   const uint32_t estr[4] = {1, static_cast<uint32_t>(g.sx), static_cast<uint32_t>(g.sy), 1};
-  if (!encode_4d(&plan->map_a, X, dims, box, estr, swizzle_of(p.BK))) {
+  bool ok = encode_u8(&plan->map_a, X, 4, dims, box, estr, swizzle_of(p.BK));
+  if (ok && p.store_span) {
+    const uint64_t ddims[4] = {static_cast<uint64_t>(g.Ocp), static_cast<uint64_t>(g.Wo), static_cast<uint64_t>(g.Ho), static_cast<uint64_t>(g.N)};
+    const uint32_t dbox[4] = {static_cast<uint32_t>(p.store_span), static_cast<uint32_t>(bw), static_cast<uint32_t>(bh), static_cast<uint32_t>(bn)};
+    ok = encode_u8(&plan->map_d, D, 4, ddims, dbox, nullptr, swizzle_of(p.store_span));
+  }
+  if (!ok) {
     delete plan;
-    return fail("gemm_tc conv: cuTensorMapEncodeTiled failed for the input");
+    return fail("gemm_tc conv: cuTensorMapEncodeTiled failed");
   }
   set_grid(plan);
   return plan;
@@ -657,7 +771,32 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
 void gemm_tc_plan_destroy(GemmTcPlan* p) { delete p; }
 
 cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
-  gemm_i8_tc_kernel<<<plan->grid, kThreadsTc, plan->smem, s>>>(plan->map_a, plan->map_b, plan->params);
+#ifdef B2VX_TC_TRACE
+  GemmTcPlan* mp = const_cast<GemmTcPlan*>(plan);
+  if (!mp->params.trace) {
+    cudaMalloc(reinterpret_cast<void**>(&mp->params.trace), 3 * 64 * 2 * sizeof(long long));
+    cudaMemset(mp->params.trace, 0, 3 * 64 * 2 * sizeof(long long));
+  }
+#endif
+  gemm_i8_tc_kernel<<<plan->grid, kThreadsTc, plan->smem, s>>>(plan->map_a, plan->map_b, plan->map_d, plan->params);
+#ifdef B2VX_TC_TRACE
+  {
+    static int launches = 0;
+    if (++launches == 3) {
+      cudaStreamSynchronize(s);
+      long long h[3 * 64 * 2];
+      cudaMemcpy(h, plan->params.trace, sizeof(h), cudaMemcpyDeviceToHost);
+      const long long t0 = h[0];
+      const GemmParams& p = plan->params;
+      std::fprintf(stderr, "trace: BN %d BK %d group %d stages %d num_kb %d m_tiles %d n_tiles %d grid %d conv %d span %d\n", p.BN, p.BK,
+                   p.group, p.stages, p.num_kb, p.m_tiles, p.n_tiles, plan->grid, p.conv, p.store_span);
+      for (int i = 0; i < 20; ++i)
+        std::fprintf(stderr, "it %2d  prodA slot-free %7lld issued %7lld | mma data-in %7lld committed %7lld | epi acc-ready %7lld done %7lld\n",
+                     i, h[(0 * 64 + i) * 2] - t0, h[(0 * 64 + i) * 2 + 1] - t0, h[(1 * 64 + i) * 2] - t0,
+                     h[(1 * 64 + i) * 2 + 1] - t0, h[(2 * 64 + i) * 2] - t0, h[(2 * 64 + i) * 2 + 1] - t0);
+    }
+  }
+#endif
   return cudaGetLastError();
 }
 
