@@ -29,7 +29,8 @@
 //                            shared memory; one thread then stores the tile
 //                            with TMA (clipped at the tensor edge).  Two
 //                            accumulator buffers and two staging tiles overlap
-//                            tile i's epilogue with tile i+1's MMAs.
+//                            tile i's epilogue with tile i+1's MMAs and with
+//                            tile i-1's store.
 // A stage holds up to `group` k-blocks so that small k-blocks share one
 // barrier round trip.  The grid is a multiple of the number of N tiles: a CTA
 // keeps one N tile for life (bias and scales staged in shared memory once) and
@@ -115,14 +116,16 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// try_wait may suspend the thread in hardware until the phase completes or the hint (ns) runs out,
+// which keeps waiting warps out of the issue slots the epilogue warps need.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(20000u)
       : "memory");
   return ok;
 }
@@ -132,7 +135,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - start > kWaitLimitCycles) {
       *abort_flag = 1;
@@ -284,7 +289,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // Lane 0 waits for the slot and announces the bytes; lanes 0..cnt-1 then issue the boxes of the
     // stage's k-blocks in one instruction.
     const bool is_a = warp == 0;
-    uint32_t it = 0;
+    uint32_t it = 0, s = 0, ph = 0;   // stage index and ring phase, advanced without divisions
     int ok = 1;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const int m_tile = tile / p.n_tiles;
@@ -298,7 +303,6 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         n0 = (rest / p.tiles_h) * p.TN;
       }
       for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
-        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
         const int cnt = min(p.group, p.num_kb - kb0);
         const uint32_t full = smem_u32(&hdr->full[s]);
         if (lane == 0) {
@@ -326,12 +330,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
         }
         if (is_a && lane == 0) TC_TRACE(0, it, 1);
+        if (++s == static_cast<uint32_t>(p.stages)) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
       int j = 0;
       const int ksteps = p.BK >> 5;
@@ -342,7 +347,6 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t tmem_d = tmem_base + a * p.acc_stride;
         uint32_t accumulate = 0;
         for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
-          const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
           if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3)) { ok = false; break; }
           TC_TRACE(1, it, 0);
           tc_fence_after();
@@ -359,6 +363,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
           tc_commit(smem_u32(&hdr->empty[s]));
           TC_TRACE(1, it, 1);
+          if (++s == static_cast<uint32_t>(p.stages)) { s = 0; ph ^= 1; }
         }
         if (ok) tc_commit(smem_u32(&hdr->tmem_full[a]));
       }
@@ -394,11 +399,6 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const int m_tile = tile / p.n_tiles;
       const uint32_t a = j & 1, aph = (j >> 1) & 1;
       uint8_t* stage_out = staging + a * staging_bytes;
-      if (span_b) {
-        // the staging tile written two tiles ago must have been read by its TMA store
-        if (store_issuer) tma_store_wait_read<1>();
-        epilogue_barrier();
-      }
       if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
       alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
       if (!alive) {
@@ -475,7 +475,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&hdr->tmem_empty[a]));
       if (span_b) {
+        // One barrier per tile.  Before it, the issuer makes sure the previous tile's store has read
+        // its staging buffer (it was issued a whole tile ago): after the barrier every thread may
+        // write that buffer for the next tile, and the issuer stores the tile just written.
         fence_smem_to_async();
+        if (store_issuer) tma_store_wait_read<0>();
         epilogue_barrier();
         if (store_issuer) {
           const int nblk = p.BN / span_b;
