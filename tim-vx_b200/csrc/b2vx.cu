@@ -116,6 +116,10 @@ struct b2vx_graph {
   int* h_status = nullptr;
   bool compiled = false;
   bool use_tc = false;
+  // the whole launch plan captured once as a CUDA graph; replays cost one launch on the host
+  cudaGraphExec_t exec = nullptr;
+  bool capture_failed = false;
+  bool use_cuda_graph = true;
 };
 
 namespace {
@@ -931,6 +935,8 @@ b2vx_status b2vx_graph_create(b2vx_context* ctx, int32_t device_id, b2vx_graph**
   g->stream = g->own_stream;
   const char* k = std::getenv("B2VX_CONV_KERNEL");
   g->use_tc = gemm_tc_available() && !(k && std::strcmp(k, "simt") == 0);
+  const char* cg = std::getenv("B2VX_CUDA_GRAPH");
+  g->use_cuda_graph = !(cg && cg[0] == '0');
   *out = g;
   return B2VX_OK;
 }
@@ -939,6 +945,7 @@ void b2vx_graph_destroy(b2vx_graph* g) {
   if (!g) return;
   DeviceGuard guard(g->device);
   cudaStreamSynchronize(g->stream);
+  if (g->exec) cudaGraphExecDestroy(g->exec);
   for (GemmTcPlan* p : g->gemm_plans) gemm_tc_plan_destroy(p);
   for (void* p : g->allocs) cudaFree(p);
   if (g->d_status) cudaFree(g->d_status);
@@ -1240,6 +1247,27 @@ b2vx_status b2vx_graph_run_async(b2vx_graph* g) {
   b2vx_status st = b2vx_graph_compile(g);
   if (st != B2VX_OK) return st;
   DeviceGuard guard(g->device);
+  if (g->use_cuda_graph && !g->exec && !g->capture_failed && !g->steps.empty()) {
+    // Record the plan once; on any failure fall back to launching kernel by kernel.
+    cudaGraph_t graph = nullptr;
+    bool ok = cudaStreamBeginCapture(g->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    if (ok) {
+      for (Step& s : g->steps) ok = ok && s.fn(g->stream) == cudaSuccess;
+      ok = (cudaStreamEndCapture(g->stream, &graph) == cudaSuccess) && ok && graph != nullptr;
+    }
+    if (ok) ok = cudaGraphInstantiate(&g->exec, graph, 0) == cudaSuccess;
+    if (graph) cudaGraphDestroy(graph);
+    if (!ok) {
+      cudaGetLastError();
+      g->exec = nullptr;
+      g->capture_failed = true;
+    }
+  }
+  if (g->exec) {
+    cudaError_t e = cudaGraphLaunch(g->exec, g->stream);
+    if (e != cudaSuccess) return fail(g, B2VX_CUDA_ERROR, std::string("cudaGraphLaunch: ") + cudaGetErrorString(e));
+    return B2VX_OK;
+  }
   for (Step& s : g->steps) {
     cudaError_t e = s.fn(g->stream);
     if (e != cudaSuccess) {

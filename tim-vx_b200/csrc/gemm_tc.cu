@@ -147,6 +147,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// One lane of a fully converged warp.  The control warps run their loops with all 32 lanes (so that
+// every value feeding a TMA or MMA instruction is warp-uniform and can live in uniform registers)
+// and elect a single lane only for the issue itself.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -286,11 +299,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   if (warp == 0 || warp == 2) {
     // ------------------------------------------------------------ TMA producers (warp 0: A, warp 2: B)
-    // Lane 0 waits for the slot and announces the bytes; lanes 0..cnt-1 then issue the boxes of the
-    // stage's k-blocks in one instruction.
+    // All lanes wait for the slot; one elected lane announces the bytes and issues the boxes of the
+    // stage's k-blocks.
     const bool is_a = warp == 0;
     uint32_t it = 0, s = 0, ph = 0;   // stage index and ring phase, advanced without divisions
-    int ok = 1;
+    bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const int m_tile = tile / p.n_tiles;
       int w0 = 0, h0 = 0, n0 = 0;
@@ -302,71 +315,90 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         h0 = (rest % p.tiles_h) * p.TH * p.sy - p.pt;
         n0 = (rest / p.tiles_h) * p.TN;
       }
+      int tap = 0, cb = 0, ky = 0, kx = 0;   // conv mode: k-block -> (tap = ky*kw + kx, channel block), stepped
       for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
         const int cnt = min(p.group, p.num_kb - kb0);
         const uint32_t full = smem_u32(&hdr->full[s]);
-        if (lane == 0) {
-          ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, is_a ? 1 : 5) ? 1 : 0;
-          if (is_a) TC_TRACE(0, it, 0);
-          if (ok) mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (is_a ? p.a_tx_bytes : b_bytes));
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, is_a ? 1 : 5);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane < cnt) {
-          const int kb = kb0 + lane;
-          const uint32_t dst = tiles_addr + s * stage_bytes + lane * sub_bytes;
-          if (p.conv) {
-            const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
-            if (is_a) {
-              const int ky = tap / p.kw, kx = tap - ky * p.kw;
-              tma_load_4d(dst, &map_a, cb * p.BK, w0 + kx * p.dx, h0 + ky * p.dy, n0, full);
+        if (is_a) TC_TRACE(0, it, 0);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (is_a ? p.a_tx_bytes : b_bytes));
+          uint32_t dst = tiles_addr + s * stage_bytes;
+          int t_tap = tap, t_cb = cb, t_ky = ky, t_kx = kx;
+          for (int gi = 0; gi < cnt; ++gi, dst += sub_bytes) {
+            if (p.conv) {
+              if (is_a) tma_load_4d(dst, &map_a, t_cb * p.BK, w0 + t_kx * p.dx, h0 + t_ky * p.dy, n0, full);
+              else tma_load_2d(dst + a_bytes, &map_b, t_tap * p.Cp + t_cb * p.BK, n_tile * p.BN, full);
+              if (++t_cb == p.cblocks) {
+                t_cb = 0;
+                ++t_tap;
+                if (++t_kx == p.kw) { t_kx = 0; ++t_ky; }
+              }
+            } else if (is_a) {
+              tma_load_2d(dst, &map_a, (kb0 + gi) * p.BK, m_tile * kBlockM, full);
             } else {
-              tma_load_2d(dst + a_bytes, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
+              tma_load_2d(dst + a_bytes, &map_b, (kb0 + gi) * p.BK, n_tile * p.BN, full);
             }
-          } else if (is_a) {
-            tma_load_2d(dst, &map_a, kb * p.BK, m_tile * kBlockM, full);
-          } else {
-            tma_load_2d(dst + a_bytes, &map_b, kb * p.BK, n_tile * p.BN, full);
           }
         }
-        if (is_a && lane == 0) TC_TRACE(0, it, 1);
+        __syncwarp();
+        if (p.conv) {
+          for (int gi = 0; gi < cnt; ++gi) {
+            if (++cb == p.cblocks) {
+              cb = 0;
+              ++tap;
+              if (++kx == p.kw) { kx = 0; ++ky; }
+            }
+          }
+        }
+        if (is_a) TC_TRACE(0, it, 1);
         if (++s == static_cast<uint32_t>(p.stages)) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      uint32_t it = 0, s = 0, ph = 0;
-      bool ok = true;
-      int j = 0;
-      const int ksteps = p.BK >> 5;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
-        const uint32_t a = j & 1, aph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2)) break;
+    uint32_t it = 0, s = 0, ph = 0;
+    bool ok = true;
+    int j = 0;
+    const int ksteps = p.BK >> 5;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
+      const uint32_t a = j & 1, aph = (j >> 1) & 1;
+      ok = mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + a * p.acc_stride;
+      uint32_t accumulate = 0;
+      for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
+        ok = mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        TC_TRACE(1, it, 0);
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + a * p.acc_stride;
-        uint32_t accumulate = 0;
-        for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
-          if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3)) { ok = false; break; }
-          TC_TRACE(1, it, 0);
-          tc_fence_after();
-          const int cnt = min(p.group, p.num_kb - kb0);
+        const int cnt = min(p.group, p.num_kb - kb0);
+        if (elect_one()) {
           uint32_t a_addr = tiles_addr + s * stage_bytes;
+          uint32_t acc_flag = accumulate;
           for (int gi = 0; gi < cnt; ++gi, a_addr += sub_bytes) {
             const uint64_t da = make_smem_desc(a_addr, p.sbo, p.layout_type);
             const uint64_t db = make_smem_desc(a_addr + a_bytes, p.sbo, p.layout_type);
             for (int k = 0; k < ksteps; ++k) {
               // advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
-              tc_mma_i8(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc, accumulate);
-              accumulate = 1;
+              tc_mma_i8(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc, acc_flag);
+              acc_flag = 1;
             }
           }
           tc_commit(smem_u32(&hdr->empty[s]));
-          TC_TRACE(1, it, 1);
-          if (++s == static_cast<uint32_t>(p.stages)) { s = 0; ph ^= 1; }
         }
-        if (ok) tc_commit(smem_u32(&hdr->tmem_full[a]));
+        __syncwarp();
+        accumulate = 1;
+        TC_TRACE(1, it, 1);
+        if (++s == static_cast<uint32_t>(p.stages)) { s = 0; ph ^= 1; }
       }
+      if (ok && elect_one()) tc_commit(smem_u32(&hdr->tmem_full[a]));
+      __syncwarp();
     }
   } else if (warp >= kFirstEpilogueWarp) {
     // ------------------------------------------------------------ epilogue

@@ -1,9 +1,11 @@
 // Synthetic networks on the tim::vx API (see networks.h).
 //
 // Quantization parameters are chosen analytically so that activations keep a
-// usable spread without a calibration pass: the builder tracks an estimate of
-// the mean square of each activation's real values and sets every layer's
-// output scale to a few standard deviations per 255 steps.
+// usable spread without a calibration pass: the builder tracks estimates of
+// the mean and mean square of each activation's real values, sets every
+// layer's output scale to a few standard deviations per 255 steps, and gives
+// each output channel the bias that cancels the expected accumulator (the
+// role batch-norm folding plays in a trained network) plus seeded noise.
 #include "networks.h"
 
 #include <algorithm>
@@ -45,6 +47,7 @@ struct Act {
   float scale;
   int zp;
   double ms;       // estimate of E[real^2]
+  double mean;     // estimate of E[real]
   uint32_t W, H, C;
 };
 
@@ -59,6 +62,33 @@ struct b2vx_net {
   uint64_t macs = 0;
   Rng rng{1};
   enum WeightKind { S8_PER_CHANNEL, U8_ZP128, U8_ASYM } wkind = S8_PER_CHANNEL;
+
+  // uint8 weights of one layer, [oc][per_oc]: with zero point 128 plain uniform bytes; otherwise every
+  // channel is drawn in mirrored pairs (w, 2*zw - w) from the widest range symmetric about the zero
+  // point, so that a channel's weights sum to zero in the real domain (what a trained, batch-norm
+  // folded layer roughly has) and the accumulator does not depend on the input's mean.  Returns the
+  // variance of one (w - zw).
+  double fill_u8_weights(std::vector<uint8_t>& wd, size_t oc, size_t per_oc, int zw, bool plain) {
+    if (plain) {
+      for (auto& v : wd) v = static_cast<uint8_t>(rng.range(0, 255));
+      return (256.0 * 256.0 - 1.0) / 12.0;
+    }
+    const int half = std::min(zw, 255 - zw);
+    for (size_t i = 0; i < oc; ++i) {
+      uint8_t* row = wd.data() + i * per_oc;
+      size_t k = 0;
+      for (; k + 1 < per_oc; k += 2) {
+        const int d = rng.range(-half, half);
+        row[k] = static_cast<uint8_t>(zw + d);
+        row[k + 1] = static_cast<uint8_t>(zw - d);
+      }
+      if (k < per_oc) row[k] = static_cast<uint8_t>(zw);
+      // shuffle so that mirrored values are not neighbours
+      for (size_t j = per_oc; j > 1; --j) std::swap(row[j - 1], row[static_cast<size_t>(rng.next() % j)]);
+    }
+    const double n = 2.0 * half + 1.0;
+    return (n * n - 1.0) / 12.0;
+  }
 
   std::shared_ptr<Tensor> transient(float scale, int zp) {
     Quantization q(QuantType::ASYMMETRIC, scale, zp);
@@ -78,9 +108,10 @@ struct b2vx_net {
     std::vector<uint32_t> wshape = depthwise ? std::vector<uint32_t>{k, k, oc, 1} : std::vector<uint32_t>{k, k, ic, oc};
     const size_t wcount = static_cast<size_t>(k) * k * (depthwise ? oc : static_cast<size_t>(ic) * oc);
     std::shared_ptr<Tensor> w, b;
-    double w_ms;   // E[w_real^2]
+    double w_var;   // variance of one real weight around its mean
     std::vector<int32_t> bias(oc);
-    for (auto& v : bias) v = rng.range(-1000, 1000);
+    const size_t per_oc = wcount / oc;
+    const double mean_xq = x.mean / x.scale;   // expected (q - zero point) of the input
     if (wkind == S8_PER_CHANNEL) {
       std::vector<float> ws(oc), bs(oc);
       std::vector<int32_t> zeros(oc, 0);
@@ -94,33 +125,43 @@ struct b2vx_net {
       }
       std::vector<int8_t> wd(wcount);
       for (auto& v : wd) v = static_cast<int8_t>(rng.range(-127, 127));
+      for (uint32_t i = 0; i < oc; ++i) {
+        long long sum = 0;
+        for (size_t k = 0; k < per_oc; ++k) sum += wd[i * per_oc + k];
+        bias[i] = static_cast<int32_t>(std::llround(-mean_xq * static_cast<double>(sum))) + rng.range(-1000, 1000);
+      }
       Quantization wq(QuantType::SYMMETRIC_PER_CHANNEL, depthwise ? 2 : 3, ws, zeros);
       Quantization bq(QuantType::SYMMETRIC_PER_CHANNEL, 0, bs, zeros);
       w = graph->CreateTensor(TensorSpec(DataType::INT8, wshape, TensorAttribute::CONSTANT, wq), wd.data());
       b = graph->CreateTensor(TensorSpec(DataType::INT32, {oc}, TensorAttribute::CONSTANT, bq), bias.data());
-      w_ms = (s2 / oc) * (127.0 * 128.0 / 3.0);   // uniform integer in [-127,127]
+      w_var = (s2 / oc) * (127.0 * 128.0 / 3.0);   // uniform integer in [-127,127]
     } else {
       const int zw = wkind == U8_ZP128 ? 128 : rng.range(100, 156);
       const float sw = wkind == U8_ZP128 ? 0.01f : rng.uniform(0.005f, 0.05f) / std::sqrt(static_cast<float>(fan_in) / 16.0f);
       std::vector<uint8_t> wd(wcount);
-      for (auto& v : wd) v = static_cast<uint8_t>(rng.range(0, 255));
+      const double q_var = fill_u8_weights(wd, oc, per_oc, zw, wkind == U8_ZP128);
+      for (uint32_t i = 0; i < oc; ++i) {
+        long long sum = 0;
+        for (size_t k = 0; k < per_oc; ++k) sum += static_cast<int>(wd[i * per_oc + k]) - zw;
+        bias[i] = static_cast<int32_t>(std::llround(-mean_xq * static_cast<double>(sum))) + rng.range(-1000, 1000);
+      }
       Quantization wq(QuantType::ASYMMETRIC, sw, zw);
       Quantization bq(QuantType::ASYMMETRIC, x.scale * sw, 0);
       w = graph->CreateTensor(TensorSpec(DataType::UINT8, wshape, TensorAttribute::CONSTANT, wq), wd.data());
       b = graph->CreateTensor(TensorSpec(DataType::INT32, {oc}, TensorAttribute::CONSTANT, bq), bias.data());
-      const double m = 127.5 - zw;
-      w_ms = static_cast<double>(sw) * sw * (m * m + (256.0 * 256.0 - 1.0) / 12.0);
+      w_var = static_cast<double>(sw) * sw * q_var;
     }
     keep.push_back(w);
     keep.push_back(b);
-    const double var = static_cast<double>(fan_in) * x.ms * w_ms;
+    // with the mean cancelled by the bias, the accumulator is roughly N(0, fan_in * E[x^2] * var(w))
+    const double var = static_cast<double>(fan_in) * x.ms * w_var;
     const float sigma = static_cast<float>(std::sqrt(std::max(var, 1e-12)));
     float s_out;
     int z_out;
-    double ms_out;
-    if (act == 0) { s_out = 6.0f * sigma / 255.0f; z_out = 128; ms_out = var; }
-    else if (act == 1) { s_out = 3.0f * sigma / 255.0f; z_out = 0; ms_out = var / 2; }
-    else { s_out = std::min(3.0f * sigma, 6.0f) / 255.0f; z_out = 0; ms_out = std::min(var / 2, 12.0); }
+    double ms_out, mean_out;
+    if (act == 0) { s_out = 6.0f * sigma / 255.0f; z_out = 128; ms_out = var; mean_out = 0.0; }
+    else if (act == 1) { s_out = 3.0f * sigma / 255.0f; z_out = 0; ms_out = var / 2; mean_out = 0.3989 * sigma; }
+    else { s_out = std::min(3.0f * sigma, 6.0f) / 255.0f; z_out = 0; ms_out = std::min(var / 2, 12.0); mean_out = std::min(0.3989 * sigma, 2.0); }
     if (out_scale_io && *out_scale_io > 0) s_out = *out_scale_io;
     if (out_scale_io) *out_scale_io = s_out;
 
@@ -134,7 +175,7 @@ struct b2vx_net {
                                                   std::array<uint32_t, 4>({pl, pr, pl, pr}), depthwise ? 1 : 0);
     (*op).BindInputs({x.t, w, b}).BindOutputs({y});
     macs += static_cast<uint64_t>(Wo) * Ho * oc * fan_in;
-    Act r{y, s_out, z_out, ms_out, Wo, Ho, oc};
+    Act r{y, s_out, z_out, ms_out, mean_out, Wo, Ho, oc};
     if (act == 1 || act == 6) {
       auto z = transient(s_out, z_out);
       if (act == 1) {
@@ -150,14 +191,15 @@ struct b2vx_net {
   }
 
   Act add(const Act& a, const Act& b, bool relu) {
-    const double var = a.ms + b.ms;
+    const double mean = a.mean + b.mean;
+    const double var = std::max(a.ms + b.ms + 2.0 * a.mean * b.mean - mean * mean, 1e-12) + mean * mean;
     const float sigma = static_cast<float>(std::sqrt(var));
     const float s = relu ? 3.5f * sigma / 255.0f : 6.0f * sigma / 255.0f;
     const int zp = relu ? 0 : 128;
     auto y = transient(s, zp);
     auto op = graph->CreateOperation<ops::Add>();
     (*op).BindInputs({a.t, b.t}).BindOutputs({y});
-    Act r{y, s, zp, relu ? var / 2 : var, a.W, a.H, a.C};
+    Act r{y, s, zp, relu ? var / 2 + mean * mean / 2 : var, relu ? std::max(mean, 0.3989 * sigma) : mean, a.W, a.H, a.C};
     if (relu) {
       auto z = transient(s, zp);
       auto ro = graph->CreateOperation<ops::Relu>();
@@ -170,8 +212,8 @@ struct b2vx_net {
   Act fc(const Act& x, uint32_t axis, uint32_t K, uint32_t n_out, bool output_tensor) {
     std::shared_ptr<Tensor> w, b;
     std::vector<int32_t> bias(n_out);
-    for (auto& v : bias) v = rng.range(-1000, 1000);
-    double w_ms;
+    const double mean_xq = x.mean / x.scale;
+    double w_var;
     if (wkind == S8_PER_CHANNEL) {
       std::vector<float> ws(n_out), bs(n_out);
       std::vector<int32_t> zeros(n_out, 0);
@@ -184,26 +226,35 @@ struct b2vx_net {
       }
       std::vector<int8_t> wd(static_cast<size_t>(K) * n_out);
       for (auto& v : wd) v = static_cast<int8_t>(rng.range(-127, 127));
+      for (uint32_t i = 0; i < n_out; ++i) {
+        long long sum = 0;
+        for (uint32_t k = 0; k < K; ++k) sum += wd[static_cast<size_t>(i) * K + k];
+        bias[i] = static_cast<int32_t>(std::llround(-mean_xq * static_cast<double>(sum))) + rng.range(-1000, 1000);
+      }
       w = graph->CreateTensor(TensorSpec(DataType::INT8, {K, n_out}, TensorAttribute::CONSTANT,
                                          Quantization(QuantType::SYMMETRIC_PER_CHANNEL, 1, ws, zeros)), wd.data());
       b = graph->CreateTensor(TensorSpec(DataType::INT32, {n_out}, TensorAttribute::CONSTANT,
                                          Quantization(QuantType::SYMMETRIC_PER_CHANNEL, 0, bs, zeros)), bias.data());
-      w_ms = (s2 / n_out) * (127.0 * 128.0 / 3.0);
+      w_var = (s2 / n_out) * (127.0 * 128.0 / 3.0);
     } else {
       const int zw = wkind == U8_ZP128 ? 128 : rng.range(100, 156);
       const float sw = wkind == U8_ZP128 ? 0.01f : rng.uniform(0.005f, 0.05f) / std::sqrt(static_cast<float>(K) / 16.0f);
       std::vector<uint8_t> wd(static_cast<size_t>(K) * n_out);
-      for (auto& v : wd) v = static_cast<uint8_t>(rng.range(0, 255));
+      const double q_var = fill_u8_weights(wd, n_out, K, zw, wkind == U8_ZP128);
+      for (uint32_t i = 0; i < n_out; ++i) {
+        long long sum = 0;
+        for (uint32_t k = 0; k < K; ++k) sum += static_cast<int>(wd[static_cast<size_t>(i) * K + k]) - zw;
+        bias[i] = static_cast<int32_t>(std::llround(-mean_xq * static_cast<double>(sum))) + rng.range(-1000, 1000);
+      }
       w = graph->CreateTensor(TensorSpec(DataType::UINT8, {K, n_out}, TensorAttribute::CONSTANT,
                                          Quantization(QuantType::ASYMMETRIC, sw, zw)), wd.data());
       b = graph->CreateTensor(TensorSpec(DataType::INT32, {n_out}, TensorAttribute::CONSTANT,
                                          Quantization(QuantType::ASYMMETRIC, x.scale * sw, 0)), bias.data());
-      const double m = 127.5 - zw;
-      w_ms = static_cast<double>(sw) * sw * (m * m + (256.0 * 256.0 - 1.0) / 12.0);
+      w_var = static_cast<double>(sw) * sw * q_var;
     }
     keep.push_back(w);
     keep.push_back(b);
-    const double var = static_cast<double>(K) * x.ms * w_ms;
+    const double var = static_cast<double>(K) * x.ms * w_var;
     const float s_out = 6.0f * static_cast<float>(std::sqrt(std::max(var, 1e-12))) / 255.0f;
     std::shared_ptr<Tensor> y;
     if (output_tensor) {
@@ -216,7 +267,7 @@ struct b2vx_net {
     auto op = graph->CreateOperation<ops::FullyConnected>(axis, n_out);
     (*op).BindInputs({x.t, w, b}).BindOutputs({y});
     macs += static_cast<uint64_t>(K) * n_out;
-    return Act{y, s_out, 128, var, 1, 1, n_out};
+    return Act{y, s_out, 128, var, 0.0, 1, 1, n_out};
   }
 
   Act make_input(uint32_t w, uint32_t h, uint32_t c, float scale, int zp) {
@@ -225,7 +276,7 @@ struct b2vx_net {
                                            Quantization(QuantType::ASYMMETRIC, scale, zp)));
     // uniform 0..255: E[(q-zp)^2] * scale^2
     const double m = 127.5 - zp;
-    return Act{input, scale, zp, static_cast<double>(scale) * scale * (m * m + (256.0 * 256.0 - 1.0) / 12.0), w, h, c};
+    return Act{input, scale, zp, static_cast<double>(scale) * scale * (m * m + (256.0 * 256.0 - 1.0) / 12.0), scale * m, w, h, c};
   }
 
   bool build_resnet50() {
@@ -323,14 +374,14 @@ struct b2vx_net {
       (*op).BindInputs({in.t, w, b}).BindOutputs({y});
       const uint32_t Wo = in.W - k + 1;
       macs += static_cast<uint64_t>(Wo) * Wo * oc * k * k * in.C;
-      return Act{y, s, 128, 1.0, Wo, Wo, oc};
+      return Act{y, s, 128, 1.0, 0.0, Wo, Wo, oc};
     };
     auto pool = [&](const Act& in) {
       auto y = transient(in.scale, in.zp);
       auto op = graph->CreateOperation<ops::Pool2d>(PoolType::MAX, PadType::NONE, std::array<uint32_t, 2>({2, 2}),
                                                     std::array<uint32_t, 2>({2, 2}));
       (*op).BindInput(in.t).BindOutput(y);
-      return Act{y, in.scale, in.zp, in.ms, in.W / 2, in.H / 2, in.C};
+      return Act{y, in.scale, in.zp, in.ms, in.mean, in.W / 2, in.H / 2, in.C};
     };
     x = pool(conv_fixed(x, 5, 20));
     x = pool(conv_fixed(x, 5, 50));
@@ -355,7 +406,7 @@ struct b2vx_net {
       auto op = graph->CreateOperation<ops::FullyConnected>(axis, n_out);
       (*op).BindInputs({in.t, w, b}).BindOutputs({y});
       macs += static_cast<uint64_t>(K) * n_out;
-      return Act{y, 0.05f, 128, 1.0, 1, 1, n_out};
+      return Act{y, 0.05f, 128, 1.0, 0.0, 1, 1, n_out};
     };
     x = fc_fixed(x, 2, 800, 500, false);
     {

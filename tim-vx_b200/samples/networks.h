@@ -8,7 +8,8 @@
  *
  *   "lenet"        LeNet-5 as in samples/lenet/lenet_asymu8.cc:115-290; uint8 weights zp 128
  *   "resnet50"     ResNet-50 v1.5, uint8 activations, per-channel int8 weights
- *   "mobilenetv2"  MobileNetV2-1.0, uint8 activations and uint8 weights (zp in [100,156])
+ *   "mobilenetv2"  MobileNetV2-1.0, uint8 activations and uint8 weights (zero point in [100,156],
+ *                  values drawn symmetrically about it so that each channel sums to zero)
  */
 #ifndef B2VX_SAMPLES_NETWORKS_H_
 #define B2VX_SAMPLES_NETWORKS_H_
