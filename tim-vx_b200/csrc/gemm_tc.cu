@@ -667,13 +667,16 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   size_t smem = ((static_cast<size_t>(stages) * stage_bytes + 1023) & ~static_cast<size_t>(1023)) + staging + sizeof(SmemHeader) + 1024;
   if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
   plan->smem = smem;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the attribute belongs to the function on one device: set it once per device of this process
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
     if (cudaFuncSetAttribute(gemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       *why = "gemm_tc: cannot raise the dynamic shared memory limit";
       return false;
     }
-    attr_set = true;
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   return true;
 }
