@@ -225,6 +225,54 @@ b2vx_status b2vx_graph_kernel_info(b2vx_graph* g, uint32_t index, b2vx_kernel_in
  * store the mean per-kernel time in b2vx_kernel_info::last_ms. */
 b2vx_status b2vx_graph_profile(b2vx_graph* g, uint32_t iters);
 
+/* ---- a convolution for callers that cannot allocate -------------------------
+ * No counterpart in the reference (there, every buffer belongs to the driver).
+ *
+ * Some callers of this library never get to call cudaMalloc: a plugin that lives
+ * inside a server whose device memory was carved up at start-up, a control loop
+ * with a hard deadline (the driver's allocator takes locks and can stall the
+ * whole device), a process running so close to the memory limit that an
+ * allocation in the middle of a request may fail.  The graph API above allocates
+ * tensors, packed weights and scratch at compile time; this entry point
+ * allocates nothing, neither on the device nor through any library: the caller
+ * passes every input and output as a device pointer, and the one intermediate
+ * the operation needs, the im2col matrix, lives in a fixed array of
+ * B2VX_NOALLOC_SCRATCH_BYTES inside the library.  Every GPU that loads the
+ * library holds that array until the process exits.
+ *
+ * The operation: a first-layer quantized convolution (uint8 image with fewer
+ * than 16 channels, int8 weights, uint8 output; at most 256 output channels),
+ * computed exactly as a Conv2d node of the graph API computes it.
+ *   x_whcn     uint8, tim::vx order [W,H,C,N] (N slowest)
+ *   w8         int8 [Ocp][Kp]: row oc holds that channel's weights in the kernel
+ *              tensor's own order, k = (c*kh + ky)*kw + kx, zero padded to
+ *              Kp = K rounded up to 16; Ocp = oc rounded up to 16, extra rows zero
+ *   bias_full  int32 [Ocp]: bias[oc] - in_zero_point * sum_k w8[oc][k]; padding 0
+ *   acc_scale  float [Ocp]: in_scale * weight_scale[oc]; padding 0
+ *   y_cl       uint8 [N*Ho*Wo][Ocp], channels-last; Wo/Ho follow from the explicit
+ *              pad {left,right,top,bottom} with floor rounding
+ * All pointers are device pointers aligned to 16 bytes.  The call returns when
+ * y_cl is complete.  A problem whose im2col matrix (N*Ho*Wo*Kp bytes) exceeds
+ * the array is refused with B2VX_INVALID_ARG and a message in err.
+ *
+ * The first call on a GPU resolves the array's device address; make that call
+ * before any stream capture.  All calls on one GPU share the array: calls whose
+ * kernels overlap on the GPU (other streams, other threads) race. */
+#define B2VX_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u)
+typedef struct b2vx_conv2d_noalloc_desc {
+  uint32_t n, h, w, c;
+  uint32_t kw, kh, oc;
+  uint32_t stride[2];
+  uint32_t dilation[2];
+  uint32_t pad[4];
+  int32_t in_zero_point;
+  float out_scale;
+  int32_t out_zero_point;
+} b2vx_conv2d_noalloc_desc;
+b2vx_status b2vx_conv2d_first_layer_noalloc(const b2vx_conv2d_noalloc_desc* d, const void* x_whcn, const int8_t* w8,
+                                            const int32_t* bias_full, const float* acc_scale, void* y_cl,
+                                            void* cuda_stream, char* err, size_t err_len);
+
 /* Pinned host memory for callers that want asynchronous tensor_write/read. */
 b2vx_status b2vx_host_alloc(void** out, size_t bytes);
 void b2vx_host_free(void* p);

@@ -27,7 +27,10 @@ def test_product_library_exports_every_declared_symbol():
 
 
 def test_oracle_library_exports_the_same_abi(oracle_lib):
+    """The oracle serves the graph ABI; the allocation-free convolution is a CUDA-only addition."""
     for n in declared_symbols():
+        if n.endswith("_noalloc"):
+            continue
         assert hasattr(oracle_lib, n), n
 
 

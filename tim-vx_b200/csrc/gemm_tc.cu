@@ -807,6 +807,45 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   return plan;
 }
 
+size_t gemm_tc_plan_bytes(void) { return sizeof(GemmTcPlan); }
+
+// Same plan as gemm_tc_plan_create, but built inside caller-provided storage (no heap allocation);
+// the caller must not pass it to gemm_tc_plan_destroy.
+GemmTcPlan* gemm_tc_plan_build_in(void* storage, size_t storage_bytes, const void* A, int a_signed, const int8_t* B, int M,
+                                  int Np, int Kp, void* D, int ldd, const ContractEpilogue& e, int* status, char* err,
+                                  size_t err_len) {
+  auto fail = [&](const char* msg) -> GemmTcPlan* {
+    if (err && err_len) std::snprintf(err, err_len, "%s", msg);
+    return nullptr;
+  };
+  if (!storage || storage_bytes < sizeof(GemmTcPlan) || (reinterpret_cast<uintptr_t>(storage) & 63))
+    return fail("gemm_tc: plan storage too small or not 64-byte aligned");
+  if (M <= 0 || Np <= 0 || Kp <= 0 || (Kp & 15) || (ldd & 15) || (Np & 15)) return fail("gemm_tc: sizes must be positive multiples of 16");
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(D) & 15))
+    return fail("gemm_tc: operands must be 16-byte aligned");
+  if (e.dz != nullptr || e.tapc != nullptr || e.out_is_float) return fail("gemm_tc: epilogue form not supported");
+  GemmTcPlan* plan = static_cast<GemmTcPlan*>(storage);
+  std::memset(plan, 0, sizeof(GemmTcPlan));
+  GemmParams& p = plan->params;
+  const char* why = "";
+  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why)) return fail(why);
+  p.M = M;
+  p.num_kb = (Kp + p.BK - 1) / p.BK;
+  p.m_tiles = (M + kBlockM - 1) / kBlockM;
+  p.a_tx_bytes = static_cast<uint32_t>(kBlockM) * p.BK;
+  const uint64_t adims[2] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(M)};
+  const uint32_t abox[2] = {static_cast<uint32_t>(p.BK), kBlockM};
+  bool ok = encode_u8(&plan->map_a, A, 2, adims, abox, nullptr, swizzle_of(p.BK));
+  if (ok && p.store_span) {
+    const uint64_t ddims[2] = {static_cast<uint64_t>(ldd), static_cast<uint64_t>(M)};
+    const uint32_t dbox[2] = {static_cast<uint32_t>(p.store_span), kBlockM};
+    ok = encode_u8(&plan->map_d, D, 2, ddims, dbox, nullptr, swizzle_of(p.store_span));
+  }
+  if (!ok) return fail("gemm_tc: cuTensorMapEncodeTiled failed");
+  set_grid(plan);
+  return plan;
+}
+
 void gemm_tc_plan_destroy(GemmTcPlan* p) { delete p; }
 
 cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {

@@ -123,6 +123,12 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
 // zero point of 0 or no padding (no border correction in the epilogue).
 GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* B, const ConvGeom& g, int Np, void* D,
                                      const ContractEpilogue& e, int* status, char* err, size_t err_len);
+// The plain-GEMM plan built inside caller-provided storage (gemm_tc_plan_bytes() bytes, 64-byte aligned)
+// instead of on the heap; not to be passed to gemm_tc_plan_destroy.
+size_t gemm_tc_plan_bytes(void);
+GemmTcPlan* gemm_tc_plan_build_in(void* storage, size_t storage_bytes, const void* A, int a_signed, const int8_t* B, int M,
+                                  int Np, int Kp, void* D, int ldd, const ContractEpilogue& e, int* status, char* err,
+                                  size_t err_len);
 void gemm_tc_plan_destroy(GemmTcPlan* p);
 cudaError_t gemm_tc_launch(const GemmTcPlan* p, cudaStream_t s);
 // 1 when this build and device can run the tensor-core path.
