@@ -36,8 +36,6 @@ sys.path.insert(0, os.path.join(ROOT, "tim-vx_b200"))
 
 SAMPLES_LIB = os.path.join(ROOT, "tim-vx_b200", "samples", "libb2vx_samples.so")
 SAMPLES_ORACLE_LIB = os.path.join(ROOT, "oracle", "_build", "libb2vx_samples_oracle.so")
-METRIC = "resnet50_int8_images_per_sec"
-UNIT = "images/s"
 
 
 def load_samples(path):
@@ -126,6 +124,105 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+
+class NetWorkload:
+    """A sample network (tim-vx_b200/samples) built through the tim::vx C++ API."""
+
+    def __init__(self, lib_path, name, batch, seed, device):
+        self.lib = load_samples(lib_path)
+        self.net = self.lib.b2vx_net_create(name.encode(), batch, seed, device)
+        assert self.net, "network creation failed"
+        self.in_bytes = self.lib.b2vx_net_input_bytes(self.net)
+        self.out_bytes = self.lib.b2vx_net_output_bytes(self.net)
+        self.units = batch
+        macs = self.lib.b2vx_net_macs_per_image(self.net)
+        self.ops = 2 * macs * batch
+        self.metric, self.unit = "%s_int8_images_per_sec" % name, "images/s"
+        self.scale = 1.0        # metric units per processed unit
+        self.describe = {"resnet50": "resnet50 v1.5 int8, 224x224x3 uint8 input, batch %d per GPU, per-channel int8 weights",
+                         "mobilenetv2": "mobilenetv2-1.0 uint8 asymmetric, 224x224x3 input, batch %d per GPU",
+                         "lenet": "lenet-5 uint8 asymmetric, 28x28x1 input, batch %d per GPU"}.get(name, name + " batch %d") % batch
+
+    def graph_handle(self):
+        return C.c_void_p(self.lib.b2vx_net_graph_handle(self.net))
+
+    def synthetic_input(self, seed, ptr):
+        self.lib.b2vx_net_synthetic_input(self.net, seed, C.c_void_p(ptr))
+
+    def set_input(self, ptr):
+        assert self.lib.b2vx_net_set_input(self.net, C.c_void_p(ptr)) == 0
+
+    def run(self):
+        assert self.lib.b2vx_net_run(self.net) == 0
+
+    def get_output(self, ptr):
+        assert self.lib.b2vx_net_get_output(self.net, C.c_void_p(ptr)) == 0
+
+    def close(self):
+        self.lib.b2vx_net_destroy(self.net)
+
+
+class OpWorkload:
+    """One operator (tim-vx_b200/opworkloads.py) built through the b2vx C ABI."""
+
+    def __init__(self, lib_path, spec, batch, seed, device):
+        import numpy as np
+        import pyb2vx as B
+        import opworkloads
+        self.B = B
+        self.g = B.Graph(B.load(lib_path), device)
+        rng = np.random.default_rng(seed)
+        self.w = opworkloads.build(spec, batch, self.g, rng)
+        self.g.compile()
+        self.in_sizes = [a.nbytes for _, a in self.w["inputs"]]
+        self.in_bytes = sum(self.in_sizes)
+        self.out_sizes = [int(np.prod(self.g.shape(t))) for t in self.w["outputs"]]
+        self.out_bytes = sum(self.out_sizes)
+        self.units = self.w["units"]
+        self.ops = self.w["ops"]
+        kind = spec.split(":")[0]
+        if kind == "add":
+            self.metric, self.unit, self.scale = "quantized_add_gbytes_per_sec", "GB/s", 3.0 / 1e9
+        else:
+            self.metric = "conv2d_int8_tops" if kind == "conv" else "fullyconnected_int8_tops"
+            self.unit, self.scale = "TOP/s", self.ops / self.units / 1e12
+        self.describe = self.w["name"]
+
+    def graph_handle(self):
+        return self.g.g
+
+    def synthetic_input(self, seed, ptr):
+        off = 0
+        for (_, a), n in zip(self.w["inputs"], self.in_sizes):
+            C.memmove(ptr + off, a.ctypes.data, n)
+            off += n
+
+    def set_input(self, ptr):
+        off = 0
+        for (t, _), n in zip(self.w["inputs"], self.in_sizes):
+            self.g.write_ptr(t, ptr + off, n)
+            off += n
+
+    def run(self):
+        self.g.run()
+
+    def get_output(self, ptr):
+        off = 0
+        for t, n in zip(self.w["outputs"], self.out_sizes):
+            self.g.read_ptr(t, ptr + off, n)
+            off += n
+
+    def close(self):
+        self.g.close()
+
+
+def make_workload(args, oracle, batch, device):
+    if ":" in args.workload:
+        import pyb2vx as B
+        return OpWorkload(B.ORACLE_LIB if oracle else B.PRODUCT_LIB, args.workload, batch, args.seed, device)
+    return NetWorkload(SAMPLES_ORACLE_LIB if oracle else SAMPLES_LIB, args.workload, batch, args.seed, device)
+
+
 def run_reference(args):
     """Reference arm: the CPU oracle (a port of the path; see module docstring) on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -133,43 +230,46 @@ def run_reference(args):
         return 0
     if not os.path.exists(SAMPLES_ORACLE_LIB):
         subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle")], stdout=subprocess.DEVNULL)
-    lib = load_samples(SAMPLES_ORACLE_LIB)
     import numpy as np
     sample = args.cpu_batch
-    net = lib.b2vx_net_create(args.net.encode(), sample, args.seed, 0)
-    assert net, "oracle network creation failed"
-    x = np.empty(lib.b2vx_net_input_bytes(net), np.uint8)
-    y = np.empty(lib.b2vx_net_output_bytes(net), np.uint8)
-    lib.b2vx_net_synthetic_input(net, args.seed, x.ctypes.data)
+    if ":" in args.workload:
+        import opworkloads
+        args.workload, sample_note = opworkloads.cpu_sample(args.workload)
+    else:
+        sample_note = "%d images per step (bounded sample of the %d-image batch)" % (sample, args.batch)
+    wl = make_workload(args, True, sample, 0)
+    x = np.empty(wl.in_bytes, np.uint8)
+    y = np.empty(wl.out_bytes, np.uint8)
+    wl.synthetic_input(args.seed, x.ctypes.data)
     for _ in range(args.warmup):
-        lib.b2vx_net_set_input(net, x.ctypes.data)
-        assert lib.b2vx_net_run(net) == 0
+        wl.set_input(x.ctypes.data)
+        wl.run()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        lib.b2vx_net_set_input(net, x.ctypes.data)
-        assert lib.b2vx_net_run(net) == 0
-        lib.b2vx_net_get_output(net, y.ctypes.data)
+        wl.set_input(x.ctypes.data)
+        wl.run()
+        wl.get_output(y.ctypes.data)
     dt = time.perf_counter() - t0
-    value = sample * args.steps / dt
+    value = wl.units * args.steps / dt * wl.scale
     cores = C.CDLL(os.path.join(ROOT, "oracle", "_build", "liboracle_ops.so")).orc_num_threads()
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": "%s batch %d per step on host cores (bounded sample of the 64-image batch)" % (args.net, sample)},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "%d images per step x %d steps" % (sample, args.steps)},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": "%s; on host cores: %s" % (wl.describe, sample_note)},
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": cores, "kind": "port",
+                         "sample": "%s x %d steps" % (sample_note, args.steps)},
+        "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
-    lib.b2vx_net_destroy(net)
+    wl.close()
     return 0
 
 
 def cpu_baseline_subprocess(args):
     """Runs the oracle in a child process (both sample libraries define the same symbols)."""
-    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--net", args.net, "--steps", "2",
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--workload", args.workload, "--batch", str(args.batch), "--steps", "2",
            "--warmup", "1", "--cpu-batch", str(args.cpu_batch), "--seed", str(args.seed)]
     env = dict(os.environ)
     for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
@@ -180,8 +280,8 @@ def cpu_baseline_subprocess(args):
             if line.startswith("{"):
                 return json.loads(line)["cpu_baseline"]
     except Exception as e:   # noqa: BLE001 - reported in the JSON line instead of failing the bench
-        return {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %s" % e}
-    return {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "no output"}
+        return {"value": None, "unit": None, "cores": 0, "kind": "port", "sample": "failed: %s" % e}
+    return {"value": None, "unit": None, "cores": 0, "kind": "port", "sample": "no output: %s" % out.stderr[-200:]}
 
 
 def main():
@@ -190,17 +290,22 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--net", default="resnet50")
+    ap.add_argument("--workload", default=None,
+                    help="resnet50 (default), mobilenetv2, lenet, or one operator: conv:k:cin:cout:hw:stride, "
+                         "gemm:m:n:k, add:elements (tim-vx_b200/opworkloads.py)")
+    ap.add_argument("--net", default="resnet50", help="older spelling of --workload for the networks")
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--cpu-batch", type=int, default=4, help="images per step of the CPU baseline sample")
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer loop (profiler captures)")
     ap.add_argument("--profile-iters", type=int, default=3)
     args = ap.parse_args()
+    if args.workload is None:
+        args.workload = args.net
     if args.impl == "reference":
         return run_reference(args)
 
-    import numpy as np
     import torch
     import pyb2vx as B
 
@@ -213,20 +318,17 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     assert os.path.exists(SAMPLES_LIB), "libb2vx_samples.so is not built: python -c 'import __graft_entry__ as g; g.build()'"
-    slib = load_samples(SAMPLES_LIB)
     blib = B.load(B.PRODUCT_LIB)
-
-    net = slib.b2vx_net_create(args.net.encode(), args.batch, args.seed, local_rank)
-    assert net, "network creation failed"
-    graph = C.c_void_p(slib.b2vx_net_graph_handle(net))
+    wl = make_workload(args, False, args.batch, local_rank)
+    graph = wl.graph_handle()
     stream = torch.cuda.Stream()   # a non-default stream: the library takes NULL to mean "its own"
     torch.cuda.set_stream(stream)
     assert blib.b2vx_graph_set_stream(graph, C.c_void_p(stream.cuda_stream)) == 0
-    in_bytes, out_bytes = slib.b2vx_net_input_bytes(net), slib.b2vx_net_output_bytes(net)
+    in_bytes, out_bytes = wl.in_bytes, wl.out_bytes
     host_in = torch.empty(in_bytes, dtype=torch.uint8).pin_memory()
     host_out = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
-    slib.b2vx_net_synthetic_input(net, args.seed + rank, C.c_void_p(host_in.data_ptr()))
-    assert slib.b2vx_net_set_input(net, C.c_void_p(host_in.data_ptr())) == 0
+    wl.synthetic_input(args.seed + rank, host_in.data_ptr())
+    wl.set_input(host_in.data_ptr())
 
     def barrier():
         torch.cuda.synchronize()
@@ -236,6 +338,11 @@ def main():
 
     n_kernels = C.c_uint32()
     blib.b2vx_graph_kernel_count(graph, C.byref(n_kernels))
+    # A pass that touches less than the L2 (126 MB) would be served from cache on repeat: write a
+    # buffer larger than L2 between timed passes and time each pass with its own pair of events.
+    flush = None
+    if in_bytes + out_bytes < 256 * 1024 * 1024 and ":" in args.workload:
+        flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
 
     # ---- device-resident timing
     for _ in range(args.warmup):
@@ -246,25 +353,37 @@ def main():
         sampler.start()
         time.sleep(0.3)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        assert blib.b2vx_graph_run_async(graph) == 0
-    e1.record(stream)
-    barrier()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            assert blib.b2vx_graph_run_async(graph) == 0
+        e1.record(stream)
+        barrier()
+        elapsed = e0.elapsed_time(e1)
+    else:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in evs:
+            flush.fill_(1)
+            a.record(stream)
+            assert blib.b2vx_graph_run_async(graph) == 0
+            b.record(stream)
+        barrier()
+        elapsed = sum(a.elapsed_time(b) for a, b in evs)
     assert blib.b2vx_graph_sync(graph) == 0, "a kernel reported a device-side timeout"
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    # ---- end to end through the tim::vx calls, host buffers pinned
-    for _ in range(2):
-        slib.b2vx_net_set_input(net, C.c_void_p(host_in.data_ptr()))
-        slib.b2vx_net_run(net)
-        slib.b2vx_net_get_output(net, C.c_void_p(host_out.data_ptr()))
+    ms = torch.tensor([elapsed], device="cuda")
+    # ---- end to end through the public calls, host buffers pinned
+    e2e_steps = 0 if args.no_e2e else args.steps
+    for _ in range(2 if e2e_steps else 0):
+        wl.set_input(host_in.data_ptr())
+        wl.run()
+        wl.get_output(host_out.data_ptr())
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        assert slib.b2vx_net_set_input(net, C.c_void_p(host_in.data_ptr())) == 0
-        assert slib.b2vx_net_run(net) == 0
-        assert slib.b2vx_net_get_output(net, C.c_void_p(host_out.data_ptr())) == 0
+    for _ in range(e2e_steps):
+        wl.set_input(host_in.data_ptr())
+        wl.run()
+        wl.get_output(host_out.data_ptr())
     torch.cuda.synchronize()
     e2e_ms = torch.tensor([1e3 * (time.perf_counter() - t0)], device="cuda")
     clocks = sampler.stop() if rank == 0 else None
@@ -274,9 +393,9 @@ def main():
     ms, e2e_ms = float(ms.item()), float(e2e_ms.item())
 
     if rank == 0:
-        images = args.batch * world * args.steps
-        value = images / (ms / 1e3)
-        e2e_value = images / (e2e_ms / 1e3)
+        units = wl.units * world * args.steps
+        value = units / (ms / 1e3) * wl.scale
+        e2e_value = units / (e2e_ms / 1e3) * wl.scale if e2e_steps else None
         # ---- roofline of the dominant kernel, per-kernel CUDA events measured live
         assert blib.b2vx_graph_profile(graph, args.profile_iters) == 0
         per = {}
@@ -309,19 +428,20 @@ def main():
                      "per_kernel_ms": {n: round(d["ms"], 4) for n, d in sorted(per.items(), key=lambda kv: -kv[1]["ms"])}})
         cpu = None if (args.no_cpu_baseline or world > 1) else cpu_baseline_subprocess(args)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u8", "data": "synthetic",
-            "config": {"workload": "%s v1.5 int8, 224x224x3 uint8 input, batch %d per GPU, per-channel int8 weights" % (args.net, args.batch),
-                       "parallelism": "batch-sharded replicas, no collective", "global_batch": args.batch * world,
-                       "l2": "per-step working set (about 1.4 GB of activations) exceeds the 126 MB L2"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
-                    "ms_per_step": e2e_ms / args.steps},
+            "config": {"workload": wl.describe,
+                       "parallelism": "batch-sharded replicas, no collective", "units_per_step": wl.units * world,
+                       "l2": ("a 192 MB buffer is rewritten between timed passes (L2 flush); each pass has its own events"
+                              if flush is not None else "the per-step working set exceeds the 126 MB L2")},
+            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
+                    "ms_per_step": e2e_ms / args.steps if e2e_steps else None},
             "gpu_launches": n_kernels.value * args.steps,
             "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
         }
         print(json.dumps(line))
-    slib.b2vx_net_destroy(net)
+    wl.close()
     if world > 1:
         dist.destroy_process_group()
     return 0

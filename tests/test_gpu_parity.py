@@ -89,6 +89,15 @@ CONV_CASES = {
     "explicit_pad_asym": G.conv2d_q(12, 12, 16, 1, 3, 3, 16, stride=(2, 2), pad_type=B.PAD_AUTO, pad=(0, 1, 0, 1)),
     "no_bias": G.conv2d_q(8, 8, 16, 1, 3, 3, 16, bias=False),
     "single_pixel": G.conv2d_q(1, 1, 64, 1, 1, 1, 16),
+    # non-zero input zero point with padding: border classes in the tensor-core epilogue
+    "zp_pad_5x5_s2": G.conv2d_q(23, 19, 32, 2, 5, 5, 48, stride=(2, 2)),
+    "zp_pad_dil3": G.conv2d_q(20, 20, 16, 1, 3, 3, 16, dilation=(3, 3)),
+    "zp_pad_window_wider_than_input": G.conv2d_q(3, 2, 16, 2, 5, 5, 16),
+    # uint8 weights with a zero point other than 128: the ones row / S column, alone and with borders,
+    # over several N tiles
+    "u8_w_oc300": G.conv2d_q(9, 9, 32, 2, 1, 1, 300, w_kind="u8"),
+    "u8_w_3x3_oc272_pad": G.conv2d_q(12, 10, 48, 1, 3, 3, 272, w_kind="u8"),
+    "u8_w_stem": G.conv2d_q(30, 30, 3, 2, 3, 3, 32, stride=(2, 2), w_kind="u8", in_q=(0.02, 114)),
 }
 
 
@@ -100,6 +109,20 @@ def test_conv2d_matches_oracle(oracle_lib, product_lib, conv_kernel, name):
     names = [k["name"] for k in kernels]
     if conv_kernel == "cudacore":
         assert not any(n.startswith("gemm_i8_tc") for n in names)
+
+
+def test_padded_conv_with_zero_point_is_implicit(product_lib):
+    """The benchmark's 3x3 SAME convolution (input zero point 128) runs as an implicit GEMM: no im2col pass."""
+    os.environ.pop("B2VX_CONV_KERNEL", None)
+    _, kernels = G.run_case(product_lib, CONV_CASES["cfg2_3x3_n3"], seed=1)
+    names = [k["name"] for k in kernels]
+    assert "gemm_i8_tc(implicit)" in names and not any(n.startswith("im2col") for n in names), names
+
+
+def test_uint8_weight_zero_point_runs_on_tensor_cores(product_lib):
+    os.environ.pop("B2VX_CONV_KERNEL", None)
+    _, kernels = G.run_case(product_lib, CONV_CASES["u8_weights_1x1"], seed=1)
+    assert any(k["name"].startswith("gemm_i8_tc") for k in kernels), [k["name"] for k in kernels]
 
 
 def test_tensor_core_path_is_taken(product_lib):
@@ -176,6 +199,59 @@ def test_elementwise_matches_oracle(oracle_lib, product_lib, name):
     want, _ = G.run_case(oracle_lib, ELTWISE_CASES[name], seed=21)
     got, _ = G.run_case(product_lib, ELTWISE_CASES[name], seed=21)
     G.assert_same(want, got)
+
+
+ADD_QUANTS = {
+    # 0.4*i + 0.7*j: one sum in ten lands on a .5 fraction (the arithmetic kernel's exact path)
+    "many_ties": dict(qa=(0.02, 128), qb=(0.035, 117), qo=(0.05, 120)),
+    "irregular": dict(qa=(0.0213, 7), qb=(0.0347, 250), qo=(0.0512, 33)),
+    "coarse_out": dict(qa=(0.11, 100), qb=(0.003, 140), qo=(0.9, 128)),
+    "fine_out": dict(qa=(0.05, 120), qb=(0.07, 130), qo=(0.004, 128)),   # saturates most sums
+    "extreme": dict(qa=(900.0, 128), qb=(0.5, 3), qo=(0.0001, 10)),      # beyond the fast rounding's range
+}
+
+
+@pytest.mark.parametrize("kernel", ["lut", "alu"])
+@pytest.mark.parametrize("quant", sorted(ADD_QUANTS))
+def test_add_kernels_match_oracle(oracle_lib, product_lib, kernel, quant):
+    """Both quantized-Add kernels (table in shared memory; packed float arithmetic) on every pair of
+    input bytes, several times over so that all lanes and both loop iterations are exercised."""
+    def build(g, rng):
+        n = 65536 * 4
+        q = ADD_QUANTS[quant]
+        a = g.tensor(B.DT_UINT8, [n], B.ATTR_INPUT, scale=q["qa"][0], zero_point=q["qa"][1])
+        b = g.tensor(B.DT_UINT8, [n], B.ATTR_INPUT, scale=q["qb"][0], zero_point=q["qb"][1])
+        y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=q["qo"][0], zero_point=q["qo"][1])
+        g.add(a, b, y)
+        i = (np.arange(n) * 40503) % 65536           # every (a, b) pair, scattered over lanes
+        return [(a, (i >> 8).astype(np.uint8)), (b, (i & 255).astype(np.uint8))], [y]
+    want, _ = G.run_case(oracle_lib, build, seed=1)
+    os.environ["B2VX_ADD_KERNEL"] = kernel
+    try:
+        got, kernels = G.run_case(product_lib, build, seed=1)
+    finally:
+        os.environ.pop("B2VX_ADD_KERNEL", None)
+    assert [k["name"] for k in kernels] == ["add_q_lut" if kernel == "lut" else "add_q"]
+    G.assert_same(want, got)
+
+
+def test_add_int8_matches_oracle(oracle_lib, product_lib):
+    def build(g, rng):
+        n = 65536
+        a = g.tensor(B.DT_INT8, [n], B.ATTR_INPUT, scale=0.03, zero_point=-5)
+        b = g.tensor(B.DT_INT8, [n], B.ATTR_INPUT, scale=0.021, zero_point=17)
+        y = g.tensor(B.DT_INT8, [], B.ATTR_OUTPUT, scale=0.04, zero_point=-20)
+        g.add(a, b, y)
+        i = np.arange(n)
+        return [(a, (i >> 8).astype(np.uint8).view(np.int8)), (b, (i & 255).astype(np.uint8).view(np.int8))], [y]
+    want, _ = G.run_case(oracle_lib, build, seed=1)
+    for kernel in ("lut", "alu"):
+        os.environ["B2VX_ADD_KERNEL"] = kernel
+        try:
+            got, _ = G.run_case(product_lib, build, seed=1)
+        finally:
+            os.environ.pop("B2VX_ADD_KERNEL", None)
+        G.assert_same(want, got)
 
 
 def test_softmax_matches_oracle(oracle_lib, product_lib):

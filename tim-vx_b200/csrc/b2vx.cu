@@ -116,6 +116,7 @@ struct b2vx_graph {
   int* h_status = nullptr;
   bool compiled = false;
   bool use_tc = false;
+  int add_mode = 0;          // quantized Add: 0 choose by size, 1 table kernel, 2 arithmetic kernel
   // the whole launch plan captured once as a CUDA graph; replays cost one launch on the host
   cudaGraphExec_t exec = nullptr;
   bool capture_failed = false;
@@ -398,11 +399,13 @@ struct PackedContraction {
 // with the zero point that still has to be subtracted from it: u8 weights are
 // shifted by 128 into int8 (dz = zw-128), s8 weights are kept (dz = zw).
 // K index = tap*Cs + ic, or ic*taps + tap when channel_major (the kernel tensor's own order,
-// used with the WHCN im2col); rows are output channels (+ the all-ones row at index
-// rows_before_ones when some dz != 0 and with_ones_row is set).
+// used with the WHCN im2col).  Rows come in n_tiles tiles of tile_rows rows: output channel oc is row
+// (oc / tile_data) * tile_rows + oc % tile_data; when some dz != 0 and tile_rows > tile_data, row
+// tile_data of every tile is the all-ones row (its dot product with an input row is S).
 void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* bias, int kw, int kh, int C, int Cs,
-                      int Kp, int Oc, int Ocp, int rows, bool channel_major, bool with_ones_row,
+                      int Kp, int Oc, int Ocp, int n_tiles, int tile_data, int tile_rows, bool channel_major,
                       PackedContraction* out) {
+  const int rows = n_tiles * tile_rows;
   const int taps = kw * kh;
   const bool w_u8 = w.d.dtype == B2VX_DT_UINT8;
   const bool per_ch = w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL;
@@ -425,11 +428,10 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
     if (dz != 0) out->need_s = true;
     out->acc_scale[oc] = sx * sw;
   }
-  const int total_rows = rows + ((with_ones_row && out->need_s) ? 1 : 0);
-  out->w8.assign(static_cast<size_t>(total_rows) * Kp, 0);
+  out->w8.assign(static_cast<size_t>(rows) * Kp, 0);
   for (int oc = 0; oc < Oc; ++oc) {
     std::fill(tapsum.begin(), tapsum.end(), 0);
-    int8_t* row = out->w8.data() + static_cast<size_t>(oc) * Kp;
+    int8_t* row = out->w8.data() + (static_cast<size_t>(oc / tile_data) * tile_rows + oc % tile_data) * Kp;
     for (int ic = 0; ic < C; ++ic) {
       for (int t = 0; t < taps; ++t) {
         const size_t src = (static_cast<size_t>(oc) * C + ic) * taps + t;   // WHIcOc, W fastest: tap = ky*kw + kx
@@ -448,10 +450,12 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
     }
     out->bias_full[oc] = static_cast<int32_t>((b ? b[oc] : 0) + all);
   }
-  if (with_ones_row && out->need_s) {
-    int8_t* ones = out->w8.data() + static_cast<size_t>(rows) * Kp;
-    for (int t = 0; t < taps; ++t)
-      for (int ic = 0; ic < C; ++ic) ones[channel_major ? static_cast<size_t>(ic) * taps + t : static_cast<size_t>(t) * Cs + ic] = 1;
+  if (tile_rows > tile_data && out->need_s) {
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      int8_t* ones = out->w8.data() + (static_cast<size_t>(tile) * tile_rows + tile_data) * Kp;
+      for (int t = 0; t < taps; ++t)
+        for (int ic = 0; ic < C; ++ic) ones[channel_major ? static_cast<size_t>(ic) * taps + t : static_cast<size_t>(t) * Cs + ic] = 1;
+    }
   }
 }
 
@@ -505,20 +509,27 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
   const int taps = kw * kh;
   const bool x_signed = x.d.dtype == B2VX_DT_INT8;
   const bool has_pad = pad[0] || pad[1] || pad[2] || pad[3];
-  bool any_dz = false;
+  bool any_dz = false, dz_is_uniform = true;
+  int dz_value = 0;
   {
     const bool w_u8 = w.d.dtype == B2VX_DT_UINT8;
     if (w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL) {
-      for (int32_t z : w.zps) any_dz = any_dz || z != 0;
+      for (size_t i = 0; i < w.zps.size(); ++i) {
+        const int dz = w_u8 ? w.zps[i] - 128 : w.zps[i];
+        any_dz = any_dz || dz != 0;
+        if (i == 0) dz_value = dz;
+        else dz_is_uniform = dz_is_uniform && dz == dz_value;
+      }
     } else {
-      any_dz = (w_u8 ? w.zp() - 128 : w.zp()) != 0;
+      dz_value = w_u8 ? w.zp() - 128 : w.zp();
+      any_dz = dz_value != 0;
     }
   }
   // The im2col matrix is the input itself when the window is 1x1/stride 1/no
   // padding, or when the window covers the whole (unpadded) input.
   const bool identity_1x1 = kw == 1 && kh == 1 && geo.sx == 1 && geo.sy == 1 && !has_pad;
   const bool identity_full = kw == x.W && kh == x.H && !has_pad && y.W == 1 && y.H == 1 && geo.dx == 1 && geo.dy == 1;
-  const bool tc_ok = g->use_tc && !any_dz;
+  const bool tc_ok = g->use_tc && (!any_dz || dz_is_uniform);   // one leftover weight zero point: the S column handles it
 
   ContractEpilogue ep;
   std::memset(&ep, 0, sizeof(ep));
@@ -528,14 +539,42 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
   if (tc_ok) {
     // Four ways to present the input to the GEMM kernel:
     //   identity  the channels-last input already is the A matrix (1x1/s1, or a window = whole input);
-    //   implicit  filter taps fetched as shifted 4-D TMA boxes, zero fill as padding (needs zx == 0 or no pad);
+    //   implicit  filter taps fetched as shifted 4-D TMA boxes, zero fill as padding; with a non-zero input
+    //             zero point the border pixels get a per-class correction in the epilogue;
     //   whcn      first layers with < 16 channels: im2col straight from the WHCN graph input, K = (c,ky,kx);
     //   im2col    everything else: explicit matrix in scratch memory, padding filled with zx.
     enum { IDENTITY, IMPLICIT, WHCN, IM2COL } mode;
     static const bool allow_strided = [] { const char* e = std::getenv("B2VX_IMPLICIT_STRIDED"); return !(e && e[0] == '0'); }();
     const bool strided = geo.sx != 1 || geo.sy != 1;
+    // Border classes of an implicit convolution: output rows (columns) grouped by which ky (kx) fall
+    // outside the input.  Few classes exist (3 x 3 for a 3x3/stride-1 SAME convolution).
+    std::vector<uint8_t> row_class(y.H, 0), col_class(y.W, 0);
+    std::vector<uint32_t> row_masks(1, 0u), col_masks(1, 0u);   // class id -> bitmask of out-of-bounds taps
+    bool classes_ok = kh <= 32 && kw <= 32;
+    const bool need_border = x.zp() != 0 && has_pad;
+    if (need_border && classes_ok) {
+      auto classify = [&](int out_n, int in_n, int k, int stride_, int dil_, int pad0, std::vector<uint8_t>& cls,
+                          std::vector<uint32_t>& masks) {
+        for (int o = 0; o < out_n; ++o) {
+          uint32_t m = 0;
+          for (int t = 0; t < k; ++t) {
+            const int i = o * stride_ - pad0 + t * dil_;
+            if (i < 0 || i >= in_n) m |= 1u << t;
+          }
+          size_t id = 0;
+          while (id < masks.size() && masks[id] != m) ++id;
+          if (id == masks.size()) masks.push_back(m);
+          if (id > 255) return false;
+          cls[o] = static_cast<uint8_t>(id);
+        }
+        return true;
+      };
+      classes_ok = classify(y.H, x.H, kh, geo.sy, geo.dy, geo.pt, row_class, row_masks) &&
+                   classify(y.W, x.W, kw, geo.sx, geo.dx, geo.pl, col_class, col_masks) &&
+                   row_masks.size() * col_masks.size() <= 256;
+    }
     if (identity_1x1 || identity_full) mode = IDENTITY;
-    else if (x.C >= 16 && (x.zp() == 0 || !has_pad) && (!strided || allow_strided)) mode = IMPLICIT;
+    else if (x.C >= 16 && (!need_border || classes_ok) && (!strided || allow_strided)) mode = IMPLICIT;
     else if (x.C < 16 && (x.d.attr & B2VX_ATTR_INPUT) && x.d_io != nullptr &&
              static_cast<size_t>(x.C) * kh * ((geo.Wo - 1) * geo.sx + (kw - 1) * geo.dx + 1) + 4u * round_up(taps * x.C, 16) <= 40u * 1024u)
       mode = WHCN;   // the staging rows of one output row fit in shared memory
@@ -548,10 +587,33 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     else if (mode == IMPLICIT) { Cs = x.Cp; Kp = taps * x.Cp; M = static_cast<int>(P); A = cl_in(x); }
     else if (mode == WHCN) { Cs = x.C; Kp = round_up(taps * x.C, 16); M = static_cast<int>(P); }
     else { Cs = x.C < 16 ? x.C : x.Cp; Kp = round_up(taps * Cs, 16); M = static_cast<int>(P); }
-    const int n_tiles = (y.Cp + 255) / 256;
-    const int BN = round_up((y.Cp + n_tiles - 1) / n_tiles, 16);
-    const int Np = n_tiles * BN;
-    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, Np, mode == WHCN, false, &pk);
+    const GemmTcTiling tiling = gemm_tc_choose_tiling(M, y.Cp, Kp, any_dz ? 1 : 0);
+    const int Np = tiling.n_tiles * tiling.rows;
+    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, tiling.n_tiles, tiling.data, tiling.rows, mode == WHCN, &pk);
+    ep.dz_uniform = any_dz ? dz_value : 0;
+    if (mode == IMPLICIT && need_border) {
+      // correction of class (r, c) = minus the folded contribution of every tap that is out of bounds there
+      const size_t ncls = row_masks.size() * col_masks.size();
+      std::vector<int32_t> corr(ncls * y.Cp, 0);
+      for (size_t r = 0; r < row_masks.size(); ++r)
+        for (size_t c = 0; c < col_masks.size(); ++c)
+          for (int ky = 0; ky < kh; ++ky)
+            for (int kx = 0; kx < kw; ++kx) {
+              if (!((row_masks[r] >> ky) & 1u) && !((col_masks[c] >> kx) & 1u)) continue;
+              const int32_t* tc = pk.tapc.data() + static_cast<size_t>(ky * kw + kx) * y.Cp;
+              int32_t* dst = corr.data() + (r * col_masks.size() + c) * y.Cp;
+              for (int oc = 0; oc < y.Cp; ++oc) dst[oc] -= tc[oc];
+            }
+      int32_t* dcorr = nullptr; uint8_t *drow = nullptr, *dcol = nullptr;
+      b2vx_status stc = upload(g, corr, &dcorr);
+      if (stc == B2VX_OK) stc = upload(g, row_class, &drow);
+      if (stc == B2VX_OK) stc = upload(g, col_class, &dcol);
+      if (stc != B2VX_OK) return stc;
+      ep.border_corr = dcorr;
+      ep.row_class = drow;
+      ep.col_class = dcol;
+      ep.n_col_classes = static_cast<int>(col_masks.size());
+    }
     int8_t* dw8 = nullptr; int32_t* dbias = nullptr; float* dscale = nullptr;
     b2vx_status st = upload(g, pk.w8, &dw8);
     if (st == B2VX_OK) st = upload(g, pk.bias_full, &dbias);
@@ -559,6 +621,16 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     if (st != B2VX_OK) return st;
     ep.bias_full = dbias;
     ep.acc_scale = dscale;
+    {
+      // largest |acc * acc_scale / out scale| any input can produce: decides whether the epilogue may
+      // use its fast rounding (valid below 2^21)
+      double bmax = 0.0, smax = 0.0;
+      for (int32_t b : pk.bias_full) bmax = std::max(bmax, std::fabs(static_cast<double>(b)));
+      for (float sc : pk.acc_scale) smax = std::max(smax, std::fabs(static_cast<double>(sc)));
+      // (twice the raw dot product's range: the S term of a weight zero point and the border corrections stay inside it)
+      const double tmax = (2.0 * static_cast<double>(Kp) * 255.0 * 128.0 + bmax) * smax / std::fabs(static_cast<double>(ep.out.scale));
+      ep.exact_only = !(tmax < 2097152.0);
+    }
     if (need_im2col) {
       const size_t need = static_cast<size_t>(M) * Kp;
       g->scratch_bytes = std::max(g->scratch_bytes, need);
@@ -596,10 +668,10 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       char err[160] = {0};
       GemmTcPlan* pl;
       if (implicit) {
-        pl = gemm_tc_conv_plan_create(A, x_signed, dw8, geo, Np, ycl, ep, g->d_status, err, sizeof(err));
+        pl = gemm_tc_conv_plan_create(A, x_signed, dw8, geo, Np, ycl, ep, g->d_status, err, sizeof(err), &tiling);
       } else {
         const void* Aptr = need_im2col ? g->scratch : A;
-        pl = gemm_tc_plan_create(Aptr, x_signed, dw8, M, Np, Kp, Oc, ycl, ldd, y_signed, ep, g->d_status, err, sizeof(err));
+        pl = gemm_tc_plan_create(Aptr, x_signed, dw8, M, Np, Kp, Oc, ycl, ldd, y_signed, ep, g->d_status, err, sizeof(err), &tiling);
       }
       if (!pl) return fail(g, B2VX_UNSUPPORTED, lbl + ": " + err);
       g->gemm_plans.push_back(pl);
@@ -616,7 +688,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
 
   // CUDA-core path: K = tap*Cp + c, out-of-bounds taps are skipped and corrected per tap.
   const int Kp = taps * x.Cp;
-  pack_contraction(x, w, bias, kw, kh, x.C, x.Cp, Kp, y.C, y.Cp, y.Cp, false, true, &pk);
+  pack_contraction(x, w, bias, kw, kh, x.C, x.Cp, Kp, y.C, y.Cp, 1, y.Cp, y.Cp + 1, false, &pk);
   int8_t* dw8 = nullptr; int32_t *dbias = nullptr, *ddz = nullptr, *dtapc = nullptr; float* dscale = nullptr;
   b2vx_status st = upload(g, pk.w8, &dw8);
   if (st == B2VX_OK) st = upload(g, pk.bias_full, &dbias);
@@ -711,6 +783,35 @@ b2vx_status plan_conv(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   void* ycl = y.d_cl;
   const int xs = x.d.dtype == B2VX_DT_INT8, zx = x.zp(), mult = c.multiplier;
   const OutQuant oq = out_quant(y);
+  if (mult == 1 && taps <= 64) {
+    // dp2a kernel: weights as positioned 16-bit halves, zero-point term folded into the bias
+    std::vector<uint32_t> wtab(static_cast<size_t>(taps) * y.Cp, 0u);
+    std::vector<int32_t> bfull(y.Cp, 0);
+    const int zx_eff = zx + (xs ? 128 : 0);
+    double bmax = 0.0, smax = 0.0;
+    for (int oc = 0; oc < y.C; ++oc) {
+      int64_t wsum = 0;
+      for (int t = 0; t < taps; ++t) {
+        const int v = wd[static_cast<size_t>(t) * y.Cp + oc];
+        wsum += v;
+        wtab[static_cast<size_t>(t) * y.Cp + oc] = (static_cast<uint32_t>(v) & 0xFFFFu) << (16 * (oc & 1));
+      }
+      bfull[oc] = static_cast<int32_t>(bv[oc] - static_cast<int64_t>(zx_eff) * wsum);
+      bmax = std::max(bmax, std::fabs(static_cast<double>(bfull[oc])));
+      smax = std::max(smax, std::fabs(static_cast<double>(sc[oc])));
+    }
+    const double tmax = (static_cast<double>(taps) * 255.0 * 255.0 + bmax) * smax / std::fabs(static_cast<double>(oq.scale));
+    const int exact_only = !(tmax < 2097152.0);
+    uint32_t* dwt = nullptr; int32_t* dbf = nullptr;
+    st = upload(g, wtab, &dwt);
+    if (st == B2VX_OK) st = upload(g, bfull, &dbf);
+    if (st != B2VX_OK) return st;
+    Step s16;
+    s16.info = make_info("depthwise_q16", idx, 2 * macs, abytes);
+    s16.fn = [=](cudaStream_t st2) { launch_depthwise_q16(xcl, xs, zx, dwt, dbf, dsc, geo, oq, exact_only, ycl, st2); return cudaGetLastError(); };
+    g->steps.push_back(std::move(s16));
+    return B2VX_OK;
+  }
   Step s;
   s.info = make_info("depthwise_q", idx, 2 * macs, abytes);
   s.fn = [=](cudaStream_t st2) { launch_depthwise_q(xcl, xs, zx, dwd, db, dsc, mult, geo, oq, ycl, st2); return cudaGetLastError(); };
@@ -794,8 +895,29 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
     const int za = a.zp(), zb = b.zp();
     const OutQuant oq = out_quant(y);
     const size_t nel = y.cl_bytes;
-    s.info = make_info("add_q", idx, 0, abytes);
-    s.fn = [=](cudaStream_t st2) { launch_add_q(ap, as, sa, za, bp, bs, sb, zb, oq, ys, yp, nel, st2); return cudaGetLastError(); };
+    // B2VX_ADD_KERNEL=lut|alu forces one of the two kernels (read when the graph is created)
+    const bool use_lut = g->add_mode == 1 || (g->add_mode == 0 && nel >= (size_t(1) << 22));
+    if (use_lut) {
+      // every pair of input bytes through the reference's float sequence, once
+      std::vector<uint8_t> table(65536);
+      for (int ia = 0; ia < 256; ++ia) {
+        const int qa = as ? static_cast<int>(static_cast<int8_t>(ia)) : ia;
+        const float fa = (static_cast<float>(qa) - static_cast<float>(za)) * sa;
+        for (int ib = 0; ib < 256; ++ib) {
+          const int qb = bs ? static_cast<int>(static_cast<int8_t>(ib)) : ib;
+          const float fb = (static_cast<float>(qb) - static_cast<float>(zb)) * sb;
+          table[ia * 256 + (ib ^ ((ia & 31) << 2))] = static_cast<uint8_t>(host_requant(fa + fb, oq) & 0xFF);
+        }
+      }
+      uint8_t* dtab = nullptr;
+      const b2vx_status st = upload(g, table, &dtab);
+      if (st != B2VX_OK) return st;
+      s.info = make_info("add_q_lut", idx, 0, abytes);
+      s.fn = [=](cudaStream_t st2) { launch_add_q_lut(ap, bp, dtab, yp, nel, st2); return cudaGetLastError(); };
+    } else {
+      s.info = make_info("add_q", idx, 0, abytes);
+      s.fn = [=](cudaStream_t st2) { launch_add_q(ap, as, sa, za, bp, bs, sb, zb, oq, ys, yp, nel, st2); return cudaGetLastError(); };
+    }
   } else {
     return fail(g, B2VX_UNSUPPORTED, "add: operands must be all int8/uint8 or all float32");
   }
@@ -935,6 +1057,8 @@ b2vx_status b2vx_graph_create(b2vx_context* ctx, int32_t device_id, b2vx_graph**
   g->stream = g->own_stream;
   const char* k = std::getenv("B2VX_CONV_KERNEL");
   g->use_tc = gemm_tc_available() && !(k && std::strcmp(k, "simt") == 0);
+  const char* ak = std::getenv("B2VX_ADD_KERNEL");
+  g->add_mode = !ak ? 0 : (std::strcmp(ak, "lut") == 0 ? 1 : 2);
   const char* cg = std::getenv("B2VX_CUDA_GRAPH");
   g->use_cuda_graph = !(cg && cg[0] == '0');
   *out = g;

@@ -76,7 +76,8 @@ constexpr int kMinDynSmem = 120 * 1024;               // keeps two CTAs from sha
 
 struct GemmParams {
   int M, Ocp, ldd;
-  int BN, BK, n_tiles, m_tiles, num_kb, stages;
+  int BN, BK, n_tiles, m_tiles, num_kb, stages;   // BN: MMA N = weight rows per N tile
+  int BNd;                 // output channels per N tile (BN, or BN - 16 when the tile carries the ones row)
   int group;               // k-blocks per pipeline stage
   int tmem_cols;
   int acc_stride;          // TMEM columns between the two accumulator buffers (BN rounded up to 32)
@@ -98,6 +99,8 @@ struct GemmParams {
   // [128 rows][store_span bytes], 16-byte chunks XOR-swizzled the way the store's tensor map expects.
   // store_span == 0: BN is not a multiple of 32, threads store their 16-byte pieces directly.
   int store_span;
+  int dz;                  // weight zero point left after the shift into int8; != 0: column BNd of the accumulator is S
+  int exact_only;          // requantize with the exact sequence only (the fast form's range check failed)
 #ifdef B2VX_TC_TRACE
   long long* trace;        // clock64 stamps of CTA 0, [3 roles][64 iterations][2]
 #endif
@@ -219,7 +222,19 @@ __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, int (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_ld_32x1(uint32_t taddr, int& r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait1(int& r) { asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r) : : "memory"); }
+// The load is asynchronous: its destination registers are valid only after tcgen05.wait::ld.  The wait
+// names them as read-write operands so that the compiler orders every use of them after it.
+__device__ __forceinline__ void tc_ld_wait(int (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are one
 // swizzle span wide: start address, LBO = 1 (unused for swizzled K-major),
@@ -259,7 +274,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t sub_bytes = a_bytes + b_bytes;     // one k-block: whole swizzle atoms, see the host-side plan
   const uint32_t stage_bytes = sub_bytes * p.group;
   const uint32_t ring_bytes = (p.stages * stage_bytes + 1023u) & ~1023u;
-  const uint32_t staging_bytes = p.store_span ? static_cast<uint32_t>(kBlockM) * p.BN : 0u;   // per buffer, multiple of 4096
+  const uint32_t staging_bytes = p.store_span ? static_cast<uint32_t>(kBlockM) * p.BNd : 0u;   // per buffer, multiple of 4096
   uint8_t* staging = tiles + ring_bytes;
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(staging + 2 * staging_bytes);
   volatile int* abort_flag = &hdr->abort_flag;
@@ -281,8 +296,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   const int n_tile = blockIdx.x % p.n_tiles;   // fixed per CTA: gridDim.x is a multiple of n_tiles
-  for (int i = threadIdx.x; i < p.BN; i += kThreadsTc) {
-    const int oc = n_tile * p.BN + i;
+  for (int i = threadIdx.x; i < p.BNd; i += kThreadsTc) {
+    const int oc = n_tile * p.BNd + i;
     hdr->bias[i] = oc < p.Ocp ? p.ep.bias_full[oc] : 0;
     hdr->scale[i] = oc < p.Ocp ? p.ep.acc_scale[oc] : 0.0f;
   }
@@ -408,18 +423,19 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int row_in_tile = quarter * 32 + lane;
     const bool store_issuer = threadIdx.x == kFirstEpilogueWarp * 32;
     const OutQuant oq = p.ep.out;
-    // Requantization, fast form (see requant.cuh for the exact sequence it must reproduce).
-    // The reference computes q = R(real / scale) with R = round-half-even except within an ulp of
-    // a .5 fraction.  r_hi and r_lo round real*(1/scale)*(1 +- 2^-22) to the nearest integer in one
-    // fused multiply-add each (adding 1.5*2^23 leaves the integer in the low mantissa bits; beyond
-    // 2^22 the bit pattern is still monotone, so saturation below stays right).  The reference's
-    // quotient real/scale (one rounding, of a divisor within half an ulp of 1/scale) lies between the
-    // two products; when both round to the same integer, that integer is the reference's result.  Chunks where any element disagrees are redone with the exact code.
-    const float inv = __frcp_rn(oq.scale);
-    const float inv_hi = __fmul_rn(inv, 1.0000002384185791015625f), inv_lo = __fmul_rn(inv, 0.9999997615814208984375f);
-    const int span = oq.hi - oq.lo;
-    const int addc = oq.zp - oq.lo - 0x4B400000;
-    const uint32_t sign_fix = oq.lo < 0 ? 0x80808080u : 0u;   // u + lo as a byte == u ^ 0x80 when lo == -128
+    RequantConsts rc;
+    {
+      const float inv = __frcp_rn(oq.scale);
+      rc.inv_hi = __fmul_rn(inv, 1.000000476837158203125f);    // 1 + 2^-21
+      rc.inv_lo = __fmul_rn(inv, 0.999999523162841796875f);    // 1 - 2^-21
+      rc.magic = 12582912.0f + static_cast<float>(oq.zp);
+      rc.inv_hi2 = f2_pack(rc.inv_hi, rc.inv_hi);
+      rc.inv_lo2 = f2_pack(rc.inv_lo, rc.inv_lo);
+      rc.magic2 = f2_pack(rc.magic, rc.magic);
+      rc.oq = oq;
+      rc.out_signed = oq.lo < 0;
+      rc.exact_only = p.exact_only;
+    }
     // position of this thread's 16-byte chunks inside a staging column block
     const int span_b = p.store_span;
     const int swz = span_b == 128 ? (row_in_tile & 7) : span_b == 64 ? ((row_in_tile >> 1) & 3) : ((row_in_tile >> 2) & 1);
@@ -441,65 +457,66 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       tc_fence_after();
       int tw = 0, th = 0, tn = 0;
       long long row = -1;   // direct-store path: output row (pixel index into D), -1 outside the tensor
+      const int32_t* corr_row = nullptr;   // border pixels of a padded convolution: their correction, this N tile
       if (p.conv) {
         tw = m_tile % p.tiles_w;
         const int rest = m_tile / p.tiles_w;
         th = rest % p.tiles_h;
         tn = rest / p.tiles_h;
-        if (!span_b) {
+        if (!span_b || p.ep.border_corr) {
           const int i = row_in_tile % p.TW, r2 = row_in_tile / p.TW;
           const int jh = r2 % p.TH, l = r2 / p.TH;
           const int wo = tw * p.TW + i, ho = th * p.TH + jh, n = tn * p.TN + l;
-          if (l < p.TN && wo < p.Wo && ho < p.Ho && n < p.Nimg) row = (static_cast<long long>(n) * p.Ho + ho) * p.Wo + wo;
+          if (l < p.TN && wo < p.Wo && ho < p.Ho && n < p.Nimg) {
+            row = (static_cast<long long>(n) * p.Ho + ho) * p.Wo + wo;
+            if (p.ep.border_corr) {
+              const int cls = __ldg(p.ep.row_class + ho) * p.ep.n_col_classes + __ldg(p.ep.col_class + wo);
+              if (cls) corr_row = p.ep.border_corr + static_cast<size_t>(cls) * p.Ocp + n_tile * p.BNd;
+            }
+          }
         }
       } else if (!span_b) {
         row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
         if (row >= p.M) row = -1;
       }
       const uint32_t taddr = tmem_base + a * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
-      for (int c0 = col_group * 16; c0 < p.BN; c0 += 64) {
-        int acc[16];
-        tc_ld_32x16(taddr + c0, acc);
-        tc_ld_wait();
-        const int cbase = n_tile * p.BN + c0;
-        if (!span_b && (row < 0 || cbase + 16 > p.Ocp)) continue;
-        float real[16];
-        int u[16];
-        int disagree = 0;
-#pragma unroll
-        for (int g4 = 0; g4 < 4; ++g4) {
-          const int4 b4 = *reinterpret_cast<const int4*>(&hdr->bias[c0 + g4 * 4]);
-          const float4 s4 = *reinterpret_cast<const float4*>(&hdr->scale[c0 + g4 * 4]);
-          real[g4 * 4 + 0] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 0] + b4.x), s4.x);
-          real[g4 * 4 + 1] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 1] + b4.y), s4.y);
-          real[g4 * 4 + 2] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 2] + b4.z), s4.z);
-          real[g4 * 4 + 3] = __fmul_rn(__int2float_rn(acc[g4 * 4 + 3] + b4.w), s4.w);
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int r_hi = __float_as_int(__fmaf_rn(real[i], inv_hi, 12582912.0f));
-          const int r_lo = __float_as_int(__fmaf_rn(real[i], inv_lo, 12582912.0f));
-          u[i] = __vimin_s32_relu(r_hi + addc, span);
-          // compared after saturation: values far outside the output range (half of them under a
-          // ReLU) agree however wide their band is
-          disagree |= u[i] ^ __vimin_s32_relu(r_lo + addc, span);
-        }
-        if (disagree) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) u[i] = requant(real[i], oq) - oq.lo;
-        }
-        uint32_t w4[4];
-#pragma unroll
-        for (int g4 = 0; g4 < 4; ++g4)
-          w4[g4] = (static_cast<uint32_t>(u[g4 * 4]) | (static_cast<uint32_t>(u[g4 * 4 + 1]) << 8) |
-                    (static_cast<uint32_t>(u[g4 * 4 + 2]) << 16) | (static_cast<uint32_t>(u[g4 * 4 + 3]) << 24)) ^ sign_fix;
-        const uint4 out16 = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      // Chunks col_group, col_group + 4, ... of 16 columns; the TMEM load of the next chunk is in flight
+      // while the current one is requantized.
+      int sub = 0;
+      if (p.dz != 0) {
+        // S = sum of this row's inputs: the accumulator column of the all-ones weight row
+        int s_val;
+        tc_ld_32x1(taddr + p.BNd, s_val);
+        tc_ld_wait1(s_val);
+        sub = p.dz * s_val;
+      }
+      auto emit = [&](const int (&acc)[16], int c0) {
+        const int cbase = n_tile * p.BNd + c0;
+        if (!span_b && (row < 0 || cbase + 16 > p.Ocp)) return;
+        const uint4 out16 = requant_chunk16(acc, &hdr->bias[c0], &hdr->scale[c0], rc, sub,
+                                            (corr_row && cbase + 16 <= p.Ocp) ? corr_row + c0 : nullptr);
         if (span_b) {
           const int blk = c0 / span_b, chunk = (c0 - blk * span_b) >> 4;
           *reinterpret_cast<uint4*>(stage_out + static_cast<size_t>(blk) * kBlockM * span_b + row_in_tile * span_b +
                                     ((chunk ^ swz) << 4)) = out16;
         } else {
           *reinterpret_cast<uint4*>(p.D + row * p.ldd + cbase) = out16;
+        }
+      };
+      {
+        int acc_a[16], acc_b[16];
+        int c0 = col_group * 16;
+        if (c0 < p.BNd) tc_ld_32x16(taddr + c0, acc_a);
+        while (c0 < p.BNd) {
+          tc_ld_wait(acc_a);
+          if (c0 + 64 < p.BNd) tc_ld_32x16(taddr + c0 + 64, acc_b);
+          emit(acc_a, c0);
+          c0 += 64;
+          if (c0 >= p.BNd) break;
+          tc_ld_wait(acc_b);
+          if (c0 + 64 < p.BNd) tc_ld_32x16(taddr + c0 + 64, acc_a);
+          emit(acc_b, c0);
+          c0 += 64;
         }
       }
       // accumulator buffer free again
@@ -514,9 +531,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (store_issuer) tma_store_wait_read<0>();
         epilogue_barrier();
         if (store_issuer) {
-          const int nblk = p.BN / span_b;
+          const int nblk = p.BNd / span_b;
           for (int blk = 0; blk < nblk; ++blk) {
-            const int col = n_tile * p.BN + blk * span_b;
+            const int col = n_tile * p.BNd + blk * span_b;
             if (col >= p.Ocp) break;
             const uint32_t src = smem_u32(stage_out + static_cast<size_t>(blk) * kBlockM * span_b);
             if (p.conv) tma_store_4d(&map_d, src, col, tw * p.TW, th * p.TH, tn * p.TN);
@@ -610,13 +627,23 @@ namespace {
 // output staging, stage count, TMEM columns, instruction descriptor, the B tensor map.
 // Kspan is the K extent one tap (or the whole GEMM) covers, used to pick BK.
 bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int taps, int ldd,
-                 const ContractEpilogue& e, void* D, int* status, const char** why) {
+                 const ContractEpilogue& e, void* D, int* status, const char** why, const GemmTcTiling* tiling) {
   GemmParams& p = plan->params;
   p.Ocp = ldd;
   p.ldd = ldd;
-  p.n_tiles = (Np + 255) / 256;
-  p.BN = (((Np + p.n_tiles - 1) / p.n_tiles) + 15) & ~15;
+  if (tiling) {
+    p.n_tiles = tiling->n_tiles;
+    p.BN = tiling->rows;
+    p.BNd = tiling->data;
+    if (p.BN > 256 || (p.BN & 15) || (p.BNd & 15) || p.BNd < 16 || p.BNd > p.BN) { *why = "gemm_tc: bad N tiling"; return false; }
+  } else {
+    p.n_tiles = (Np + 255) / 256;
+    p.BN = (((Np + p.n_tiles - 1) / p.n_tiles) + 15) & ~15;
+    p.BNd = p.BN;
+  }
   if (p.n_tiles * p.BN != Np) { *why = "gemm_tc: weight rows must be packed to n_tiles*BN"; return false; }
+  p.dz = e.dz_uniform;
+  if (p.dz != 0 && p.BNd == p.BN) { *why = "gemm_tc: a weight zero point needs the ones row in every N tile"; return false; }
   // K block: the swizzle span (32/64/128 bytes) that wastes the least tail.
   int best_bk = 32;
   long long best_cost = -1;
@@ -629,8 +656,8 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.layout_type = p.BK == 128 ? 2u : (p.BK == 64 ? 4u : 6u);
   p.sbo = 8u * p.BK;
   // Output staging for the TMA store: column blocks as wide as the widest swizzle span dividing BN.
-  p.store_span = p.BN % 128 == 0 ? 128 : (p.BN % 64 == 0 ? 64 : (p.BN % 32 == 0 ? 32 : 0));
-  const size_t staging = p.store_span ? 2 * static_cast<size_t>(kBlockM) * p.BN : 0;
+  p.store_span = p.BNd % 128 == 0 ? 128 : (p.BNd % 64 == 0 ? 64 : (p.BNd % 32 == 0 ? 32 : 0));
+  const size_t staging = p.store_span ? 2 * static_cast<size_t>(kBlockM) * p.BNd : 0;
   // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
   // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
   // aligned start of the ring.  Several k-blocks share a stage (one barrier round trip) when they are
@@ -656,6 +683,7 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.idesc = (2u << 4) | (static_cast<uint32_t>(a_signed ? 1 : 0) << 7) | (1u << 10) |
             (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
   p.ep = e;
+  p.exact_only = e.exact_only;
   p.D = static_cast<uint8_t*>(D);
   p.status = status;
   const uint64_t bdims[2] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(Np)};
@@ -698,7 +726,7 @@ void set_grid(GemmTcPlan* plan) {
 
 GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, int M, int Np, int Kp, int Oc, void* D,
                                 int ldd, int d_signed, const ContractEpilogue& e, int* status, char* err,
-                                size_t err_len) {
+                                size_t err_len, const GemmTcTiling* tiling) {
   (void)Oc;
   (void)d_signed;
   auto fail = [&](const char* msg) -> GemmTcPlan* {
@@ -715,7 +743,7 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   std::memset(&p, 0, sizeof(p));
   std::memset(&plan->map_d, 0, sizeof(plan->map_d));
   const char* why = "";
-  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why)) {
+  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why, tiling)) {
     delete plan;
     return fail(why);
   }
@@ -740,7 +768,8 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
 }
 
 GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* B, const ConvGeom& g, int Np, void* D,
-                                     const ContractEpilogue& e, int* status, char* err, size_t err_len) {
+                                     const ContractEpilogue& e, int* status, char* err, size_t err_len,
+                                     const GemmTcTiling* tiling) {
   auto fail = [&](const char* msg) -> GemmTcPlan* {
     if (err && err_len) std::snprintf(err, err_len, "%s", msg);
     return nullptr;
@@ -756,7 +785,7 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   std::memset(&plan->map_d, 0, sizeof(plan->map_d));
   const char* why = "";
   const int Kp = g.kh * g.kw * g.Cp;
-  if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.kh * g.kw, g.Ocp, e, D, status, &why)) {
+  if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.kh * g.kw, g.Ocp, e, D, status, &why, tiling)) {
     delete plan;
     return fail(why);
   }
@@ -807,6 +836,52 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   return plan;
 }
 
+GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int extra = with_s ? 16 : 0;
+  const int max_data = 256 - extra;
+  const long long m_tiles = (M + kBlockM - 1) / kBlockM;
+  const double rows = static_cast<double>(M < kBlockM ? M : kBlockM);
+  GemmTcTiling best = {0, 0, 0};
+  double best_time = 0.0;
+  int last_data = 0;
+  for (int nt = (Ocp + max_data - 1) / max_data; nt <= sms && nt * 16 <= Ocp + 15; ++nt) {
+    const int data = (((Ocp + nt - 1) / nt) + 15) & ~15;
+    if (data == last_data) continue;          // same tile width with more (empty) tiles
+    last_data = data;
+    if ((nt - 1) * data >= Ocp) continue;
+    const int bn = data + extra;
+    const long long tiles = m_tiles * nt;
+    long long grid = (sms / nt) * nt;
+    if (grid > tiles) grid = tiles;
+    const double per_cta = static_cast<double>((tiles + grid - 1) / grid);
+    // cycles per tile: tensor pipe (8192 MAC/clk), operand bytes (HBM share per SM when all SMs load,
+    // more when few do), epilogue issue slots
+    const double mma = static_cast<double>(Kp) * bn / 64.0;
+    double bytes_per_clk = 24.0 * sms / static_cast<double>(grid);
+    if (bytes_per_clk > 64.0) bytes_per_clk = 64.0;
+    const double load = (rows + bn) * Kp / bytes_per_clk;
+    const double epi = 9.0 * data + 300.0;
+    const double mainloop = mma > load ? mma : load;
+    const double steady = mainloop > epi ? mainloop : epi;
+    const double time = mainloop + epi + (per_cta - 1.0) * steady;
+    if (best.n_tiles == 0 || time < best_time * 0.97) {   // prefer wider tiles unless clearly slower
+      best.n_tiles = nt;
+      best.data = data;
+      best.rows = bn;
+      best_time = time;
+    }
+  }
+  if (best.n_tiles == 0) {
+    best.n_tiles = (Ocp + max_data - 1) / max_data;
+    best.data = (((Ocp + best.n_tiles - 1) / best.n_tiles) + 15) & ~15;
+    best.rows = best.data + extra;
+  }
+  return best;
+}
+
 size_t gemm_tc_plan_bytes(void) { return sizeof(GemmTcPlan); }
 
 // Same plan as gemm_tc_plan_create, but built inside caller-provided storage (no heap allocation);
@@ -828,7 +903,7 @@ GemmTcPlan* gemm_tc_plan_build_in(void* storage, size_t storage_bytes, const voi
   std::memset(plan, 0, sizeof(GemmTcPlan));
   GemmParams& p = plan->params;
   const char* why = "";
-  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why)) return fail(why);
+  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why, nullptr)) return fail(why);
   p.M = M;
   p.num_kb = (Kp + p.BK - 1) / p.BK;
   p.m_tiles = (M + kBlockM - 1) / kBlockM;

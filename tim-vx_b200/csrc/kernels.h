@@ -49,6 +49,21 @@ struct ContractEpilogue {
   const int32_t* tapc;       // null when the input zero point is 0 or there is no padding
   OutQuant out;
   int out_is_float;          // write float(acc)*acc_scale instead of quantizing
+  // Tensor-core epilogue only: 1 = requantize with the exact sequence only.  The fast form needs
+  // |acc * acc_scale / out.scale| < 2^21 for every possible accumulator, which the planner checks
+  // from K, the bias and the scales.
+  int exact_only;
+  // Tensor-core path, weights with one zero point left over (dz_uniform = zw - 128 for uint8 weights):
+  // the packed weights carry an all-ones row per N tile, whose accumulator column is S.
+  int dz_uniform;
+  // Tensor-core implicit convolution with a non-zero input zero point and padding: out-of-bounds taps
+  // read as 0 instead of the zero point, which the bias folding assumed.  Output rows/columns are
+  // classified by their set of out-of-bounds taps (row_class[Ho], col_class[Wo], class 0 = none) and
+  // border_corr[(row_class * n_col_classes + col_class) * Ocp + oc] is added to the accumulator.
+  const int32_t* border_corr;   // null = no correction
+  const uint8_t* row_class;
+  const uint8_t* col_class;
+  int n_col_classes;
 };
 
 // ---- layout converters (elem = 1 or 4 bytes) -------------------------------
@@ -66,6 +81,12 @@ void launch_depthwise_q(const void* x, int x_signed, int zx, const int16_t* wd, 
                         const float* acc_scale, int multiplier, const ConvGeom& g, OutQuant out,
                         void* y, cudaStream_t s);
 
+// The multiplier-1 case, 16 channels x 2 pixels per thread with the weights in shared memory:
+// wtab [kh*kw][Ocp] words, each w - zw as a 16-bit half in position (channel & 1);
+// bias_full = bias - zx' * sum_taps (w - zw) with zx' = zx (+128 for int8 input).  Needs kh*kw <= 64.
+void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* wtab, const int32_t* bias_full,
+                          const float* acc_scale, const ConvGeom& g, OutQuant out, int exact_only, void* y, cudaStream_t s);
+
 // ---- float32 convolution (dense or depthwise), accumulation order ic,ky,kx --
 // w: original WHIcOc layout; bias may be null.
 void launch_conv_f32(const float* x, const float* w, const float* bias, int multiplier, int w_ic,
@@ -79,6 +100,9 @@ void launch_pool_f32(const float* x, int type, const ConvGeom& g, float* y, cuda
 // ---- elementwise over n elements of channels-last storage -------------------
 void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, int b_signed, float sb, int zb,
                   OutQuant out, int out_signed, void* y, size_t n, cudaStream_t s);
+// The same Add through a 64 KB byte table in shared memory (exact whatever the data; chosen for large
+// tensors): table[a*256 + (b ^ ((a & 31) << 2))] = quantized sum for raw input bytes a, b.
+void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* y, size_t n, cudaStream_t s);
 void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s);
 // y[i] = lut[x[i]] over n bytes: Relu/Relu6 between any two 8-bit quantizations,
 // the 256-entry device table being built on the host with the reference's float sequence
@@ -114,15 +138,26 @@ void launch_im2col_whcn(const void* x, int Kp, int zx, const ConvGeom& g, void* 
 // error code; the kernel's bounded waits report through *status (device int,
 // 0 = ok).
 struct GemmTcPlan;   // opaque: tensor maps + launch geometry, built once at compile
+// N tiling of a GEMM: n_tiles tiles of `data` output channels each.  The packed weight matrix has
+// n_tiles * rows rows; inside a tile, rows [0, data) are output channels, and when rows > data row
+// `data` is the all-ones row (S column) and the rest is zero.
+struct GemmTcTiling {
+  int n_tiles, data, rows;
+};
+// Picks the tiling for M x Ocp x Kp from a small cost model (waves of tiles over the SMs, operand
+// bytes per tile, epilogue work per tile).  with_s: reserve 16 rows per tile for the ones row.
+GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s);
+// tiling == null: ceil(Np / 256) equal tiles of Np / n_tiles rows, no ones row.
 GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, int M, int Np, int Kp, int Oc,
                                 void* D, int ldd, int d_signed, const ContractEpilogue& e, int* status,
-                                char* err, size_t err_len);
+                                char* err, size_t err_len, const GemmTcTiling* tiling = nullptr);
 // Implicit-GEMM convolution on the same kernel: X is the channels-last input [N][H][W][Cp], B is
 // [Np][kh*kw*Cp] with K = tap*Cp + c, D the channels-last output.  Filter taps are fetched as
-// shifted 4-D TMA boxes; positions in the padding read as zero, so this form requires an input
-// zero point of 0 or no padding (no border correction in the epilogue).
+// shifted 4-D TMA boxes; positions in the padding read as zero, so with a non-zero input zero point
+// and padding the epilogue needs e.border_corr.
 GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* B, const ConvGeom& g, int Np, void* D,
-                                     const ContractEpilogue& e, int* status, char* err, size_t err_len);
+                                     const ContractEpilogue& e, int* status, char* err, size_t err_len,
+                                     const GemmTcTiling* tiling = nullptr);
 // The plain-GEMM plan built inside caller-provided storage (gemm_tc_plan_bytes() bytes, 64-byte aligned)
 // instead of on the heap; not to be passed to gemm_tc_plan_destroy.
 size_t gemm_tc_plan_bytes(void);

@@ -2,6 +2,8 @@
 // any-shape quantized convolution, depthwise convolution, pooling, Add, Relu,
 // Softmax, im2col and the float32 variants.  All work on channels-last
 // storage (kernels.h) with 128-bit or 32-bit accesses along the channel axis.
+#include <cmath>
+
 #include "kernels.h"
 #include "requant.cuh"
 
@@ -14,30 +16,130 @@ inline unsigned grid_for(long long n, int threads) { return static_cast<unsigned
 
 // ---------------------------------------------------------------- layout
 
-template <typename T>
-__global__ void whcn_to_cl_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int C, int H, int W, int Cp) {
-  const long long total = static_cast<long long>(N) * H * W * Cp;
-  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (i >= total) return;
-  int c = static_cast<int>(i % Cp);
-  long long r = i / Cp;
-  int w = static_cast<int>(r % W); r /= W;
-  int h = static_cast<int>(r % H);
-  int n = static_cast<int>(r / H);
-  dst[i] = c < C ? src[((static_cast<long long>(n) * C + c) * H + h) * W + w] : T(0);
+// A WHCN image is a [C][H*W] matrix (pixels contiguous), the channels-last image its transpose
+// [H*W][Cp].  Both converters move 64-channel x 64-pixel byte tiles through shared memory so that
+// either side is touched in 64-byte runs; a thread transposes one 4 x 4 byte block in registers.
+// Shared tile: [64 pixels][16 words of 4 channels], the four 16-byte chunks of a pixel XOR-swizzled
+// with the pixel's block index to spread the banks.
+
+// 4 x 4 byte transpose: r[j] holds bytes (j, 0..3); on return r[i] holds bytes (0..3, i).
+__device__ __forceinline__ void transpose4x4(uint32_t (&r)[4]) {
+  const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[0], r[1], 0x7362);
+  const uint32_t t2 = __byte_perm(r[2], r[3], 0x5140), t3 = __byte_perm(r[2], r[3], 0x7362);
+  r[0] = __byte_perm(t0, t2, 0x5410);
+  r[1] = __byte_perm(t0, t2, 0x7632);
+  r[2] = __byte_perm(t1, t3, 0x5410);
+  r[3] = __byte_perm(t1, t3, 0x7632);
 }
 
-template <typename T>
-__global__ void cl_to_whcn_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int C, int H, int W, int Cp) {
-  const long long total = static_cast<long long>(N) * C * H * W;
-  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (i >= total) return;
-  int w = static_cast<int>(i % W);
-  long long r = i / W;
-  int h = static_cast<int>(r % H); r /= H;
-  int c = static_cast<int>(r % C);
-  int n = static_cast<int>(r / C);
-  dst[i] = src[((static_cast<long long>(n) * H + h) * W + w) * Cp + c];
+template <bool ALIGNED>
+__global__ void __launch_bounds__(256) whcn_to_cl_u8_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int C,
+                                                            int HW, int Cp) {
+  __shared__ uint4 tile[64 * 4];
+  const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 64, n = blockIdx.z;
+  const int t = threadIdx.x;
+  {
+    const int pb = t & 15, cb = t >> 4;
+    const int p = p0 + 4 * pb;
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = c0 + 4 * cb + j;
+      r[j] = 0;
+      if (c < C) {
+        const uint8_t* row = src + (static_cast<size_t>(n) * C + c) * HW;
+        if (ALIGNED) {
+          if (p < HW) r[j] = *reinterpret_cast<const uint32_t*>(row + p);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (p + i < HW) r[j] |= static_cast<uint32_t>(row[p + i]) << (8 * i);
+        }
+      }
+    }
+    transpose4x4(r);   // r[i] = pixel 4*pb+i, channels 4*cb .. 4*cb+3
+    uint32_t* words = reinterpret_cast<uint32_t*>(tile);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) words[(4 * pb + i) * 16 + (((cb >> 2) ^ (pb & 3)) << 2) + (cb & 3)] = r[i];
+  }
+  __syncthreads();
+  {
+    const int px = t >> 2, chunk = t & 3;
+    const int p = p0 + px, c = c0 + 16 * chunk;
+    if (p < HW && c < Cp)
+      *reinterpret_cast<uint4*>(dst + (static_cast<size_t>(n) * HW + p) * Cp + c) = tile[px * 4 + (chunk ^ ((px >> 2) & 3))];
+  }
+}
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(256) cl_to_whcn_u8_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int C,
+                                                            int HW, int Cp) {
+  __shared__ uint4 tile[64 * 4];
+  const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 64, n = blockIdx.z;
+  const int t = threadIdx.x;
+  {
+    const int px = t >> 2, chunk = t & 3;
+    const int p = p0 + px, c = c0 + 16 * chunk;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (p < HW && c < Cp) v = *reinterpret_cast<const uint4*>(src + (static_cast<size_t>(n) * HW + p) * Cp + c);
+    tile[px * 4 + (chunk ^ ((px >> 2) & 3))] = v;
+  }
+  __syncthreads();
+  {
+    const int pb = t & 15, cb = t >> 4;
+    const int p = p0 + 4 * pb;
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(tile);
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = words[(4 * pb + i) * 16 + (((cb >> 2) ^ (pb & 3)) << 2) + (cb & 3)];
+    transpose4x4(r);   // r[j] = channel 4*cb+j, pixels 4*pb .. 4*pb+3
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = c0 + 4 * cb + j;
+      if (c >= C) continue;
+      uint8_t* row = dst + (static_cast<size_t>(n) * C + c) * HW;
+      if (ALIGNED) {
+        if (p < HW) *reinterpret_cast<uint32_t*>(row + p) = r[j];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (p + i < HW) row[p + i] = static_cast<uint8_t>(r[j] >> (8 * i));
+      }
+    }
+  }
+}
+
+// 32-bit elements: the classic 32 x 32 tile with a padded row.
+__global__ void __launch_bounds__(256) whcn_to_cl_u32_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int C,
+                                                             int HW, int Cp) {
+  __shared__ uint32_t tile[32][33];
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32, n = blockIdx.z;
+  const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
+  for (int j = ly; j < 32; j += 8) {
+    const int c = c0 + j, p = p0 + lx;
+    tile[j][lx] = (c < C && p < HW) ? src[(static_cast<size_t>(n) * C + c) * HW + p] : 0u;
+  }
+  __syncthreads();
+  for (int j = ly; j < 32; j += 8) {
+    const int p = p0 + j, c = c0 + lx;
+    if (p < HW && c < Cp) dst[(static_cast<size_t>(n) * HW + p) * Cp + c] = tile[lx][j];
+  }
+}
+
+__global__ void __launch_bounds__(256) cl_to_whcn_u32_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int C,
+                                                             int HW, int Cp) {
+  __shared__ uint32_t tile[32][33];
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32, n = blockIdx.z;
+  const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
+  for (int j = ly; j < 32; j += 8) {
+    const int p = p0 + j, c = c0 + lx;
+    tile[j][lx] = (p < HW && c < Cp) ? src[(static_cast<size_t>(n) * HW + p) * Cp + c] : 0u;
+  }
+  __syncthreads();
+  for (int j = ly; j < 32; j += 8) {
+    const int c = c0 + j, p = p0 + lx;
+    if (c < C && p < HW) dst[(static_cast<size_t>(n) * C + c) * HW + p] = tile[lx][j];
+  }
 }
 
 // ---------------------------------------------------------------- quantized conv, CUDA cores
@@ -181,6 +283,122 @@ __global__ void depthwise_q_kernel(const uint8_t* __restrict__ x, int zx, const 
   *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(p) * g.Ocp + oc0) = word;
 }
 
+// ---------------------------------------------------------------- depthwise, quantized, multiplier 1
+
+// A block owns a slab of up to 64 channels and a run of output-pixel pairs; a thread owns 16 channels
+// (one 128-bit access) of two horizontally adjacent output pixels.  The slab's weights sit in shared
+// memory as one 32-bit word per (tap, channel): w - zw as a 16-bit half placed so that one dp2a
+// multiplies it with that channel's byte of an input word (channel c of a word: half c & 1, byte pair
+// c >> 1), i.e. one instruction per multiply-accumulate with no byte extraction.  Out-of-bounds taps
+// read as the input zero point, so the zero-point term is a per-channel constant folded into the bias:
+//   acc = sum_taps x * (w - zw)  +  [bias - zx * sum_taps (w - zw)].
+// Signed inputs are biased by 128 on load (and zx with them).  The epilogue is the 16-value
+// requantization shared with the tensor-core GEMM.
+struct DwParams {
+  ConvGeom g;
+  const uint32_t* wtab;      // [taps][Ocp] words
+  const int32_t* bias_full;  // [Ocp]
+  const float* acc_scale;    // [Ocp]
+  OutQuant out;
+  uint32_t x_flip;           // 0x80808080 for int8 input
+  uint32_t zx_word;          // biased zero point replicated into four bytes
+  int exact_only;
+  int slab;                  // channels per block: min(Ocp, 64)
+};
+
+template <int MODE>
+__device__ __forceinline__ int dp2a_su(uint32_t w16x2, uint32_t x8x4, int c) {
+  int d;
+  if (MODE == 0) asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(w16x2), "r"(x8x4), "r"(c));
+  else asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(w16x2), "r"(x8x4), "r"(c));
+  return d;
+}
+
+__device__ __forceinline__ void dw_mac16(int (&acc)[16], const uint4& x, const uint4 (&w)[4]) {
+  const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    acc[4 * k + 0] = dp2a_su<0>(w[k].x, xw[k], acc[4 * k + 0]);
+    acc[4 * k + 1] = dp2a_su<0>(w[k].y, xw[k], acc[4 * k + 1]);
+    acc[4 * k + 2] = dp2a_su<1>(w[k].z, xw[k], acc[4 * k + 2]);
+    acc[4 * k + 3] = dp2a_su<1>(w[k].w, xw[k], acc[4 * k + 3]);
+  }
+}
+
+__global__ void __launch_bounds__(256) depthwise_q16_kernel(const uint8_t* __restrict__ x, DwParams p, uint8_t* __restrict__ y) {
+  extern __shared__ uint4 dw_smem[];               // [taps][slab / 4] groups of four weight words
+  const ConvGeom& g = p.g;
+  const int taps = g.kh * g.kw;
+  const int c_slab = blockIdx.y * p.slab;
+  const int slab_ch = min(p.slab, g.Ocp - c_slab);   // multiple of 16
+  const int quads = p.slab >> 2;
+  for (int i = threadIdx.x; i < taps * quads; i += blockDim.x) {
+    const int t = i / quads, q = i - t * quads;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (4 * q < slab_ch) v = *reinterpret_cast<const uint4*>(p.wtab + static_cast<size_t>(t) * g.Ocp + c_slab + 4 * q);
+    dw_smem[i] = v;
+  }
+  __syncthreads();
+  const int chunks = p.slab >> 4;                   // thread mapping is the same in every slab
+  const int pairs_w = (g.Wo + 1) >> 1;
+  const long long total_pairs = static_cast<long long>(g.N) * g.Ho * pairs_w;
+  const int pairs_per_block = blockDim.x / chunks;
+  const int chunk = threadIdx.x % chunks;
+  const int local_pair = threadIdx.x / chunks;
+  if (local_pair >= pairs_per_block || 16 * chunk >= slab_ch) return;
+  const long long pair = static_cast<long long>(blockIdx.x) * pairs_per_block + local_pair;
+  if (pair >= total_pairs) return;
+  const int pw = static_cast<int>(pair % pairs_w);
+  const long long t2 = pair / pairs_w;
+  const int ho = static_cast<int>(t2 % g.Ho);
+  const int n = static_cast<int>(t2 / g.Ho);
+  const int wo0 = 2 * pw;
+  const bool second = wo0 + 1 < g.Wo;
+  const int c0 = c_slab + 16 * chunk;
+  const uint4 zx4 = make_uint4(p.zx_word, p.zx_word, p.zx_word, p.zx_word);
+  int acc0[16], acc1[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { acc0[i] = 0; acc1[i] = 0; }
+  const uint8_t* img = x + static_cast<size_t>(n) * g.H * g.W * g.Cp + c0;
+  for (int ky = 0; ky < g.kh; ++ky) {
+    const int hi = ho * g.sy - g.pt + ky * g.dy;
+    const bool row_ok = hi >= 0 && hi < g.H;
+    const uint8_t* rowp = img + static_cast<size_t>(row_ok ? hi : 0) * g.W * g.Cp;
+    for (int kx = 0; kx < g.kw; ++kx) {
+      const uint4* wq = dw_smem + (ky * g.kw + kx) * quads + 4 * chunk;
+      const uint4 w[4] = {wq[0], wq[1], wq[2], wq[3]};
+      const int wi0 = wo0 * g.sx - g.pl + kx * g.dx, wi1 = wi0 + g.sx;
+      uint4 xa = zx4, xb = zx4;
+      if (row_ok && wi0 >= 0 && wi0 < g.W) {
+        xa = *reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi0) * g.Cp);
+        xa.x ^= p.x_flip; xa.y ^= p.x_flip; xa.z ^= p.x_flip; xa.w ^= p.x_flip;
+      }
+      if (second && row_ok && wi1 >= 0 && wi1 < g.W) {
+        xb = *reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi1) * g.Cp);
+        xb.x ^= p.x_flip; xb.y ^= p.x_flip; xb.z ^= p.x_flip; xb.w ^= p.x_flip;
+      }
+      dw_mac16(acc0, xa, w);
+      dw_mac16(acc1, xb, w);
+    }
+  }
+  RequantConsts rc;
+  {
+    const float inv = __frcp_rn(p.out.scale);
+    rc.inv_hi = __fmul_rn(inv, 1.000000476837158203125f);
+    rc.inv_lo = __fmul_rn(inv, 0.999999523162841796875f);
+    rc.magic = 12582912.0f + static_cast<float>(p.out.zp);
+    rc.inv_hi2 = f2_pack(rc.inv_hi, rc.inv_hi);
+    rc.inv_lo2 = f2_pack(rc.inv_lo, rc.inv_lo);
+    rc.magic2 = f2_pack(rc.magic, rc.magic);
+    rc.oq = p.out;
+    rc.out_signed = p.out.lo < 0;
+    rc.exact_only = p.exact_only;
+  }
+  uint8_t* out = y + ((static_cast<size_t>(n) * g.Ho + ho) * g.Wo + wo0) * g.Ocp + c0;
+  *reinterpret_cast<uint4*>(out) = requant_chunk16(acc0, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
+  if (second) *reinterpret_cast<uint4*>(out + g.Ocp) = requant_chunk16(acc1, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
+}
+
 // ---------------------------------------------------------------- float32 conv
 
 // One thread per output element; the sum runs ic (outer), ky, kx (inner) with
@@ -271,6 +489,72 @@ __global__ void pool_q_kernel(const uint8_t* __restrict__ x, int type, float in_
   *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(p) * g.Cp + cw * 4) = word;
 }
 
+// The same pooling with 16 channels (one 128-bit access) per thread and byte-SIMD arithmetic: max with
+// __vmaxu4/__vmaxs4, sums as packed 16-bit pairs (so the window may hold at most 256 taps).
+template <bool XS>
+__global__ void __launch_bounds__(256) pool_q16_kernel(const uint8_t* __restrict__ x, int type, float in_scale, int in_zp,
+                                                       int same_quant, ConvGeom g, OutQuant out, uint8_t* __restrict__ y) {
+  const int chunks = g.Cp >> 4;
+  const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * chunks;
+  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= total) return;
+  const int ch = static_cast<int>(i % chunks);
+  const long long p = i / chunks;
+  const int wo = static_cast<int>(p % g.Wo);
+  const long long t = p / g.Wo;
+  const int ho = static_cast<int>(t % g.Ho);
+  const int n = static_cast<int>(t / g.Ho);
+  const int h_lo = max(0, ho * g.sy - g.pt), h_hi = min(g.H, ho * g.sy - g.pt + g.kh);
+  const int w_lo = max(0, wo * g.sx - g.pl), w_hi = min(g.W, wo * g.sx - g.pl + g.kw);
+  const int count = max(0, h_hi - h_lo) * max(0, w_hi - w_lo);
+  const uint32_t flip = XS ? 0x80808080u : 0u;       // signed bytes are handled as value + 128
+  uint32_t mx[4] = {0u, 0u, 0u, 0u};                 // unsigned max of the biased bytes
+  uint32_t even[4] = {0u, 0u, 0u, 0u}, odd[4] = {0u, 0u, 0u, 0u};   // 16-bit sums of bytes 0,2 and 1,3 of each word
+  for (int hi = h_lo; hi < h_hi; ++hi) {
+    const uint8_t* rowp = x + ((static_cast<size_t>(n) * g.H + hi) * g.W) * g.Cp + ch * 16;
+    for (int wi = w_lo; wi < w_hi; ++wi) {
+      const uint4 v = *reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi) * g.Cp);
+      const uint32_t w4[4] = {v.x ^ flip, v.y ^ flip, v.z ^ flip, v.w ^ flip};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (type == 0) {
+          mx[k] = __vmaxu4(mx[k], w4[k]);
+        } else {
+          even[k] += w4[k] & 0x00FF00FFu;
+          odd[k] += (w4[k] >> 8) & 0x00FF00FFu;
+        }
+      }
+    }
+  }
+  const int bias = XS ? 128 : 0;
+  const float div = type == 1 ? static_cast<float>(g.kw * g.kh) : static_cast<float>(count);
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (type == 0 && same_quant) {
+      o[k] = count ? (mx[k] ^ flip) : (static_cast<uint32_t>(in_zp & 0xFF) * 0x01010101u);
+      continue;
+    }
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int q;
+      if (type == 0) {
+        q = count ? static_cast<int>((mx[k] >> (8 * j)) & 0xFF) - bias : in_zp;
+        q = requant(__fmul_rn(__fsub_rn(__int2float_rn(q), __int2float_rn(in_zp)), in_scale), out);
+      } else {
+        const uint32_t pair = (j & 1) ? odd[k] : even[k];
+        const int sum = static_cast<int>((pair >> (16 * (j >> 1))) & 0xFFFF) - count * (in_zp + bias);
+        const float avg = count ? __fdiv_rn(__fmul_rn(__int2float_rn(sum), in_scale), div) : 0.0f;
+        q = requant(avg, out);
+      }
+      word |= static_cast<uint32_t>(q & 0xFF) << (8 * j);
+    }
+    o[k] = word;
+  }
+  *reinterpret_cast<uint4*>(y + static_cast<size_t>(p) * g.Cp + ch * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 __global__ void pool_f32_kernel(const float* __restrict__ x, int type, ConvGeom g, float* __restrict__ y) {
   const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * g.C;
   long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -309,39 +593,117 @@ __device__ __forceinline__ int byte_at(uint32_t word, int j) {
   return S ? static_cast<int>(static_cast<int8_t>(b)) : static_cast<int>(b);
 }
 
-// 16 elements per thread, 128-bit loads and stores.  The two dequantizations
-// ((q - zp) * scale, 256 possible values each) are tabulated in shared memory
-// by the block; the sum is requantized with requant_fast.
-template <bool AS, bool BS>
-__global__ void add_q_kernel(const uint4* __restrict__ a, float sa, int za, const uint4* __restrict__ b, float sb, int zb,
-                             OutQuant out, uint4* __restrict__ y, size_t n16) {
-  __shared__ float fa[256], fb[256];
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-    const int qa = AS ? static_cast<int>(static_cast<int8_t>(i)) : i;
-    const int qb = BS ? static_cast<int>(static_cast<int8_t>(i)) : i;
-    fa[i] = __fmul_rn(__fsub_rn(__int2float_rn(qa), __int2float_rn(za)), sa);
-    fb[i] = __fmul_rn(__fsub_rn(__int2float_rn(qb), __int2float_rn(zb)), sb);
+// Quantized Add, 16 elements per thread and step, 128-bit loads and stores.
+//
+// Per element the reference computes (qa - za)*sa + (qb - zb)*sb in float and requantizes the sum.
+// Here a byte becomes the float 2^23 + q by a byte permute into a float's mantissa (signed inputs are
+// biased by 128 first), the zero point is removed by an exact float subtraction, and every float
+// operation handles two elements (f32x2).  Rounding: r = sum*inv + (1.5*2^23 + zp) leaves
+// rint(sum*inv) + zp in the low mantissa bits; it is evaluated with inv*(1 +- 2^-21) and the two results
+// agree unless sum/scale lies within about 2^-21 (relative) of a .5 fraction, in which case that
+// element is redone with the exact sequence.  FAST = false is the exact sequence only, for
+// scale ratios so extreme that the magic-number addition could leave its binade.
+struct AddParams {
+  float sa, sb, scale;          // input scales, output scale
+  float ca, cb;                 // -(2^23 + za [+128]), -(2^23 + zb [+128])
+  float inv_hi, inv_lo, magic;  // 1/scale * (1 +- 2^-21), 1.5*2^23 + zp
+  int za, zb;
+  uint32_t a_flip, b_flip;      // 0x80808080 for signed inputs
+  OutQuant out;
+  int out_signed;
+};
+
+__device__ __forceinline__ int add_q_exact(uint32_t aw, uint32_t bw, int j, const AddParams& p) {
+  const int qa = static_cast<int>((aw >> (8 * j)) & 0xFF) - (p.a_flip ? 128 : 0);
+  const int qb = static_cast<int>((bw >> (8 * j)) & 0xFF) - (p.b_flip ? 128 : 0);
+  const float fa = __fmul_rn(__int2float_rn(qa - p.za), p.sa), fb = __fmul_rn(__int2float_rn(qb - p.zb), p.sb);
+  return requant(__fadd_rn(fa, fb), p.out);
+}
+
+// aw, bw: four input bytes each, signed inputs already biased by 128
+template <bool FAST>
+__device__ __forceinline__ uint32_t add_q_word(uint32_t aw, uint32_t bw, const AddParams& p) {
+  int v[4];
+  uint32_t d[4];
+  if (FAST) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t a0 = __byte_perm(aw, 0x4B000000u, h ? 0x7542 : 0x7540), a1 = __byte_perm(aw, 0x4B000000u, h ? 0x7543 : 0x7541);
+      const uint32_t b0 = __byte_perm(bw, 0x4B000000u, h ? 0x7542 : 0x7540), b1 = __byte_perm(bw, 0x4B000000u, h ? 0x7543 : 0x7541);
+      // The two products are scalar mul.rn (never contracted): a packed multiply feeding the packed
+      // addition came back fused into one multiply-add on sm_100a, i.e. with the product unrounded,
+      // also when it was written as fma(a, b, -0).
+      float da0, da1, db0, db1;
+      f2_unpack(f2_add(f2_pack_bits(a0, a1), f2_pack(p.ca, p.ca)), da0, da1);
+      f2_unpack(f2_add(f2_pack_bits(b0, b1), f2_pack(p.cb, p.cb)), db0, db1);
+      const f32x2 fa = f2_pack(__fmul_rn(da0, p.sa), __fmul_rn(da1, p.sa));
+      const f32x2 fb = f2_pack(__fmul_rn(db0, p.sb), __fmul_rn(db1, p.sb));
+      const f32x2 sum = f2_add(fa, fb);
+      const f32x2 m = f2_pack(p.magic, p.magic);
+      uint32_t h0, h1, l0, l1;
+      f2_unpack_bits(f2_fma(sum, f2_pack(p.inv_hi, p.inv_hi), m), h0, h1);
+      f2_unpack_bits(f2_fma(sum, f2_pack(p.inv_lo, p.inv_lo), m), l0, l1);
+      d[2 * h] = h0 ^ l0;
+      d[2 * h + 1] = h1 ^ l1;
+      v[2 * h] = static_cast<int>(h0) - 0x4B400000;
+      v[2 * h + 1] = static_cast<int>(h1) - 0x4B400000;
+    }
+  } else {
+    d[0] = d[1] = d[2] = d[3] = 1u;
   }
-  __syncthreads();
-  const float inv_scale = __frcp_rn(out.scale);
-  const int span = out.hi - out.lo, addc = out.zp - out.lo - 0x4B400000;
-  const uint32_t sign_fix = out.lo < 0 ? 0x80808080u : 0u;
+  if (d[0] | d[1] | d[2] | d[3]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (d[j]) v[j] = add_q_exact(aw, bw, j, p);
+  }
+  return p.out_signed ? pack_sat_s8(v[1], v[0], pack_sat_s8(v[3], v[2], 0u)) : pack_sat_u8(v[1], v[0], pack_sat_u8(v[3], v[2], 0u));
+}
+
+template <bool FAST>
+__global__ void __launch_bounds__(256) add_q_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, AddParams p,
+                                                    uint4* __restrict__ y, size_t n16) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
-    const uint4 av = a[i], bv = b[i];
-    const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
-    uint32_t ow[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float r = __fadd_rn(fa[(aw[k] >> (8 * j)) & 0xFF], fb[(bw[k] >> (8 * j)) & 0xFF]);
-        word |= static_cast<uint32_t>(requant_fast(r, out, inv_scale, addc, span)) << (8 * j);
-      }
-      ow[k] = word ^ sign_fix;
-    }
-    y[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
+    av.x ^= p.a_flip; av.y ^= p.a_flip; av.z ^= p.a_flip; av.w ^= p.a_flip;
+    bv.x ^= p.b_flip; bv.y ^= p.b_flip; bv.z ^= p.b_flip; bv.w ^= p.b_flip;
+    uint4 o;
+    o.x = add_q_word<FAST>(av.x, bv.x, p);
+    o.y = add_q_word<FAST>(av.y, bv.y, p);
+    o.z = add_q_word<FAST>(av.z, bv.z, p);
+    o.w = add_q_word<FAST>(av.w, bv.w, p);
+    y[i] = o;
+  }
+}
+
+// Quantized Add by table: the result is a function of the two input bytes, so a 64 KB table (built on the
+// host with the reference's float sequence) answers every element exactly, whatever the share of
+// near-tie sums that would send the arithmetic kernel to its exact path.  The table lives in shared
+// memory; entry (a, b) sits at a*256 + (b ^ ((a & 31) << 2)), which spreads pairs that share b over
+// the banks.  Per element: build the index, one byte load, pack.
+__device__ __forceinline__ uint32_t add_lut_word(uint32_t aw, uint32_t bw, const uint8_t* tab) {
+  uint32_t p01 = __byte_perm(bw, aw, 0x5140), p23 = __byte_perm(bw, aw, 0x7362);   // [b0 a0 b1 a1], [b2 a2 b3 a3]
+  p01 ^= (p01 >> 6) & 0x007C007Cu;
+  p23 ^= (p23 >> 6) & 0x007C007Cu;
+  const uint32_t r0 = tab[p01 & 0xFFFFu], r1 = tab[p01 >> 16], r2 = tab[p23 & 0xFFFFu], r3 = tab[p23 >> 16];
+  return __byte_perm(__byte_perm(r0, r1, 0x0040), __byte_perm(r2, r3, 0x0040), 0x5410);
+}
+
+__global__ void __launch_bounds__(256) add_q_lut_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
+                                                        const uint4* __restrict__ table, uint4* __restrict__ y, size_t n16) {
+  extern __shared__ uint4 tab4[];
+  for (int i = threadIdx.x; i < 4096; i += 256) tab4[i] = table[i];
+  __syncthreads();
+  const uint8_t* tab = reinterpret_cast<const uint8_t*>(tab4);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
+    const uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
+    uint4 o;
+    o.x = add_lut_word(av.x, bv.x, tab);
+    o.y = add_lut_word(av.y, bv.y, tab);
+    o.z = add_lut_word(av.z, bv.z, tab);
+    o.w = add_lut_word(av.w, bv.w, tab);
+    y[i] = o;
   }
 }
 
@@ -512,25 +874,31 @@ __global__ void im2col_whcn_kernel(const uint8_t* __restrict__ x, int Kp, int zx
 // ---------------------------------------------------------------- wrappers
 
 void launch_whcn_to_cl(const void* src, void* dst, int N, int C, int H, int W, int Cp, int elem, cudaStream_t s) {
-  const long long total = static_cast<long long>(N) * H * W * Cp;
-  if (total == 0) return;
-  if (elem == 1)
-    whcn_to_cl_kernel<uint8_t><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(src),
-                                                                           static_cast<uint8_t*>(dst), N, C, H, W, Cp);
-  else
-    whcn_to_cl_kernel<uint32_t><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint32_t*>(src),
-                                                                            static_cast<uint32_t*>(dst), N, C, H, W, Cp);
+  const int HW = H * W;
+  if (N == 0 || HW == 0 || Cp == 0) return;
+  if (elem == 1) {
+    const dim3 grid((HW + 63) / 64, (Cp + 63) / 64, N);
+    const bool aligned = (HW & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
+    if (aligned) whcn_to_cl_u8_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+    else whcn_to_cl_u8_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+  } else {
+    const dim3 grid((HW + 31) / 32, (Cp + 31) / 32, N);
+    whcn_to_cl_u32_kernel<<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), C, HW, Cp);
+  }
 }
 
 void launch_cl_to_whcn(const void* src, void* dst, int N, int C, int H, int W, int Cp, int elem, cudaStream_t s) {
-  const long long total = static_cast<long long>(N) * C * H * W;
-  if (total == 0) return;
-  if (elem == 1)
-    cl_to_whcn_kernel<uint8_t><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(src),
-                                                                           static_cast<uint8_t*>(dst), N, C, H, W, Cp);
-  else
-    cl_to_whcn_kernel<uint32_t><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint32_t*>(src),
-                                                                            static_cast<uint32_t*>(dst), N, C, H, W, Cp);
+  const int HW = H * W;
+  if (N == 0 || HW == 0 || C == 0) return;
+  if (elem == 1) {
+    const dim3 grid((HW + 63) / 64, (C + 63) / 64, N);
+    const bool aligned = (HW & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0;
+    if (aligned) cl_to_whcn_u8_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+    else cl_to_whcn_u8_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+  } else {
+    const dim3 grid((HW + 31) / 32, (C + 31) / 32, N);
+    cl_to_whcn_u32_kernel<<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), C, HW, Cp);
+  }
 }
 
 void launch_conv_simt(const void* x, int x_signed, const int8_t* w8, int Kp, const ConvGeom& g,
@@ -559,6 +927,27 @@ void launch_depthwise_q(const void* x, int x_signed, int zx, const int16_t* wd, 
                                                                           static_cast<uint8_t*>(y));
 }
 
+void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* wtab, const int32_t* bias_full,
+                          const float* acc_scale, const ConvGeom& g, OutQuant out, int exact_only, void* y, cudaStream_t s) {
+  if (static_cast<long long>(g.N) * g.Ho * g.Wo == 0) return;
+  DwParams p;
+  p.g = g;
+  p.wtab = wtab;
+  p.bias_full = bias_full;
+  p.acc_scale = acc_scale;
+  p.out = out;
+  p.x_flip = x_signed ? 0x80808080u : 0u;
+  p.zx_word = static_cast<uint32_t>((zx + (x_signed ? 128 : 0)) & 0xFF) * 0x01010101u;
+  p.exact_only = exact_only;
+  p.slab = g.Ocp < 64 ? g.Ocp : 64;
+  const int chunks = p.slab / 16;
+  const int pairs_per_block = 256 / chunks;
+  const long long total_pairs = static_cast<long long>(g.N) * g.Ho * ((g.Wo + 1) / 2);
+  const dim3 grid(static_cast<unsigned>((total_pairs + pairs_per_block - 1) / pairs_per_block), (g.Ocp + p.slab - 1) / p.slab);
+  const size_t smem = static_cast<size_t>(g.kh) * g.kw * (p.slab / 4) * sizeof(uint4);
+  depthwise_q16_kernel<<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(x), p, static_cast<uint8_t*>(y));
+}
+
 void launch_conv_f32(const float* x, const float* w, const float* bias, int multiplier, int w_ic, const ConvGeom& g,
                      float* y, cudaStream_t s) {
   const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * g.Oc;
@@ -568,14 +957,19 @@ void launch_conv_f32(const float* x, const float* w, const float* bias, int mult
 
 void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int in_zp, int same_quant, const ConvGeom& g,
                    OutQuant out, void* y, cudaStream_t s) {
+  const uint8_t* xp = static_cast<const uint8_t*>(x);
+  uint8_t* yp = static_cast<uint8_t*>(y);
+  if (g.kw * g.kh <= 256 && g.dx == 1 && g.dy == 1) {
+    const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * (g.Cp / 16);
+    if (total == 0) return;
+    if (is_signed) pool_q16_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(xp, type, in_scale, in_zp, same_quant, g, out, yp);
+    else pool_q16_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(xp, type, in_scale, in_zp, same_quant, g, out, yp);
+    return;
+  }
   const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * (g.Cp / 4);
   if (total == 0) return;
-  if (is_signed)
-    pool_q_kernel<true><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(x), type, in_scale, in_zp,
-                                                                    same_quant, g, out, static_cast<uint8_t*>(y));
-  else
-    pool_q_kernel<false><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(x), type, in_scale,
-                                                                     in_zp, same_quant, g, out, static_cast<uint8_t*>(y));
+  if (is_signed) pool_q_kernel<true><<<grid_for(total, kThreads), kThreads, 0, s>>>(xp, type, in_scale, in_zp, same_quant, g, out, yp);
+  else pool_q_kernel<false><<<grid_for(total, kThreads), kThreads, 0, s>>>(xp, type, in_scale, in_zp, same_quant, g, out, yp);
 }
 
 void launch_pool_f32(const float* x, int type, const ConvGeom& g, float* y, cudaStream_t s) {
@@ -585,18 +979,51 @@ void launch_pool_f32(const float* x, int type, const ConvGeom& g, float* y, cuda
 }
 
 void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, int b_signed, float sb, int zb,
-                  OutQuant out, int /*out_signed*/, void* y, size_t n, cudaStream_t s) {
+                  OutQuant out, int out_signed, void* y, size_t n, cudaStream_t s) {
   const size_t n16 = n / 16;
   if (n16 == 0) return;
-  unsigned grid = grid_for(static_cast<long long>(n16), kThreads);
-  if (grid > 148u * 16u) grid = 148u * 16u;
+  AddParams p;
+  p.sa = sa; p.sb = sb; p.scale = out.scale;
+  p.za = za; p.zb = zb;
+  p.a_flip = a_signed ? 0x80808080u : 0u;
+  p.b_flip = b_signed ? 0x80808080u : 0u;
+  p.ca = -(8388608.0f + static_cast<float>(za + (a_signed ? 128 : 0)));
+  p.cb = -(8388608.0f + static_cast<float>(zb + (b_signed ? 128 : 0)));
+  const float inv = 1.0f / out.scale;
+  p.inv_hi = inv * (1.0f + 4.76837158203125e-7f);
+  p.inv_lo = inv * (1.0f - 4.76837158203125e-7f);
+  p.magic = 12582912.0f + static_cast<float>(out.zp);
+  p.out = out;
+  p.out_signed = out_signed;
+  // the saturating pack clamps to the type's range; a narrower range or a huge scale ratio takes the exact path
+  const bool full_range = out_signed ? (out.lo == -128 && out.hi == 127) : (out.lo == 0 && out.hi == 255);
+  const float bound = 256.0f * (fabsf(sa) + fabsf(sb)) * fabsf(inv) + 512.0f;
+  const bool fast = full_range && bound < B2VX_FAST_ROUND_LIMIT && out.scale > 0.0f && std::isfinite(inv);
+  // two 16-element steps per thread keep enough loads in flight; at most 8 blocks per SM
+  unsigned grid = grid_for(static_cast<long long>((n16 + 1) / 2), 256);
+  if (grid > 148u * 8u) grid = 148u * 8u;
   const uint4* pa = static_cast<const uint4*>(a);
   const uint4* pb = static_cast<const uint4*>(b);
   uint4* py = static_cast<uint4*>(y);
-  if (a_signed && b_signed) add_q_kernel<true, true><<<grid, kThreads, 0, s>>>(pa, sa, za, pb, sb, zb, out, py, n16);
-  else if (a_signed) add_q_kernel<true, false><<<grid, kThreads, 0, s>>>(pa, sa, za, pb, sb, zb, out, py, n16);
-  else if (b_signed) add_q_kernel<false, true><<<grid, kThreads, 0, s>>>(pa, sa, za, pb, sb, zb, out, py, n16);
-  else add_q_kernel<false, false><<<grid, kThreads, 0, s>>>(pa, sa, za, pb, sb, zb, out, py, n16);
+  if (fast) add_q_kernel<true><<<grid, 256, 0, s>>>(pa, pb, p, py, n16);
+  else add_q_kernel<false><<<grid, 256, 0, s>>>(pa, pb, p, py, n16);
+}
+
+void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* y, size_t n, cudaStream_t s) {
+  const size_t n16 = n / 16;
+  if (n16 == 0) return;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    cudaFuncSetAttribute(add_q_lut_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  // three 64 KB blocks per SM; every block should have enough elements to repay its table load
+  unsigned grid = grid_for(static_cast<long long>((n16 + 3) / 4), 256);
+  if (grid > 148u * 3u) grid = 148u * 3u;
+  add_q_lut_kernel<<<grid, 256, 65536, s>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
+                                            reinterpret_cast<const uint4*>(table), static_cast<uint4*>(y), n16);
 }
 
 void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s) {

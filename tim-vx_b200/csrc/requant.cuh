@@ -59,5 +59,130 @@ __device__ __forceinline__ int requant_fast(float real, const OutQuant& q, float
   return u;
 }
 
+
+// ---- two float32 lanes per instruction (sm_100 packed arithmetic) -----------
+// Each half is an IEEE round-to-nearest operation, bit-identical to the scalar
+// intrinsic; the point is one issue slot for two results in instruction-bound
+// requantization loops.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_pack_bits(uint32_t lo, uint32_t hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void f2_unpack_bits(f32x2 v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// Caution: a packed product consumed by a packed addition was observed to come back as one fused
+// multiply-add on sm_100a (product unrounded) despite the .rn qualifiers.  Where the reference rounds
+// the product and the sum separately, compute the product with the scalar __fmul_rn instead.
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// d = sat_u8(a) << 8 | sat_u8(b) | c << 16 (or the s8 form): saturating narrow + pack in one instruction.
+__device__ __forceinline__ uint32_t pack_sat_u8(int hi, int lo, uint32_t upper) {
+  uint32_t d;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_sat_s8(int hi, int lo, uint32_t upper) {
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+  return d;
+}
+
+// Host-side test for the two-sided fast rounding used by the hot loops: the value real/scale must stay
+// far inside the range where adding 1.5*2^23 leaves the integer in the low mantissa bits.
+#define B2VX_FAST_ROUND_LIMIT 2097152.0f   /* 2^21 */
+
+// Requantization of one 16-column chunk of an accumulator row: acc + folded bias -> float ->
+// * accumulator scale -> quantized bytes (the exact sequence is requant() in requant.cuh).
+//
+// Fast form.  The reference computes q = R(real / scale) + zp with R = round-half-even except within an
+// ulp of a .5 fraction.  r_hi and r_lo round real*(1/scale)*(1 +- 2^-21) + zp to the nearest integer in
+// one fused multiply-add each: adding 1.5*2^23 + zp leaves the integer in the low mantissa bits, and
+// as long as real/scale stays above -1.5*2^23 (the host checks a bound on it when the plan is made, and
+// sets exact_only otherwise) the bit pattern is monotone, so the saturating narrow below stays right.
+// The reference's quotient (one rounding, of a divisor within half an ulp of 1/scale) lies strictly
+// between the two products; when both give the same byte after saturation, that byte is the
+// reference's result.  Elements that disagree are redone with the exact code.  Float work is done two
+// lanes per instruction (f32x2) and four results are narrowed and packed by two cvt.pack.sat.
+struct RequantConsts {
+  f32x2 inv_hi2, inv_lo2, magic2;
+  float inv_hi, inv_lo, magic;
+  OutQuant oq;
+  int out_signed;
+  int exact_only;
+};
+
+__device__ __forceinline__ uint32_t sat_pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3, int out_signed) {
+  const int v0 = static_cast<int>(b0) - 0x4B400000, v1 = static_cast<int>(b1) - 0x4B400000;
+  const int v2 = static_cast<int>(b2) - 0x4B400000, v3 = static_cast<int>(b3) - 0x4B400000;
+  return out_signed ? pack_sat_s8(v1, v0, pack_sat_s8(v3, v2, 0u)) : pack_sat_u8(v1, v0, pack_sat_u8(v3, v2, 0u));
+}
+
+// sub: dz * S of this row (0 without a weight zero point); corr: this row's border correction for the
+// chunk's 16 channels, or null.
+__device__ __forceinline__ uint4 requant_chunk16(const int (&acc)[16], const int* bias, const float* scale,
+                                                 const RequantConsts& rc, int sub, const int32_t* corr) {
+  f32x2 real[8];
+#pragma unroll
+  for (int g4 = 0; g4 < 4; ++g4) {
+    int4 b4 = *reinterpret_cast<const int4*>(bias + g4 * 4);
+    b4.x -= sub; b4.y -= sub; b4.z -= sub; b4.w -= sub;
+    if (corr) {
+      const int4 c4 = __ldg(reinterpret_cast<const int4*>(corr + g4 * 4));
+      b4.x += c4.x; b4.y += c4.y; b4.z += c4.z; b4.w += c4.w;
+    }
+    const ulonglong2 s4 = *reinterpret_cast<const ulonglong2*>(scale + g4 * 4);   // two f32x2
+    real[2 * g4] = f2_mul(f2_pack(__int2float_rn(acc[g4 * 4 + 0] + b4.x), __int2float_rn(acc[g4 * 4 + 1] + b4.y)), s4.x);
+    real[2 * g4 + 1] = f2_mul(f2_pack(__int2float_rn(acc[g4 * 4 + 2] + b4.z), __int2float_rn(acc[g4 * 4 + 3] + b4.w)), s4.y);
+  }
+  uint32_t wh[4], wl[4];
+#pragma unroll
+  for (int g4 = 0; g4 < 4; ++g4) {
+    uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+    f2_unpack_bits(f2_fma(real[2 * g4], rc.inv_hi2, rc.magic2), h0, h1);
+    f2_unpack_bits(f2_fma(real[2 * g4 + 1], rc.inv_hi2, rc.magic2), h2, h3);
+    f2_unpack_bits(f2_fma(real[2 * g4], rc.inv_lo2, rc.magic2), l0, l1);
+    f2_unpack_bits(f2_fma(real[2 * g4 + 1], rc.inv_lo2, rc.magic2), l2, l3);
+    wh[g4] = sat_pack4(h0, h1, h2, h3, rc.out_signed);
+    wl[g4] = sat_pack4(l0, l1, l2, l3, rc.out_signed);
+  }
+  if (((wh[0] ^ wl[0]) | (wh[1] ^ wl[1]) | (wh[2] ^ wl[2]) | (wh[3] ^ wl[3])) != 0u || rc.exact_only) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t m = 0xFFu << (8 * (i & 3));
+      if (((wh[i >> 2] ^ wl[i >> 2]) & m) != 0u || rc.exact_only) {
+        float lo, hi;
+        f2_unpack(real[i >> 1], lo, hi);
+        const uint32_t q = static_cast<uint32_t>(requant((i & 1) ? hi : lo, rc.oq)) & 0xFFu;
+        wh[i >> 2] = (wh[i >> 2] & ~m) | (q << (8 * (i & 3)));
+      }
+    }
+  }
+  return make_uint4(wh[0], wh[1], wh[2], wh[3]);
+}
+
 }  // namespace b2vx
 #endif  // B2VX_REQUANT_CUH_

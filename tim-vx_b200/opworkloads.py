@@ -1,0 +1,93 @@
+"""Single-operator workloads of the quantized path, built through the b2vx C ABI.
+
+Three seeded shapes families, each a graph with one compute node (plus the Relu the
+convolution sweep fuses):
+
+  conv:<k>:<cin>:<cout>:<hw>:<stride>   Conv2d k x k, SAME padding, uint8 input (scale 0.02,
+                                         zero point 128), per-channel symmetric int8 weights with
+                                         scales U(0.001, 0.01), int32 bias, Relu, uint8 output
+                                         (scale 0.05, zero point 0); batch = images
+  gemm:<m>:<n>:<k>                       FullyConnected: uint8 [k, m] (zero point 128, scale 0.02)
+                                         x int8 per-channel [k, n] -> uint8 [n, m]
+  add:<elements>                         quantized Add of two uint8 tensors with different scales
+
+build(spec, batch, graph, rng) adds the tensors and the node to `graph` (a pyb2vx.Graph on either
+the CUDA library or the CPU oracle library) and returns a dict describing the work of one pass.
+"""
+import numpy as np
+
+import pyb2vx as B
+
+
+def parse(spec):
+    f = spec.split(":")
+    kind = f[0]
+    nums = [int(v) for v in f[1:]]
+    if kind == "conv" and len(nums) == 5:
+        return kind, nums
+    if kind == "gemm" and len(nums) == 3:
+        return kind, nums
+    if kind == "add" and len(nums) == 1:
+        return kind, nums
+    raise ValueError("workload must be conv:k:cin:cout:hw:stride, gemm:m:n:k or add:elements, got %r" % spec)
+
+
+def _u8(rng, shape):
+    return rng.integers(0, 256, size=shape, dtype=np.uint8)
+
+
+def build(spec, batch, g, rng):
+    kind, v = parse(spec)
+    if kind == "conv":
+        k, cin, cout, hw, stride = v
+        x = g.tensor(B.DT_UINT8, [hw, hw, cin, batch], B.ATTR_INPUT, scale=0.02, zero_point=128)
+        ws = rng.uniform(0.001, 0.01, cout).astype(np.float32)
+        wd = rng.integers(-127, 128, size=(cout, cin, k, k)).astype(np.int8)
+        w = g.tensor(B.DT_INT8, [k, k, cin, cout], B.ATTR_CONSTANT, scales=ws, channel_dim=3, data=wd)
+        b = g.tensor(B.DT_INT32, [cout], B.ATTR_CONSTANT, scales=np.float32(0.02) * ws, channel_dim=0,
+                     data=rng.integers(-1000, 1001, size=cout).astype(np.int32))
+        y = g.tensor(B.DT_UINT8, [], B.ATTR_TRANSIENT, scale=0.05, zero_point=0)
+        z = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.05, zero_point=0)
+        g.conv2d(x, w, b, y, stride=(stride, stride), pad_type=B.PAD_SAME)
+        g.relu(y, z)
+        ho = (hw + stride - 1) // stride
+        macs = batch * ho * ho * cout * cin * k * k
+        return {"inputs": [(x, _u8(rng, (batch, cin, hw, hw)))], "outputs": [z], "ops": 2 * macs,
+                "bytes": batch * hw * hw * cin + batch * ho * ho * cout + cout * cin * k * k + 4 * cout,
+                "bound": "tensor", "units": batch,
+                "name": "Conv2d %dx%d %d->%d on %dx%d stride %d SAME + Relu, batch %d" % (k, k, cin, cout, hw, hw, stride, batch)}
+    if kind == "gemm":
+        m, n, k = v
+        x = g.tensor(B.DT_UINT8, [k, m], B.ATTR_INPUT, scale=0.02, zero_point=128)
+        ws = (rng.uniform(0.001, 0.01, n) / np.sqrt(k / 64.0)).astype(np.float32)
+        wd = rng.integers(-127, 128, size=(n, k)).astype(np.int8)
+        w = g.tensor(B.DT_INT8, [k, n], B.ATTR_CONSTANT, scales=ws, channel_dim=1, data=wd)
+        b = g.tensor(B.DT_INT32, [n], B.ATTR_CONSTANT, scales=np.float32(0.02) * ws, channel_dim=0,
+                     data=rng.integers(-1000, 1001, size=n).astype(np.int32))
+        y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.1, zero_point=100)
+        g.fully_connected(x, w, b, y, axis=0, weights=n)
+        return {"inputs": [(x, _u8(rng, (m, k)))], "outputs": [y], "ops": 2 * m * n * k,
+                "bytes": m * k + n * k + m * n + 4 * n, "bound": "tensor" if m >= 512 else "hbm", "units": m,
+                "name": "FullyConnected M=%d N=%d K=%d" % (m, n, k)}
+    n = v[0]
+    c = 256
+    assert n % c == 0, "add: element count must be a multiple of 256"
+    dims = [c, n // c]
+    a = g.tensor(B.DT_UINT8, dims, B.ATTR_INPUT, scale=0.02, zero_point=128)
+    b = g.tensor(B.DT_UINT8, dims, B.ATTR_INPUT, scale=0.035, zero_point=117)
+    y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.05, zero_point=120)
+    g.add(a, b, y)
+    return {"inputs": [(a, _u8(rng, (n // c, c))), (b, _u8(rng, (n // c, c)))], "outputs": [y], "ops": 0,
+            "bytes": 3 * n, "bound": "hbm", "units": n, "name": "quantized Add of %d uint8 elements" % n}
+
+
+def cpu_sample(spec):
+    """A bounded slice of `spec` for timing on host cores: (spec of the slice, description)."""
+    kind, v = parse(spec)
+    if kind == "gemm":
+        m = min(v[0], 64)
+        return "gemm:%d:%d:%d" % (m, v[1], v[2]), "%d of the %d rows per step" % (m, v[0])
+    if kind == "add":
+        n = min(v[0], 1 << 24)
+        return "add:%d" % n, "%d of the %d elements per step" % (n, v[0])
+    return spec, "a reduced batch per step (--cpu-batch)"
