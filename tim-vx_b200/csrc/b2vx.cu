@@ -896,7 +896,25 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
     const OutQuant oq = out_quant(y);
     const size_t nel = y.cl_bytes;
     // B2VX_ADD_KERNEL=lut|alu forces one of the two kernels (read when the graph is created)
-    const bool use_lut = g->add_mode == 1 || (g->add_mode == 0 && nel >= (size_t(1) << 22));
+    // The arithmetic kernel is the faster one unless many byte pairs give a sum whose quotient by the
+    // output scale is (nearly) a .5 fraction, each of which costs it an exact re-evaluation: scales in a
+    // simple ratio do that (0.4*i + 0.7*j hits .5 for one pair in ten).  Count such pairs; large tensors
+    // with more than 2% of them use the table kernel.
+    bool use_lut = g->add_mode == 1;
+    if (g->add_mode == 0 && nel >= (size_t(1) << 23)) {
+      int near = 0;
+      const float inv = 1.0f / oq.scale;
+      for (int ia = 0; ia < 256; ia += 3) {
+        const float fa = (static_cast<float>(as ? static_cast<int>(static_cast<int8_t>(ia)) : ia) - static_cast<float>(za)) * sa;
+        for (int ib = 0; ib < 256; ib += 5) {
+          const float fb = (static_cast<float>(bs ? static_cast<int>(static_cast<int8_t>(ib)) : ib) - static_cast<float>(zb)) * sb;
+          const double t = static_cast<double>(fa + fb) * inv;
+          const double frac = std::fabs(t) - std::floor(std::fabs(t));
+          if (std::fabs(frac - 0.5) < std::fabs(t) * 1e-6 + 1e-9) ++near;
+        }
+      }
+      use_lut = near * 50 > 86 * 52;   // 86 x 52 pairs sampled
+    }
     if (use_lut) {
       // every pair of input bytes through the reference's float sequence, once
       std::vector<uint8_t> table(65536);
