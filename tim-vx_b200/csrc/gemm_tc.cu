@@ -45,9 +45,12 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "kernels.h"
+#include "pdl.cuh"
 #include "requant.cuh"
 
 // Build with -DB2VX_TC_TRACE to record, for CTA 0, when each role passed its waits (a debugging aid
@@ -55,8 +58,11 @@
 #ifdef B2VX_TC_TRACE
 #define TC_TRACE(role, idx, slot) \
   do { if (p.trace && blockIdx.x == 0 && (idx) < 64) p.trace[((role) * 64 + (idx)) * 2 + (slot)] = clock64(); } while (0)
+#define TC_MARK(k) \
+  do { if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[384 + (k)] = clock64(); } while (0)
 #else
 #define TC_TRACE(role, idx, slot) do { } while (0)
+#define TC_MARK(k) do { } while (0)
 #endif
 
 namespace b2vx {
@@ -102,7 +108,7 @@ struct GemmParams {
   int dz;                  // weight zero point left after the shift into int8; != 0: column BNd of the accumulator is S
   int exact_only;          // requantize with the exact sequence only (the fast form's range check failed)
 #ifdef B2VX_TC_TRACE
-  long long* trace;        // clock64 stamps of CTA 0, [3 roles][64 iterations][2]
+  long long* trace;        // clock64 stamps of CTA 0, [3 roles][64 iterations][2], then 8 marks
 #endif
 };
 
@@ -261,10 +267,15 @@ struct SmemHeader {
   alignas(16) float scale[256];
 };
 
+// EXTRA: rows carry a weight-zero-point term (p.dz, S column) and/or border corrections
+// (p.ep.border_corr); the plain form contains no code for either.
+template <bool EXTRA>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
+  TC_MARK(0);
+  pdl_trigger();   // the next kernel of the stream may begin its own prologue
   // [ring of stages | two staging tiles | header], the first two 1024-byte aligned (128-byte swizzle)
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
@@ -283,6 +294,12 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.m_tiles * p.n_tiles;
 
+  if (threadIdx.x == 32) {
+    // descriptor fetches overlap the rest of the prologue instead of delaying the first loads
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+    if (p.store_span) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_d)) : "memory");
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&hdr->full[s]), 2);     // A producer + B producer
@@ -296,6 +313,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   const int n_tile = blockIdx.x % p.n_tiles;   // fixed per CTA: gridDim.x is a multiple of n_tiles
+  // hence the j-th tile of this CTA is M tile m_tile0 + j * m_step (no division per tile)
+  const int m_tile0 = blockIdx.x / p.n_tiles, m_step = gridDim.x / p.n_tiles;
   for (int i = threadIdx.x; i < p.BNd; i += kThreadsTc) {
     const int oc = n_tile * p.BNd + i;
     hdr->bias[i] = oc < p.Ocp ? p.ep.bias_full[oc] : 0;
@@ -311,6 +330,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = hdr->tmem_base;
+  TC_MARK(1);
 
   if (warp == 0 || warp == 2) {
     // ------------------------------------------------------------ TMA producers (warp 0: A, warp 2: B)
@@ -318,9 +338,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // stage's k-blocks.
     const bool is_a = warp == 0;
     uint32_t it = 0, s = 0, ph = 0;   // stage index and ring phase, advanced without divisions
+    // Everything above touched only constants and this CTA's own shared/tensor memory.  The operand
+    // loads are the first access to what earlier kernels of the stream produced (and every later
+    // access of this kernel, the output stores included, depends on them through the barriers).
+    pdl_wait();
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const int m_tile = tile / p.n_tiles;
+    int m_tile = m_tile0;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, m_tile += m_step) {
       int w0 = 0, h0 = 0, n0 = 0;
       if (p.conv) {
         // tile -> first output pixel (tw, th, tn), turned into input coordinates of tap (0,0).
@@ -423,28 +447,17 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int row_in_tile = quarter * 32 + lane;
     const bool store_issuer = threadIdx.x == kFirstEpilogueWarp * 32;
     const OutQuant oq = p.ep.out;
-    RequantConsts rc;
-    {
-      const float inv = __frcp_rn(oq.scale);
-      rc.inv_hi = __fmul_rn(inv, 1.000000476837158203125f);    // 1 + 2^-21
-      rc.inv_lo = __fmul_rn(inv, 0.999999523162841796875f);    // 1 - 2^-21
-      rc.magic = 12582912.0f + static_cast<float>(oq.zp);
-      rc.inv_hi2 = f2_pack(rc.inv_hi, rc.inv_hi);
-      rc.inv_lo2 = f2_pack(rc.inv_lo, rc.inv_lo);
-      rc.magic2 = f2_pack(rc.magic, rc.magic);
-      rc.oq = oq;
-      rc.out_signed = oq.lo < 0;
-      rc.exact_only = p.exact_only;
-    }
+    const RequantConsts rc = make_requant_consts(oq, p.exact_only);
     // position of this thread's 16-byte chunks inside a staging column block
     const int span_b = p.store_span;
+    const int span_shift = span_b == 128 ? 7 : (span_b == 64 ? 6 : 5);
     const int swz = span_b == 128 ? (row_in_tile & 7) : span_b == 64 ? ((row_in_tile >> 1) & 3) : ((row_in_tile >> 2) & 1);
     int j = 0;
     // Once a wait has given up (alive == false) a thread does no more work, but it keeps running the
     // loop and both barriers of every tile, so the other epilogue threads never wait for it.
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
-      const int m_tile = tile / p.n_tiles;
+      const int m_tile = m_tile0 + j * m_step;
       const uint32_t a = j & 1, aph = (j >> 1) & 1;
       uint8_t* stage_out = staging + a * staging_bytes;
       if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
@@ -463,13 +476,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int rest = m_tile / p.tiles_w;
         th = rest % p.tiles_h;
         tn = rest / p.tiles_h;
-        if (!span_b || p.ep.border_corr) {
+        if (!span_b || (EXTRA && p.ep.border_corr)) {
           const int i = row_in_tile % p.TW, r2 = row_in_tile / p.TW;
           const int jh = r2 % p.TH, l = r2 / p.TH;
           const int wo = tw * p.TW + i, ho = th * p.TH + jh, n = tn * p.TN + l;
           if (l < p.TN && wo < p.Wo && ho < p.Ho && n < p.Nimg) {
             row = (static_cast<long long>(n) * p.Ho + ho) * p.Wo + wo;
-            if (p.ep.border_corr) {
+            if (EXTRA && p.ep.border_corr) {
               const int cls = __ldg(p.ep.row_class + ho) * p.ep.n_col_classes + __ldg(p.ep.col_class + wo);
               if (cls) corr_row = p.ep.border_corr + static_cast<size_t>(cls) * p.Ocp + n_tile * p.BNd;
             }
@@ -483,7 +496,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       // Chunks col_group, col_group + 4, ... of 16 columns; the TMEM load of the next chunk is in flight
       // while the current one is requantized.
       int sub = 0;
-      if (p.dz != 0) {
+      if (EXTRA && p.dz != 0) {
         // S = sum of this row's inputs: the accumulator column of the all-ones weight row
         int s_val;
         tc_ld_32x1(taddr + p.BNd, s_val);
@@ -493,10 +506,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       auto emit = [&](const int (&acc)[16], int c0) {
         const int cbase = n_tile * p.BNd + c0;
         if (!span_b && (row < 0 || cbase + 16 > p.Ocp)) return;
-        const uint4 out16 = requant_chunk16(acc, &hdr->bias[c0], &hdr->scale[c0], rc, sub,
-                                            (corr_row && cbase + 16 <= p.Ocp) ? corr_row + c0 : nullptr);
+        const uint4 out16 = requant_chunk16<EXTRA>(acc, &hdr->bias[c0], &hdr->scale[c0], rc, sub,
+                                                   (corr_row && cbase + 16 <= p.Ocp) ? corr_row + c0 : nullptr);
         if (span_b) {
-          const int blk = c0 / span_b, chunk = (c0 - blk * span_b) >> 4;
+          const int blk = c0 >> span_shift, chunk = (c0 & (span_b - 1)) >> 4;   // span_b is 32, 64 or 128
           *reinterpret_cast<uint4*>(stage_out + static_cast<size_t>(blk) * kBlockM * span_b + row_in_tile * span_b +
                                     ((chunk ^ swz) << 4)) = out16;
         } else {
@@ -544,12 +557,15 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
       if (warp == kFirstEpilogueWarp && lane == 0) TC_TRACE(2, j, 1);
     }
-    if (store_issuer) tma_store_wait_all();
+    // The staging buffers only have to stay intact until the last store has read them; the writes
+    // themselves are complete, like any other store, when the grid is.
+    if (store_issuer) tma_store_wait_read<0>();
   }
 
   // ---------------------------------------------------------------- common exit
   tc_fence_before();
   __syncthreads();
+  TC_MARK(2);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -700,7 +716,8 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       *why = "gemm_tc: cannot raise the dynamic shared memory limit";
       return false;
     }
@@ -846,6 +863,18 @@ GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s) {
   const double rows = static_cast<double>(M < kBlockM ? M : kBlockM);
   GemmTcTiling best = {0, 0, 0};
   double best_time = 0.0;
+  // B2VX_TC_BN=<width>: force the tile width (a tuning aid; ignored when it does not fit)
+  static const int forced = [] { const char* e = std::getenv("B2VX_TC_BN"); return e ? std::atoi(e) : 0; }();
+  if (forced >= 16 && forced <= max_data && (forced & 15) == 0) {
+    const int nt = (Ocp + forced - 1) / forced;
+    const int data = (((Ocp + nt - 1) / nt) + 15) & ~15;
+    if (nt <= sms) {
+      best.n_tiles = nt;
+      best.data = data;
+      best.rows = data + extra;
+      return best;
+    }
+  }
   int last_data = 0;
   for (int nt = (Ocp + max_data - 1) / max_data; nt <= sms && nt * 16 <= Ocp + 15; ++nt) {
     const int data = (((Ocp + nt - 1) / nt) + 15) & ~15;
@@ -927,22 +956,30 @@ cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
 #ifdef B2VX_TC_TRACE
   GemmTcPlan* mp = const_cast<GemmTcPlan*>(plan);
   if (!mp->params.trace) {
-    cudaMalloc(reinterpret_cast<void**>(&mp->params.trace), 3 * 64 * 2 * sizeof(long long));
-    cudaMemset(mp->params.trace, 0, 3 * 64 * 2 * sizeof(long long));
+    cudaMalloc(reinterpret_cast<void**>(&mp->params.trace), (3 * 64 * 2 + 8) * sizeof(long long));
+    cudaMemset(mp->params.trace, 0, (3 * 64 * 2 + 8) * sizeof(long long));
   }
 #endif
-  gemm_i8_tc_kernel<<<plan->grid, kThreadsTc, plan->smem, s>>>(plan->map_a, plan->map_b, plan->map_d, plan->params);
+  cudaError_t launched;
+  if (plan->params.dz != 0 || plan->params.ep.border_corr != nullptr)
+    launched = launch_pdl(gemm_i8_tc_kernel<true>, dim3(plan->grid), dim3(kThreadsTc), plan->smem, s, plan->map_a, plan->map_b,
+                          plan->map_d, plan->params);
+  else
+    launched = launch_pdl(gemm_i8_tc_kernel<false>, dim3(plan->grid), dim3(kThreadsTc), plan->smem, s, plan->map_a, plan->map_b,
+                          plan->map_d, plan->params);
+  if (launched != cudaSuccess) return launched;
 #ifdef B2VX_TC_TRACE
   {
     static int launches = 0;
     if (++launches == 3) {
       cudaStreamSynchronize(s);
-      long long h[3 * 64 * 2];
+      long long h[3 * 64 * 2 + 8];
       cudaMemcpy(h, plan->params.trace, sizeof(h), cudaMemcpyDeviceToHost);
       const long long t0 = h[0];
       const GemmParams& p = plan->params;
       std::fprintf(stderr, "trace: BN %d BK %d group %d stages %d num_kb %d m_tiles %d n_tiles %d grid %d conv %d span %d\n", p.BN, p.BK,
                    p.group, p.stages, p.num_kb, p.m_tiles, p.n_tiles, plan->grid, p.conv, p.store_span);
+      std::fprintf(stderr, "marks: entry %lld  prologue done %lld  all roles done %lld (cycles from first producer wait)\n", h[384] - t0, h[385] - t0, h[386] - t0);
       for (int i = 0; i < 20; ++i)
         std::fprintf(stderr, "it %2d  prodA slot-free %7lld issued %7lld | mma data-in %7lld committed %7lld | epi acc-ready %7lld done %7lld\n",
                      i, h[(0 * 64 + i) * 2] - t0, h[(0 * 64 + i) * 2 + 1] - t0, h[(1 * 64 + i) * 2] - t0,

@@ -5,6 +5,7 @@
 #include <cmath>
 
 #include "kernels.h"
+#include "pdl.cuh"
 #include "requant.cuh"
 
 namespace b2vx {
@@ -35,6 +36,8 @@ __device__ __forceinline__ void transpose4x4(uint32_t (&r)[4]) {
 template <bool ALIGNED>
 __global__ void __launch_bounds__(256) whcn_to_cl_u8_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int C,
                                                             int HW, int Cp) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ uint4 tile[64 * 4];
   const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 64, n = blockIdx.z;
   const int t = threadIdx.x;
@@ -74,6 +77,8 @@ __global__ void __launch_bounds__(256) whcn_to_cl_u8_kernel(const uint8_t* __res
 template <bool ALIGNED>
 __global__ void __launch_bounds__(256) cl_to_whcn_u8_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int C,
                                                             int HW, int Cp) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ uint4 tile[64 * 4];
   const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 64, n = blockIdx.z;
   const int t = threadIdx.x;
@@ -325,10 +330,16 @@ __device__ __forceinline__ void dw_mac16(int (&acc)[16], const uint4& x, const u
   }
 }
 
-__global__ void __launch_bounds__(256) depthwise_q16_kernel(const uint8_t* __restrict__ x, DwParams p, uint8_t* __restrict__ y) {
+// KH, KW > 0: window known at compile time, both tap loops unroll and the loads of all taps can be in
+// flight together (the kernel is latency-bound otherwise); 0: any window.
+template <int KH, int KW, bool XS>
+__global__ void __launch_bounds__(256, 2) depthwise_q16_kernel(const uint8_t* __restrict__ x, DwParams p, uint8_t* __restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ uint4 dw_smem[];               // [taps][slab / 4] groups of four weight words
   const ConvGeom& g = p.g;
-  const int taps = g.kh * g.kw;
+  const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
+  const int taps = kh * kw;
   const int c_slab = blockIdx.y * p.slab;
   const int slab_ch = min(p.slab, g.Ocp - c_slab);   // multiple of 16
   const int quads = p.slab >> 2;
@@ -360,43 +371,118 @@ __global__ void __launch_bounds__(256) depthwise_q16_kernel(const uint8_t* __res
 #pragma unroll
   for (int i = 0; i < 16; ++i) { acc0[i] = 0; acc1[i] = 0; }
   const uint8_t* img = x + static_cast<size_t>(n) * g.H * g.W * g.Cp + c0;
-  for (int ky = 0; ky < g.kh; ++ky) {
+#pragma unroll
+  for (int ky = 0; ky < kh; ++ky) {
     const int hi = ho * g.sy - g.pt + ky * g.dy;
     const bool row_ok = hi >= 0 && hi < g.H;
     const uint8_t* rowp = img + static_cast<size_t>(row_ok ? hi : 0) * g.W * g.Cp;
-    for (int kx = 0; kx < g.kw; ++kx) {
-      const uint4* wq = dw_smem + (ky * g.kw + kx) * quads + 4 * chunk;
+#pragma unroll
+    for (int kx = 0; kx < kw; ++kx) {
+      const uint4* wq = dw_smem + (ky * kw + kx) * quads + 4 * chunk;
       const uint4 w[4] = {wq[0], wq[1], wq[2], wq[3]};
       const int wi0 = wo0 * g.sx - g.pl + kx * g.dx, wi1 = wi0 + g.sx;
       uint4 xa = zx4, xb = zx4;
       if (row_ok && wi0 >= 0 && wi0 < g.W) {
-        xa = *reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi0) * g.Cp);
-        xa.x ^= p.x_flip; xa.y ^= p.x_flip; xa.z ^= p.x_flip; xa.w ^= p.x_flip;
+        xa = __ldg(reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi0) * g.Cp));
+        if (XS) { xa.x ^= 0x80808080u; xa.y ^= 0x80808080u; xa.z ^= 0x80808080u; xa.w ^= 0x80808080u; }
       }
       if (second && row_ok && wi1 >= 0 && wi1 < g.W) {
-        xb = *reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi1) * g.Cp);
-        xb.x ^= p.x_flip; xb.y ^= p.x_flip; xb.z ^= p.x_flip; xb.w ^= p.x_flip;
+        xb = __ldg(reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi1) * g.Cp));
+        if (XS) { xb.x ^= 0x80808080u; xb.y ^= 0x80808080u; xb.z ^= 0x80808080u; xb.w ^= 0x80808080u; }
       }
       dw_mac16(acc0, xa, w);
       dw_mac16(acc1, xb, w);
     }
   }
-  RequantConsts rc;
-  {
-    const float inv = __frcp_rn(p.out.scale);
-    rc.inv_hi = __fmul_rn(inv, 1.000000476837158203125f);
-    rc.inv_lo = __fmul_rn(inv, 0.999999523162841796875f);
-    rc.magic = 12582912.0f + static_cast<float>(p.out.zp);
-    rc.inv_hi2 = f2_pack(rc.inv_hi, rc.inv_hi);
-    rc.inv_lo2 = f2_pack(rc.inv_lo, rc.inv_lo);
-    rc.magic2 = f2_pack(rc.magic, rc.magic);
-    rc.oq = p.out;
-    rc.out_signed = p.out.lo < 0;
-    rc.exact_only = p.exact_only;
-  }
+  const RequantConsts rc = make_requant_consts(p.out, p.exact_only);
   uint8_t* out = y + ((static_cast<size_t>(n) * g.Ho + ho) * g.Wo + wo0) * g.Ocp + c0;
-  *reinterpret_cast<uint4*>(out) = requant_chunk16(acc0, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
-  if (second) *reinterpret_cast<uint4*>(out + g.Ocp) = requant_chunk16(acc1, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
+  *reinterpret_cast<uint4*>(out) = requant_chunk16<false>(acc0, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
+  if (second) *reinterpret_cast<uint4*>(out + g.Ocp) = requant_chunk16<false>(acc1, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
+}
+
+// The same computation with the input staged in shared memory: a block owns a 64-channel slab of an
+// 8 x TW tile of output pixels (TW = 8 or 16), copies the input patch it needs (halo included, the
+// zero point where the patch leaves the image, signed bytes already biased) with independent 128-bit
+// loads that are all in flight together, and then computes from shared memory with no bounds checks.
+// Several blocks per SM overlap one block's copy with another's arithmetic.  A thread owns 16
+// channels of pixel q (and q + 64 when TW = 16) of the tile.
+template <int KH, int KW, bool XS>
+__global__ void __launch_bounds__(256) depthwise_q16s_kernel(const uint8_t* __restrict__ x, DwParams p, int tw_shift,
+                                                             int IH, int IW, uint8_t* __restrict__ y) {
+  pdl_trigger();
+  extern __shared__ uint4 dw_smem[];               // [taps][16] weight quads, then [IH][IW][4] input chunks
+  const ConvGeom& g = p.g;
+  const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
+  const int taps = kh * kw;
+  const int TW = 1 << tw_shift;
+  const int tiles_w = (g.Wo + TW - 1) >> tw_shift, tiles_h = (g.Ho + 7) >> 3;
+  int tile = blockIdx.x;
+  const int tile_w = tile % tiles_w; tile /= tiles_w;
+  const int tile_h = tile % tiles_h;
+  const int n = tile / tiles_h;
+  const int c_slab = blockIdx.y * 64;
+  const int slab_chunks = min(64, g.Ocp - c_slab) >> 4;
+  const int ho0 = tile_h * 8, wo0 = tile_w * TW;
+  const int hi0 = ho0 * g.sy - g.pt, wi0 = wo0 * g.sx - g.pl;
+  uint4* wsm = dw_smem;
+  uint4* xsm = dw_smem + taps * 16;
+  for (int i = threadIdx.x; i < taps * 16; i += 256) {
+    const int t = i >> 4, q = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if ((q >> 2) < slab_chunks) v = *reinterpret_cast<const uint4*>(p.wtab + static_cast<size_t>(t) * g.Ocp + c_slab + 4 * q);
+    wsm[i] = v;
+  }
+  pdl_wait();   // weights are constants; the input is the first thing another kernel produced
+  {
+    const uint4 zx4 = make_uint4(p.zx_word, p.zx_word, p.zx_word, p.zx_word);
+    const uint8_t* img = x + static_cast<size_t>(n) * g.H * g.W * g.Cp + c_slab;
+    const int units = IH * IW * 4;
+    const int chunk = threadIdx.x & 3;
+    int pix = threadIdx.x >> 2;
+    int ih = pix / IW, iw = pix - ih * IW;          // 64 pixels further per step
+    const int step_h = 64 / IW, step_w = 64 - step_h * IW;
+#pragma unroll 4
+    for (int u = threadIdx.x; u < units; u += 256) {
+      const int hi = hi0 + ih, wi = wi0 + iw;
+      uint4 v = zx4;
+      if (chunk < slab_chunks && hi >= 0 && hi < g.H && wi >= 0 && wi < g.W) {
+        v = __ldg(reinterpret_cast<const uint4*>(img + (static_cast<size_t>(hi) * g.W + wi) * g.Cp + 16 * chunk));
+        if (XS) { v.x ^= 0x80808080u; v.y ^= 0x80808080u; v.z ^= 0x80808080u; v.w ^= 0x80808080u; }
+      }
+      xsm[u] = v;
+      ih += step_h; iw += step_w;
+      if (iw >= IW) { iw -= IW; ++ih; }
+    }
+  }
+  __syncthreads();
+  const int chunk = threadIdx.x & 3;
+  if (chunk >= slab_chunks) return;
+  const int q = threadIdx.x >> 2;                  // 0..63
+  const int tr = q >> 3, tc = q & 7;
+  const bool two = TW == 16;
+  int acc0[16], acc1[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { acc0[i] = 0; acc1[i] = 0; }
+  const uint4* xrow0 = xsm + ((tr * g.sy) * IW + tc * g.sx) * 4 + chunk;
+  const int second_off = 8 * g.sx * 4;
+#pragma unroll
+  for (int ky = 0; ky < kh; ++ky) {
+#pragma unroll
+    for (int kx = 0; kx < kw; ++kx) {
+      const uint4* wq = wsm + (ky * kw + kx) * 16 + 4 * chunk;
+      const uint4 w[4] = {wq[0], wq[1], wq[2], wq[3]};
+      const uint4* xp = xrow0 + (ky * g.dy * IW + kx * g.dx) * 4;
+      dw_mac16(acc0, xp[0], w);
+      if (two) dw_mac16(acc1, xp[second_off], w);
+    }
+  }
+  const RequantConsts rc = make_requant_consts(p.out, p.exact_only);
+  const int ho = ho0 + tr, wo = wo0 + tc, c0 = c_slab + 16 * chunk;
+  if (ho >= g.Ho) return;
+  uint8_t* out = y + ((static_cast<size_t>(n) * g.Ho + ho) * g.Wo + wo) * g.Ocp + c0;
+  if (wo < g.Wo) *reinterpret_cast<uint4*>(out) = requant_chunk16<false>(acc0, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
+  if (two && wo + 8 < g.Wo)
+    *reinterpret_cast<uint4*>(out + 8 * g.Ocp) = requant_chunk16<false>(acc1, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
 }
 
 // ---------------------------------------------------------------- float32 conv
@@ -494,6 +580,8 @@ __global__ void pool_q_kernel(const uint8_t* __restrict__ x, int type, float in_
 template <bool XS>
 __global__ void __launch_bounds__(256) pool_q16_kernel(const uint8_t* __restrict__ x, int type, float in_scale, int in_zp,
                                                        int same_quant, ConvGeom g, OutQuant out, uint8_t* __restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const int chunks = g.Cp >> 4;
   const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * chunks;
   long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -662,6 +750,8 @@ __device__ __forceinline__ uint32_t add_q_word(uint32_t aw, uint32_t bw, const A
 template <bool FAST>
 __global__ void __launch_bounds__(256) add_q_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, AddParams p,
                                                     uint4* __restrict__ y, size_t n16) {
+  pdl_wait();
+  pdl_trigger();
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
     uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
@@ -691,9 +781,11 @@ __device__ __forceinline__ uint32_t add_lut_word(uint32_t aw, uint32_t bw, const
 
 __global__ void __launch_bounds__(256) add_q_lut_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
                                                         const uint4* __restrict__ table, uint4* __restrict__ y, size_t n16) {
+  pdl_trigger();
   extern __shared__ uint4 tab4[];
-  for (int i = threadIdx.x; i < 4096; i += 256) tab4[i] = table[i];
+  for (int i = threadIdx.x; i < 4096; i += 256) tab4[i] = table[i];   // a constant of the graph
   __syncthreads();
+  pdl_wait();
   const uint8_t* tab = reinterpret_cast<const uint8_t*>(tab4);
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
@@ -716,6 +808,8 @@ __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restr
 // quantization) as a 256-entry table built on the host with the reference's
 // float sequence; 16 elements per thread.
 __global__ void lut_q_kernel(const uint4* __restrict__ x, const uint8_t* __restrict__ lut, uint4* __restrict__ y, size_t n16) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ uint8_t t[256];
   for (int i = threadIdx.x; i < 256; i += blockDim.x) t[i] = lut[i];
   __syncthreads();
@@ -830,6 +924,8 @@ __global__ void im2col_kernel(const uint8_t* __restrict__ x, int Cs, int Kp, int
 // pieces of im2col rows from a per-k offset table.
 __global__ void im2col_whcn_kernel(const uint8_t* __restrict__ x, int Kp, int zx, ConvGeom g, int rowlen,
                                    uint8_t* __restrict__ col) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ uint8_t sm[];
   const int n = blockIdx.y, ho = blockIdx.x;
   const int rows = g.C * g.kh;
@@ -879,8 +975,8 @@ void launch_whcn_to_cl(const void* src, void* dst, int N, int C, int H, int W, i
   if (elem == 1) {
     const dim3 grid((HW + 63) / 64, (Cp + 63) / 64, N);
     const bool aligned = (HW & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
-    if (aligned) whcn_to_cl_u8_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
-    else whcn_to_cl_u8_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+    if (aligned) launch_pdl(whcn_to_cl_u8_kernel<true>, dim3(grid), dim3(256), 0, s, static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+    else launch_pdl(whcn_to_cl_u8_kernel<false>, dim3(grid), dim3(256), 0, s, static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
   } else {
     const dim3 grid((HW + 31) / 32, (Cp + 31) / 32, N);
     whcn_to_cl_u32_kernel<<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), C, HW, Cp);
@@ -893,8 +989,8 @@ void launch_cl_to_whcn(const void* src, void* dst, int N, int C, int H, int W, i
   if (elem == 1) {
     const dim3 grid((HW + 63) / 64, (C + 63) / 64, N);
     const bool aligned = (HW & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0;
-    if (aligned) cl_to_whcn_u8_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
-    else cl_to_whcn_u8_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+    if (aligned) launch_pdl(cl_to_whcn_u8_kernel<true>, dim3(grid), dim3(256), 0, s, static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
+    else launch_pdl(cl_to_whcn_u8_kernel<false>, dim3(grid), dim3(256), 0, s, static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), C, HW, Cp);
   } else {
     const dim3 grid((HW + 31) / 32, (C + 31) / 32, N);
     cl_to_whcn_u32_kernel<<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), C, HW, Cp);
@@ -945,7 +1041,43 @@ void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* w
   const long long total_pairs = static_cast<long long>(g.N) * g.Ho * ((g.Wo + 1) / 2);
   const dim3 grid(static_cast<unsigned>((total_pairs + pairs_per_block - 1) / pairs_per_block), (g.Ocp + p.slab - 1) / p.slab);
   const size_t smem = static_cast<size_t>(g.kh) * g.kw * (p.slab / 4) * sizeof(uint4);
-  depthwise_q16_kernel<<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(x), p, static_cast<uint8_t*>(y));
+  const uint8_t* xp = static_cast<const uint8_t*>(x);
+  uint8_t* yp = static_cast<uint8_t*>(y);
+  {
+    // staged form when the input patch of an 8 x TW output tile fits comfortably in shared memory
+    const int tw_shift = g.Wo <= 8 ? 3 : 4;
+    const int TW = 1 << tw_shift;
+    const int IH = 7 * g.sy + (g.kh - 1) * g.dy + 1, IW = (TW - 1) * g.sx + (g.kw - 1) * g.dx + 1;
+    const size_t smem_s = (static_cast<size_t>(g.kh) * g.kw * 16 + static_cast<size_t>(IH) * IW * 4) * sizeof(uint4);
+    if (smem_s <= 72 * 1024 && IW >= 1) {
+      const dim3 grid_s(static_cast<unsigned>(((g.Wo + TW - 1) / TW) * ((g.Ho + 7) / 8) * g.N), (g.Ocp + 63) / 64);
+      static bool attr_set[64] = {false};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        cudaFuncSetAttribute(depthwise_q16s_kernel<3, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        cudaFuncSetAttribute(depthwise_q16s_kernel<3, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        cudaFuncSetAttribute(depthwise_q16s_kernel<0, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        cudaFuncSetAttribute(depthwise_q16s_kernel<0, 0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+      }
+      if (g.kh == 3 && g.kw == 3) {
+        if (x_signed) launch_pdl(depthwise_q16s_kernel<3, 3, true>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
+        else launch_pdl(depthwise_q16s_kernel<3, 3, false>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
+      } else {
+        if (x_signed) launch_pdl(depthwise_q16s_kernel<0, 0, true>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
+        else launch_pdl(depthwise_q16s_kernel<0, 0, false>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
+      }
+      return;
+    }
+  }
+  if (g.kh == 3 && g.kw == 3) {
+    if (x_signed) launch_pdl(depthwise_q16_kernel<3, 3, true>, dim3(grid), dim3(256), smem, s, xp, p, yp);
+    else launch_pdl(depthwise_q16_kernel<3, 3, false>, dim3(grid), dim3(256), smem, s, xp, p, yp);
+  } else {
+    if (x_signed) launch_pdl(depthwise_q16_kernel<0, 0, true>, dim3(grid), dim3(256), smem, s, xp, p, yp);
+    else launch_pdl(depthwise_q16_kernel<0, 0, false>, dim3(grid), dim3(256), smem, s, xp, p, yp);
+  }
 }
 
 void launch_conv_f32(const float* x, const float* w, const float* bias, int multiplier, int w_ic, const ConvGeom& g,
@@ -962,8 +1094,8 @@ void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int i
   if (g.kw * g.kh <= 256 && g.dx == 1 && g.dy == 1) {
     const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * (g.Cp / 16);
     if (total == 0) return;
-    if (is_signed) pool_q16_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(xp, type, in_scale, in_zp, same_quant, g, out, yp);
-    else pool_q16_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(xp, type, in_scale, in_zp, same_quant, g, out, yp);
+    if (is_signed) launch_pdl(pool_q16_kernel<true>, dim3(grid_for(total, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
+    else launch_pdl(pool_q16_kernel<false>, dim3(grid_for(total, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
     return;
   }
   const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * (g.Cp / 4);
@@ -1005,8 +1137,8 @@ void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, 
   const uint4* pa = static_cast<const uint4*>(a);
   const uint4* pb = static_cast<const uint4*>(b);
   uint4* py = static_cast<uint4*>(y);
-  if (fast) add_q_kernel<true><<<grid, 256, 0, s>>>(pa, pb, p, py, n16);
-  else add_q_kernel<false><<<grid, 256, 0, s>>>(pa, pb, p, py, n16);
+  if (fast) launch_pdl(add_q_kernel<true>, dim3(grid), dim3(256), 0, s, pa, pb, p, py, n16);
+  else launch_pdl(add_q_kernel<false>, dim3(grid), dim3(256), 0, s, pa, pb, p, py, n16);
 }
 
 void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* y, size_t n, cudaStream_t s) {
@@ -1022,7 +1154,7 @@ void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* 
   // three 64 KB blocks per SM; every block should have enough elements to repay its table load
   unsigned grid = grid_for(static_cast<long long>((n16 + 3) / 4), 256);
   if (grid > 148u * 3u) grid = 148u * 3u;
-  add_q_lut_kernel<<<grid, 256, 65536, s>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
+  launch_pdl(add_q_lut_kernel, dim3(grid), dim3(256), 65536, s, static_cast<const uint4*>(a), static_cast<const uint4*>(b),
                                             reinterpret_cast<const uint4*>(table), static_cast<uint4*>(y), n16);
 }
 
@@ -1036,7 +1168,7 @@ void launch_lut_q(const void* x, const uint8_t* lut, void* y, size_t n, cudaStre
   if (n16 == 0) return;
   unsigned grid = grid_for(static_cast<long long>(n16), kThreads);
   if (grid > 148u * 16u) grid = 148u * 16u;
-  lut_q_kernel<<<grid, kThreads, 0, s>>>(static_cast<const uint4*>(x), lut, static_cast<uint4*>(y), n16);
+  launch_pdl(lut_q_kernel, dim3(grid), dim3(kThreads), 0, s, static_cast<const uint4*>(x), lut, static_cast<uint4*>(y), n16);
 }
 
 void launch_relu_f32(const float* x, float upper, float* y, size_t n, cudaStream_t s) {
@@ -1064,7 +1196,7 @@ void launch_im2col_whcn(const void* x, int Kp, int zx, const ConvGeom& g, void* 
   const int rowlen = (g.Wo - 1) * g.sx + (g.kw - 1) * g.dx + 1;
   const size_t smem = static_cast<size_t>(Kp) * sizeof(int) + static_cast<size_t>(g.C) * g.kh * rowlen;
   dim3 grid(g.Ho, g.N);
-  im2col_whcn_kernel<<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(x), Kp, zx, g, rowlen, static_cast<uint8_t*>(col));
+  launch_pdl(im2col_whcn_kernel, dim3(grid), dim3(256), smem, s, static_cast<const uint8_t*>(x), Kp, zx, g, rowlen, static_cast<uint8_t*>(col));
 }
 
 }  // namespace b2vx

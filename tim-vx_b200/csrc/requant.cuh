@@ -132,27 +132,53 @@ struct RequantConsts {
   float inv_hi, inv_lo, magic;
   OutQuant oq;
   int out_signed;
+  uint32_t out_flip;
   int exact_only;
 };
 
-__device__ __forceinline__ uint32_t sat_pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3, int out_signed) {
+// Four rounded values (bit patterns of r = t + magic) -> four saturated bytes.  The magic constant carries
+// zp, plus 128 for int8 outputs, so that the saturation is always the unsigned one; out_flip
+// (0x80808080 for int8, else 0) turns the biased bytes back into two's complement afterwards.
+__device__ __forceinline__ uint32_t sat_pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
   const int v0 = static_cast<int>(b0) - 0x4B400000, v1 = static_cast<int>(b1) - 0x4B400000;
   const int v2 = static_cast<int>(b2) - 0x4B400000, v3 = static_cast<int>(b3) - 0x4B400000;
-  return out_signed ? pack_sat_s8(v1, v0, pack_sat_s8(v3, v2, 0u)) : pack_sat_u8(v1, v0, pack_sat_u8(v3, v2, 0u));
+  return pack_sat_u8(v1, v0, pack_sat_u8(v3, v2, 0u));
 }
 
-// sub: dz * S of this row (0 without a weight zero point); corr: this row's border correction for the
-// chunk's 16 channels, or null.
+// Constants of one output quantization for requant_chunk16.
+__device__ __forceinline__ RequantConsts make_requant_consts(const OutQuant& oq, int exact_only) {
+  RequantConsts rc;
+  const float inv = __frcp_rn(oq.scale);
+  rc.inv_hi = __fmul_rn(inv, 1.000000476837158203125f);    // 1 + 2^-21
+  rc.inv_lo = __fmul_rn(inv, 0.999999523162841796875f);    // 1 - 2^-21
+  rc.out_signed = oq.lo < 0;
+  rc.magic = 12582912.0f + static_cast<float>(oq.zp + (rc.out_signed ? 128 : 0));
+  rc.inv_hi2 = f2_pack(rc.inv_hi, rc.inv_hi);
+  rc.inv_lo2 = f2_pack(rc.inv_lo, rc.inv_lo);
+  rc.magic2 = f2_pack(rc.magic, rc.magic);
+  rc.oq = oq;
+  rc.out_flip = rc.out_signed ? 0x80808080u : 0u;
+  rc.exact_only = exact_only;
+  return rc;
+}
+
+// EXTRA: the row has a term to subtract from every accumulator (sub = dz * S of this row) and/or a
+// border correction (corr: 16 values for this chunk's channels, or null); without EXTRA both are
+// ignored.  A template parameter because as run-time conditions they were compiled into instructions
+// every chunk pays for.
+template <bool EXTRA>
 __device__ __forceinline__ uint4 requant_chunk16(const int (&acc)[16], const int* bias, const float* scale,
                                                  const RequantConsts& rc, int sub, const int32_t* corr) {
   f32x2 real[8];
 #pragma unroll
   for (int g4 = 0; g4 < 4; ++g4) {
     int4 b4 = *reinterpret_cast<const int4*>(bias + g4 * 4);
-    b4.x -= sub; b4.y -= sub; b4.z -= sub; b4.w -= sub;
-    if (corr) {
-      const int4 c4 = __ldg(reinterpret_cast<const int4*>(corr + g4 * 4));
-      b4.x += c4.x; b4.y += c4.y; b4.z += c4.z; b4.w += c4.w;
+    if (EXTRA) {
+      b4.x -= sub; b4.y -= sub; b4.z -= sub; b4.w -= sub;
+      if (corr) {
+        const int4 c4 = __ldg(reinterpret_cast<const int4*>(corr + g4 * 4));
+        b4.x += c4.x; b4.y += c4.y; b4.z += c4.z; b4.w += c4.w;
+      }
     }
     const ulonglong2 s4 = *reinterpret_cast<const ulonglong2*>(scale + g4 * 4);   // two f32x2
     real[2 * g4] = f2_mul(f2_pack(__int2float_rn(acc[g4 * 4 + 0] + b4.x), __int2float_rn(acc[g4 * 4 + 1] + b4.y)), s4.x);
@@ -166,22 +192,26 @@ __device__ __forceinline__ uint4 requant_chunk16(const int (&acc)[16], const int
     f2_unpack_bits(f2_fma(real[2 * g4 + 1], rc.inv_hi2, rc.magic2), h2, h3);
     f2_unpack_bits(f2_fma(real[2 * g4], rc.inv_lo2, rc.magic2), l0, l1);
     f2_unpack_bits(f2_fma(real[2 * g4 + 1], rc.inv_lo2, rc.magic2), l2, l3);
-    wh[g4] = sat_pack4(h0, h1, h2, h3, rc.out_signed);
-    wl[g4] = sat_pack4(l0, l1, l2, l3, rc.out_signed);
+    wh[g4] = sat_pack4(h0, h1, h2, h3);
+    wl[g4] = sat_pack4(l0, l1, l2, l3);
   }
-  if (((wh[0] ^ wl[0]) | (wh[1] ^ wl[1]) | (wh[2] ^ wl[2]) | (wh[3] ^ wl[3])) != 0u || rc.exact_only) {
+  uint32_t differ = (wh[0] ^ wl[0]) | (wh[1] ^ wl[1]) | (wh[2] ^ wl[2]) | (wh[3] ^ wl[3]);
+  // Opaque to the optimizer: otherwise it notices that each per-element test below implies this one,
+  // drops it, and every chunk pays for sixteen tests.
+  asm volatile("" : "+r"(differ));
+  if (differ != 0u || rc.exact_only) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const uint32_t m = 0xFFu << (8 * (i & 3));
       if (((wh[i >> 2] ^ wl[i >> 2]) & m) != 0u || rc.exact_only) {
         float lo, hi;
         f2_unpack(real[i >> 1], lo, hi);
-        const uint32_t q = static_cast<uint32_t>(requant((i & 1) ? hi : lo, rc.oq)) & 0xFFu;
+        const uint32_t q = (static_cast<uint32_t>(requant((i & 1) ? hi : lo, rc.oq)) ^ rc.out_flip) & 0xFFu;
         wh[i >> 2] = (wh[i >> 2] & ~m) | (q << (8 * (i & 3)));
       }
     }
   }
-  return make_uint4(wh[0], wh[1], wh[2], wh[3]);
+  return make_uint4(wh[0] ^ rc.out_flip, wh[1] ^ rc.out_flip, wh[2] ^ rc.out_flip, wh[3] ^ rc.out_flip);
 }
 
 }  // namespace b2vx
