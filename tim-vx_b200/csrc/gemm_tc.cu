@@ -24,13 +24,15 @@
 //   warps 4-19  epilogue     16 warps (four per SM scheduler, to hide latency).
 //                            A warp owns the 32 TMEM lanes (tile rows) its id
 //                            maps to and every fourth 16-column chunk:
-//                            tcgen05.ld, folded bias, requantize, pack 16
-//                            bytes, write them swizzled into a staging tile in
-//                            shared memory; one thread then stores the tile
-//                            with TMA (clipped at the tensor edge).  Two
-//                            accumulator buffers and two staging tiles overlap
-//                            tile i's epilogue with tile i+1's MMAs and with
-//                            tile i-1's store.
+//                            tcgen05.ld (the next chunk's load in flight),
+//                            folded bias, requantize two floats per
+//                            instruction, saturating pack, and a 16-byte store
+//                            per thread straight to the output.  No barrier
+//                            joins the warps, so they drift apart and work on
+//                            neighbouring tiles; two accumulator buffers
+//                            overlap tile i's epilogue with tile i+1's MMAs.
+//                            (B2VX_TC_STORE=tma: write the bytes swizzled into
+//                            a staging tile instead and store it with TMA.)
 // A stage holds up to `group` k-blocks so that small k-blocks share one
 // barrier round trip.  The grid is a multiple of the number of N tiles: a CTA
 // keeps one N tile for life (bias and scales staged in shared memory once) and
@@ -673,6 +675,12 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.sbo = 8u * p.BK;
   // Output staging for the TMA store: column blocks as wide as the widest swizzle span dividing BN.
   p.store_span = p.BNd % 128 == 0 ? 128 : (p.BNd % 64 == 0 ? 64 : (p.BNd % 32 == 0 ? 32 : 0));
+  // Measured over the ResNet-50 layer shapes, threads storing their 16-byte pieces themselves beat the
+  // staged TMA store (no CTA-wide barrier per tile, epilogue warps drift apart and overlap tiles, and
+  // the staging memory goes to the operand ring instead), so that is the default;
+  // B2VX_TC_STORE=tma selects the staged store.
+  static const bool tma_store = [] { const char* e = std::getenv("B2VX_TC_STORE"); return e && std::strcmp(e, "tma") == 0; }();
+  if (!tma_store) p.store_span = 0;
   const size_t staging = p.store_span ? 2 * static_cast<size_t>(kBlockM) * p.BNd : 0;
   // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
   // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
