@@ -98,6 +98,9 @@ CONV_CASES = {
     "u8_w_oc300": G.conv2d_q(9, 9, 32, 2, 1, 1, 300, w_kind="u8"),
     "u8_w_3x3_oc272_pad": G.conv2d_q(12, 10, 48, 1, 3, 3, 272, w_kind="u8"),
     "u8_w_stem": G.conv2d_q(30, 30, 3, 2, 3, 3, 32, stride=(2, 2), w_kind="u8", in_q=(0.02, 114)),
+    # wide first-layer filters: the row-of-8 im2col, with and without a weight zero point
+    "stem5x5_c3_u8w": G.conv2d_q(31, 29, 3, 2, 5, 5, 24, w_kind="u8", in_q=(0.02, 114)),
+    "stem8x6_c4_s1": G.conv2d_q(20, 17, 4, 1, 8, 6, 16, in_q=(0.03, 9)),
 }
 
 

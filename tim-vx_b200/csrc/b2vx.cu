@@ -398,17 +398,22 @@ struct PackedContraction {
 // Weight element (kx,ky,ic,oc) of a WHIcOc kernel as a signed value together
 // with the zero point that still has to be subtracted from it: u8 weights are
 // shifted by 128 into int8 (dz = zw-128), s8 weights are kept (dz = zw).
-// K index = tap*Cs + ic, or ic*taps + tap when channel_major (the kernel tensor's own order,
-// used with the WHCN im2col).  Rows come in n_tiles tiles of tile_rows rows: output channel oc is row
+// K index by k_order: 0 tap*Cs + ic; 1 ic*taps + tap (the kernel tensor's own order, used with the
+// WHCN im2col); 2 (ky*C + ic)*8 + kx (filter rows padded to 8 taps, used with the row-of-8 im2col).  Rows come in n_tiles tiles of tile_rows rows: output channel oc is row
 // (oc / tile_data) * tile_rows + oc % tile_data; when some dz != 0 and tile_rows > tile_data, row
 // tile_data of every tile is the all-ones row (its dot product with an input row is S).
 void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* bias, int kw, int kh, int C, int Cs,
-                      int Kp, int Oc, int Ocp, int n_tiles, int tile_data, int tile_rows, bool channel_major,
+                      int Kp, int Oc, int Ocp, int n_tiles, int tile_data, int tile_rows, int k_order,
                       PackedContraction* out) {
   const int rows = n_tiles * tile_rows;
   const int taps = kw * kh;
   const bool w_u8 = w.d.dtype == B2VX_DT_UINT8;
   const bool per_ch = w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL;
+  auto kidx = [&](int t, int ic) -> size_t {
+    if (k_order == 1) return static_cast<size_t>(ic) * taps + t;
+    if (k_order == 2) return (static_cast<size_t>(t / kw) * C + ic) * 8 + t % kw;
+    return static_cast<size_t>(t) * Cs + ic;
+  };
   out->rows = rows;
   out->Kp = Kp;
   out->bias_full.assign(Ocp, 0);
@@ -436,7 +441,7 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
       for (int t = 0; t < taps; ++t) {
         const size_t src = (static_cast<size_t>(oc) * C + ic) * taps + t;   // WHIcOc, W fastest: tap = ky*kw + kx
         const int v = w_u8 ? static_cast<int>(w.host[src]) - 128 : static_cast<int>(reinterpret_cast<const int8_t*>(w.host.data())[src]);
-        row[channel_major ? static_cast<size_t>(ic) * taps + t : static_cast<size_t>(t) * Cs + ic] = static_cast<int8_t>(v);
+        row[kidx(t, ic)] = static_cast<int8_t>(v);
         tapsum[t] += v;
       }
     }
@@ -454,7 +459,7 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
     for (int tile = 0; tile < n_tiles; ++tile) {
       int8_t* ones = out->w8.data() + (static_cast<size_t>(tile) * tile_rows + tile_data) * Kp;
       for (int t = 0; t < taps; ++t)
-        for (int ic = 0; ic < C; ++ic) ones[channel_major ? static_cast<size_t>(ic) * taps + t : static_cast<size_t>(t) * Cs + ic] = 1;
+        for (int ic = 0; ic < C; ++ic) ones[kidx(t, ic)] = 1;
     }
   }
 }
@@ -543,7 +548,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     //             zero point the border pixels get a per-class correction in the epilogue;
     //   whcn      first layers with < 16 channels: im2col straight from the WHCN graph input, K = (c,ky,kx);
     //   im2col    everything else: explicit matrix in scratch memory, padding filled with zx.
-    enum { IDENTITY, IMPLICIT, WHCN, IM2COL } mode;
+    enum { IDENTITY, IMPLICIT, WHCN, WHCN8, IM2COL } mode;
     static const bool allow_strided = [] { const char* e = std::getenv("B2VX_IMPLICIT_STRIDED"); return !(e && e[0] == '0'); }();
     const bool strided = geo.sx != 1 || geo.sy != 1;
     // Border classes of an implicit convolution: output rows (columns) grouped by which ky (kx) fall
@@ -575,21 +580,25 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     }
     if (identity_1x1 || identity_full) mode = IDENTITY;
     else if (x.C >= 16 && (!need_border || classes_ok) && (!strided || allow_strided)) mode = IMPLICIT;
+    else if (x.C < 16 && (x.d.attr & B2VX_ATTR_INPUT) && x.d_io != nullptr && kw >= 5 && kw <= 8 && geo.dx == 1 && geo.dy == 1 &&
+             static_cast<size_t>(x.C) * kh * im2col_whcn8_pitch(geo) + 16 <= 40u * 1024u)
+      mode = WHCN8;  // wide filter rows: 8 consecutive input bytes per (pixel, ky, c)
     else if (x.C < 16 && (x.d.attr & B2VX_ATTR_INPUT) && x.d_io != nullptr &&
              static_cast<size_t>(x.C) * kh * ((geo.Wo - 1) * geo.sx + (kw - 1) * geo.dx + 1) + 4u * round_up(taps * x.C, 16) <= 40u * 1024u)
       mode = WHCN;   // the staging rows of one output row fit in shared memory
     else mode = IM2COL;
     int Cs, Kp, M;
     const void* A = nullptr;
-    const bool need_im2col = mode == WHCN || mode == IM2COL;
+    const bool need_im2col = mode == WHCN || mode == WHCN8 || mode == IM2COL;
     if (mode == IDENTITY && identity_1x1) { Cs = x.Cp; Kp = x.Cp; M = static_cast<int>(P); A = cl_in(x); }
     else if (mode == IDENTITY) { Cs = x.Cp; Kp = taps * x.Cp; M = y.N; A = cl_in(x); }
     else if (mode == IMPLICIT) { Cs = x.Cp; Kp = taps * x.Cp; M = static_cast<int>(P); A = cl_in(x); }
     else if (mode == WHCN) { Cs = x.C; Kp = round_up(taps * x.C, 16); M = static_cast<int>(P); }
+    else if (mode == WHCN8) { Cs = x.C; Kp = round_up(kh * x.C * 8, 16); M = static_cast<int>(P); }
     else { Cs = x.C < 16 ? x.C : x.Cp; Kp = round_up(taps * Cs, 16); M = static_cast<int>(P); }
     const GemmTcTiling tiling = gemm_tc_choose_tiling(M, y.Cp, Kp, any_dz ? 1 : 0);
     const int Np = tiling.n_tiles * tiling.rows;
-    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, tiling.n_tiles, tiling.data, tiling.rows, mode == WHCN, &pk);
+    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, tiling.n_tiles, tiling.data, tiling.rows, mode == WHCN ? 1 : (mode == WHCN8 ? 2 : 0), &pk);
     ep.dz_uniform = any_dz ? dz_value : 0;
     if (mode == IMPLICIT && need_border) {
       // correction of class (r, c) = minus the folded contribution of every tap that is out of bounds there
@@ -643,7 +652,16 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     const std::string lbl = label;
     void* ycl = y.d_cl;
     const int ldd = y.Cp, Oc = y.C, y_signed = y.d.dtype == B2VX_DT_INT8;
-    if (mode == WHCN) {
+    if (mode == WHCN8) {
+      const void* xio = x.d_io;
+      Step s_col;
+      s_col.info = make_info("im2col_whcn8", node_index, 0, x.elems() + static_cast<uint64_t>(M) * Kp);
+      s_col.fn = [=](cudaStream_t st2) {
+        launch_im2col_whcn8(xio, Kp, zx, geo, g->scratch, st2);
+        return cudaGetLastError();
+      };
+      g->steps.push_back(std::move(s_col));
+    } else if (mode == WHCN) {
       const void* xio = x.d_io;
       Step s_col;
       s_col.info = make_info("im2col_whcn", node_index, 0, x.elems() + static_cast<uint64_t>(M) * Kp);
@@ -688,7 +706,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
 
   // CUDA-core path: K = tap*Cp + c, out-of-bounds taps are skipped and corrected per tap.
   const int Kp = taps * x.Cp;
-  pack_contraction(x, w, bias, kw, kh, x.C, x.Cp, Kp, y.C, y.Cp, 1, y.Cp, y.Cp + 1, false, &pk);
+  pack_contraction(x, w, bias, kw, kh, x.C, x.Cp, Kp, y.C, y.Cp, 1, y.Cp, y.Cp + 1, 0, &pk);
   int8_t* dw8 = nullptr; int32_t *dbias = nullptr, *ddz = nullptr, *dtapc = nullptr; float* dscale = nullptr;
   b2vx_status st = upload(g, pk.w8, &dw8);
   if (st == B2VX_OK) st = upload(g, pk.bias_full, &dbias);

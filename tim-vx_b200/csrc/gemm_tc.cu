@@ -78,6 +78,7 @@ constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kThreadsTc = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kMaxGroup = 8;
+constexpr int kMaxAccBuffers = 8;
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 constexpr int kSmemBudget = 226 * 1024;               // dynamic shared memory requested at most
 constexpr int kMinDynSmem = 120 * 1024;               // keeps two CTAs from sharing an SM (and its TMEM)
@@ -88,7 +89,8 @@ struct GemmParams {
   int BNd;                 // output channels per N tile (BN, or BN - 16 when the tile carries the ones row)
   int group;               // k-blocks per pipeline stage
   int tmem_cols;
-  int acc_stride;          // TMEM columns between the two accumulator buffers (BN rounded up to 32)
+  int acc_stride;          // TMEM columns between accumulator buffers (BN rounded up to 32)
+  int acc_shift;           // log2 of the number of accumulator buffers (2, 4 or 8 of them)
   uint32_t idesc;
   uint32_t layout_type;    // UMMA smem descriptor swizzle code
   uint32_t sbo;            // bytes between 8-row groups
@@ -260,8 +262,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t sbo_b
 struct SmemHeader {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
-  unsigned long long tmem_full[2];
-  unsigned long long tmem_empty[2];
+  unsigned long long tmem_full[kMaxAccBuffers];
+  unsigned long long tmem_empty[kMaxAccBuffers];
   uint32_t tmem_base;
   int abort_flag;
   // this CTA's N tile: folded bias and accumulator scale per column; read as 128-bit vectors
@@ -307,7 +309,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(smem_u32(&hdr->full[s]), 2);     // A producer + B producer
       mbar_init(smem_u32(&hdr->empty[s]), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kMaxAccBuffers; ++a) {
       mbar_init(smem_u32(&hdr->tmem_full[a]), 1);
       mbar_init(smem_u32(&hdr->tmem_empty[a]), kEpilogueWarps);
     }
@@ -405,7 +407,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     int j = 0;
     const int ksteps = p.BK >> 5;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
-      const uint32_t a = j & 1, aph = (j >> 1) & 1;
+      const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
       ok = mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -460,7 +462,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
       const int m_tile = m_tile0 + j * m_step;
-      const uint32_t a = j & 1, aph = (j >> 1) & 1;
+      const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
       uint8_t* stage_out = staging + a * staging_bytes;
       if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
       alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
@@ -700,9 +702,13 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   if (stages < 2) { *why = "gemm_tc: tile does not fit shared memory"; return false; }
   p.stages = stages;
   // the epilogue reads 16 columns at a time; buffers start on 32-column boundaries
+  // As many accumulator buffers as the 512 TMEM columns hold (2, 4 or 8): with narrow tiles the
+  // epilogue of a tile is a latency chain, and more tiles in flight hide it.
   p.acc_stride = (p.BN + 31) & ~31;
+  p.acc_shift = 1;
+  while (p.acc_shift < 3 && (2 << p.acc_shift) * p.acc_stride <= 512) ++p.acc_shift;
   int cols = 32;
-  while (cols < 2 * p.acc_stride) cols <<= 1;
+  while (cols < (1 << p.acc_shift) * p.acc_stride) cols <<= 1;
   p.tmem_cols = cols;
   p.idesc = (2u << 4) | (static_cast<uint32_t>(a_signed ? 1 : 0) << 7) | (1u << 10) |
             (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);

@@ -965,6 +965,77 @@ __global__ void im2col_whcn_kernel(const uint8_t* __restrict__ x, int Kp, int zx
   }
 }
 
+// im2col from a WHCN input with few channels, K index = (ky*C + c)*8 + kx (filter rows padded to 8
+// taps, kw <= 8, dilation 1): the 8 bytes of one (pixel, ky, c) are 8 consecutive input bytes, so a
+// 16-byte piece of the matrix is two unaligned 8-byte reads of the staged rows instead of sixteen
+// gathered bytes.  The byte in the padding slot (kx >= kw) belongs to the neighbouring pixel; its
+// weight is zero.  One block per output row (n, ho); staged rows have pitch `pitch` (a multiple of 4,
+// at least 8 bytes beyond the last input column used).
+__global__ void __launch_bounds__(256) im2col_whcn8_kernel(const uint8_t* __restrict__ x, int Kp, int zx, ConvGeom g, int pitch,
+                                                           uint8_t* __restrict__ col) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ uint32_t sm_words[];
+  uint8_t* img = reinterpret_cast<uint8_t*>(sm_words);     // [kh*C][pitch]
+  const int n = blockIdx.y, ho = blockIdx.x;
+  const int rows = g.kh * g.C;
+  // Staged column j holds input column j - lead; lead = pad_left rounded up to 4 keeps input words
+  // aligned with shared-memory words.  First everything becomes the zero point, then the in-bounds
+  // part of each row is copied (as 32-bit words when the input rows allow it).
+  const int lead = (g.pl + 3) & ~3;
+  const uint32_t zx_word = static_cast<uint32_t>(zx & 0xFF) * 0x01010101u;
+  const int pitch_w = pitch >> 2;
+  for (int idx = threadIdx.x; idx < rows * pitch_w; idx += blockDim.x) sm_words[idx] = zx_word;
+  __syncthreads();
+  const int copy_cols = min(g.W, pitch - lead);            // input columns that fit in a staged row
+  if ((g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0) {
+    const int wpr = copy_cols >> 2;                         // whole words; the ragged rest below
+    for (int idx = threadIdx.x; idx < rows * wpr; idx += blockDim.x) {
+      const int r = idx / wpr, w = idx - r * wpr;
+      const int ky = r / g.C, c = r - ky * g.C;
+      const int hi = ho * g.sy - g.pt + ky;
+      if (hi >= 0 && hi < g.H)
+        sm_words[r * pitch_w + (lead >> 2) + w] =
+            __ldg(reinterpret_cast<const uint32_t*>(x + ((static_cast<size_t>(n) * g.C + c) * g.H + hi) * g.W) + w);
+    }
+    const int rest = copy_cols & 3;
+    for (int idx = threadIdx.x; idx < rows * rest; idx += blockDim.x) {
+      const int r = idx / rest, wi = (copy_cols & ~3) + (idx - r * rest);
+      const int ky = r / g.C, c = r - ky * g.C;
+      const int hi = ho * g.sy - g.pt + ky;
+      if (hi >= 0 && hi < g.H) img[r * pitch + lead + wi] = x[((static_cast<size_t>(n) * g.C + c) * g.H + hi) * g.W + wi];
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < rows * copy_cols; idx += blockDim.x) {
+      const int r = idx / copy_cols, wi = idx - r * copy_cols;
+      const int ky = r / g.C, c = r - ky * g.C;
+      const int hi = ho * g.sy - g.pt + ky;
+      if (hi >= 0 && hi < g.H) img[r * pitch + lead + wi] = x[((static_cast<size_t>(n) * g.C + c) * g.H + hi) * g.W + wi];
+    }
+  }
+  __syncthreads();
+  const int shift0 = lead - g.pl;                          // staged column of output pixel 0, tap 0
+  const int chunks = Kp >> 4;
+  uint8_t* out = col + (static_cast<size_t>(n) * g.Ho + ho) * g.Wo * Kp;
+  for (int q = threadIdx.x; q < g.Wo * chunks; q += blockDim.x) {
+    const int wo = q / chunks, ch = q - wo * chunks;
+    uint32_t w4[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = 2 * ch + h;
+      if (r < rows) {
+        const int byte = r * pitch + wo * g.sx + shift0;
+        const uint32_t* wp = sm_words + (byte >> 2);
+        const uint32_t sh = (byte & 3) * 8;
+        const uint32_t a0 = wp[0], a1 = wp[1], a2 = wp[2];
+        w4[2 * h] = __funnelshift_r(a0, a1, sh);
+        w4[2 * h + 1] = __funnelshift_r(a1, a2, sh);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(wo) * Kp + ch * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+  }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------- wrappers
@@ -1188,6 +1259,24 @@ void launch_im2col(const void* x, int Cs, int Kp, int zx, const ConvGeom& g, voi
   if (total == 0) return;
   im2col_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(x), Cs, Kp, zx, g,
                                                              static_cast<uint8_t*>(col));
+}
+
+void launch_im2col_whcn8(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s) {
+  if (g.N == 0 || g.Ho == 0 || g.Wo == 0) return;
+  const int pitch = im2col_whcn8_pitch(g);
+  const size_t smem = static_cast<size_t>(g.C) * g.kh * pitch + 16;
+  dim3 grid(g.Ho, g.N);
+  launch_pdl(im2col_whcn8_kernel, dim3(grid), dim3(256), smem, s, static_cast<const uint8_t*>(x), Kp, zx, g, pitch,
+             static_cast<uint8_t*>(col));
+}
+
+int im2col_whcn8_pitch(const ConvGeom& g) {
+  // up to 3 bytes of alignment lead, the 8-byte read of the last pixel, the third word of the funnel
+  // shift; 4 mod 64 spreads consecutive row pairs over the banks
+  const int need = 3 + (g.Wo - 1) * g.sx + 8 + 4;
+  int pitch = (need + 3) & ~3;
+  while ((pitch & 63) != 4) pitch += 4;
+  return pitch;
 }
 
 void launch_im2col_whcn(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s) {
