@@ -594,7 +594,11 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     else if (mode == IDENTITY) { Cs = x.Cp; Kp = taps * x.Cp; M = y.N; A = cl_in(x); }
     else if (mode == IMPLICIT) { Cs = x.Cp; Kp = taps * x.Cp; M = static_cast<int>(P); A = cl_in(x); }
     else if (mode == WHCN) { Cs = x.C; Kp = round_up(taps * x.C, 16); M = static_cast<int>(P); }
-    else if (mode == WHCN8) { Cs = x.C; Kp = round_up(kh * x.C * 8, 16); M = static_cast<int>(P); }
+    else if (mode == WHCN8) {
+      // rows of the matrix are read by TMA in 64- or 128-byte pieces: a pitch that is a multiple of 64
+      // keeps every piece on whole 32-byte sectors
+      Cs = x.C; Kp = round_up(kh * x.C * 8, 16); if (Kp > 64) Kp = round_up(Kp, 64); M = static_cast<int>(P);
+    }
     else { Cs = x.C < 16 ? x.C : x.Cp; Kp = round_up(taps * Cs, 16); M = static_cast<int>(P); }
     const GemmTcTiling tiling = gemm_tc_choose_tiling(M, y.Cp, Kp, any_dz ? 1 : 0);
     const int Np = tiling.n_tiles * tiling.rows;
