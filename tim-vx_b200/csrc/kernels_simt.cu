@@ -752,9 +752,15 @@ __global__ void __launch_bounds__(256) add_q_kernel(const uint4* __restrict__ a,
                                                     uint4* __restrict__ y, size_t n16) {
   pdl_wait();
   pdl_trigger();
+  // Two groups per step, all four loads issued before any arithmetic: the kernel needs about 64 KB of
+  // loads in flight per SM to keep HBM busy.
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += 2 * stride) {
+    const size_t i2 = i + stride;
+    const bool two = i2 < n16;
     uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
+    uint4 av2 = make_uint4(0, 0, 0, 0), bv2 = make_uint4(0, 0, 0, 0);
+    if (two) { av2 = __ldcs(a + i2); bv2 = __ldcs(b + i2); }
     av.x ^= p.a_flip; av.y ^= p.a_flip; av.z ^= p.a_flip; av.w ^= p.a_flip;
     bv.x ^= p.b_flip; bv.y ^= p.b_flip; bv.z ^= p.b_flip; bv.w ^= p.b_flip;
     uint4 o;
@@ -763,6 +769,15 @@ __global__ void __launch_bounds__(256) add_q_kernel(const uint4* __restrict__ a,
     o.z = add_q_word<FAST>(av.z, bv.z, p);
     o.w = add_q_word<FAST>(av.w, bv.w, p);
     y[i] = o;
+    if (two) {
+      av2.x ^= p.a_flip; av2.y ^= p.a_flip; av2.z ^= p.a_flip; av2.w ^= p.a_flip;
+      bv2.x ^= p.b_flip; bv2.y ^= p.b_flip; bv2.z ^= p.b_flip; bv2.w ^= p.b_flip;
+      o.x = add_q_word<FAST>(av2.x, bv2.x, p);
+      o.y = add_q_word<FAST>(av2.y, bv2.y, p);
+      o.z = add_q_word<FAST>(av2.z, bv2.z, p);
+      o.w = add_q_word<FAST>(av2.w, bv2.w, p);
+      y[i2] = o;
+    }
   }
 }
 
@@ -787,15 +802,28 @@ __global__ void __launch_bounds__(256) add_q_lut_kernel(const uint4* __restrict_
   __syncthreads();
   pdl_wait();
   const uint8_t* tab = reinterpret_cast<const uint8_t*>(tab4);
+  // Four groups per step with all eight loads issued first: 64 KB of shared memory allow only three
+  // blocks per SM, so each thread has to keep more bytes in flight.
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += stride) {
-    const uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
-    uint4 o;
-    o.x = add_lut_word(av.x, bv.x, tab);
-    o.y = add_lut_word(av.y, bv.y, tab);
-    o.z = add_lut_word(av.z, bv.z, tab);
-    o.w = add_lut_word(av.w, bv.w, tab);
-    y[i] = o;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += 4 * stride) {
+    uint4 av[4], bv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const size_t ik = i + k * stride;
+      if (ik < n16) { av[k] = __ldcs(a + ik); bv[k] = __ldcs(b + ik); }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const size_t ik = i + k * stride;
+      if (ik < n16) {
+        uint4 o;
+        o.x = add_lut_word(av[k].x, bv[k].x, tab);
+        o.y = add_lut_word(av[k].y, bv[k].y, tab);
+        o.z = add_lut_word(av[k].z, bv[k].z, tab);
+        o.w = add_lut_word(av[k].w, bv[k].w, tab);
+        y[ik] = o;
+      }
+    }
   }
 }
 
@@ -990,13 +1018,14 @@ __global__ void __launch_bounds__(256) im2col_whcn8_kernel(const uint8_t* __rest
   const int copy_cols = min(g.W, pitch - lead);            // input columns that fit in a staged row
   if ((g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0) {
     const int wpr = copy_cols >> 2;                         // whole words; the ragged rest below
-    for (int idx = threadIdx.x; idx < rows * wpr; idx += blockDim.x) {
-      const int r = idx / wpr, w = idx - r * wpr;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < rows; r += 8) {                  // a warp per staged row, lanes along it
       const int ky = r / g.C, c = r - ky * g.C;
       const int hi = ho * g.sy - g.pt + ky;
-      if (hi >= 0 && hi < g.H)
-        sm_words[r * pitch_w + (lead >> 2) + w] =
-            __ldg(reinterpret_cast<const uint32_t*>(x + ((static_cast<size_t>(n) * g.C + c) * g.H + hi) * g.W) + w);
+      if (hi < 0 || hi >= g.H) continue;
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(x + ((static_cast<size_t>(n) * g.C + c) * g.H + hi) * g.W);
+      uint32_t* dst = sm_words + r * pitch_w + (lead >> 2);
+      for (int w = lane; w < wpr; w += 32) dst[w] = __ldg(src + w);
     }
     const int rest = copy_cols & 3;
     for (int idx = threadIdx.x; idx < rows * rest; idx += blockDim.x) {
@@ -1017,8 +1046,11 @@ __global__ void __launch_bounds__(256) im2col_whcn8_kernel(const uint8_t* __rest
   const int shift0 = lead - g.pl;                          // staged column of output pixel 0, tap 0
   const int chunks = Kp >> 4;
   uint8_t* out = col + (static_cast<size_t>(n) * g.Ho + ho) * g.Wo * Kp;
-  for (int q = threadIdx.x; q < g.Wo * chunks; q += blockDim.x) {
-    const int wo = q / chunks, ch = q - wo * chunks;
+  // piece q = wo * chunks + ch; a thread's next piece is 256 further, stepped without divisions
+  int wo = threadIdx.x / chunks, ch = threadIdx.x - wo * chunks;
+  const int step_wo = 256 / chunks, step_ch = 256 - step_wo * chunks;
+  for (int q = threadIdx.x; q < g.Wo * chunks; q += 256, wo += step_wo, ch += step_ch) {
+    if (ch >= chunks) { ch -= chunks; ++wo; }
     uint32_t w4[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -1203,7 +1235,7 @@ void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, 
   const float bound = 256.0f * (fabsf(sa) + fabsf(sb)) * fabsf(inv) + 512.0f;
   const bool fast = full_range && bound < B2VX_FAST_ROUND_LIMIT && out.scale > 0.0f && std::isfinite(inv);
   // two 16-element steps per thread keep enough loads in flight; at most 8 blocks per SM
-  unsigned grid = grid_for(static_cast<long long>((n16 + 1) / 2), 256);
+  unsigned grid = grid_for(static_cast<long long>((n16 + 3) / 4), 256);
   if (grid > 148u * 8u) grid = 148u * 8u;
   const uint4* pa = static_cast<const uint4*>(a);
   const uint4* pb = static_cast<const uint4*>(b);
@@ -1223,7 +1255,7 @@ void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* 
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   // three 64 KB blocks per SM; every block should have enough elements to repay its table load
-  unsigned grid = grid_for(static_cast<long long>((n16 + 3) / 4), 256);
+  unsigned grid = grid_for(static_cast<long long>((n16 + 7) / 8), 256);
   if (grid > 148u * 3u) grid = 148u * 3u;
   launch_pdl(add_q_lut_kernel, dim3(grid), dim3(256), 65536, s, static_cast<const uint4*>(a), static_cast<const uint4*>(b),
                                             reinterpret_cast<const uint4*>(table), static_cast<uint4*>(y), n16);
