@@ -228,6 +228,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # all host threads this process may use (torchrun exports OMP_NUM_THREADS=1 to its workers)
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     if not os.path.exists(SAMPLES_ORACLE_LIB):
         subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle")], stdout=subprocess.DEVNULL)
     import numpy as np

@@ -160,6 +160,13 @@ FC_CASES = {
     "fc_k800_from4d": G.fc_q(800, 500, 3, from_4d=(4, 4, 50), w_kind="u8z128"),
     "fc_u8_zp": G.fc_q(1280, 1000, 2, w_kind="u8"),
     "fc_2048_1000": G.fc_q(2048, 1000, 4),
+    # the row-count variants of the small-M kernel, ragged channel counts, a weight zero point
+    "fc_m7_n1001": G.fc_q(768, 1001, 7),
+    "fc_m8_n30": G.fc_q(4096, 30, 8),
+    "fc_m16_n30": G.fc_q(4096, 30, 16),
+    "fc_m3_u8zp": G.fc_q(512, 200, 3, w_kind="u8"),
+    "fc_m9_u8zp": G.fc_q(1024, 64, 9, w_kind="u8"),
+    "fc_m6_u8zp": G.fc_q(1024, 64, 6, w_kind="u8"),
 }
 
 
@@ -168,6 +175,25 @@ def test_fully_connected_matches_oracle(oracle_lib, product_lib, conv_kernel, na
     want, _ = G.run_case(oracle_lib, FC_CASES[name], seed=3)
     got, _ = G.run_case(product_lib, FC_CASES[name], seed=3)
     G.assert_same(want, got)
+
+
+@pytest.mark.parametrize("name", ["fc_m8_n30", "fc_1024_m1", "fc_u8_zp", "fc_k800_from4d"])
+def test_small_m_fc_on_tensor_cores_matches_oracle(oracle_lib, product_lib, name):
+    """The same few-row shapes kept on the tcgen05 kernel (128-row tiles, mostly out of bounds)."""
+    want, _ = G.run_case(oracle_lib, FC_CASES[name], seed=3)
+    os.environ["B2VX_FC_SMALL_M"] = "0"
+    os.environ.pop("B2VX_CONV_KERNEL", None)
+    try:
+        got, kernels = G.run_case(product_lib, FC_CASES[name], seed=3)
+    finally:
+        os.environ.pop("B2VX_FC_SMALL_M", None)
+    assert any(k["name"].startswith("gemm_i8_tc") for k in kernels), [k["name"] for k in kernels]
+    G.assert_same(want, got)
+
+
+def test_small_m_fc_kernel_is_taken(product_lib):
+    _, kernels = G.run_case(product_lib, FC_CASES["fc_1024_m1"], seed=3)
+    assert [k["name"] for k in kernels if k["name"].startswith(("fc_", "gemm_"))] == ["fc_small_m"], [k["name"] for k in kernels]
 
 
 POOL_CASES = {

@@ -116,6 +116,7 @@ struct b2vx_graph {
   int* h_status = nullptr;
   bool compiled = false;
   bool use_tc = false;
+  bool fc_small_m = true;    // FullyConnected with <= 16 rows on the CUDA-core streaming kernel
   int add_mode = 0;          // quantized Add: 0 choose by size, 1 table kernel, 2 arithmetic kernel
   // the whole launch plan captured once as a CUDA graph; replays cost one launch on the host
   cudaGraphExec_t exec = nullptr;
@@ -600,6 +601,31 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       Cs = x.C; Kp = round_up(kh * x.C * 8, 16); if (Kp > 64) Kp = round_up(Kp, 64); M = static_cast<int>(P);
     }
     else { Cs = x.C < 16 ? x.C : x.Cp; Kp = round_up(taps * Cs, 16); M = static_cast<int>(P); }
+    // Few rows (decode-like FullyConnected, 1x1 on a handful of pixels): weight streaming on CUDA cores.
+    // (B2VX_FC_SMALL_M=0, read when the graph is created, keeps such shapes on the tensor-core kernel)
+    // Measured at N = K = 4096: faster than the 128-row tile up to 8 rows (1.8x at one row); at 16 rows the
+    // dp4a rate bounds it and the tensor-core kernel is level or better.
+    if (g->fc_small_m && mode == IDENTITY && M <= 8 && (!any_dz || x.C == x.Cp)) {
+      pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, 1, y.Cp, y.Cp, 0, &pk);
+      int8_t* dw8s = nullptr; int32_t* dbias_s = nullptr; float* dscale_s = nullptr;
+      b2vx_status sts = upload(g, pk.w8, &dw8s);
+      if (sts == B2VX_OK) sts = upload(g, pk.bias_full, &dbias_s);
+      if (sts == B2VX_OK) sts = upload(g, pk.acc_scale, &dscale_s);
+      if (sts != B2VX_OK) return sts;
+      ep.bias_full = dbias_s;
+      ep.acc_scale = dscale_s;
+      ep.dz_uniform = any_dz ? dz_value : 0;
+      void* ycl_s = y.d_cl;
+      const int ldd_s = y.Cp, oc_s = y.C, ocp_s = y.Cp;
+      Step s_fc;
+      s_fc.info = make_info("fc_small_m", node_index, 2 * macs, abytes);
+      s_fc.fn = [=](cudaStream_t st2) {
+        launch_fc_small_m(A, x_signed, dw8s, M, Kp, oc_s, ocp_s, ep, ycl_s, ldd_s, st2);
+        return cudaGetLastError();
+      };
+      g->steps.push_back(std::move(s_fc));
+      return B2VX_OK;
+    }
     const GemmTcTiling tiling = gemm_tc_choose_tiling(M, y.Cp, Kp, any_dz ? 1 : 0);
     const int Np = tiling.n_tiles * tiling.rows;
     pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, tiling.n_tiles, tiling.data, tiling.rows, mode == WHCN ? 1 : (mode == WHCN8 ? 2 : 0), &pk);
@@ -1097,6 +1123,8 @@ b2vx_status b2vx_graph_create(b2vx_context* ctx, int32_t device_id, b2vx_graph**
   g->stream = g->own_stream;
   const char* k = std::getenv("B2VX_CONV_KERNEL");
   g->use_tc = gemm_tc_available() && !(k && std::strcmp(k, "simt") == 0);
+  const char* fs = std::getenv("B2VX_FC_SMALL_M");
+  g->fc_small_m = !(fs && fs[0] == '0');
   const char* ak = std::getenv("B2VX_ADD_KERNEL");
   g->add_mode = !ak ? 0 : (std::strcmp(ak, "lut") == 0 ? 1 : 2);
   const char* cg = std::getenv("B2VX_CUDA_GRAPH");

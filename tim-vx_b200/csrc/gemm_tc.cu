@@ -41,8 +41,8 @@
 // Every mbarrier wait is bounded: after kWaitLimitCycles the waiting thread
 // records a code in *status, raises a CTA-wide abort flag that all other waits
 // poll, and the CTA falls through to its common exit where outstanding TMA
-// stores are drained and tensor memory is released.  No cluster launch, no
-// multicast.
+// stores are drained and tensor memory is released.  Every CTA is on its own:
+// no cluster launch, every load has exactly one destination CTA.
 #include <cuda.h>
 #include <cuda_runtime.h>
 

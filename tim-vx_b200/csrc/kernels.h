@@ -122,6 +122,13 @@ struct SoftmaxGeom {
 void launch_softmax(const void* x, int x_kind, float sx, int zx, void* y, int y_kind, OutQuant out, float beta,
                     const SoftmaxGeom& g, cudaStream_t s);
 
+// ---- FullyConnected / 1x1-on-one-pixel with at most 16 rows, on CUDA cores ----
+// D[M][ldd] = requant(A[M][Kp] * B[Ocp][Kp]^T): B is the packed weight matrix with plain row order
+// (one N tile, no ones row), e.bias_full / e.acc_scale / e.out / e.dz_uniform as for the GEMM; with
+// dz_uniform != 0 every byte of A's rows must be real data (K == Kp).
+void launch_fc_small_m(const void* A, int a_signed, const int8_t* B, int M, int Kp, int Oc, int Ocp, const ContractEpilogue& e,
+                       void* D, int ldd, cudaStream_t s);
+
 // ---- explicit im2col for the tensor-core GEMM -------------------------------
 // col [M][Kp] bytes, M = N*Ho*Wo, K index = tap*Cs + c with Cs = g.C (dense) or
 // g.Cp; out-of-bounds taps are filled with the input zero point, the K tail

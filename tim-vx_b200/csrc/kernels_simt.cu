@@ -1068,6 +1068,116 @@ __global__ void __launch_bounds__(256) im2col_whcn8_kernel(const uint8_t* __rest
   }
 }
 
+// ---------------------------------------------------------------- FullyConnected with few rows (M <= 16)
+
+// Decode-like shapes are bound by streaming the weights once; a 128-row tensor-core tile would spend its
+// time on pipeline latency with a handful of CTAs.  Here a block of eight warps owns CH = 4 output
+// channels and all M input rows, and its 256 lanes split K in 16-byte slices: a lane loads the four
+// weight slices (the only HBM traffic, coalesced along K) and the M input slices (L1/L2-resident) and
+// issues 4*4*M dp4a.  With K = 4096 every load of the block is in flight at once, and there are
+// Ocp/4 blocks to fill the machine.  The CH*MT partial sums per lane are combined inside the warp by a
+// halving exchange (each step a lane gives away half of its values: 31 shuffles for 32 values
+// instead of 5 per value), then across the eight warps through shared memory.  HAS_DZ: the weights
+// keep a zero point dz, removed as dz * sum(x) accumulated alongside (K must then be unpadded).
+template <int CH, int MT, bool XS, bool HAS_DZ>
+__global__ void __launch_bounds__(256, 2) fc_small_m_kernel(const uint8_t* __restrict__ A, const int8_t* __restrict__ B, int M, int Kp,
+                                                         int Oc, int Ocp, ContractEpilogue ep, uint8_t* __restrict__ D, int ldd) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int V = CH * MT;                        // partial sums per lane: 4 ... 64
+  constexpr int KEEP = V >= 64 ? 2 : 1;             // values a lane still holds after the exchange
+  __shared__ int partial[8][32 * KEEP];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * CH;
+  int v[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) v[i] = 0;
+  int sx[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) sx[m] = 0;
+  const int8_t* brow = B + static_cast<size_t>(c0) * Kp;
+#pragma unroll 1
+  for (int k = threadIdx.x * 16; k < Kp; k += 256 * 16) {
+    uint4 w[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      w[c] = make_uint4(0, 0, 0, 0);
+      if (c0 + c < Ocp) w[c] = __ldcs(reinterpret_cast<const uint4*>(brow + static_cast<size_t>(c) * Kp + k));
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const int row = m < M ? m : M - 1;            // rows beyond M repeat the last one; their sums are dropped
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(A + static_cast<size_t>(row) * Kp + k));
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        int a = v[c * MT + m];
+        a = dp4<XS>(x.x, w[c].x, a);
+        a = dp4<XS>(x.y, w[c].y, a);
+        a = dp4<XS>(x.z, w[c].z, a);
+        a = dp4<XS>(x.w, w[c].w, a);
+        v[c * MT + m] = a;
+      }
+      if (HAS_DZ) {
+        int t = sx[m];
+        t = dp4<XS>(x.x, 0x01010101u, t);
+        t = dp4<XS>(x.y, 0x01010101u, t);
+        t = dp4<XS>(x.z, 0x01010101u, t);
+        t = dp4<XS>(x.w, 0x01010101u, t);
+        sx[m] = t;
+      }
+    }
+  }
+  if (HAS_DZ) {
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) v[c * MT + m] -= ep.dz_uniform * sx[m];
+  }
+  // Halving exchange.  Step s (offset 16 >> s) starts with V >> s values per lane: a lane keeps the
+  // upper half if its offset bit is set, else the lower half, each added to the partner's copy.  Once
+  // a single value is left the remaining steps are plain butterfly additions, after which the lanes
+  // with those bits set hold duplicates.
+  int idx = 0;
+  bool owner = true;
+#pragma unroll
+  for (int step = 0; step < 5; ++step) {
+    const int off = 16 >> step;
+    if ((V >> step) > 1) {
+      const int n = (V >> step) >> 1;
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int j = 0; j < n; ++j) {
+        const int send = upper ? v[j] : v[j + n];
+        const int keep = upper ? v[j + n] : v[j];
+        v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+      if (upper) idx += n;
+    } else {
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+      if (lane & off) owner = false;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) partial[warp][lane * KEEP + j] = v[j];
+  __syncthreads();
+  if (warp == 0 && owner) {
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      int total = 0;
+#pragma unroll
+      for (int w8 = 0; w8 < 8; ++w8) total += partial[w8][lane * KEEP + j];
+      const int id = idx + j;
+      const int c = id / MT, m = id - c * MT;
+      const int oc = c0 + c;
+      if (m < M && oc < Oc) {
+        const int acc = total + ep.bias_full[oc];
+        const float real = __fmul_rn(__int2float_rn(acc), ep.acc_scale[oc]);
+        D[static_cast<size_t>(m) * ldd + oc] = static_cast<uint8_t>(requant(real, ep.out) & 0xFF);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------- wrappers
@@ -1291,6 +1401,31 @@ void launch_im2col(const void* x, int Cs, int Kp, int zx, const ConvGeom& g, voi
   if (total == 0) return;
   im2col_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(x), Cs, Kp, zx, g,
                                                              static_cast<uint8_t*>(col));
+}
+
+template <int CH, int MT>
+static void launch_fc_small_m_t(const void* A, int a_signed, const int8_t* B, int M, int Kp, int Oc, int Ocp,
+                                const ContractEpilogue& e, void* D, int ldd, cudaStream_t s) {
+  const uint8_t* a = static_cast<const uint8_t*>(A);
+  uint8_t* d = static_cast<uint8_t*>(D);
+  const unsigned grid = static_cast<unsigned>((Ocp + CH - 1) / CH);   // one block per channel group
+  const bool dz = e.dz_uniform != 0;
+  if (a_signed) {
+    if (dz) launch_pdl(fc_small_m_kernel<CH, MT, true, true>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+    else launch_pdl(fc_small_m_kernel<CH, MT, true, false>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+  } else {
+    if (dz) launch_pdl(fc_small_m_kernel<CH, MT, false, true>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+    else launch_pdl(fc_small_m_kernel<CH, MT, false, false>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+  }
+}
+
+void launch_fc_small_m(const void* A, int a_signed, const int8_t* B, int M, int Kp, int Oc, int Ocp, const ContractEpilogue& e,
+                       void* D, int ldd, cudaStream_t s) {
+  if (M <= 0 || Ocp <= 0) return;
+  if (M <= 1) launch_fc_small_m_t<4, 1>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);
+  else if (M <= 4) launch_fc_small_m_t<4, 4>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);
+  else if (M <= 8) launch_fc_small_m_t<4, 8>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);
+  else launch_fc_small_m_t<4, 16>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);
 }
 
 void launch_im2col_whcn8(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s) {
