@@ -400,47 +400,50 @@ __global__ void __launch_bounds__(256, 2) depthwise_q16_kernel(const uint8_t* __
   if (second) *reinterpret_cast<uint4*>(out + g.Ocp) = requant_chunk16<false>(acc1, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
 }
 
-// The same computation with the input staged in shared memory: a block owns a 64-channel slab of an
-// 8 x TW tile of output pixels (TW = 8 or 16), copies the input patch it needs (halo included, the
-// zero point where the patch leaves the image, signed bytes already biased) with independent 128-bit
-// loads that are all in flight together, and then computes from shared memory with no bounds checks.
-// Several blocks per SM overlap one block's copy with another's arithmetic.  A thread owns 16
-// channels of pixel q (and q + 64 when TW = 16) of the tile.
+// The same computation with the input staged in shared memory: a block owns a slab of CK = 1, 2 or 4
+// 16-channel chunks (whichever wastes fewest channels) of a TH x TW tile of output pixels, TW = 8 or
+// 16 and TH = 256 / (8 * CK), copies the input patch it needs (halo included, the zero point where the
+// patch leaves the image, signed bytes already biased) with independent 128-bit loads that are all
+// in flight together, and then computes from shared memory with no bounds checks.  Several blocks
+// per SM overlap one block's copy with another's arithmetic.  A thread owns one chunk of pixel
+// (row q / 8, column q % 8) of the tile and, when TW = 16, of the pixel 8 columns to the right.
 template <int KH, int KW, bool XS>
-__global__ void __launch_bounds__(256) depthwise_q16s_kernel(const uint8_t* __restrict__ x, DwParams p, int tw_shift,
-                                                             int IH, int IW, uint8_t* __restrict__ y) {
-  pdl_trigger();
-  extern __shared__ uint4 dw_smem[];               // [taps][16] weight quads, then [IH][IW][4] input chunks
+__global__ void __launch_bounds__(256, (KH == 3 ? 3 : 2)) depthwise_q16s_kernel(const uint8_t* __restrict__ x, DwParams p, int tw_shift,
+                                                                int ck_shift, int IH, int IW, uint8_t* __restrict__ y) {
+  extern __shared__ uint4 dw_smem[];               // [taps][4 * CK] weight quads, then [IH][IW][CK] input chunks
   const ConvGeom& g = p.g;
   const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
   const int taps = kh * kw;
-  const int TW = 1 << tw_shift;
-  const int tiles_w = (g.Wo + TW - 1) >> tw_shift, tiles_h = (g.Ho + 7) >> 3;
+  const int TW = 1 << tw_shift, CK = 1 << ck_shift;
+  const int TH = 32 >> ck_shift;                    // 256 threads = CK chunks x 8 columns x TH rows
+  const int tiles_w = (g.Wo + TW - 1) >> tw_shift, tiles_h = (g.Ho + TH - 1) / TH;
   int tile = blockIdx.x;
   const int tile_w = tile % tiles_w; tile /= tiles_w;
   const int tile_h = tile % tiles_h;
   const int n = tile / tiles_h;
-  const int c_slab = blockIdx.y * 64;
-  const int slab_chunks = min(64, g.Ocp - c_slab) >> 4;
-  const int ho0 = tile_h * 8, wo0 = tile_w * TW;
+  const int c_slab = blockIdx.y * 16 * CK;
+  const int slab_chunks = min(16 * CK, g.Ocp - c_slab) >> 4;
+  const int ho0 = tile_h * TH, wo0 = tile_w * TW;
   const int hi0 = ho0 * g.sy - g.pt, wi0 = wo0 * g.sx - g.pl;
   uint4* wsm = dw_smem;
-  uint4* xsm = dw_smem + taps * 16;
-  for (int i = threadIdx.x; i < taps * 16; i += 256) {
-    const int t = i >> 4, q = i & 15;
+  uint4* xsm = dw_smem + taps * 4 * CK;
+  pdl_trigger();
+  for (int i = threadIdx.x; i < taps * 4 * CK; i += 256) {
+    const int t = i >> (2 + ck_shift), q = i & (4 * CK - 1);
     uint4 v = make_uint4(0, 0, 0, 0);
     if ((q >> 2) < slab_chunks) v = *reinterpret_cast<const uint4*>(p.wtab + static_cast<size_t>(t) * g.Ocp + c_slab + 4 * q);
     wsm[i] = v;
   }
   pdl_wait();   // weights are constants; the input is the first thing another kernel produced
+  const int chunk = threadIdx.x & (CK - 1);
   {
     const uint4 zx4 = make_uint4(p.zx_word, p.zx_word, p.zx_word, p.zx_word);
     const uint8_t* img = x + static_cast<size_t>(n) * g.H * g.W * g.Cp + c_slab;
-    const int units = IH * IW * 4;
-    const int chunk = threadIdx.x & 3;
-    int pix = threadIdx.x >> 2;
-    int ih = pix / IW, iw = pix - ih * IW;          // 64 pixels further per step
-    const int step_h = 64 / IW, step_w = 64 - step_h * IW;
+    const int units = IH * IW * CK;
+    const int ppi = 256 >> ck_shift;               // staged pixels per step
+    int pix = threadIdx.x >> ck_shift;
+    int ih = pix / IW, iw = pix - ih * IW;
+    const int step_h = ppi / IW, step_w = ppi - step_h * IW;
 #pragma unroll 4
     for (int u = threadIdx.x; u < units; u += 256) {
       const int hi = hi0 + ih, wi = wi0 + iw;
@@ -455,23 +458,22 @@ __global__ void __launch_bounds__(256) depthwise_q16s_kernel(const uint8_t* __re
     }
   }
   __syncthreads();
-  const int chunk = threadIdx.x & 3;
   if (chunk >= slab_chunks) return;
-  const int q = threadIdx.x >> 2;                  // 0..63
+  const int q = threadIdx.x >> ck_shift;           // 0 .. 8*TH-1
   const int tr = q >> 3, tc = q & 7;
   const bool two = TW == 16;
   int acc0[16], acc1[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) { acc0[i] = 0; acc1[i] = 0; }
-  const uint4* xrow0 = xsm + ((tr * g.sy) * IW + tc * g.sx) * 4 + chunk;
-  const int second_off = 8 * g.sx * 4;
+  const uint4* xrow0 = xsm + (((tr * g.sy) * IW + tc * g.sx) << ck_shift) + chunk;
+  const int second_off = (8 * g.sx) << ck_shift;
 #pragma unroll
   for (int ky = 0; ky < kh; ++ky) {
 #pragma unroll
     for (int kx = 0; kx < kw; ++kx) {
-      const uint4* wq = wsm + (ky * kw + kx) * 16 + 4 * chunk;
+      const uint4* wq = wsm + (((ky * kw + kx) << ck_shift) + chunk) * 4;
       const uint4 w[4] = {wq[0], wq[1], wq[2], wq[3]};
-      const uint4* xp = xrow0 + (ky * g.dy * IW + kx * g.dx) * 4;
+      const uint4* xp = xrow0 + ((ky * g.dy * IW + kx * g.dx) << ck_shift);
       dw_mac16(acc0, xp[0], w);
       if (two) dw_mac16(acc1, xp[second_off], w);
     }
@@ -1257,13 +1259,21 @@ void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* w
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* yp = static_cast<uint8_t*>(y);
   {
-    // staged form when the input patch of an 8 x TW output tile fits comfortably in shared memory
+    // staged form when the input patch of a TH x TW output tile fits comfortably in shared memory
     const int tw_shift = g.Wo <= 8 ? 3 : 4;
     const int TW = 1 << tw_shift;
-    const int IH = 7 * g.sy + (g.kh - 1) * g.dy + 1, IW = (TW - 1) * g.sx + (g.kw - 1) * g.dx + 1;
-    const size_t smem_s = (static_cast<size_t>(g.kh) * g.kw * 16 + static_cast<size_t>(IH) * IW * 4) * sizeof(uint4);
-    if (smem_s <= 72 * 1024 && IW >= 1) {
-      const dim3 grid_s(static_cast<unsigned>(((g.Wo + TW - 1) / TW) * ((g.Ho + 7) / 8) * g.N), (g.Ocp + 63) / 64);
+    // chunks per slab: the choice of 4, 2, 1 that leaves the fewest idle channel chunks (ties: the larger)
+    const int nchunks = g.Ocp / 16;
+    int ck_shift = 2, best_waste = 1 << 30;
+    for (int cs = 2; cs >= 0; --cs) {
+      const int ck = 1 << cs, waste = (nchunks + ck - 1) / ck * ck - nchunks;
+      if (waste < best_waste) { best_waste = waste; ck_shift = cs; }
+    }
+    const int CK = 1 << ck_shift, TH = 32 >> ck_shift;
+    const int IH = (TH - 1) * g.sy + (g.kh - 1) * g.dy + 1, IW = (TW - 1) * g.sx + (g.kw - 1) * g.dx + 1;
+    const size_t smem_s = (static_cast<size_t>(g.kh) * g.kw * 4 * CK + static_cast<size_t>(IH) * IW * CK) * sizeof(uint4);
+    if (smem_s <= 72 * 1024) {
+      const dim3 grid_s(static_cast<unsigned>(((g.Wo + TW - 1) / TW) * ((g.Ho + TH - 1) / TH) * g.N), (nchunks + CK - 1) / CK);
       static bool attr_set[64] = {false};
       int dev = 0;
       cudaGetDevice(&dev);
@@ -1275,11 +1285,11 @@ void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* w
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
       }
       if (g.kh == 3 && g.kw == 3) {
-        if (x_signed) launch_pdl(depthwise_q16s_kernel<3, 3, true>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
-        else launch_pdl(depthwise_q16s_kernel<3, 3, false>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
+        if (x_signed) launch_pdl(depthwise_q16s_kernel<3, 3, true>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, ck_shift, IH, IW, yp);
+        else launch_pdl(depthwise_q16s_kernel<3, 3, false>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, ck_shift, IH, IW, yp);
       } else {
-        if (x_signed) launch_pdl(depthwise_q16s_kernel<0, 0, true>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
-        else launch_pdl(depthwise_q16s_kernel<0, 0, false>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, IH, IW, yp);
+        if (x_signed) launch_pdl(depthwise_q16s_kernel<0, 0, true>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, ck_shift, IH, IW, yp);
+        else launch_pdl(depthwise_q16s_kernel<0, 0, false>, dim3(grid_s), dim3(256), smem_s, s, xp, p, tw_shift, ck_shift, IH, IW, yp);
       }
       return;
     }
