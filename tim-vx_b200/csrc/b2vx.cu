@@ -1530,12 +1530,39 @@ b2vx_status b2vx_graph_profile(b2vx_graph* g, uint32_t iters) {
   std::vector<cudaEvent_t> ev(g->steps.size() + 1);
   for (auto& e : ev) CUDA_TRY(g, cudaEventCreate(&e));
   std::vector<double> total(g->steps.size(), 0.0);
+  // Per-kernel times from events recorded between the kernels.  Submitted launch by launch, the host
+  // cannot keep up with kernels of a few microseconds and the gaps would be booked to the kernels, so
+  // the sequence (kernels + event records) is captured into a CUDA graph and replayed; direct
+  // submission is the fallback.
+  cudaGraphExec_t exec = nullptr;
+  if (g->use_cuda_graph) {
+    cudaGraph_t graph = nullptr;
+    bool ok = cudaStreamBeginCapture(g->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    if (ok) {
+      ok = cudaEventRecordWithFlags(ev[0], g->stream, cudaEventRecordExternal) == cudaSuccess;
+      for (size_t i = 0; ok && i < g->steps.size(); ++i) {
+        ok = g->steps[i].fn(g->stream) == cudaSuccess &&
+             cudaEventRecordWithFlags(ev[i + 1], g->stream, cudaEventRecordExternal) == cudaSuccess;
+      }
+      ok = (cudaStreamEndCapture(g->stream, &graph) == cudaSuccess) && ok && graph != nullptr;
+    }
+    if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+    if (graph) cudaGraphDestroy(graph);
+    if (!ok) {
+      exec = nullptr;
+      cudaGetLastError();
+    }
+  }
   for (uint32_t it = 0; it < iters; ++it) {
-    CUDA_TRY(g, cudaEventRecord(ev[0], g->stream));
-    for (size_t i = 0; i < g->steps.size(); ++i) {
-      cudaError_t e = g->steps[i].fn(g->stream);
-      if (e != cudaSuccess) return fail(g, B2VX_CUDA_ERROR, std::string(g->steps[i].info.name) + ": " + cudaGetErrorString(e));
-      CUDA_TRY(g, cudaEventRecord(ev[i + 1], g->stream));
+    if (exec) {
+      CUDA_TRY(g, cudaGraphLaunch(exec, g->stream));
+    } else {
+      CUDA_TRY(g, cudaEventRecord(ev[0], g->stream));
+      for (size_t i = 0; i < g->steps.size(); ++i) {
+        cudaError_t e = g->steps[i].fn(g->stream);
+        if (e != cudaSuccess) return fail(g, B2VX_CUDA_ERROR, std::string(g->steps[i].info.name) + ": " + cudaGetErrorString(e));
+        CUDA_TRY(g, cudaEventRecord(ev[i + 1], g->stream));
+      }
     }
     CUDA_TRY(g, cudaStreamSynchronize(g->stream));
     for (size_t i = 0; i < g->steps.size(); ++i) {
@@ -1544,6 +1571,7 @@ b2vx_status b2vx_graph_profile(b2vx_graph* g, uint32_t iters) {
       total[i] += ms;
     }
   }
+  if (exec) cudaGraphExecDestroy(exec);
   for (size_t i = 0; i < g->steps.size(); ++i) g->steps[i].info.last_ms = static_cast<float>(total[i] / iters);
   for (auto& e : ev) cudaEventDestroy(e);
   return b2vx_graph_sync(g);

@@ -645,6 +645,78 @@ __global__ void __launch_bounds__(256) pool_q16_kernel(const uint8_t* __restrict
   *reinterpret_cast<uint4*>(y + static_cast<size_t>(p) * g.Cp + ch * 16) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// Large windows with few outputs (global average pooling): one warp per (output pixel, 16-channel
+// chunk), the lanes share out the window's taps and combine their byte-SIMD maxima / packed sums by
+// shuffles, so the 49 loads of a 7x7 window are in flight together instead of queued in one thread.
+template <bool XS>
+__global__ void __launch_bounds__(256) pool_q16_warp_kernel(const uint8_t* __restrict__ x, int type, float in_scale, int in_zp,
+                                                            int same_quant, ConvGeom g, OutQuant out, uint8_t* __restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
+  const int chunks = g.Cp >> 4;
+  const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * chunks;
+  const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= total) return;
+  const int ch = static_cast<int>(i % chunks);
+  const long long p = i / chunks;
+  const int wo = static_cast<int>(p % g.Wo);
+  const long long t = p / g.Wo;
+  const int ho = static_cast<int>(t % g.Ho);
+  const int n = static_cast<int>(t / g.Ho);
+  const int h_lo = max(0, ho * g.sy - g.pt), h_hi = min(g.H, ho * g.sy - g.pt + g.kh);
+  const int w_lo = max(0, wo * g.sx - g.pl), w_hi = min(g.W, wo * g.sx - g.pl + g.kw);
+  const int ww = max(0, w_hi - w_lo);
+  const int count = max(0, h_hi - h_lo) * ww;
+  const uint32_t flip = XS ? 0x80808080u : 0u;
+  uint32_t mx[4] = {0u, 0u, 0u, 0u}, even[4] = {0u, 0u, 0u, 0u}, odd[4] = {0u, 0u, 0u, 0u};
+  const uint8_t* base = x + static_cast<size_t>(n) * g.H * g.W * g.Cp + ch * 16;
+  for (int tap = lane; tap < count; tap += 32) {
+    const int r = tap / ww, c = tap - r * ww;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (static_cast<size_t>(h_lo + r) * g.W + (w_lo + c)) * g.Cp));
+    const uint32_t w4[4] = {v.x ^ flip, v.y ^ flip, v.z ^ flip, v.w ^ flip};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      mx[k] = __vmaxu4(mx[k], w4[k]);
+      even[k] += w4[k] & 0x00FF00FFu;
+      odd[k] += (w4[k] >> 8) & 0x00FF00FFu;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      mx[k] = __vmaxu4(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], off));
+      even[k] += __shfl_xor_sync(0xffffffffu, even[k], off);     // 16-bit lanes: at most 256 taps x 255
+      odd[k] += __shfl_xor_sync(0xffffffffu, odd[k], off);
+    }
+  }
+  if (lane >= 4) return;
+  const int k = lane;                                           // lane k finishes word k of the chunk
+  const int bias = XS ? 128 : 0;
+  const float div = type == 1 ? static_cast<float>(g.kw * g.kh) : static_cast<float>(count);
+  uint32_t word = 0;
+  if (type == 0 && same_quant) {
+    word = count ? (mx[k] ^ flip) : (static_cast<uint32_t>(in_zp & 0xFF) * 0x01010101u);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int q;
+      if (type == 0) {
+        q = count ? static_cast<int>((mx[k] >> (8 * j)) & 0xFF) - bias : in_zp;
+        q = requant(__fmul_rn(__fsub_rn(__int2float_rn(q), __int2float_rn(in_zp)), in_scale), out);
+      } else {
+        const uint32_t pair = (j & 1) ? odd[k] : even[k];
+        const int sum = static_cast<int>((pair >> (16 * (j >> 1))) & 0xFFFF) - count * (in_zp + bias);
+        const float avg = count ? __fdiv_rn(__fmul_rn(__int2float_rn(sum), in_scale), div) : 0.0f;
+        q = requant(avg, out);
+      }
+      word |= static_cast<uint32_t>(q & 0xFF) << (8 * j);
+    }
+  }
+  *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(p) * g.Cp + ch * 16 + 4 * k) = word;
+}
+
 __global__ void pool_f32_kernel(const float* __restrict__ x, int type, ConvGeom g, float* __restrict__ y) {
   const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * g.C;
   long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -1317,6 +1389,12 @@ void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int i
   if (g.kw * g.kh <= 256 && g.dx == 1 && g.dy == 1) {
     const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * (g.Cp / 16);
     if (total == 0) return;
+    if (g.kw * g.kh >= 32 && total <= 148LL * 2048 / 32 * 8) {
+      // few outputs, many taps each: a warp per output chunk
+      if (is_signed) launch_pdl(pool_q16_warp_kernel<true>, dim3(grid_for(total * 32, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
+      else launch_pdl(pool_q16_warp_kernel<false>, dim3(grid_for(total * 32, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
+      return;
+    }
     if (is_signed) launch_pdl(pool_q16_kernel<true>, dim3(grid_for(total, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
     else launch_pdl(pool_q16_kernel<false>, dim3(grid_for(total, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
     return;
