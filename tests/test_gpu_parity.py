@@ -264,6 +264,42 @@ def test_add_kernels_match_oracle(oracle_lib, product_lib, kernel, quant):
     G.assert_same(want, got)
 
 
+BROADCAST_SHAPES = {
+    "per_channel": ([8, 6, 20, 2], [1, 1, 20, 1]),
+    "per_pixel": ([8, 6, 20, 2], [8, 6, 1, 2]),
+    "both_sides": ([1, 1, 20, 2], [8, 6, 20, 1]),
+    "rank2_row": ([48, 5], [48, 1]),
+    "scalar_like": ([7, 3, 17, 1], [1, 1, 1, 1]),
+}
+
+
+@pytest.mark.parametrize("dtype", ["u8", "f32"])
+@pytest.mark.parametrize("name", sorted(BROADCAST_SHAPES))
+def test_add_broadcast_matches_oracle(oracle_lib, product_lib, name, dtype):
+    """numpy-style broadcasting of Add (equal ranks, ones repeat), quantized and float32."""
+    da, db = BROADCAST_SHAPES[name]
+    def build(g, rng):
+        if dtype == "u8":
+            a = g.tensor(B.DT_UINT8, da, B.ATTR_INPUT, scale=0.02, zero_point=128)
+            b = g.tensor(B.DT_UINT8, db, B.ATTR_INPUT, scale=0.035, zero_point=117)
+            y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.05, zero_point=120)
+            av = rng.integers(0, 256, size=da[::-1]).astype(np.uint8)
+            bv = rng.integers(0, 256, size=db[::-1]).astype(np.uint8)
+        else:
+            a = g.tensor(B.DT_FLOAT32, da, B.ATTR_INPUT)
+            b = g.tensor(B.DT_FLOAT32, db, B.ATTR_INPUT)
+            y = g.tensor(B.DT_FLOAT32, [], B.ATTR_OUTPUT)
+            av = rng.standard_normal(da[::-1]).astype(np.float32)
+            bv = rng.standard_normal(db[::-1]).astype(np.float32)
+        g.add(a, b, y)
+        return [(a, av), (b, bv)], [y]
+    want, _ = G.run_case(oracle_lib, build, seed=4)
+    got, kernels = G.run_case(product_lib, build, seed=4)
+    assert any(k["name"] == "add_broadcast" for k in kernels), [k["name"] for k in kernels]
+    assert want[0].shape == tuple(max(x, y) for x, y in zip(da, db))[::-1]
+    G.assert_same(want, got)
+
+
 def test_add_int8_matches_oracle(oracle_lib, product_lib):
     def build(g, rng):
         n = 65536

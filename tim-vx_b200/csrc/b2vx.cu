@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <array>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -275,9 +276,16 @@ b2vx_status infer_node(b2vx_graph* g, NodeRec& n) {
     case B2VX_NODE_ADD: {
       const TensorRec& b = g->tensors[n.in[1]];
       if (!b.has_shape) return fail(g, B2VX_SHAPE_MISMATCH, "add: input has no shape");
-      if (b.d.rank != x.d.rank || !std::equal(x.d.dims, x.d.dims + x.d.rank, b.d.dims))
-        return fail(g, B2VX_UNSUPPORTED, "add: broadcasting is not supported, operands must have equal shapes");
-      return set_shape(g, n.out, std::vector<uint32_t>(x.d.dims, x.d.dims + x.d.rank), "add", false);
+      // numpy-style broadcast per dimension (vsi_nn_op_eltwise.c:147-214); operands of different rank
+      // map to different storage axes here, so equal ranks are required (pad the shape with ones)
+      if (b.d.rank != x.d.rank) return fail(g, B2VX_UNSUPPORTED, "add: operands must have the same rank (pad the smaller shape with ones)");
+      std::vector<uint32_t> dims(x.d.rank);
+      for (uint32_t i = 0; i < x.d.rank; ++i) {
+        const uint32_t da = x.d.dims[i], db = b.d.dims[i];
+        if (da != db && da != 1 && db != 1) return fail(g, B2VX_SHAPE_MISMATCH, "add: shapes do not broadcast");
+        dims[i] = std::max(da, db);
+      }
+      return set_shape(g, n.out, dims, "add", false);
     }
     default:
       return set_shape(g, n.out, std::vector<uint32_t>(x.d.dims, x.d.dims + x.d.rank), "unary", false);
@@ -929,6 +937,27 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   TensorRec& y = g->tensors[n.out];
   const uint64_t abytes = a.bytes() + b.bytes() + y.bytes();
   Step s;
+  const bool same_shape = a.N == y.N && a.H == y.H && a.W == y.W && a.C == y.C && b.N == y.N && b.H == y.H && b.W == y.W && b.C == y.C;
+  if (!same_shape) {
+    const bool all_f32 = a.d.dtype == B2VX_DT_FLOAT32 && b.d.dtype == B2VX_DT_FLOAT32 && y.d.dtype == B2VX_DT_FLOAT32;
+    const bool all_q8 = is_q8(a.d.dtype) && is_q8(b.d.dtype) && is_q8(y.d.dtype);
+    if (!all_f32 && !all_q8) return fail(g, B2VX_UNSUPPORTED, "add: operands must be all int8/uint8 or all float32");
+    const void *ap = cl_in(a), *bp = cl_in(b);
+    void* yp = y.d_cl;
+    const int as = a.d.dtype == B2VX_DT_INT8, bs = b.d.dtype == B2VX_DT_INT8;
+    const float sa = all_q8 ? a.scale() : 1.0f, sb = all_q8 ? b.scale() : 1.0f;
+    const int za = all_q8 ? a.zp() : 0, zb = all_q8 ? b.zp() : 0;
+    const OutQuant oq = out_quant(y);
+    const std::array<int, 5> ad = {a.N, a.H, a.W, a.C, a.Cp}, bd = {b.N, b.H, b.W, b.C, b.Cp}, yd = {y.N, y.H, y.W, y.C, y.Cp};
+    const int elem = all_f32 ? 4 : 1;
+    s.info = make_info("add_broadcast", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) {
+      launch_add_broadcast(ap, as, sa, za, ad.data(), bp, bs, sb, zb, bd.data(), oq, yd.data(), elem, yp, st2);
+      return cudaGetLastError();
+    };
+    g->steps.push_back(std::move(s));
+    return B2VX_OK;
+  }
   if (a.d.dtype == B2VX_DT_FLOAT32 && b.d.dtype == B2VX_DT_FLOAT32 && y.d.dtype == B2VX_DT_FLOAT32) {
     const float *ap = static_cast<const float*>(cl_in(a)), *bp = static_cast<const float*>(cl_in(b));
     float* yp = static_cast<float*>(y.d_cl);

@@ -901,6 +901,38 @@ __global__ void __launch_bounds__(256) add_q_lut_kernel(const uint4* __restrict_
   }
 }
 
+// Add with numpy-style broadcasting (equal ranks, a dimension of 1 repeats): one output element per
+// thread, operand indices from per-axis strides (0 along a broadcast axis), the exact float sequence.
+// A slow path by design; the equal-shape case never comes here.
+struct BroadcastGeom {
+  int N, H, W, C, Cp;                  // output
+  long long as[4], bs[4];              // element strides of a and b along (n, h, w, c); 0 = broadcast
+};
+template <typename T>
+__global__ void add_broadcast_kernel(const T* __restrict__ a, float sa, int za, int a_signed, const T* __restrict__ b, float sb,
+                                     int zb, int b_signed, OutQuant out, BroadcastGeom g, T* __restrict__ y) {
+  const long long total = static_cast<long long>(g.N) * g.H * g.W * g.C;
+  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= total) return;
+  const int c = static_cast<int>(i % g.C);
+  long long r = i / g.C;
+  const int w = static_cast<int>(r % g.W); r /= g.W;
+  const int h = static_cast<int>(r % g.H);
+  const int n = static_cast<int>(r / g.H);
+  const long long ai = n * g.as[0] + h * g.as[1] + w * g.as[2] + c * g.as[3];
+  const long long bi = n * g.bs[0] + h * g.bs[1] + w * g.bs[2] + c * g.bs[3];
+  const size_t yi = ((static_cast<size_t>(n) * g.H + h) * g.W + w) * g.Cp + c;
+  if (sizeof(T) == 4) {
+    reinterpret_cast<float*>(y)[yi] = __fadd_rn(reinterpret_cast<const float*>(a)[ai], reinterpret_cast<const float*>(b)[bi]);
+  } else {
+    const int qa = a_signed ? static_cast<int>(static_cast<int8_t>(a[ai])) : static_cast<int>(a[ai]);
+    const int qb = b_signed ? static_cast<int>(static_cast<int8_t>(b[bi])) : static_cast<int>(b[bi]);
+    const float fa = __fmul_rn(__fsub_rn(__int2float_rn(qa), __int2float_rn(za)), sa);
+    const float fb = __fmul_rn(__fsub_rn(__int2float_rn(qb), __int2float_rn(zb)), sb);
+    y[yi] = static_cast<T>(requant(__fadd_rn(fa, fb), out) & 0xFF);
+  }
+}
+
 __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y, size_t n) {
   size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   if (i < n) y[i] = __fadd_rn(a[i], b[i]);
@@ -1457,6 +1489,28 @@ void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* 
   if (grid > 148u * 3u) grid = 148u * 3u;
   launch_pdl(add_q_lut_kernel, dim3(grid), dim3(256), 65536, s, static_cast<const uint4*>(a), static_cast<const uint4*>(b),
                                             reinterpret_cast<const uint4*>(table), static_cast<uint4*>(y), n16);
+}
+
+void launch_add_broadcast(const void* a, int a_signed, float sa, int za, const int a_dims[5], const void* b, int b_signed, float sb,
+                          int zb, const int b_dims[5], OutQuant out, const int y_dims[5], int elem, void* y, cudaStream_t s) {
+  BroadcastGeom g;
+  g.N = y_dims[0]; g.H = y_dims[1]; g.W = y_dims[2]; g.C = y_dims[3]; g.Cp = y_dims[4];
+  auto strides = [&](const int d[5], long long st[4]) {
+    const long long full[4] = {static_cast<long long>(d[1]) * d[2] * d[4], static_cast<long long>(d[2]) * d[4], d[4], 1};
+    for (int k = 0; k < 4; ++k) st[k] = (d[k] == 1 && y_dims[k] != 1) ? 0 : full[k];
+  };
+  strides(a_dims, g.as);
+  strides(b_dims, g.bs);
+  const long long total = static_cast<long long>(g.N) * g.H * g.W * g.C;
+  if (total == 0) return;
+  if (elem == 4)
+    add_broadcast_kernel<uint32_t><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint32_t*>(a), sa, za, a_signed,
+                                                                                static_cast<const uint32_t*>(b), sb, zb, b_signed, out, g,
+                                                                                static_cast<uint32_t*>(y));
+  else
+    add_broadcast_kernel<uint8_t><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(a), sa, za, a_signed,
+                                                                               static_cast<const uint8_t*>(b), sb, zb, b_signed, out, g,
+                                                                               static_cast<uint8_t*>(y));
 }
 
 void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s) {
