@@ -579,7 +579,8 @@ __global__ void pool_q_kernel(const uint8_t* __restrict__ x, int type, float in_
 
 // The same pooling with 16 channels (one 128-bit access) per thread and byte-SIMD arithmetic: max with
 // __vmaxu4/__vmaxs4, sums as packed 16-bit pairs (so the window may hold at most 256 taps).
-template <bool XS>
+// K = 2 or 3: a K x K window known at compile time, so that all its loads are in flight together; 0: any window.
+template <bool XS, int K>
 __global__ void __launch_bounds__(256) pool_q16_kernel(const uint8_t* __restrict__ x, int type, float in_scale, int in_zp,
                                                        int same_quant, ConvGeom g, OutQuant out, uint8_t* __restrict__ y) {
   pdl_wait();
@@ -600,20 +601,40 @@ __global__ void __launch_bounds__(256) pool_q16_kernel(const uint8_t* __restrict
   const uint32_t flip = XS ? 0x80808080u : 0u;       // signed bytes are handled as value + 128
   uint32_t mx[4] = {0u, 0u, 0u, 0u};                 // unsigned max of the biased bytes
   uint32_t even[4] = {0u, 0u, 0u, 0u}, odd[4] = {0u, 0u, 0u, 0u};   // 16-bit sums of bytes 0,2 and 1,3 of each word
-  for (int hi = h_lo; hi < h_hi; ++hi) {
-    const uint8_t* rowp = x + ((static_cast<size_t>(n) * g.H + hi) * g.W) * g.Cp + ch * 16;
-    for (int wi = w_lo; wi < w_hi; ++wi) {
-      const uint4 v = *reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi) * g.Cp);
-      const uint32_t w4[4] = {v.x ^ flip, v.y ^ flip, v.z ^ flip, v.w ^ flip};
+  auto take = [&](const uint4& v) {
+    const uint32_t w4[4] = {v.x ^ flip, v.y ^ flip, v.z ^ flip, v.w ^ flip};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (type == 0) {
-          mx[k] = __vmaxu4(mx[k], w4[k]);
-        } else {
-          even[k] += w4[k] & 0x00FF00FFu;
-          odd[k] += (w4[k] >> 8) & 0x00FF00FFu;
-        }
+    for (int k = 0; k < 4; ++k) {
+      if (type == 0) {
+        mx[k] = __vmaxu4(mx[k], w4[k]);
+      } else {
+        even[k] += w4[k] & 0x00FF00FFu;
+        odd[k] += (w4[k] >> 8) & 0x00FF00FFu;
       }
+    }
+  };
+  if (K > 0) {
+    const uint8_t* img = x + static_cast<size_t>(n) * g.H * g.W * g.Cp + ch * 16;
+    constexpr int KK = K > 0 ? K * K : 1;
+    uint4 v[KK];
+    bool ok[KK];
+#pragma unroll
+    for (int ky = 0; ky < K; ++ky) {
+#pragma unroll
+      for (int kx = 0; kx < K; ++kx) {
+        const int hi = ho * g.sy - g.pt + ky, wi = wo * g.sx - g.pl + kx;
+        ok[ky * K + kx] = hi >= 0 && hi < g.H && wi >= 0 && wi < g.W;
+        v[ky * K + kx] = make_uint4(0, 0, 0, 0);
+        if (ok[ky * K + kx]) v[ky * K + kx] = __ldg(reinterpret_cast<const uint4*>(img + (static_cast<size_t>(hi) * g.W + wi) * g.Cp));
+      }
+    }
+#pragma unroll
+    for (int t9 = 0; t9 < K * K; ++t9)
+      if (ok[t9]) take(v[t9]);
+  } else {
+    for (int hi = h_lo; hi < h_hi; ++hi) {
+      const uint8_t* rowp = x + ((static_cast<size_t>(n) * g.H + hi) * g.W) * g.Cp + ch * 16;
+      for (int wi = w_lo; wi < w_hi; ++wi) take(*reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(wi) * g.Cp));
     }
   }
   const int bias = XS ? 128 : 0;
@@ -868,16 +889,15 @@ __device__ __forceinline__ uint32_t add_lut_word(uint32_t aw, uint32_t bw, const
   return __byte_perm(__byte_perm(r0, r1, 0x0040), __byte_perm(r2, r3, 0x0040), 0x5410);
 }
 
-__global__ void __launch_bounds__(256) add_q_lut_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
+__global__ void __launch_bounds__(1024) add_q_lut_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
                                                         const uint4* __restrict__ table, uint4* __restrict__ y, size_t n16) {
   pdl_trigger();
   extern __shared__ uint4 tab4[];
-  for (int i = threadIdx.x; i < 4096; i += 256) tab4[i] = table[i];   // a constant of the graph
+  for (int i = threadIdx.x; i < 4096; i += blockDim.x) tab4[i] = table[i];   // a constant of the graph
   __syncthreads();
   pdl_wait();
   const uint8_t* tab = reinterpret_cast<const uint8_t*>(tab4);
-  // Four groups per step with all eight loads issued first: 64 KB of shared memory allow only three
-  // blocks per SM, so each thread has to keep more bytes in flight.
+  // Four groups per step with all eight loads issued first, to keep enough bytes in flight.
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16; i += 4 * stride) {
     uint4 av[4], bv[4];
@@ -1427,8 +1447,12 @@ void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int i
       else launch_pdl(pool_q16_warp_kernel<false>, dim3(grid_for(total * 32, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
       return;
     }
-    if (is_signed) launch_pdl(pool_q16_kernel<true>, dim3(grid_for(total, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
-    else launch_pdl(pool_q16_kernel<false>, dim3(grid_for(total, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
+    const dim3 grid(grid_for(total, 256));
+#define B2VX_POOL_LAUNCH(XS_, K_) launch_pdl(pool_q16_kernel<XS_, K_>, grid, dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp)
+    if (g.kw == 3 && g.kh == 3) { if (is_signed) B2VX_POOL_LAUNCH(true, 3); else B2VX_POOL_LAUNCH(false, 3); }
+    else if (g.kw == 2 && g.kh == 2) { if (is_signed) B2VX_POOL_LAUNCH(true, 2); else B2VX_POOL_LAUNCH(false, 2); }
+    else { if (is_signed) B2VX_POOL_LAUNCH(true, 0); else B2VX_POOL_LAUNCH(false, 0); }
+#undef B2VX_POOL_LAUNCH
     return;
   }
   const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * (g.Cp / 4);
@@ -1485,9 +1509,10 @@ void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* 
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   // three 64 KB blocks per SM; every block should have enough elements to repay its table load
-  unsigned grid = grid_for(static_cast<long long>((n16 + 7) / 8), 256);
-  if (grid > 148u * 3u) grid = 148u * 3u;
-  launch_pdl(add_q_lut_kernel, dim3(grid), dim3(256), 65536, s, static_cast<const uint4*>(a), static_cast<const uint4*>(b),
+  // 1024 threads share one table: two blocks (64 warps, the SM's maximum) per SM
+  unsigned grid = grid_for(static_cast<long long>((n16 + 7) / 8), 1024);
+  if (grid > 148u * 2u) grid = 148u * 2u;
+  launch_pdl(add_q_lut_kernel, dim3(grid), dim3(1024), 65536, s, static_cast<const uint4*>(a), static_cast<const uint4*>(b),
                                             reinterpret_cast<const uint4*>(table), static_cast<uint4*>(y), n16);
 }
 
