@@ -143,13 +143,16 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
-// Bounded wait.  Returns false when the CTA is aborting.
+// Bounded wait.  Returns false when the CTA is aborting.  Polls back off: a wait that is not over after
+// a few tries is a long one (a control warp waiting for the epilogue, say), and a warp that keeps
+// polling takes issue slots from the warps it is waiting for; sleeps grow from 64 ns to 1 us.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
+  unsigned sleep_ns = 32;
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - start > kWaitLimitCycles) {
@@ -157,6 +160,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       atomicCAS(status, 0, code);
       return false;
     }
+    if (sleep_ns < 1024) sleep_ns <<= 1;
+    __nanosleep(sleep_ns);
   }
 }
 
