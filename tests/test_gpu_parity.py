@@ -300,6 +300,73 @@ def test_add_broadcast_matches_oracle(oracle_lib, product_lib, name, dtype):
     G.assert_same(want, got)
 
 
+def conv_then_add(W, H, C, N, k, Oc, swap=False, w_kind="s8pc", in_q=(0.02, 0), conv_q=(0.04, 131), res_q=(0.03, 7),
+                  out_q=(0.06, 0), relu=True, dtype=B.DT_UINT8, stride=1):
+    """x -> Conv2d -> t; Add(t, r) [operands swapped on request] -> Relu -> y, with r a second graph input."""
+    def build(g, rng):
+        x = g.tensor(dtype, [W, H, C, N], B.ATTR_INPUT, scale=in_q[0], zero_point=in_q[1])
+        wshape = [k, k, C, Oc]
+        if w_kind == "s8pc":
+            ws = rng.uniform(0.001, 0.01, Oc).astype(np.float32)
+            w = g.tensor(B.DT_INT8, wshape, B.ATTR_CONSTANT, scales=ws, channel_dim=3,
+                         data=rng.integers(-127, 128, size=wshape[::-1]).astype(np.int8))
+            bq = dict(scales=np.float32(in_q[0]) * ws, channel_dim=0)
+        else:
+            w = g.tensor(B.DT_UINT8, wshape, B.ATTR_CONSTANT, scale=0.01, zero_point=int(rng.integers(100, 157)),
+                         data=rng.integers(0, 256, size=wshape[::-1]).astype(np.uint8))
+            bq = dict(scale=float(np.float32(in_q[0]) * np.float32(0.01)), zero_point=0)
+        b = g.tensor(B.DT_INT32, [Oc], B.ATTR_CONSTANT, data=rng.integers(-1000, 1001, size=Oc).astype(np.int32), **bq)
+        t = g.tensor(dtype, [], B.ATTR_TRANSIENT, scale=conv_q[0], zero_point=conv_q[1])
+        g.conv2d(x, w, b, t, stride=(stride, stride), pad_type=B.PAD_SAME)
+        Wo, Ho = (W + stride - 1) // stride, (H + stride - 1) // stride
+        r = g.tensor(dtype, [Wo, Ho, Oc, N], B.ATTR_INPUT, scale=res_q[0], zero_point=res_q[1])
+        s_ = g.tensor(dtype, [], B.ATTR_TRANSIENT if relu else B.ATTR_OUTPUT, scale=out_q[0], zero_point=out_q[1])
+        if swap:
+            g.add(r, t, s_)
+        else:
+            g.add(t, r, s_)
+        y = s_
+        if relu:
+            y = g.tensor(dtype, [], B.ATTR_OUTPUT, scale=out_q[0], zero_point=out_q[1])
+            g.relu(s_, y)
+        lo, hi = (0, 256) if dtype == B.DT_UINT8 else (-128, 128)
+        np_t = B.NP_DTYPE[dtype]
+        return [(x, rng.integers(lo, hi, size=(N, C, H, W)).astype(np_t)),
+                (r, rng.integers(lo, hi, size=(N, Oc, Ho, Wo)).astype(np_t))], [y]
+    return build
+
+
+FUSED_ADD_CASES = {
+    "expand_1x1": conv_then_add(14, 14, 64, 2, 1, 256),
+    "expand_1x1_swapped": conv_then_add(14, 14, 64, 2, 1, 256, swap=True),
+    "conv3x3_zp_border": conv_then_add(13, 11, 32, 2, 3, 48, in_q=(0.02, 128)),
+    "u8_weights_linear": conv_then_add(9, 9, 96, 3, 1, 24, w_kind="u8", in_q=(0.03, 0), relu=False, out_q=(0.05, 120)),
+    "stride2_3x3": conv_then_add(16, 16, 32, 1, 3, 64, stride=2),
+    "int8_everything": conv_then_add(10, 10, 16, 2, 1, 32, dtype=B.DT_INT8, in_q=(0.05, -3), conv_q=(0.1, 4), res_q=(0.08, -9),
+                                     out_q=(0.15, -128)),
+    "oc_300_two_tiles": conv_then_add(7, 7, 64, 2, 1, 300),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FUSED_ADD_CASES))
+def test_residual_add_fused_into_conv_matches_oracle(oracle_lib, product_lib, name):
+    """Conv2d -> Add(-> Relu): the Add runs in the convolution's epilogue through its 64 KB table; the same
+    graph with the fusion switched off and the oracle must give the same bytes."""
+    os.environ.pop("B2VX_CONV_KERNEL", None)
+    want, _ = G.run_case(oracle_lib, FUSED_ADD_CASES[name], seed=31)
+    got, kernels = G.run_case(product_lib, FUSED_ADD_CASES[name], seed=31)
+    names = [k["name"] for k in kernels]
+    assert any("+add" in n for n in names) and not any(n.startswith("add_q") for n in names), names
+    G.assert_same(want, got)
+    os.environ["B2VX_FUSE_ADD"] = "0"
+    try:
+        unfused, kernels2 = G.run_case(product_lib, FUSED_ADD_CASES[name], seed=31)
+    finally:
+        os.environ.pop("B2VX_FUSE_ADD", None)
+    assert any(k["name"].startswith("add_q") for k in kernels2)
+    G.assert_same(want, unfused)
+
+
 def test_add_int8_matches_oracle(oracle_lib, product_lib):
     def build(g, rng):
         n = 65536

@@ -86,6 +86,8 @@ struct NodeRec {
   } p;
   uint32_t pad[4];
   bool removed = false;   // folded into its producer at compile
+  int fuse_add = -1;      // index of the Add node this convolution's epilogue may absorb
+  uint32_t fuse_residual = B2VX_NO_TENSOR;   // that Add's other operand
 };
 
 struct Step {
@@ -117,6 +119,10 @@ struct b2vx_graph {
   int* h_status = nullptr;
   bool compiled = false;
   bool use_tc = false;
+  bool fuse_add = true;      // residual Add into the preceding convolution's epilogue (B2VX_FUSE_ADD=0 disables)
+  int fuse_request = -1;     // set while planning a convolution that may absorb an Add: that Add's node index
+  uint32_t fuse_residual = B2VX_NO_TENSOR;
+  bool fuse_done = false;
   bool fc_small_m = true;    // FullyConnected with <= 16 rows on the CUDA-core streaming kernel
   int add_mode = 0;          // quantized Add: 0 choose by size, 1 table kernel, 2 arithmetic kernel
   // the whole launch plan captured once as a CUDA graph; replays cost one launch on the host
@@ -678,6 +684,36 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       const double tmax = (2.0 * static_cast<double>(Kp) * 255.0 * 128.0 + bmax) * smax / std::fabs(static_cast<double>(ep.out.scale));
       ep.exact_only = !(tmax < 2097152.0);
     }
+    void* fused_out = nullptr;
+    if (g->fuse_request >= 0) {
+      // absorb the Add that follows: table over (this convolution's byte, the residual's byte)
+      NodeRec& ad = g->nodes[g->fuse_request];
+      TensorRec& res = g->tensors[g->fuse_residual];
+      TensorRec& ao = g->tensors[ad.out];
+      if (res.Cp == y.Cp && ao.Cp == y.Cp && res.cl_bytes == y.cl_bytes && ao.cl_bytes == y.cl_bytes) {
+        const bool ys = y.d.dtype == B2VX_DT_INT8, rs = res.d.dtype == B2VX_DT_INT8;
+        const OutQuant aq = out_quant(ao);
+        std::vector<uint8_t> table(65536);
+        for (int iq = 0; iq < 256; ++iq) {
+          const int q = ys ? static_cast<int>(static_cast<int8_t>(iq)) : iq;
+          const float fq = (static_cast<float>(q) - static_cast<float>(y.zp())) * y.scale();
+          for (int ir = 0; ir < 256; ++ir) {
+            const int r = rs ? static_cast<int>(static_cast<int8_t>(ir)) : ir;
+            const float fr = (static_cast<float>(r) - static_cast<float>(res.zp())) * res.scale();
+            // operand order of the float addition as in the Add node (addition commutes, kept for the record)
+            const float sum = ad.in[0] == g->fuse_residual ? fr + fq : fq + fr;
+            table[iq * 256 + (ir ^ ((iq & 31) << 2))] = static_cast<uint8_t>(host_requant(sum, aq) & 0xFF);
+          }
+        }
+        uint8_t* dtab = nullptr;
+        const b2vx_status stt = upload(g, table, &dtab);
+        if (stt != B2VX_OK) return stt;
+        ep.add_residual = static_cast<const uint8_t*>(cl_in(res));
+        ep.add_table = dtab;
+        fused_out = ao.d_cl;
+        g->fuse_done = true;
+      }
+    }
     if (need_im2col) {
       const size_t need = static_cast<size_t>(M) * Kp;
       g->scratch_bytes = std::max(g->scratch_bytes, need);
@@ -688,7 +724,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     // finalizer that Compile runs at its end.
     const int zx = x.zp();
     const std::string lbl = label;
-    void* ycl = y.d_cl;
+    void* ycl = fused_out ? fused_out : y.d_cl;
     const int ldd = y.Cp, Oc = y.C, y_signed = y.d.dtype == B2VX_DT_INT8;
     if (mode == WHCN8) {
       const void* xio = x.d_io;
@@ -735,8 +771,13 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       return B2VX_OK;
     });
     Step s_gemm;
-    s_gemm.info = make_info(implicit ? "gemm_i8_tc(implicit)" : (need_im2col ? "gemm_i8_tc(im2col)" : "gemm_i8_tc"), node_index,
-                            2 * macs, abytes);
+    {
+      std::string kname = implicit ? "gemm_i8_tc(implicit" : (need_im2col ? "gemm_i8_tc(im2col" : "gemm_i8_tc(");
+      if (fused_out) kname += kname.back() == '(' ? "+add" : ",+add";
+      kname += ")";
+      if (kname == "gemm_i8_tc()") kname = "gemm_i8_tc";
+      s_gemm.info = make_info(kname.c_str(), node_index, 2 * macs, abytes + (fused_out ? y.bytes() : 0));
+    }
     s_gemm.fn = [=](cudaStream_t st2) -> cudaError_t { return gemm_tc_launch(*plan_holder, st2); };
     g->steps.push_back(std::move(s_gemm));
     return B2VX_OK;
@@ -1098,6 +1139,9 @@ b2vx_status add_node(b2vx_graph* g, int32_t kind, uint32_t i0, uint32_t i1, uint
   else std::memset(&n, 0, sizeof(n));
   n.kind = kind;
   n.in[0] = i0; n.in[1] = i1; n.in[2] = i2; n.out = out;
+  n.removed = false;
+  n.fuse_add = -1;
+  n.fuse_residual = B2VX_NO_TENSOR;
   g->nodes.push_back(n);
   return B2VX_OK;
 }
@@ -1152,6 +1196,8 @@ b2vx_status b2vx_graph_create(b2vx_context* ctx, int32_t device_id, b2vx_graph**
   g->stream = g->own_stream;
   const char* k = std::getenv("B2VX_CONV_KERNEL");
   g->use_tc = gemm_tc_available() && !(k && std::strcmp(k, "simt") == 0);
+  const char* fa = std::getenv("B2VX_FUSE_ADD");
+  g->fuse_add = !(fa && fa[0] == '0');
   const char* fs = std::getenv("B2VX_FC_SMALL_M");
   g->fc_small_m = !(fs && fs[0] == '0');
   const char* ak = std::getenv("B2VX_ADD_KERNEL");
@@ -1368,6 +1414,50 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
     r.removed = true;
   }
 
+  // 1c. A quantized Add one of whose operands is the output of a convolution that nothing else reads
+  // can be done in that convolution's epilogue (tensor-core path): the convolution's byte and the
+  // other operand's byte index the Add's 64 KB table.  The absorbing convolution is the operand
+  // produced later in the order; the other operand is then ready when it runs.  Whether the fusion
+  // happens is decided when the convolution is planned (it needs the tensor-core path).
+  if (g->fuse_add && g->use_tc) {
+    std::vector<int> pos(g->nodes.size(), -1);
+    for (size_t i = 0; i < g->order.size(); ++i) pos[g->order[i]] = static_cast<int>(i);
+    for (size_t ai = 0; ai < g->nodes.size(); ++ai) {
+      NodeRec& ad = g->nodes[ai];
+      if (ad.removed || ad.kind != B2VX_NODE_ADD) continue;
+      const TensorRec& t0 = g->tensors[ad.in[0]];
+      const TensorRec& t1 = g->tensors[ad.in[1]];
+      const TensorRec& to = g->tensors[ad.out];
+      if (!is_q8(t0.d.dtype) || !is_q8(t1.d.dtype) || !is_q8(to.d.dtype)) continue;
+      if (t0.d.rank != t1.d.rank || !std::equal(t0.d.dims, t0.d.dims + t0.d.rank, t1.d.dims)) continue;
+      int best = -1, best_operand = -1;
+      for (int k = 0; k < 2; ++k) {
+        const uint32_t tid = ad.in[k];
+        if (g->tensors[tid].d.attr != B2VX_ATTR_TRANSIENT) continue;
+        int consumers = 0, producer = -1;
+        for (size_t ni = 0; ni < g->nodes.size(); ++ni) {
+          const NodeRec& n = g->nodes[ni];
+          if (n.removed) continue;
+          for (uint32_t id : n.in) consumers += id == tid;
+          if (n.out == tid) producer = static_cast<int>(ni);
+        }
+        if (consumers != 1 || producer < 0) continue;
+        const NodeRec& pn = g->nodes[producer];
+        if (pn.kind != B2VX_NODE_CONV2D || pn.p.conv.multiplier >= 1 || pn.fuse_add >= 0) continue;
+        if (best < 0 || pos[producer] > pos[best]) { best = producer; best_operand = k; }
+      }
+      if (best < 0) continue;
+      // the other operand must exist before the absorbing convolution runs
+      const uint32_t other = ad.in[1 - best_operand];
+      int other_producer = -1;
+      for (size_t ni = 0; ni < g->nodes.size(); ++ni)
+        if (!g->nodes[ni].removed && g->nodes[ni].out == other) other_producer = static_cast<int>(ni);
+      if (other_producer >= 0 && pos[other_producer] > pos[best]) continue;
+      g->nodes[best].fuse_add = static_cast<int>(ai);
+      g->nodes[best].fuse_residual = other;
+    }
+  }
+
   // 2. which tensors are activations (touched by a node as data, not as weights/bias)
   for (const NodeRec& n : g->nodes) {
     if (n.removed) continue;
@@ -1401,7 +1491,14 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
     if (n.removed) continue;
     b2vx_status st = B2VX_UNSUPPORTED;
     switch (n.kind) {
-      case B2VX_NODE_CONV2D: st = plan_conv(g, idx, n); break;
+      case B2VX_NODE_CONV2D:
+        g->fuse_request = n.fuse_add;
+        g->fuse_residual = n.fuse_residual;
+        g->fuse_done = false;
+        st = plan_conv(g, idx, n);
+        if (st == B2VX_OK && g->fuse_done) g->nodes[n.fuse_add].removed = true;   // the Add happens in this node's kernel
+        g->fuse_request = -1;
+        break;
       case B2VX_NODE_FULLY_CONNECTED: st = plan_fc(g, idx, n); break;
       case B2VX_NODE_POOL2D: st = plan_pool(g, idx, n); break;
       case B2VX_NODE_ADD: st = plan_add(g, idx, n); break;

@@ -278,7 +278,10 @@ struct SmemHeader {
 
 // EXTRA: rows carry a weight-zero-point term (p.dz, S column) and/or border corrections
 // (p.ep.border_corr); the plain form contains no code for either.
-template <bool EXTRA>
+// FUSE: a residual Add follows the convolution and is done here: the 64 KB table of that Add sits in
+// shared memory behind the operand ring, the epilogue loads the residual's 16 bytes beside its own
+// and stores the table's answers instead (direct stores only).
+template <bool EXTRA, bool FUSE>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
@@ -296,7 +299,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t ring_bytes = (p.stages * stage_bytes + 1023u) & ~1023u;
   const uint32_t staging_bytes = p.store_span ? static_cast<uint32_t>(kBlockM) * p.BNd : 0u;   // per buffer, multiple of 4096
   uint8_t* staging = tiles + ring_bytes;
-  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(staging + 2 * staging_bytes);
+  uint8_t* add_tab = staging + 2 * staging_bytes;                 // 64 KB when FUSE
+  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(add_tab + (FUSE ? 65536 : 0));
   volatile int* abort_flag = &hdr->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -328,6 +332,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int oc = n_tile * p.BNd + i;
     hdr->bias[i] = oc < p.Ocp ? p.ep.bias_full[oc] : 0;
     hdr->scale[i] = oc < p.Ocp ? p.ep.acc_scale[oc] : 0.0f;
+  }
+  if (FUSE) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.ep.add_table);   // a constant of the graph
+    uint4* dst = reinterpret_cast<uint4*>(add_tab);
+    for (int i = threadIdx.x; i < 4096; i += kThreadsTc) dst[i] = __ldg(src + i);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hdr->tmem_base)),
@@ -485,7 +494,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int rest = m_tile / p.tiles_w;
         th = rest % p.tiles_h;
         tn = rest / p.tiles_h;
-        if (!span_b || (EXTRA && p.ep.border_corr)) {
+        if (!span_b || FUSE || (EXTRA && p.ep.border_corr)) {
           const int i = row_in_tile % p.TW, r2 = row_in_tile / p.TW;
           const int jh = r2 % p.TH, l = r2 / p.TH;
           const int wo = tw * p.TW + i, ho = th * p.TH + jh, n = tn * p.TN + l;
@@ -497,7 +506,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
           }
         }
-      } else if (!span_b) {
+      } else if (!span_b || FUSE) {
         row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
         if (row >= p.M) row = -1;
       }
@@ -515,8 +524,16 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       auto emit = [&](const int (&acc)[16], int c0) {
         const int cbase = n_tile * p.BNd + c0;
         if (!span_b && (row < 0 || cbase + 16 > p.Ocp)) return;
-        const uint4 out16 = requant_chunk16<EXTRA>(acc, &hdr->bias[c0], &hdr->scale[c0], rc, sub,
-                                                   (corr_row && cbase + 16 <= p.Ocp) ? corr_row + c0 : nullptr);
+        uint4 res16 = make_uint4(0, 0, 0, 0);
+        if (FUSE) res16 = __ldg(reinterpret_cast<const uint4*>(p.ep.add_residual + row * p.ldd + cbase));   // in flight during the math
+        uint4 out16 = requant_chunk16<EXTRA>(acc, &hdr->bias[c0], &hdr->scale[c0], rc, sub,
+                                             (corr_row && cbase + 16 <= p.Ocp) ? corr_row + c0 : nullptr);
+        if (FUSE) {
+          out16.x = add_lut_word(out16.x, res16.x, add_tab);
+          out16.y = add_lut_word(out16.y, res16.y, add_tab);
+          out16.z = add_lut_word(out16.z, res16.z, add_tab);
+          out16.w = add_lut_word(out16.w, res16.w, add_tab);
+        }
         if (span_b) {
           const int blk = c0 >> span_shift, chunk = (c0 & (span_b - 1)) >> 4;   // span_b is 32, 64 or 128
           *reinterpret_cast<uint4*>(stage_out + static_cast<size_t>(blk) * kBlockM * span_b + row_in_tile * span_b +
@@ -687,14 +704,15 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   // the staging memory goes to the operand ring instead), so that is the default;
   // B2VX_TC_STORE=tma selects the staged store.
   static const bool tma_store = [] { const char* e = std::getenv("B2VX_TC_STORE"); return e && std::strcmp(e, "tma") == 0; }();
-  if (!tma_store) p.store_span = 0;
+  if (!tma_store || e.add_residual != nullptr) p.store_span = 0;
   const size_t staging = p.store_span ? 2 * static_cast<size_t>(kBlockM) * p.BNd : 0;
   // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
   // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
   // aligned start of the ring.  Several k-blocks share a stage (one barrier round trip) when they are
   // small: up to 64 KiB per stage.
   const size_t sub_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
-  const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging;
+  const size_t add_table_bytes = e.add_residual != nullptr ? 65536 : 0;
+  const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging - add_table_bytes;
   int group = static_cast<int>((64 * 1024) / sub_bytes);
   if (group > kblocks_per_tile) group = kblocks_per_tile;
   if (group > kMaxGroup) group = kMaxGroup;
@@ -727,7 +745,7 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
     *why = "gemm_tc: cuTensorMapEncodeTiled failed for the weights";
     return false;
   }
-  size_t smem = ((static_cast<size_t>(stages) * stage_bytes + 1023) & ~static_cast<size_t>(1023)) + staging + sizeof(SmemHeader) + 1024;
+  size_t smem = ((static_cast<size_t>(stages) * stage_bytes + 1023) & ~static_cast<size_t>(1023)) + staging + add_table_bytes + sizeof(SmemHeader) + 1024;
   if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
   plan->smem = smem;
   // the attribute belongs to the function on one device: set it once per device of this process
@@ -735,8 +753,10 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_i8_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_i8_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_i8_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_i8_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       *why = "gemm_tc: cannot raise the dynamic shared memory limit";
       return false;
     }
@@ -980,12 +1000,13 @@ cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
   }
 #endif
   cudaError_t launched;
-  if (plan->params.dz != 0 || plan->params.ep.border_corr != nullptr)
-    launched = launch_pdl(gemm_i8_tc_kernel<true>, dim3(plan->grid), dim3(kThreadsTc), plan->smem, s, plan->map_a, plan->map_b,
-                          plan->map_d, plan->params);
-  else
-    launched = launch_pdl(gemm_i8_tc_kernel<false>, dim3(plan->grid), dim3(kThreadsTc), plan->smem, s, plan->map_a, plan->map_b,
-                          plan->map_d, plan->params);
+  const bool extra = plan->params.dz != 0 || plan->params.ep.border_corr != nullptr;
+  const bool fuse = plan->params.ep.add_residual != nullptr;
+#define B2VX_GEMM_LAUNCH(E_, F_) launch_pdl(gemm_i8_tc_kernel<E_, F_>, dim3(plan->grid), dim3(kThreadsTc), plan->smem, s, plan->map_a, \
+                                            plan->map_b, plan->map_d, plan->params)
+  if (fuse) launched = extra ? B2VX_GEMM_LAUNCH(true, true) : B2VX_GEMM_LAUNCH(false, true);
+  else launched = extra ? B2VX_GEMM_LAUNCH(true, false) : B2VX_GEMM_LAUNCH(false, false);
+#undef B2VX_GEMM_LAUNCH
   if (launched != cudaSuccess) return launched;
 #ifdef B2VX_TC_TRACE
   {

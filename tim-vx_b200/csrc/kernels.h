@@ -64,6 +64,12 @@ struct ContractEpilogue {
   const uint8_t* row_class;
   const uint8_t* col_class;
   int n_col_classes;
+  // Tensor-core path, residual Add fused into the epilogue: the convolution's own quantized byte q
+  // (quantization `out`) and the byte r at the same position of `add_residual` (a channels-last tensor
+  // of the output's shape) are replaced by add_table[q*256 + (r ^ ((q & 31) << 2))], the 64 KB table
+  // of the Add that follows (launch_add_q_lut's layout, first operand = this convolution).
+  const uint8_t* add_residual;  // null = no fused Add
+  const uint8_t* add_table;
 };
 
 // ---- layout converters (elem = 1 or 4 bytes) -------------------------------

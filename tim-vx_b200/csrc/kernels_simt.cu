@@ -881,14 +881,6 @@ __global__ void __launch_bounds__(256) add_q_kernel(const uint4* __restrict__ a,
 // near-tie sums that would send the arithmetic kernel to its exact path.  The table lives in shared
 // memory; entry (a, b) sits at a*256 + (b ^ ((a & 31) << 2)), which spreads pairs that share b over
 // the banks.  Per element: build the index, one byte load, pack.
-__device__ __forceinline__ uint32_t add_lut_word(uint32_t aw, uint32_t bw, const uint8_t* tab) {
-  uint32_t p01 = __byte_perm(bw, aw, 0x5140), p23 = __byte_perm(bw, aw, 0x7362);   // [b0 a0 b1 a1], [b2 a2 b3 a3]
-  p01 ^= (p01 >> 6) & 0x007C007Cu;
-  p23 ^= (p23 >> 6) & 0x007C007Cu;
-  const uint32_t r0 = tab[p01 & 0xFFFFu], r1 = tab[p01 >> 16], r2 = tab[p23 & 0xFFFFu], r3 = tab[p23 >> 16];
-  return __byte_perm(__byte_perm(r0, r1, 0x0040), __byte_perm(r2, r3, 0x0040), 0x5410);
-}
-
 __global__ void __launch_bounds__(1024) add_q_lut_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
                                                         const uint4* __restrict__ table, uint4* __restrict__ y, size_t n16) {
   pdl_trigger();

@@ -214,5 +214,15 @@ __device__ __forceinline__ uint4 requant_chunk16(const int (&acc)[16], const int
   return make_uint4(wh[0] ^ rc.out_flip, wh[1] ^ rc.out_flip, wh[2] ^ rc.out_flip, wh[3] ^ rc.out_flip);
 }
 
+// Quantized Add of four byte pairs through the 64 KB table (entry (a, b) at a*256 + (b ^ ((a & 31) << 2)),
+// which spreads pairs that share b over the shared-memory banks): build the indices, four byte loads, pack.
+__device__ __forceinline__ uint32_t add_lut_word(uint32_t aw, uint32_t bw, const uint8_t* tab) {
+  uint32_t p01 = __byte_perm(bw, aw, 0x5140), p23 = __byte_perm(bw, aw, 0x7362);   // [b0 a0 b1 a1], [b2 a2 b3 a3]
+  p01 ^= (p01 >> 6) & 0x007C007Cu;
+  p23 ^= (p23 >> 6) & 0x007C007Cu;
+  const uint32_t r0 = tab[p01 & 0xFFFFu], r1 = tab[p01 >> 16], r2 = tab[p23 & 0xFFFFu], r3 = tab[p23 >> 16];
+  return __byte_perm(__byte_perm(r0, r1, 0x0040), __byte_perm(r2, r3, 0x0040), 0x5410);
+}
+
 }  // namespace b2vx
 #endif  // B2VX_REQUANT_CUH_
