@@ -7,6 +7,7 @@
 #include "tim/vx/ops/conv2d.h"
 #include "tim/vx/ops/elementwise.h"
 #include "tim/vx/ops/fullyconnected.h"
+#include "tim/vx/ops/nbg.h"
 #include "tim/vx/ops/pool2d.h"
 #include "tim/vx/ops/softmax.h"
 #endif  // TIM_VX_OPS_H_

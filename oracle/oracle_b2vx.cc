@@ -437,7 +437,8 @@ b2vx_status b2vx_context_create(b2vx_context** out) {
 }
 void b2vx_context_destroy(b2vx_context* ctx) { delete ctx; }
 const char* b2vx_last_error(const b2vx_context* ctx) { return ctx ? ctx->err.c_str() : ""; }
-int32_t b2vx_device_count(void) { return 0; }
+// the host counts as one device, so that device-enumerating callers (tim::vx::platform) work on the oracle too
+int32_t b2vx_device_count(void) { return 1; }
 
 b2vx_status b2vx_graph_create(b2vx_context* ctx, int32_t, b2vx_graph** out) {
   if (!ctx || !out) return B2VX_INVALID_ARG;

@@ -76,6 +76,8 @@ class TensorImpl : public Tensor {
   float* ConvertTensorToFloat32Data() override;
 
   void RefreshShape();
+  // CONSTANT tensors keep a copy of their data for Graph::CompileToBinary
+  const std::vector<uint8_t>& ConstData() const { return const_copy_; }
 
  private:
   bool EnsureHostBuffer();
@@ -85,6 +87,7 @@ class TensorImpl : public Tensor {
   void* host_ = nullptr;      // host side of an INPUT/OUTPUT tensor (map, handles)
   bool host_owned_ = false;   // allocated by b2vx_host_alloc
   int8_t is_scalar_ = 0;
+  std::vector<uint8_t> const_copy_;
 };
 
 // Stand-in for an optional input that was not supplied.
@@ -135,7 +138,12 @@ class OpImpl {
     b2vx_pool2d_desc pool2d;
     b2vx_softmax_desc softmax;
   } desc_;
+  std::vector<uint8_t> blob_;   // ops::NBG: the serialised graph this op stands for
 };
+
+// Node kind of ops::NBG inside this layer; it never reaches the C ABI: Compile expands the op into the
+// nodes and tensors of its blob.
+constexpr uint32_t kNodeKindNbg = 0x4E4247u;
 
 class GraphImpl : public Graph {
  public:
@@ -176,6 +184,7 @@ class GraphImpl : public Graph {
 
  private:
   bool EmitNodes();
+  bool ExpandBlob(const OpImpl* op);
   ContextImpl* context_;
   CompileOption options_;
   b2vx_graph* graph_ = nullptr;

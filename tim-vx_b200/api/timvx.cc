@@ -17,6 +17,7 @@
 #include "tim/vx/ops/conv2d.h"
 #include "tim/vx/ops/elementwise.h"
 #include "tim/vx/ops/fullyconnected.h"
+#include "tim/vx/ops/nbg.h"
 #include "tim/vx/ops/pool2d.h"
 #include "tim/vx/ops/softmax.h"
 
@@ -180,6 +181,10 @@ TensorImpl::TensorImpl(GraphImpl* graph, const TensorSpec& spec, const void* dat
   }
   id_ = id;
   host_ = io_handle;
+  if (data && (spec_.attr_ & TensorAttribute::CONSTANT)) {
+    const uint8_t* p = static_cast<const uint8_t*>(data);
+    const_copy_.assign(p, p + static_cast<size_t>(spec_.GetByteSize()));
+  }
 }
 
 TensorImpl::~TensorImpl() {
@@ -515,6 +520,7 @@ bool GraphImpl::EmitNodes() {
       case B2VX_NODE_RELU: st = b2vx_node_relu(graph_, in(0), out(0)); break;
       case B2VX_NODE_RELU6: st = b2vx_node_relu6(graph_, in(0), out(0)); break;
       case B2VX_NODE_SOFTMAX: st = b2vx_node_softmax(graph_, in(0), out(0), &p->desc_.softmax); break;
+      case kNodeKindNbg: st = ExpandBlob(p) ? B2VX_OK : B2VX_INVALID_ARG; break;
       default: break;
     }
     if (st != B2VX_OK) {
@@ -541,9 +547,249 @@ bool GraphImpl::Compile() {
   return compiled_ok_;
 }
 
-bool GraphImpl::CompileToBinary(void* /*buf*/, size_t* /*size*/) {
-  TVX_LOGE("CompileToBinary: serialised graphs are not provided by this backend");
-  return false;
+// ---------------------------------------------------------------- serialised graphs
+//
+// Graph::CompileToBinary (src/tim/vx/graph.cc:385-387 hands this to vsi_nn_GenerateNBG) writes what
+// this layer recorded: every tensor an op touches (descriptor, quantization, constant data) and every
+// op (kind, descriptor, bindings), plus which tensors are the graph's inputs and outputs, in order.
+// ops::NBG (include/tim/vx/ops/nbg.h) takes such a blob; at Compile it is expanded into the nodes it
+// describes, its graph inputs and outputs replaced by the tensors bound to the op.  The format is
+// this backend's own ("B2VB", little endian, version 1); kernels are planned again on load, for the
+// GPU the loading graph is bound to.
+namespace {
+
+constexpr uint32_t kBlobMagic = 0x42563242u;   // "B2VB"
+constexpr uint32_t kBlobVersion = 1;
+
+struct BlobWriter {
+  std::vector<uint8_t> b;
+  template <typename T> void put(const T& v) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(&v);
+    b.insert(b.end(), p, p + sizeof(T));
+  }
+  void bytes(const void* p, size_t n) {
+    const uint8_t* q = static_cast<const uint8_t*>(p);
+    b.insert(b.end(), q, q + n);
+  }
+};
+
+struct BlobReader {
+  const uint8_t* p;
+  size_t left;
+  bool ok = true;
+  template <typename T> T get() {
+    T v{};
+    if (left < sizeof(T)) { ok = false; return v; }
+    std::memcpy(&v, p, sizeof(T));
+    p += sizeof(T);
+    left -= sizeof(T);
+    return v;
+  }
+  const uint8_t* bytes(size_t n) {
+    if (left < n) { ok = false; return nullptr; }
+    const uint8_t* q = p;
+    p += n;
+    left -= n;
+    return q;
+  }
+};
+
+}  // namespace
+
+bool GraphImpl::CompileToBinary(void* buf, size_t* size) {
+  if (!size) return false;
+  std::map<const Tensor*, uint32_t> index;
+  std::vector<std::shared_ptr<Tensor>> tensors;
+  auto add = [&](const std::shared_ptr<Tensor>& t) {
+    if (!t || t->IsPlaceHolder()) return;
+    if (index.emplace(t.get(), static_cast<uint32_t>(tensors.size())).second) tensors.push_back(t);
+  };
+  for (const auto& op : op_vector_) {
+    if (op->impl()->kind_ == kNodeKindNbg) {
+      TVX_LOGE("CompileToBinary: a graph that contains an NBG op cannot be serialised again");
+      return false;
+    }
+    for (const auto& t : op->impl()->inputs_tensor_) add(t);
+    for (const auto& t : op->impl()->outputs_tensor_) add(t);
+  }
+  BlobWriter w;
+  w.put(kBlobMagic);
+  w.put(kBlobVersion);
+  w.put<uint64_t>(0);   // total size, patched below
+  w.put(static_cast<uint32_t>(tensors.size()));
+  w.put(static_cast<uint32_t>(op_vector_.size()));
+  w.put(static_cast<uint32_t>(inputs_tensor_.size()));
+  w.put(static_cast<uint32_t>(outputs_tensor_.size()));
+  for (const auto& t : tensors) {
+    TensorSpec& sp = t->GetSpec();
+    const Quantization& q = sp.quantization_;
+    w.put(static_cast<int32_t>(sp.datatype_));
+    w.put(static_cast<int32_t>(sp.attr_));
+    // TRANSIENT tensors go in without a shape, as the user declared them (Compile infers it again)
+    const bool shapeless = sp.attr_ == TensorAttribute::TRANSIENT;
+    w.put(static_cast<uint32_t>(shapeless ? 0 : sp.shape_.size()));
+    if (!shapeless) for (uint32_t d : sp.shape_) w.put(d);
+    w.put(static_cast<int32_t>(q.Type()));
+    w.put(static_cast<int32_t>(q.ChannelDim()));
+    w.put(static_cast<uint32_t>(q.Scales().size()));
+    for (float v : q.Scales()) w.put(v);
+    w.put(static_cast<uint32_t>(q.ZeroPoints().size()));
+    for (int32_t v : q.ZeroPoints()) w.put(v);
+    const std::vector<uint8_t>& data = static_cast<TensorImpl*>(t.get())->ConstData();
+    if ((sp.attr_ & TensorAttribute::CONSTANT) && data.empty()) {
+      TVX_LOGE("CompileToBinary: a CONSTANT tensor was created without data");
+      return false;
+    }
+    w.put(static_cast<uint64_t>(data.size()));
+    w.bytes(data.data(), data.size());
+  }
+  auto put_ids = [&](const std::vector<std::shared_ptr<Tensor>>& v) {
+    w.put(static_cast<uint32_t>(v.size()));
+    for (const auto& t : v) w.put(t && !t->IsPlaceHolder() ? index[t.get()] : B2VX_NO_TENSOR);
+  };
+  for (const auto& op : op_vector_) {
+    const OpImpl* p = op->impl().get();
+    w.put(p->kind_);
+    w.bytes(&p->desc_, sizeof(p->desc_));
+    put_ids(p->inputs_tensor_);
+    put_ids(p->outputs_tensor_);
+  }
+  for (const auto& t : inputs_tensor_) w.put(index.count(t.get()) ? index[t.get()] : B2VX_NO_TENSOR);
+  for (const auto& t : outputs_tensor_) w.put(index.count(t.get()) ? index[t.get()] : B2VX_NO_TENSOR);
+  const uint64_t total = w.b.size();
+  std::memcpy(w.b.data() + 8, &total, sizeof(total));
+  if (buf) {
+    if (*size < total) {
+      TVX_LOGE("CompileToBinary: buffer of %zu bytes, %llu needed", *size, static_cast<unsigned long long>(total));
+      return false;
+    }
+    std::memcpy(buf, w.b.data(), total);
+  }
+  *size = static_cast<size_t>(total);
+  return true;
+}
+
+bool GraphImpl::ExpandBlob(const OpImpl* op) {
+  BlobReader r{op->blob_.data(), op->blob_.size()};
+  if (r.get<uint32_t>() != kBlobMagic || r.get<uint32_t>() != kBlobVersion) {
+    TVX_LOGE("NBG: not a graph serialised by this backend");
+    return false;
+  }
+  r.get<uint64_t>();
+  const uint32_t n_tensors = r.get<uint32_t>(), n_ops = r.get<uint32_t>(), n_in = r.get<uint32_t>(), n_out = r.get<uint32_t>();
+  if (!r.ok || op->inputs_tensor_.size() != n_in || op->outputs_tensor_.size() != n_out) {
+    TVX_LOGE("NBG: the blob has %u inputs and %u outputs, the op has %zu and %zu bound", n_in, n_out,
+             op->inputs_tensor_.size(), op->outputs_tensor_.size());
+    return false;
+  }
+  struct Rec {
+    b2vx_tensor_desc d;
+    std::vector<float> scales;
+    std::vector<int32_t> zps;
+    const uint8_t* data = nullptr;
+    uint64_t bytes = 0;
+  };
+  std::vector<Rec> recs(n_tensors);
+  for (Rec& t : recs) {
+    std::memset(&t.d, 0, sizeof(t.d));
+    t.d.dtype = r.get<int32_t>();
+    t.d.attr = r.get<int32_t>();
+    t.d.rank = r.get<uint32_t>();
+    if (!r.ok || t.d.rank > B2VX_MAX_RANK) return false;
+    for (uint32_t i = 0; i < t.d.rank; ++i) t.d.dims[i] = r.get<uint32_t>();
+    const int32_t qtype = r.get<int32_t>();
+    t.d.channel_dim = r.get<int32_t>();
+    const uint32_t ns = r.get<uint32_t>();
+    if (!r.ok || ns > (1u << 24)) return false;
+    t.scales.resize(ns);
+    for (float& v : t.scales) v = r.get<float>();
+    const uint32_t nz = r.get<uint32_t>();
+    if (!r.ok || nz > (1u << 24)) return false;
+    t.zps.resize(nz);
+    for (int32_t& v : t.zps) v = r.get<int32_t>();
+    switch (static_cast<QuantType>(qtype)) {
+      case QuantType::NONE: t.d.quant_type = B2VX_QUANT_NONE; break;
+      case QuantType::ASYMMETRIC:
+        t.d.quant_type = B2VX_QUANT_ASYMMETRIC;
+        t.d.scale = t.scales.empty() ? 1.0f : t.scales[0];
+        t.d.zero_point = t.zps.empty() ? 0 : t.zps[0];
+        break;
+      case QuantType::SYMMETRIC_PER_CHANNEL:
+        t.d.quant_type = B2VX_QUANT_SYMMETRIC_PER_CHANNEL;
+        t.d.n_channel = ns;
+        break;
+      default: return false;
+    }
+    t.bytes = r.get<uint64_t>();
+    t.data = r.bytes(static_cast<size_t>(t.bytes));
+    if (!r.ok) return false;
+  }
+  struct OpRec {
+    uint32_t kind;
+    decltype(OpImpl::desc_) desc;
+    std::vector<uint32_t> in, out;
+  };
+  std::vector<OpRec> ops(n_ops);
+  for (OpRec& o : ops) {
+    o.kind = r.get<uint32_t>();
+    const uint8_t* d = r.bytes(sizeof(o.desc));
+    if (!r.ok) return false;
+    std::memcpy(&o.desc, d, sizeof(o.desc));
+    o.in.resize(r.get<uint32_t>());
+    if (!r.ok || o.in.size() > 16) return false;
+    for (uint32_t& v : o.in) v = r.get<uint32_t>();
+    o.out.resize(r.get<uint32_t>());
+    if (!r.ok || o.out.size() > 16) return false;
+    for (uint32_t& v : o.out) v = r.get<uint32_t>();
+  }
+  std::vector<uint32_t> id(n_tensors, B2VX_NO_TENSOR);
+  for (uint32_t k = 0; k < n_in; ++k) {
+    const uint32_t t = r.get<uint32_t>();
+    if (!r.ok || t >= n_tensors || !op->inputs_tensor_[k]) return false;
+    id[t] = op->inputs_tensor_[k]->GetId();
+  }
+  for (uint32_t k = 0; k < n_out; ++k) {
+    const uint32_t t = r.get<uint32_t>();
+    if (!r.ok || t >= n_tensors || !op->outputs_tensor_[k]) return false;
+    id[t] = op->outputs_tensor_[k]->GetId();
+  }
+  for (uint32_t t = 0; t < n_tensors; ++t) {
+    if (id[t] != B2VX_NO_TENSOR) continue;
+    Rec& rec = recs[t];
+    if (rec.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL) {
+      rec.d.scales = rec.scales.data();
+      rec.d.zero_points = rec.zps.size() == rec.scales.size() ? rec.zps.data() : nullptr;
+    }
+    // a blob input or output that the op does not bind cannot occur (counts were checked); everything
+    // else is created as recorded
+    if (b2vx_tensor_create(graph_, &rec.d, rec.bytes ? rec.data : nullptr, &id[t]) != B2VX_OK) {
+      LogBackendError("NBG tensor");
+      return false;
+    }
+  }
+  auto at = [&](const std::vector<uint32_t>& v, size_t i) -> uint32_t {
+    return i < v.size() && v[i] != B2VX_NO_TENSOR && v[i] < n_tensors ? id[v[i]] : B2VX_NO_TENSOR;
+  };
+  for (OpRec& o : ops) {
+    b2vx_status st = B2VX_UNSUPPORTED;
+    switch (o.kind) {
+      case B2VX_NODE_CONV2D: st = b2vx_node_conv2d(graph_, at(o.in, 0), at(o.in, 1), at(o.in, 2), at(o.out, 0), &o.desc.conv2d); break;
+      case B2VX_NODE_FULLY_CONNECTED:
+        st = b2vx_node_fully_connected(graph_, at(o.in, 0), at(o.in, 1), at(o.in, 2), at(o.out, 0), &o.desc.fc);
+        break;
+      case B2VX_NODE_POOL2D: st = b2vx_node_pool2d(graph_, at(o.in, 0), at(o.out, 0), &o.desc.pool2d); break;
+      case B2VX_NODE_ADD: st = b2vx_node_add(graph_, at(o.in, 0), at(o.in, 1), at(o.out, 0)); break;
+      case B2VX_NODE_RELU: st = b2vx_node_relu(graph_, at(o.in, 0), at(o.out, 0)); break;
+      case B2VX_NODE_RELU6: st = b2vx_node_relu6(graph_, at(o.in, 0), at(o.out, 0)); break;
+      case B2VX_NODE_SOFTMAX: st = b2vx_node_softmax(graph_, at(o.in, 0), at(o.out, 0), &o.desc.softmax); break;
+      default: break;
+    }
+    if (st != B2VX_OK) {
+      LogBackendError("NBG node");
+      return false;
+    }
+  }
+  return true;
 }
 
 bool GraphImpl::Run() {
@@ -738,6 +984,17 @@ std::shared_ptr<Operation> Add::Clone(std::shared_ptr<Graph>& graph) const { ret
 
 Relu::Relu(Graph* graph) : BuiltinOp(graph, B2VX_NODE_RELU, 1, 1) {}
 std::shared_ptr<Operation> Relu::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Relu>(); }
+
+NBG::NBG(Graph* graph, const char* binary, size_t input_count, size_t output_count)
+    : BuiltinOp(graph, kNodeKindNbg, static_cast<int>(input_count), static_cast<int>(output_count)) {
+  // the blob states its own length in its header (the reference's constructor takes no size either)
+  uint64_t total = 0;
+  if (binary) std::memcpy(&total, binary + 8, sizeof(total));
+  if (binary && total >= 32 && total < (1ull << 40)) impl_->blob_.assign(binary, binary + total);
+}
+std::shared_ptr<Operation> NBG::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<NBG>(reinterpret_cast<const char*>(impl_->blob_.data()), impl_->input_cnt_, impl_->output_cnt_);
+}
 
 Relu6::Relu6(Graph* graph) : BuiltinOp(graph, B2VX_NODE_RELU6, 1, 1) {}
 std::shared_ptr<Operation> Relu6::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Relu6>(); }
