@@ -10,7 +10,7 @@ the vector the test compared against.  Those cases are packed (arrays as
 base64(zlib(raw bytes))) into reference_cases.json, and a one-line-per-test
 verdict of "reference test vs oracle" goes to reference_report.txt.
 
-usage: python tests/golden/make_goldens.py [--reference /root/reference]
+usage: python tests/golden/make_goldens.py --reference <TIM-VX source tree>
 """
 import argparse
 import base64
@@ -62,7 +62,7 @@ def max_diff(case):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a TIM-VX v1.2.22 source tree")
     args = ap.parse_args()
     ref = args.reference
     subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle")], stdout=subprocess.DEVNULL)
