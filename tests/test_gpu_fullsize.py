@@ -103,6 +103,16 @@ def test_full_size_conv_sweep_prefix_matches_oracle(oracle_lib, product_lib):
         assert np.array_equal(got[0][:2], want[0])
 
 
+def test_full_size_conv_with_fused_residual_add_prefix_matches_oracle(oracle_lib, product_lib):
+    """The tail of a bottleneck block (1x1 expand convolution, residual Add, Relu) at batch 256: one fused launch."""
+    for spec in ("convadd:1:64:256:56:1", "convadd:3:64:64:56:1"):
+        got, xs, kernels = _run_graph(product_lib, spec, 256, seed=10)
+        assert any(k.startswith("gemm_i8_tc") and "+add" in k for k in kernels), kernels
+        assert not any(k.startswith("add_q") for k in kernels), kernels
+        want, _, _ = _run_graph(oracle_lib, spec, 2, seed=10, inputs=[x[:2] for x in xs])
+        assert np.array_equal(got[0][:2], want[0])
+
+
 def test_full_size_add_kernels_agree_and_prefix_matches_oracle(oracle_lib, product_lib):
     spec = "add:67108864"
     lut, xs, k1 = _run_graph(product_lib, spec, 1, seed=9, env={"B2VX_ADD_KERNEL": "lut"})

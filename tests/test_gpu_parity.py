@@ -386,6 +386,30 @@ def test_add_int8_matches_oracle(oracle_lib, product_lib):
         G.assert_same(want, got)
 
 
+def test_add_int32_matches_oracle(oracle_lib, product_lib):
+    """INT32 + INT32 as the reference's platform sample adds them (samples/platform_sample/platform_sample.cc:36-47),
+    plain and with quantization parameters; values near the int32 limits saturate."""
+    def case(quant):
+        def build(g, rng):
+            n = 4099
+            kw = [dict(scale=0.5, zero_point=3), dict(scale=0.25, zero_point=-7), dict(scale=0.125, zero_point=11)] if quant else [{}, {}, {}]
+            a = g.tensor(B.DT_INT32, [n], B.ATTR_INPUT, **kw[0])
+            b = g.tensor(B.DT_INT32, [n], B.ATTR_INPUT, **kw[1])
+            y = g.tensor(B.DT_INT32, [], B.ATTR_OUTPUT, **kw[2])
+            g.add(a, b, y)
+            av = rng.integers(-100000, 100000, size=n).astype(np.int32)
+            bv = rng.integers(-100000, 100000, size=n).astype(np.int32)
+            av[:4] = [2147483647, -2147483648, 2147483000, 5]
+            bv[:4] = [2147483647, -2147483648, 1000, -5]
+            return [(a, av), (b, bv)], [y]
+        return build
+    for quant in (False, True):
+        want, _ = G.run_case(oracle_lib, case(quant), seed=4)
+        got, kernels = G.run_case(product_lib, case(quant), seed=4)
+        assert "add_i32" in [k["name"] for k in kernels]
+        G.assert_same(want, got)
+
+
 def test_softmax_matches_oracle(oracle_lib, product_lib):
     for build in (G.softmax_q(10, 7), G.softmax_q(1000, 3, beta=0.5)):
         want, _ = G.run_case(oracle_lib, build, seed=2)

@@ -1054,8 +1054,17 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
       s.info = make_info("add_q", idx, 0, abytes);
       s.fn = [=](cudaStream_t st2) { launch_add_q(ap, as, sa, za, bp, bs, sb, zb, oq, ys, yp, nel, st2); return cudaGetLastError(); };
     }
+  } else if (a.d.dtype == B2VX_DT_INT32 && b.d.dtype == B2VX_DT_INT32 && y.d.dtype == B2VX_DT_INT32) {
+    const int *ap = static_cast<const int*>(cl_in(a)), *bp = static_cast<const int*>(cl_in(b));
+    int* yp = static_cast<int*>(y.d_cl);
+    const float sa = a.scale(), sb = b.scale();
+    const int za = a.zp(), zb = b.zp();
+    const OutQuant oq = out_quant(y);
+    const size_t nel = y.cl_bytes / 4;
+    s.info = make_info("add_i32", idx, 0, abytes);
+    s.fn = [=](cudaStream_t st2) { launch_add_i32(ap, sa, za, bp, sb, zb, oq, yp, nel, st2); return cudaGetLastError(); };
   } else {
-    return fail(g, B2VX_UNSUPPORTED, "add: operands must be all int8/uint8 or all float32");
+    return fail(g, B2VX_UNSUPPORTED, "add: operands must be all int8/uint8, all int32 or all float32");
   }
   g->steps.push_back(std::move(s));
   return B2VX_OK;
@@ -1464,11 +1473,13 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
     g->tensors[n.in[0]].is_activation = true;
     g->tensors[n.out].is_activation = true;
     if (n.kind == B2VX_NODE_ADD) g->tensors[n.in[1]].is_activation = true;
+    // 32-bit integer activations exist only between Add nodes (the reference's platform sample adds INT32 vectors)
+    else if (g->tensors[n.in[0]].d.dtype == B2VX_DT_INT32 || g->tensors[n.out].d.dtype == B2VX_DT_INT32)
+      return fail(g, B2VX_UNSUPPORTED, "int32 activations are supported by Add only");
   }
   for (TensorRec& t : g->tensors) {
     if (!t.is_activation) continue;
     if (!t.has_shape) return fail(g, B2VX_SHAPE_MISMATCH, "an activation tensor has no shape");
-    if (t.d.dtype == B2VX_DT_INT32) return fail(g, B2VX_UNSUPPORTED, "int32 activations are not supported");
     map_dims(t);
     b2vx_status st = dev_alloc(g, &t.d_cl, t.cl_bytes);
     if (st != B2VX_OK) return st;

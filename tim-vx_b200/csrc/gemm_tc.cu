@@ -473,28 +473,15 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     int j = 0;
     // Once a wait has given up (alive == false) a thread does no more work, but it keeps running the
     // loop and both barriers of every tile, so the other epilogue threads never wait for it.
-    bool alive = true;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
-      const int m_tile = m_tile0 + j * m_step;
-      const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
-      uint8_t* stage_out = staging + a * staging_bytes;
-      if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
-      alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
-      if (!alive) {
-        if (span_b) epilogue_barrier();
-        continue;
-      }
-      if (warp == kFirstEpilogueWarp && lane == 0) TC_TRACE(2, j, 0);
-      tc_fence_after();
-      int tw = 0, th = 0, tn = 0;
-      long long row = -1;   // direct-store path: output row (pixel index into D), -1 outside the tensor
-      const int32_t* corr_row = nullptr;   // border pixels of a padded convolution: their correction, this N tile
+    // Output row of this thread in M tile m_tile (-1 outside the tensor) and, for a border pixel of a padded
+    // convolution, the row of corrections of its class.
+    auto locate = [&](int m_tile, long long& row, const int32_t*& corr_row) {
+      row = -1;
+      corr_row = nullptr;
       if (p.conv) {
-        tw = m_tile % p.tiles_w;
-        const int rest = m_tile / p.tiles_w;
-        th = rest % p.tiles_h;
-        tn = rest / p.tiles_h;
         if (!span_b || FUSE || (EXTRA && p.ep.border_corr)) {
+          const int tw = m_tile % p.tiles_w, rest = m_tile / p.tiles_w;
+          const int th = rest % p.tiles_h, tn = rest / p.tiles_h;
           const int i = row_in_tile % p.TW, r2 = row_in_tile / p.TW;
           const int jh = r2 % p.TH, l = r2 / p.TH;
           const int wo = tw * p.TW + i, ho = th * p.TH + jh, n = tn * p.TN + l;
@@ -510,6 +497,49 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         row = static_cast<long long>(m_tile) * kBlockM + row_in_tile;
         if (row >= p.M) row = -1;
       }
+    };
+    // FUSE: the residual rows of a tile are asked into L2 a whole tile before they are read (those of the
+    // first tile while its accumulator is still being computed), so its position is worked out one tile early.
+    auto prefetch_residual = [&](long long r) {
+      const int pc = n_tile * p.BNd + col_group * 64;   // the four warps that share a row cover its 256 bytes
+      if (r >= 0 && col_group * 64 < p.BNd && pc < p.Ocp) {
+        const uint8_t* pa = p.ep.add_residual + r * p.ldd + pc;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + 32));
+      }
+    };
+    long long row_ahead = -1;
+    const int32_t* corr_ahead = nullptr;
+    if (FUSE && static_cast<int>(blockIdx.x) < num_tiles) {
+      pdl_wait();   // the residual is an earlier kernel's output
+      locate(m_tile0, row_ahead, corr_ahead);
+      prefetch_residual(row_ahead);
+    }
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
+      const int m_tile = m_tile0 + j * m_step;
+      const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
+      uint8_t* stage_out = staging + a * staging_bytes;
+      long long row;                 // direct-store path: output row (pixel index into D), -1 outside the tensor
+      const int32_t* corr_row;       // border pixels of a padded convolution: their correction, this N tile
+      if (FUSE) {
+        row = row_ahead;
+        corr_row = corr_ahead;
+        if (tile + static_cast<int>(gridDim.x) < num_tiles) {
+          locate(m_tile + m_step, row_ahead, corr_ahead);
+          prefetch_residual(row_ahead);
+        }
+      } else {
+        locate(m_tile, row, corr_row);
+      }
+      if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
+      alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
+      if (!alive) {
+        if (span_b) epilogue_barrier();
+        continue;
+      }
+      if (warp == kFirstEpilogueWarp && lane == 0) TC_TRACE(2, j, 0);
+      tc_fence_after();
       const uint32_t taddr = tmem_base + a * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
       // Chunks col_group, col_group + 4, ... of 16 columns; the TMEM load of the next chunk is in flight
       // while the current one is requantized.
@@ -575,7 +605,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int col = n_tile * p.BNd + blk * span_b;
             if (col >= p.Ocp) break;
             const uint32_t src = smem_u32(stage_out + static_cast<size_t>(blk) * kBlockM * span_b);
-            if (p.conv) tma_store_4d(&map_d, src, col, tw * p.TW, th * p.TH, tn * p.TN);
+            if (p.conv) {
+              const int rest = m_tile / p.tiles_w;
+              tma_store_4d(&map_d, src, col, (m_tile % p.tiles_w) * p.TW, (rest % p.tiles_h) * p.TH, (rest / p.tiles_h) * p.TN);
+            }
             else tma_store_2d(&map_d, src, col, m_tile * kBlockM);
           }
           tma_store_commit();

@@ -110,6 +110,7 @@ void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, 
 // tensors): table[a*256 + (b ^ ((a & 31) << 2))] = quantized sum for raw input bytes a, b.
 void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* y, size_t n, cudaStream_t s);
 void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s);
+void launch_add_i32(const int* a, float sa, int za, const int* b, float sb, int zb, OutQuant out, int* y, size_t n, cudaStream_t s);
 // Add with broadcasting over channels-last operands; dims = {N, H, W, C, Cp} of a, b and the output
 // (a dimension of 1 repeats along the output's), elem = 1 (quantized) or 4 (float32).
 void launch_add_broadcast(const void* a, int a_signed, float sa, int za, const int a_dims[5], const void* b, int b_signed, float sb,

@@ -950,6 +950,17 @@ __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restr
   if (i < n) y[i] = __fadd_rn(a[i], b[i]);
 }
 
+// Add on 32-bit integer tensors (the reference's platform sample adds INT32 vectors): the same real-domain
+// sequence as the 8-bit kernels, with the int32 range as the saturation bounds.
+__global__ void add_i32_kernel(const int* __restrict__ a, float sa, int za, const int* __restrict__ b, float sb, int zb,
+                               OutQuant out, int* __restrict__ y, size_t n) {
+  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  const float fa = __fmul_rn(__fsub_rn(__int2float_rn(a[i]), __int2float_rn(za)), sa);
+  const float fb = __fmul_rn(__fsub_rn(__int2float_rn(b[i]), __int2float_rn(zb)), sb);
+  y[i] = requant_wide(__fadd_rn(fa, fb), out);
+}
+
 // Any 8-bit -> 8-bit pointwise map (Relu, Relu6 with arbitrary input/output
 // quantization) as a 256-entry table built on the host with the reference's
 // float sequence; 16 elements per thread.
@@ -1528,6 +1539,11 @@ void launch_add_broadcast(const void* a, int a_signed, float sa, int za, const i
     add_broadcast_kernel<uint8_t><<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(a), sa, za, a_signed,
                                                                                static_cast<const uint8_t*>(b), sb, zb, b_signed, out, g,
                                                                                static_cast<uint8_t*>(y));
+}
+
+void launch_add_i32(const int* a, float sa, int za, const int* b, float sb, int zb, OutQuant out, int* y, size_t n, cudaStream_t s) {
+  if (n == 0) return;
+  add_i32_kernel<<<grid_for(static_cast<long long>(n), kThreads), kThreads, 0, s>>>(a, sa, za, b, sb, zb, out, y, n);
 }
 
 void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s) {

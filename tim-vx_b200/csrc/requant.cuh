@@ -36,6 +36,27 @@ __device__ __forceinline__ int requant(float real, const OutQuant& q) {
   return static_cast<int>(v);
 }
 
+// The same conversion for 32-bit outputs, where the rounded quotient itself can leave the int32 range:
+// the reference adds the zero point in double and saturates afterwards.
+__device__ __forceinline__ int requant_wide(float real, const OutQuant& q) {
+  if (isinf(real)) return real < 0.0f ? q.lo : q.hi;
+  const float x = __fdiv_rn(real, q.scale);
+  if (!(x == x)) return max(q.lo, min(q.hi, 0));
+  const float ax = fabsf(x);
+  const float fl = floorf(ax);
+  float r;
+  if (__fsub_rn(ax, fl) == 0.5f) {
+    r = __fadd_rn(fl, static_cast<float>(static_cast<int>(fl) & 1));   // a .5 fraction exists only below 2^23
+  } else {
+    r = floorf(__fadd_rn(ax, 0.5f));
+  }
+  r = copysignf(fminf(r, 1.0e12f), x);
+  long long v = __float2ll_rn(r) + q.zp;
+  v = v < q.lo ? q.lo : v;
+  v = v > q.hi ? q.hi : v;
+  return static_cast<int>(v);
+}
+
 // Fast form of the same conversion for hot epilogues.  Returns q - lo, in
 // [0, span] with span = hi - lo.  inv_scale = 1/scale (rounded), addc =
 // zp - lo - 0x4B400000.

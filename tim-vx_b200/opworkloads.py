@@ -1,12 +1,15 @@
 """Single-operator workloads of the quantized path, built through the b2vx C ABI.
 
-Three seeded shapes families, each a graph with one compute node (plus the Relu the
+Four seeded families of shapes, each a graph around one compute node (plus the Relu the
 convolution sweep fuses):
 
   conv:<k>:<cin>:<cout>:<hw>:<stride>   Conv2d k x k, SAME padding, uint8 input (scale 0.02,
                                          zero point 128), per-channel symmetric int8 weights with
                                          scales U(0.001, 0.01), int32 bias, Relu, uint8 output
                                          (scale 0.05, zero point 0); batch = images
+  convadd:<k>:<cin>:<cout>:<hw>:<stride> the same convolution without its Relu, followed by the residual
+                                         Add of a second uint8 input (scale 0.04, zero point 0) and a
+                                         Relu: the tail of a ResNet bottleneck block
   gemm:<m>:<n>:<k>                       FullyConnected: uint8 [k, m] (zero point 128, scale 0.02)
                                          x int8 per-channel [k, n] -> uint8 [n, m]
   add:<elements>                         quantized Add of two uint8 tensors with different scales
@@ -23,13 +26,14 @@ def parse(spec):
     f = spec.split(":")
     kind = f[0]
     nums = [int(v) for v in f[1:]]
-    if kind == "conv" and len(nums) == 5:
+    if kind in ("conv", "convadd") and len(nums) == 5:
         return kind, nums
     if kind == "gemm" and len(nums) == 3:
         return kind, nums
     if kind == "add" and len(nums) == 1:
         return kind, nums
-    raise ValueError("workload must be conv:k:cin:cout:hw:stride, gemm:m:n:k or add:elements, got %r" % spec)
+    raise ValueError("workload must be conv:k:cin:cout:hw:stride, convadd:k:cin:cout:hw:stride, gemm:m:n:k or add:elements, "
+                     "got %r" % spec)
 
 
 def _u8(rng, shape):
@@ -38,7 +42,7 @@ def _u8(rng, shape):
 
 def build(spec, batch, g, rng):
     kind, v = parse(spec)
-    if kind == "conv":
+    if kind in ("conv", "convadd"):
         k, cin, cout, hw, stride = v
         x = g.tensor(B.DT_UINT8, [hw, hw, cin, batch], B.ATTR_INPUT, scale=0.02, zero_point=128)
         ws = rng.uniform(0.001, 0.01, cout).astype(np.float32)
@@ -46,12 +50,23 @@ def build(spec, batch, g, rng):
         w = g.tensor(B.DT_INT8, [k, k, cin, cout], B.ATTR_CONSTANT, scales=ws, channel_dim=3, data=wd)
         b = g.tensor(B.DT_INT32, [cout], B.ATTR_CONSTANT, scales=np.float32(0.02) * ws, channel_dim=0,
                      data=rng.integers(-1000, 1001, size=cout).astype(np.int32))
+        ho = (hw + stride - 1) // stride
+        macs = batch * ho * ho * cout * cin * k * k
         y = g.tensor(B.DT_UINT8, [], B.ATTR_TRANSIENT, scale=0.05, zero_point=0)
         z = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.05, zero_point=0)
         g.conv2d(x, w, b, y, stride=(stride, stride), pad_type=B.PAD_SAME)
+        if kind == "convadd":
+            r = g.tensor(B.DT_UINT8, [ho, ho, cout, batch], B.ATTR_INPUT, scale=0.04, zero_point=0)
+            t = g.tensor(B.DT_UINT8, [], B.ATTR_TRANSIENT, scale=0.05, zero_point=0)
+            g.add(y, r, t)
+            g.relu(t, z)
+            return {"inputs": [(x, _u8(rng, (batch, cin, hw, hw))), (r, _u8(rng, (batch, cout, ho, ho)))], "outputs": [z],
+                    "ops": 2 * macs,
+                    "bytes": batch * hw * hw * cin + 2 * batch * ho * ho * cout + cout * cin * k * k + 4 * cout,
+                    "bound": "tensor", "units": batch,
+                    "name": "Conv2d %dx%d %d->%d on %dx%d stride %d SAME + residual Add + Relu, batch %d" % (
+                        k, k, cin, cout, hw, hw, stride, batch)}
         g.relu(y, z)
-        ho = (hw + stride - 1) // stride
-        macs = batch * ho * ho * cout * cin * k * k
         return {"inputs": [(x, _u8(rng, (batch, cin, hw, hw)))], "outputs": [z], "ops": 2 * macs,
                 "bytes": batch * hw * hw * cin + batch * ho * ho * cout + cout * cin * k * k + 4 * cout,
                 "bound": "tensor", "units": batch,
