@@ -85,6 +85,20 @@ __device__ __forceinline__ int requant_fast(float real, const OutQuant& q, float
 // Each half is an IEEE round-to-nearest operation, bit-identical to the scalar
 // intrinsic; the point is one issue slot for two results in instruction-bound
 // requantization loops.
+#ifndef B2VX_F2_ASM
+// float2 values and the sm_100 packed intrinsics: the compiler keeps each value in a register pair.
+typedef float2 f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) { return make_float2(lo, hi); }
+__device__ __forceinline__ f32x2 f2_pack_bits(uint32_t lo, uint32_t hi) { return make_float2(__uint_as_float(lo), __uint_as_float(hi)); }
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) { lo = v.x; hi = v.y; }
+__device__ __forceinline__ void f2_unpack_bits(f32x2 v, uint32_t& lo, uint32_t& hi) { lo = __float_as_uint(v.x); hi = __float_as_uint(v.y); }
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) { return __fmul2_rn(a, b); }
+// Caution: a packed product consumed by a packed addition was observed to come back as one fused
+// multiply-add on sm_100a (product unrounded) despite the .rn qualifiers.  Where the reference rounds
+// the product and the sum separately, compute the product with the scalar __fmul_rn instead.
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) { return __ffma2_rn(a, b, c); }
+#else
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
   f32x2 r;
@@ -112,14 +126,12 @@ __device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-// Caution: a packed product consumed by a packed addition was observed to come back as one fused
-// multiply-add on sm_100a (product unrounded) despite the .rn qualifiers.  Where the reference rounds
-// the product and the sum separately, compute the product with the scalar __fmul_rn instead.
 __device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
   f32x2 r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+#endif
 // d = sat_u8(a) << 8 | sat_u8(b) | c << 16 (or the s8 form): saturating narrow + pack in one instruction.
 __device__ __forceinline__ uint32_t pack_sat_u8(int hi, int lo, uint32_t upper) {
   uint32_t d;
@@ -201,9 +213,9 @@ __device__ __forceinline__ uint4 requant_chunk16(const int (&acc)[16], const int
         b4.x += c4.x; b4.y += c4.y; b4.z += c4.z; b4.w += c4.w;
       }
     }
-    const ulonglong2 s4 = *reinterpret_cast<const ulonglong2*>(scale + g4 * 4);   // two f32x2
-    real[2 * g4] = f2_mul(f2_pack(__int2float_rn(acc[g4 * 4 + 0] + b4.x), __int2float_rn(acc[g4 * 4 + 1] + b4.y)), s4.x);
-    real[2 * g4 + 1] = f2_mul(f2_pack(__int2float_rn(acc[g4 * 4 + 2] + b4.z), __int2float_rn(acc[g4 * 4 + 3] + b4.w)), s4.y);
+    const float4 s4 = *reinterpret_cast<const float4*>(scale + g4 * 4);
+    real[2 * g4] = f2_mul(f2_pack(__int2float_rn(acc[g4 * 4 + 0] + b4.x), __int2float_rn(acc[g4 * 4 + 1] + b4.y)), f2_pack(s4.x, s4.y));
+    real[2 * g4 + 1] = f2_mul(f2_pack(__int2float_rn(acc[g4 * 4 + 2] + b4.z), __int2float_rn(acc[g4 * 4 + 3] + b4.w)), f2_pack(s4.z, s4.w));
   }
   uint32_t wh[4], wl[4];
 #pragma unroll
