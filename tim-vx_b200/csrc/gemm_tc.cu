@@ -109,6 +109,9 @@ struct GemmParams {
   // [128 rows][store_span bytes], 16-byte chunks XOR-swizzled the way the store's tensor map expects.
   // store_span == 0: BN is not a multiple of 32, threads store their 16-byte pieces directly.
   int store_span;
+  // FUSE: the residual tile comes into the same staging memory by TMA (tensor map in the output map's
+  // slot, column blocks of res_span bytes); 0: BN is not a multiple of 32, threads load their pieces.
+  int res_span;
   int dz;                  // weight zero point left after the shift into int8; != 0: column BNd of the accumulator is S
   int exact_only;          // requantize with the exact sequence only (the fast form's range check failed)
 #ifdef B2VX_TC_TRACE
@@ -269,6 +272,8 @@ struct SmemHeader {
   unsigned long long empty[kMaxStages];
   unsigned long long tmem_full[kMaxAccBuffers];
   unsigned long long tmem_empty[kMaxAccBuffers];
+  unsigned long long res_full[2];    // FUSE: residual tile landed / read by all epilogue warps
+  unsigned long long res_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   // this CTA's N tile: folded bias and accumulator scale per column; read as 128-bit vectors
@@ -297,7 +302,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t sub_bytes = a_bytes + b_bytes;     // one k-block: whole swizzle atoms, see the host-side plan
   const uint32_t stage_bytes = sub_bytes * p.group;
   const uint32_t ring_bytes = (p.stages * stage_bytes + 1023u) & ~1023u;
-  const uint32_t staging_bytes = p.store_span ? static_cast<uint32_t>(kBlockM) * p.BNd : 0u;   // per buffer, multiple of 4096
+  const uint32_t staging_bytes = (p.store_span || p.res_span) ? static_cast<uint32_t>(kBlockM) * p.BNd : 0u;   // per buffer, multiple of 4096
   uint8_t* staging = tiles + ring_bytes;
   uint8_t* add_tab = staging + 2 * staging_bytes;                 // 64 KB when FUSE
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(add_tab + (FUSE ? 65536 : 0));
@@ -311,7 +316,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // descriptor fetches overlap the rest of the prologue instead of delaying the first loads
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
-    if (p.store_span) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_d)) : "memory");
+    if (p.store_span || p.res_span) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_d)) : "memory");
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -321,6 +326,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     for (int a = 0; a < kMaxAccBuffers; ++a) {
       mbar_init(smem_u32(&hdr->tmem_full[a]), 1);
       mbar_init(smem_u32(&hdr->tmem_empty[a]), kEpilogueWarps);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&hdr->res_full[b]), 1);
+      mbar_init(smem_u32(&hdr->res_empty[b]), kEpilogueWarps);
     }
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -457,6 +466,41 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (ok && elect_one()) tc_commit(smem_u32(&hdr->tmem_full[a]));
       __syncwarp();
     }
+  } else if (FUSE && warp == 3) {
+    // ------------------------------------------------------------ residual producer (FUSE)
+    // The residual tile of the Add (same rows and columns as the output tile) is brought into the
+    // staging memory by TMA, two tiles deep, so that the epilogue reads it from shared memory.
+    if (p.res_span) {
+      pdl_wait();   // the residual is an earlier kernel's output
+      const int span = p.res_span;
+      int nload = 0;
+      for (int blk = 0; blk * span < p.BNd; ++blk)
+        if (n_tile * p.BNd + blk * span < p.Ocp) ++nload;
+      const uint32_t box_bytes = static_cast<uint32_t>(p.conv ? p.TW * p.TH * p.TN : kBlockM) * span;
+      bool ok = true;
+      int m_tile = m_tile0, j = 0;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, m_tile += m_step, ++j) {
+        const uint32_t b = j & 1, ph = (j >> 1) & 1;
+        ok = mbar_wait(smem_u32(&hdr->res_empty[b]), ph ^ 1, abort_flag, p.status, 6);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (elect_one()) {
+          const uint32_t full = smem_u32(&hdr->res_full[b]);
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(nload) * box_bytes);
+          uint32_t dst = smem_u32(staging + b * staging_bytes);
+          for (int blk = 0; blk < nload; ++blk, dst += static_cast<uint32_t>(kBlockM) * span) {
+            const int col = n_tile * p.BNd + blk * span;
+            if (p.conv) {
+              const int rest = m_tile / p.tiles_w;
+              tma_load_4d(dst, &map_d, col, (m_tile % p.tiles_w) * p.TW, (rest % p.tiles_h) * p.TH, (rest / p.tiles_h) * p.TN, full);
+            } else {
+              tma_load_2d(dst, &map_d, col, m_tile * kBlockM, full);
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
   } else if (warp >= kFirstEpilogueWarp) {
     // ------------------------------------------------------------ epilogue
     const int ew = warp - kFirstEpilogueWarp;     // 0..15
@@ -468,8 +512,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const RequantConsts rc = make_requant_consts(oq, p.exact_only);
     // position of this thread's 16-byte chunks inside a staging column block
     const int span_b = p.store_span;
-    const int span_shift = span_b == 128 ? 7 : (span_b == 64 ? 6 : 5);
-    const int swz = span_b == 128 ? (row_in_tile & 7) : span_b == 64 ? ((row_in_tile >> 1) & 3) : ((row_in_tile >> 2) & 1);
+    const int span_r = FUSE ? p.res_span : 0;        // never both: a fused Add stores directly
+    const int span_s = span_b ? span_b : span_r;     // layout of the staging memory either way
+    const int span_shift = span_s == 128 ? 7 : (span_s == 64 ? 6 : 5);
+    const int swz = span_s == 128 ? (row_in_tile & 7) : span_s == 64 ? ((row_in_tile >> 1) & 3) : ((row_in_tile >> 2) & 1);
     int j = 0;
     // Once a wait has given up (alive == false) a thread does no more work, but it keeps running the
     // loop and both barriers of every tile, so the other epilogue threads never wait for it.
@@ -498,23 +544,6 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (row >= p.M) row = -1;
       }
     };
-    // FUSE: the residual rows of a tile are asked into L2 a whole tile before they are read (those of the
-    // first tile while its accumulator is still being computed), so its position is worked out one tile early.
-    auto prefetch_residual = [&](long long r) {
-      const int pc = n_tile * p.BNd + col_group * 64;   // the four warps that share a row cover its 256 bytes
-      if (r >= 0 && col_group * 64 < p.BNd && pc < p.Ocp) {
-        const uint8_t* pa = p.ep.add_residual + r * p.ldd + pc;
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + 32));
-      }
-    };
-    long long row_ahead = -1;
-    const int32_t* corr_ahead = nullptr;
-    if (FUSE && static_cast<int>(blockIdx.x) < num_tiles) {
-      pdl_wait();   // the residual is an earlier kernel's output
-      locate(m_tile0, row_ahead, corr_ahead);
-      prefetch_residual(row_ahead);
-    }
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
       const int m_tile = m_tile0 + j * m_step;
@@ -522,21 +551,17 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint8_t* stage_out = staging + a * staging_bytes;
       long long row;                 // direct-store path: output row (pixel index into D), -1 outside the tensor
       const int32_t* corr_row;       // border pixels of a padded convolution: their correction, this N tile
-      if (FUSE) {
-        row = row_ahead;
-        corr_row = corr_ahead;
-        if (tile + static_cast<int>(gridDim.x) < num_tiles) {
-          locate(m_tile + m_step, row_ahead, corr_ahead);
-          prefetch_residual(row_ahead);
-        }
-      } else {
-        locate(m_tile, row, corr_row);
-      }
+      locate(m_tile, row, corr_row);
       if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
       alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
       if (!alive) {
         if (span_b) epilogue_barrier();
         continue;
+      }
+      if (span_r) {
+        alive = mbar_wait(smem_u32(&hdr->res_full[j & 1]), (j >> 1) & 1, abort_flag, p.status, 7);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) continue;
       }
       if (warp == kFirstEpilogueWarp && lane == 0) TC_TRACE(2, j, 0);
       tc_fence_after();
@@ -555,7 +580,15 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int cbase = n_tile * p.BNd + c0;
         if (!span_b && (row < 0 || cbase + 16 > p.Ocp)) return;
         uint4 res16 = make_uint4(0, 0, 0, 0);
-        if (FUSE) res16 = __ldg(reinterpret_cast<const uint4*>(p.ep.add_residual + row * p.ldd + cbase));   // in flight during the math
+        if (FUSE) {
+          if (span_r) {
+            const int blk = c0 >> span_shift, chunk = (c0 & (span_r - 1)) >> 4;
+            res16 = *reinterpret_cast<const uint4*>(staging + (j & 1) * staging_bytes + static_cast<size_t>(blk) * kBlockM * span_r +
+                                                    row_in_tile * span_r + ((chunk ^ swz) << 4));
+          } else if (row >= 0 && cbase + 16 <= p.Ocp) {
+            res16 = __ldg(reinterpret_cast<const uint4*>(p.ep.add_residual + row * p.ldd + cbase));
+          }
+        }
         uint4 out16 = requant_chunk16<EXTRA>(acc, &hdr->bias[c0], &hdr->scale[c0], rc, sub,
                                              (corr_row && cbase + 16 <= p.Ocp) ? corr_row + c0 : nullptr);
         if (FUSE) {
@@ -588,10 +621,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           c0 += 64;
         }
       }
-      // accumulator buffer free again
+      // accumulator buffer (and residual buffer) free again
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&hdr->tmem_empty[a]));
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&hdr->tmem_empty[a]));
+        if (span_r) mbar_arrive(smem_u32(&hdr->res_empty[j & 1]));
+      }
       if (span_b) {
         // One barrier per tile.  Before it, the issuer makes sure the previous tile's store has read
         // its staging buffer (it was issued a whole tile ago): after the barrier every thread may
@@ -727,7 +763,6 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bk = bk; }
   }
   p.BK = best_bk;
-  const int kblocks_per_tile = taps * ((Kspan + p.BK - 1) / p.BK);
   p.layout_type = p.BK == 128 ? 2u : (p.BK == 64 ? 4u : 6u);
   p.sbo = 8u * p.BK;
   // Output staging for the TMA store: column blocks as wide as the widest swizzle span dividing BN.
@@ -737,14 +772,28 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   // the staging memory goes to the operand ring instead), so that is the default;
   // B2VX_TC_STORE=tma selects the staged store.
   static const bool tma_store = [] { const char* e = std::getenv("B2VX_TC_STORE"); return e && std::strcmp(e, "tma") == 0; }();
+  p.res_span = e.add_residual != nullptr ? p.store_span : 0;
   if (!tma_store || e.add_residual != nullptr) p.store_span = 0;
-  const size_t staging = p.store_span ? 2 * static_cast<size_t>(kBlockM) * p.BNd : 0;
+  const size_t add_table_bytes = e.add_residual != nullptr ? 65536 : 0;
+  if (p.res_span) {
+    // The Add's table and two residual tiles leave less for the operand ring: three stages must remain,
+    // with 64-byte K blocks if 128-byte ones do not fit (these layers are bound by their epilogue, not by
+    // the main loop); failing that the epilogue threads load their residual pieces themselves.
+    const size_t left = kSmemBudget - 2048 - sizeof(SmemHeader) - add_table_bytes - 2 * static_cast<size_t>(kBlockM) * p.BNd;
+    if (left < 3 * static_cast<size_t>(kBlockM + p.BN) * p.BK && p.BK == 128) {
+      p.BK = 64;
+      p.layout_type = 4u;
+      p.sbo = 8u * p.BK;
+    }
+    if (left < 3 * static_cast<size_t>(kBlockM + p.BN) * p.BK) p.res_span = 0;
+  }
+  const int kblocks_per_tile = taps * ((Kspan + p.BK - 1) / p.BK);
+  const size_t staging = (p.store_span || p.res_span) ? 2 * static_cast<size_t>(kBlockM) * p.BNd : 0;
   // A and B tiles are whole swizzle atoms (8 rows x BK bytes; BN and 128 are multiples of 8), so every
   // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
   // aligned start of the ring.  Several k-blocks share a stage (one barrier round trip) when they are
   // small: up to 64 KiB per stage.
   const size_t sub_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
-  const size_t add_table_bytes = e.add_residual != nullptr ? 65536 : 0;
   const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging - add_table_bytes;
   int group = static_cast<int>((64 * 1024) / sub_bytes);
   if (group > kblocks_per_tile) group = kblocks_per_tile;
@@ -843,10 +892,12 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   const uint64_t adims[2] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(M)};
   const uint32_t abox[2] = {static_cast<uint32_t>(p.BK), kBlockM};
   bool ok = encode_u8(&plan->map_a, A, 2, adims, abox, nullptr, swizzle_of(p.BK));
-  if (ok && p.store_span) {
+  if (ok && (p.store_span || p.res_span)) {
+    // the output tile for the staged store, or (fused Add) the residual tile of the same geometry
+    const int span = p.store_span ? p.store_span : p.res_span;
     const uint64_t ddims[2] = {static_cast<uint64_t>(ldd), static_cast<uint64_t>(M)};
-    const uint32_t dbox[2] = {static_cast<uint32_t>(p.store_span), kBlockM};
-    ok = encode_u8(&plan->map_d, D, 2, ddims, dbox, nullptr, swizzle_of(p.store_span));
+    const uint32_t dbox[2] = {static_cast<uint32_t>(span), kBlockM};
+    ok = encode_u8(&plan->map_d, p.store_span ? D : static_cast<const void*>(e.add_residual), 2, ddims, dbox, nullptr, swizzle_of(span));
   }
   if (!ok) {
     delete plan;
@@ -912,10 +963,11 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
                            static_cast<uint32_t>((bh - 1) * g.sy + 1), static_cast<uint32_t>(bn)};
   const uint32_t estr[4] = {1, static_cast<uint32_t>(g.sx), static_cast<uint32_t>(g.sy), 1};
   bool ok = encode_u8(&plan->map_a, X, 4, dims, box, estr, swizzle_of(p.BK));
-  if (ok && p.store_span) {
+  if (ok && (p.store_span || p.res_span)) {
+    const int span = p.store_span ? p.store_span : p.res_span;
     const uint64_t ddims[4] = {static_cast<uint64_t>(g.Ocp), static_cast<uint64_t>(g.Wo), static_cast<uint64_t>(g.Ho), static_cast<uint64_t>(g.N)};
-    const uint32_t dbox[4] = {static_cast<uint32_t>(p.store_span), static_cast<uint32_t>(bw), static_cast<uint32_t>(bh), static_cast<uint32_t>(bn)};
-    ok = encode_u8(&plan->map_d, D, 4, ddims, dbox, nullptr, swizzle_of(p.store_span));
+    const uint32_t dbox[4] = {static_cast<uint32_t>(span), static_cast<uint32_t>(bw), static_cast<uint32_t>(bh), static_cast<uint32_t>(bn)};
+    ok = encode_u8(&plan->map_d, p.store_span ? D : static_cast<const void*>(e.add_residual), 4, ddims, dbox, nullptr, swizzle_of(span));
   }
   if (!ok) {
     delete plan;
@@ -935,6 +987,7 @@ GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s) {
   const double rows = static_cast<double>(M < kBlockM ? M : kBlockM);
   GemmTcTiling best = {0, 0, 0};
   double best_time = 0.0;
+  const bool l2_resident = (static_cast<double>(M) + Ocp) * Kp < 48.0e6;
   // B2VX_TC_BN=<width>: force the tile width (a tuning aid; ignored when it does not fit)
   static const int forced = [] { const char* e = std::getenv("B2VX_TC_BN"); return e ? std::atoi(e) : 0; }();
   if (forced >= 16 && forced <= max_data && (forced & 15) == 0) {
@@ -961,8 +1014,10 @@ GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s) {
     // cycles per tile: tensor pipe (8192 MAC/clk), operand bytes (HBM share per SM when all SMs load,
     // more when few do), epilogue issue slots
     const double mma = static_cast<double>(Kp) * bn / 64.0;
+    // operands of a layer that fits the L2 several times over (a previous layer's output and a small
+    // weight matrix) are served by the L2 at its per-SM rate; otherwise by the CTA's share of HBM
     double bytes_per_clk = 24.0 * sms / static_cast<double>(grid);
-    if (bytes_per_clk > 64.0) bytes_per_clk = 64.0;
+    if (bytes_per_clk > 64.0 || l2_resident) bytes_per_clk = 64.0;
     const double load = (rows + bn) * Kp / bytes_per_clk;
     const double epi = 9.0 * data + 300.0;
     const double mainloop = mma > load ? mma : load;
@@ -1012,10 +1067,12 @@ GemmTcPlan* gemm_tc_plan_build_in(void* storage, size_t storage_bytes, const voi
   const uint64_t adims[2] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(M)};
   const uint32_t abox[2] = {static_cast<uint32_t>(p.BK), kBlockM};
   bool ok = encode_u8(&plan->map_a, A, 2, adims, abox, nullptr, swizzle_of(p.BK));
-  if (ok && p.store_span) {
+  if (ok && (p.store_span || p.res_span)) {
+    // the output tile for the staged store, or (fused Add) the residual tile of the same geometry
+    const int span = p.store_span ? p.store_span : p.res_span;
     const uint64_t ddims[2] = {static_cast<uint64_t>(ldd), static_cast<uint64_t>(M)};
-    const uint32_t dbox[2] = {static_cast<uint32_t>(p.store_span), kBlockM};
-    ok = encode_u8(&plan->map_d, D, 2, ddims, dbox, nullptr, swizzle_of(p.store_span));
+    const uint32_t dbox[2] = {static_cast<uint32_t>(span), kBlockM};
+    ok = encode_u8(&plan->map_d, p.store_span ? D : static_cast<const void*>(e.add_residual), 2, ddims, dbox, nullptr, swizzle_of(span));
   }
   if (!ok) return fail("gemm_tc: cuTensorMapEncodeTiled failed");
   set_grid(plan);

@@ -85,7 +85,7 @@ __device__ __forceinline__ int requant_fast(float real, const OutQuant& q, float
 // Each half is an IEEE round-to-nearest operation, bit-identical to the scalar
 // intrinsic; the point is one issue slot for two results in instruction-bound
 // requantization loops.
-#ifndef B2VX_F2_ASM
+#ifdef B2VX_F2_INTRINSICS
 // float2 values and the sm_100 packed intrinsics: the compiler keeps each value in a register pair.
 typedef float2 f32x2;
 __device__ __forceinline__ f32x2 f2_pack(float lo, float hi) { return make_float2(lo, hi); }
