@@ -188,6 +188,8 @@ class OpWorkload:
         kind = spec.split(":")[0]
         if kind == "add":
             self.metric, self.unit, self.scale = "quantized_add_gbytes_per_sec", "GB/s", 3.0 / 1e9
+        elif kind in ("concat", "transpose"):
+            self.metric, self.unit, self.scale = kind + "_gbytes_per_sec", "GB/s", 2.0 / 1e9   # each element read and written once
         else:
             self.metric = "conv2d_int8_tops" if kind in ("conv", "convadd") else "fullyconnected_int8_tops"
             self.unit, self.scale = "TOP/s", self.ops / self.units / 1e12
@@ -299,7 +301,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None,
                     help="resnet50 (default), mobilenetv2, lenet, or one operator: conv:k:cin:cout:hw:stride, "
-                         "convadd:k:cin:cout:hw:stride, gemm:m:n:k, add:elements (tim-vx_b200/opworkloads.py)")
+                         "convadd:k:cin:cout:hw:stride, gemm:m:n:k, add:elements, concat:c1:c2:hw, transpose:c:hw "
+                         "(tim-vx_b200/opworkloads.py)")
     ap.add_argument("--net", default="resnet50", help="older spelling of --workload for the networks")
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--cpu-batch", type=int, default=4, help="images per step of the CPU baseline sample")

@@ -93,8 +93,15 @@ enum {
   B2VX_NODE_ADD = 4,
   B2VX_NODE_RELU = 5,
   B2VX_NODE_RELU6 = 6,
-  B2VX_NODE_SOFTMAX = 7
+  B2VX_NODE_SOFTMAX = 7,
+  B2VX_NODE_RESHAPE = 8,
+  B2VX_NODE_TRANSPOSE = 9,
+  B2VX_NODE_CONCAT = 10,
+  B2VX_NODE_DATACONVERT = 11
 };
+
+/* most tensors one node reads (Concat) */
+#define B2VX_MAX_NODE_INPUTS 16
 
 /* Replaces vsi_nn_tensor_attr_t as filled by PackTensorDtype and
  * TensorImpl::Init (src/tim/vx/tensor.cc:40-99,391-459).  rank == 0 with the
@@ -147,6 +154,12 @@ typedef struct b2vx_pool2d_desc {
   uint32_t pad[4];
   int32_t round_type;
 } b2vx_pool2d_desc;
+
+/* A list of up to B2VX_MAX_RANK numbers: a target shape (Reshape) or a permutation (Transpose). */
+typedef struct b2vx_dims_desc {
+  uint32_t rank;
+  uint32_t v[8];
+} b2vx_dims_desc;
 
 /* Replaces vsi_nn_softmax_param (src/tim/vx/ops/softmax.cc:33-37). */
 typedef struct b2vx_softmax_desc {
@@ -201,6 +214,17 @@ b2vx_status b2vx_node_add(b2vx_graph* g, uint32_t a, uint32_t b, uint32_t y);
 b2vx_status b2vx_node_relu(b2vx_graph* g, uint32_t x, uint32_t y);
 b2vx_status b2vx_node_relu6(b2vx_graph* g, uint32_t x, uint32_t y);
 b2vx_status b2vx_node_softmax(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_softmax_desc* d);
+/* Data movement between the compute nodes, as the reference's exported graphs use it
+ * (samples/multi_device/vx_mobilenet.cc:570-571,832-840; vx_resnet50.cc:1347-1349).
+ * Reshape (src/tim/vx/ops/reshape.cc:34-47): same elements in WHCN order under a new shape.
+ * Transpose (src/tim/vx/ops/transpose.cc:34-45): output dimension i is input dimension perm[i].
+ * Concat (src/tim/vx/ops/concat.cc:33-41): inputs joined along `axis`; 8-bit inputs whose
+ * quantization differs from the output's are requantized.
+ * DataConvert (src/tim/vx/ops/simple_operations.cc): quantize / dequantize / requantize. */
+b2vx_status b2vx_node_reshape(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_dims_desc* shape);
+b2vx_status b2vx_node_transpose(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_dims_desc* perm);
+b2vx_status b2vx_node_concat(b2vx_graph* g, const uint32_t* inputs, uint32_t n_inputs, uint32_t axis, uint32_t y);
+b2vx_status b2vx_node_dataconvert(b2vx_graph* g, uint32_t x, uint32_t y);
 
 /* ---- compile / run: vsi_nn_SetupGraph + vsi_nn_VerifyGraph
  *      (src/tim/vx/graph.cc:328-383) and vsi_nn_RunGraph (graph.cc:389-391).

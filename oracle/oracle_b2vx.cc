@@ -71,13 +71,15 @@ struct OTensor {
 
 struct ONode {
   int32_t kind;
-  uint32_t in[3];
+  uint32_t in[B2VX_MAX_NODE_INPUTS];   // unused slots hold B2VX_NO_TENSOR
   uint32_t out;
   union {
     b2vx_conv2d_desc conv;
     b2vx_fc_desc fc;
     b2vx_pool2d_desc pool;
     b2vx_softmax_desc softmax;
+    b2vx_dims_desc dims;      // Reshape: target shape; Transpose: permutation
+    uint32_t concat_axis;
   } p;
   uint32_t pad_resolved[4];
 };
@@ -163,7 +165,9 @@ void write_case(b2vx_graph* g) {
   std::fprintf(f, " ],\n \"nodes\": [\n");
   for (size_t i = 0; i < g->nodes.size(); ++i) {
     const ONode& n = g->nodes[i];
-    std::fprintf(f, "  {\"kind\": %d, \"in\": [%u, %u, %u], \"out\": %u", n.kind, n.in[0], n.in[1], n.in[2], n.out);
+    std::fprintf(f, "  {\"kind\": %d, \"in\": [%u, %u, %u", n.kind, n.in[0], n.in[1], n.in[2]);
+    for (uint32_t k = 3; k < B2VX_MAX_NODE_INPUTS && n.in[k] != B2VX_NO_TENSOR; ++k) std::fprintf(f, ", %u", n.in[k]);
+    std::fprintf(f, "], \"out\": %u", n.out);
     if (n.kind == B2VX_NODE_CONV2D) {
       const b2vx_conv2d_desc& c = n.p.conv;
       std::fprintf(f, ", \"weights\": %u, \"pad_type\": %d, \"ksize\": [%u, %u], \"stride\": [%u, %u], \"dilation\": [%u, %u], \"pad\": [%u, %u, %u, %u], \"multiplier\": %d",
@@ -178,6 +182,12 @@ void write_case(b2vx_graph* g) {
                    c.round_type);
     } else if (n.kind == B2VX_NODE_SOFTMAX) {
       std::fprintf(f, ", \"beta\": %.9g, \"axis\": %d", n.p.softmax.beta, n.p.softmax.axis);
+    } else if (n.kind == B2VX_NODE_RESHAPE || n.kind == B2VX_NODE_TRANSPOSE) {
+      std::fprintf(f, ", \"dims\": [");
+      for (uint32_t k = 0; k < n.p.dims.rank; ++k) std::fprintf(f, "%s%u", k ? ", " : "", n.p.dims.v[k]);
+      std::fprintf(f, "]");
+    } else if (n.kind == B2VX_NODE_CONCAT) {
+      std::fprintf(f, ", \"axis\": %u", n.p.concat_axis);
     }
     std::fprintf(f, "}%s\n", i + 1 < g->nodes.size() ? "," : "");
   }
@@ -289,6 +299,46 @@ b2vx_status infer_node(b2vx_graph* g, ONode& n) {
       }
       return set_shape(g, n.out, dims, "add");
     }
+    case B2VX_NODE_RESHAPE: {
+      // src/tim/vx/ops/reshape.cc:46-58: the target shape is the output's shape; element counts must agree
+      const b2vx_dims_desc& d = n.p.dims;
+      std::vector<uint32_t> dims(d.v, d.v + d.rank);
+      size_t want = 1;
+      for (uint32_t v : dims) want *= v;
+      if (want != x.elems()) return fail(g, B2VX_SHAPE_MISMATCH, "reshape: element count changes");
+      OTensor& y = g->tensors[n.out];
+      if (y.has_shape) return y.elems() == want ? B2VX_OK : fail(g, B2VX_SHAPE_MISMATCH, "reshape: declared output size");
+      return set_shape(g, n.out, dims, "reshape");
+    }
+    case B2VX_NODE_TRANSPOSE: {
+      // vsi_nn_op_permute.c op_setup: out.size[i] = in.size[perm[i]]
+      const b2vx_dims_desc& d = n.p.dims;
+      if (d.rank != x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "transpose: permutation length != input rank");
+      std::vector<uint32_t> dims(d.rank);
+      uint32_t seen = 0;
+      for (uint32_t i = 0; i < d.rank; ++i) {
+        if (d.v[i] >= d.rank || (seen >> d.v[i]) & 1u) return fail(g, B2VX_INVALID_ARG, "transpose: not a permutation");
+        seen |= 1u << d.v[i];
+        dims[i] = x.d.dims[d.v[i]];
+      }
+      return set_shape(g, n.out, dims, "transpose");
+    }
+    case B2VX_NODE_CONCAT: {
+      // vsi_nn_op_concat.c op_setup: all dimensions but `axis` agree; the axis extents add up
+      const uint32_t axis = n.p.concat_axis;
+      if (axis >= x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "concat: axis outside the input rank");
+      std::vector<uint32_t> dims(x.d.dims, x.d.dims + x.d.rank);
+      dims[axis] = 0;
+      for (uint32_t id : n.in) {
+        if (id == B2VX_NO_TENSOR) continue;
+        const OTensor& t = g->tensors[id];
+        if (!t.has_shape || t.d.rank != x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "concat: input ranks differ");
+        for (uint32_t i = 0; i < x.d.rank; ++i)
+          if (i != axis && t.d.dims[i] != x.d.dims[i]) return fail(g, B2VX_SHAPE_MISMATCH, "concat: input shapes differ off the axis");
+        dims[axis] += t.d.dims[axis];
+      }
+      return set_shape(g, n.out, dims, "concat");
+    }
     default: {
       std::vector<uint32_t> dims(x.d.dims, x.d.dims + x.d.rank);
       return set_shape(g, n.out, dims, "unary");
@@ -378,6 +428,89 @@ b2vx_status exec_node(b2vx_graph* g, ONode& n) {
       rc = orc_relu(x.data.data(), x.d.dtype, x.quant(), y.data.data(), y.d.dtype, y.quant(), x.elems(),
                     n.kind == B2VX_NODE_RELU6 ? 6.0f : -1.0f);
       break;
+    case B2VX_NODE_RESHAPE:
+      if (x.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "reshape: input/output dtype differ");
+      std::memcpy(y.data.data(), x.data.data(), y.bytes());
+      rc = 0;
+      break;
+    case B2VX_NODE_TRANSPOSE: {
+      if (x.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "transpose: input/output dtype differ");
+      const size_t es = dtype_size(x.d.dtype);
+      const uint32_t rank = x.d.rank;
+      size_t istride[8], s0 = 1;
+      for (uint32_t i = 0; i < rank; ++i) { istride[i] = s0; s0 *= x.d.dims[i]; }
+      const size_t total = y.elems();
+      for (size_t o = 0; o < total; ++o) {
+        size_t rem = o, src = 0;
+        for (uint32_t i = 0; i < rank; ++i) {
+          const size_t c = rem % y.d.dims[i];
+          rem /= y.d.dims[i];
+          src += c * istride[n.p.dims.v[i]];
+        }
+        std::memcpy(y.data.data() + o * es, x.data.data() + src * es, es);
+      }
+      rc = 0;
+      break;
+    }
+    case B2VX_NODE_CONCAT: {
+      const uint32_t axis = n.p.concat_axis, rank = y.d.rank;
+      const size_t es = dtype_size(y.d.dtype);
+      size_t inner = 1, outer = 1;
+      for (uint32_t i = 0; i < axis; ++i) inner *= y.d.dims[i];
+      for (uint32_t i = axis + 1; i < rank; ++i) outer *= y.d.dims[i];
+      size_t offset = 0;   // along the axis
+      for (uint32_t id : n.in) {
+        if (id == B2VX_NO_TENSOR) continue;
+        OTensor& t = g->tensors[id];
+        if (t.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "concat: input/output dtype differ");
+        const orc_quant tq = t.quant(), yq = y.quant();
+        const bool q8 = t.d.dtype == B2VX_DT_UINT8 || t.d.dtype == B2VX_DT_INT8;
+        const bool convert = q8 && (tq.scale != yq.scale || tq.zp != yq.zp);
+        const size_t ext = t.d.dims[axis];
+        for (size_t o = 0; o < outer; ++o)
+          for (size_t a = 0; a < ext; ++a) {
+            const size_t src = (o * ext + a) * inner, dst = (o * y.d.dims[axis] + offset + a) * inner;
+            if (!convert) {
+              std::memcpy(y.data.data() + dst * es, t.data.data() + src * es, inner * es);
+            } else {
+              for (size_t i = 0; i < inner; ++i) {
+                const int32_t v = t.d.dtype == B2VX_DT_UINT8 ? static_cast<int32_t>(t.data[src + i])
+                                                             : static_cast<int32_t>(static_cast<int8_t>(t.data[src + i]));
+                const int32_t q = orc_fp32_to_affine(orc_affine_to_fp32(v, tq.scale, tq.zp), yq.scale, yq.zp, y.d.dtype);
+                y.data[dst + i] = static_cast<uint8_t>(q & 0xFF);
+              }
+            }
+          }
+        offset += ext;
+      }
+      rc = 0;
+      break;
+    }
+    case B2VX_NODE_DATACONVERT: {
+      // dequantize with the input's parameters, quantize with the output's (float32 passes through)
+      const orc_quant xq = x.quant(), yq = y.quant();
+      const size_t total = x.elems();
+      rc = 0;
+      for (size_t i = 0; i < total && rc == 0; ++i) {
+        float real;
+        switch (x.d.dtype) {
+          case B2VX_DT_FLOAT32: real = reinterpret_cast<const float*>(x.data.data())[i]; break;
+          case B2VX_DT_UINT8: real = orc_affine_to_fp32(x.data[i], xq.scale, xq.zp); break;
+          case B2VX_DT_INT8: real = orc_affine_to_fp32(static_cast<int8_t>(x.data[i]), xq.scale, xq.zp); break;
+          case B2VX_DT_INT32: real = orc_affine_to_fp32(reinterpret_cast<const int32_t*>(x.data.data())[i], xq.scale, xq.zp); break;
+          default: rc = -1; real = 0.0f; break;
+        }
+        switch (y.d.dtype) {
+          case B2VX_DT_FLOAT32: reinterpret_cast<float*>(y.data.data())[i] = real; break;
+          case B2VX_DT_UINT8: case B2VX_DT_INT8:
+            y.data[i] = static_cast<uint8_t>(orc_fp32_to_affine(real, yq.scale, yq.zp, y.d.dtype) & 0xFF);
+            break;
+          case B2VX_DT_INT32: reinterpret_cast<int32_t*>(y.data.data())[i] = orc_fp32_to_affine(real, yq.scale, yq.zp, y.d.dtype); break;
+          default: rc = -1; break;
+        }
+      }
+      break;
+    }
     case B2VX_NODE_SOFTMAX:
       rc = orc_softmax(x.data.data(), x.d.dtype, x.quant(), y.data.data(), y.d.dtype, y.quant(), x.d.dims,
                        x.d.rank, n.p.softmax.axis, n.p.softmax.beta);
@@ -401,6 +534,7 @@ b2vx_status add_node(b2vx_graph* g, int32_t kind, uint32_t i0, uint32_t i1, uint
   ONode n = proto ? *proto : ONode();
   if (!proto) std::memset(&n, 0, sizeof(n));
   n.kind = kind;
+  for (uint32_t& id : n.in) id = B2VX_NO_TENSOR;
   n.in[0] = i0; n.in[1] = i1; n.in[2] = i2; n.out = out;
   g->nodes.push_back(n);
   return B2VX_OK;
@@ -549,6 +683,36 @@ b2vx_status b2vx_node_relu(b2vx_graph* g, uint32_t x, uint32_t y) {
 }
 b2vx_status b2vx_node_relu6(b2vx_graph* g, uint32_t x, uint32_t y) {
   return add_node(g, B2VX_NODE_RELU6, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
+}
+b2vx_status b2vx_node_reshape(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_dims_desc* shape) {
+  if (!g || !shape || shape->rank == 0 || shape->rank > B2VX_MAX_RANK) return g ? fail(g, B2VX_INVALID_ARG, "reshape: bad shape") : B2VX_INVALID_ARG;
+  ONode n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.dims = *shape;
+  return add_node(g, B2VX_NODE_RESHAPE, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+}
+b2vx_status b2vx_node_transpose(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_dims_desc* perm) {
+  if (!g || !perm || perm->rank == 0 || perm->rank > B2VX_MAX_RANK) return g ? fail(g, B2VX_INVALID_ARG, "transpose: bad permutation") : B2VX_INVALID_ARG;
+  ONode n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.dims = *perm;
+  return add_node(g, B2VX_NODE_TRANSPOSE, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+}
+b2vx_status b2vx_node_concat(b2vx_graph* g, const uint32_t* inputs, uint32_t n_inputs, uint32_t axis, uint32_t y) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (!inputs || n_inputs == 0 || n_inputs > B2VX_MAX_NODE_INPUTS) return fail(g, B2VX_INVALID_ARG, "concat: 1 to 16 inputs");
+  for (uint32_t i = 0; i < n_inputs; ++i)
+    if (!valid_id(g, inputs[i])) return fail(g, B2VX_INVALID_ARG, "concat: bad tensor id");
+  ONode n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.concat_axis = axis;
+  b2vx_status st = add_node(g, B2VX_NODE_CONCAT, inputs[0], B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+  if (st != B2VX_OK) return st;
+  for (uint32_t i = 0; i < n_inputs; ++i) g->nodes.back().in[i] = inputs[i];
+  return B2VX_OK;
+}
+b2vx_status b2vx_node_dataconvert(b2vx_graph* g, uint32_t x, uint32_t y) {
+  return add_node(g, B2VX_NODE_DATACONVERT, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
 }
 b2vx_status b2vx_node_softmax(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_softmax_desc* d) {
   if (!d) return B2VX_INVALID_ARG;

@@ -32,6 +32,7 @@ TEST_FILES = [
     "src/tim/vx/ops/max_pool_test.cc",
     "src/tim/vx/ops/fullyconnected_test.cc",
     "src/tim/vx/ops/softmax_test.cc",
+    "src/tim/vx/ops/transpose_test.cc",
 ]
 
 

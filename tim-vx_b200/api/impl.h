@@ -137,6 +137,8 @@ class OpImpl {
     b2vx_fc_desc fc;
     b2vx_pool2d_desc pool2d;
     b2vx_softmax_desc softmax;
+    b2vx_dims_desc dims;     // Reshape: target shape; Transpose: permutation
+    uint32_t concat_axis;
   } desc_;
   std::vector<uint8_t> blob_;   // ops::NBG: the serialised graph this op stands for
 };

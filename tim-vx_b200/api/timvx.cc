@@ -13,6 +13,10 @@
 
 #include "impl.h"
 #include "tim/vx/builtin_op.h"
+#include "tim/vx/ops/concat.h"
+#include "tim/vx/ops/reshape.h"
+#include "tim/vx/ops/simple_operations.h"
+#include "tim/vx/ops/transpose.h"
 #include "tim/vx/ops/activations.h"
 #include "tim/vx/ops/conv2d.h"
 #include "tim/vx/ops/elementwise.h"
@@ -520,6 +524,15 @@ bool GraphImpl::EmitNodes() {
       case B2VX_NODE_RELU: st = b2vx_node_relu(graph_, in(0), out(0)); break;
       case B2VX_NODE_RELU6: st = b2vx_node_relu6(graph_, in(0), out(0)); break;
       case B2VX_NODE_SOFTMAX: st = b2vx_node_softmax(graph_, in(0), out(0), &p->desc_.softmax); break;
+      case B2VX_NODE_RESHAPE: st = b2vx_node_reshape(graph_, in(0), out(0), &p->desc_.dims); break;
+      case B2VX_NODE_TRANSPOSE: st = b2vx_node_transpose(graph_, in(0), out(0), &p->desc_.dims); break;
+      case B2VX_NODE_DATACONVERT: st = b2vx_node_dataconvert(graph_, in(0), out(0)); break;
+      case B2VX_NODE_CONCAT: {
+        std::vector<uint32_t> ids;
+        for (size_t k = 0; k < p->inputs_tensor_.size(); ++k) ids.push_back(in(k));
+        st = b2vx_node_concat(graph_, ids.data(), static_cast<uint32_t>(ids.size()), p->desc_.concat_axis, out(0));
+        break;
+      }
       case kNodeKindNbg: st = ExpandBlob(p) ? B2VX_OK : B2VX_INVALID_ARG; break;
       default: break;
     }
@@ -782,6 +795,15 @@ bool GraphImpl::ExpandBlob(const OpImpl* op) {
       case B2VX_NODE_RELU: st = b2vx_node_relu(graph_, at(o.in, 0), at(o.out, 0)); break;
       case B2VX_NODE_RELU6: st = b2vx_node_relu6(graph_, at(o.in, 0), at(o.out, 0)); break;
       case B2VX_NODE_SOFTMAX: st = b2vx_node_softmax(graph_, at(o.in, 0), at(o.out, 0), &o.desc.softmax); break;
+      case B2VX_NODE_RESHAPE: st = b2vx_node_reshape(graph_, at(o.in, 0), at(o.out, 0), &o.desc.dims); break;
+      case B2VX_NODE_TRANSPOSE: st = b2vx_node_transpose(graph_, at(o.in, 0), at(o.out, 0), &o.desc.dims); break;
+      case B2VX_NODE_DATACONVERT: st = b2vx_node_dataconvert(graph_, at(o.in, 0), at(o.out, 0)); break;
+      case B2VX_NODE_CONCAT: {
+        std::vector<uint32_t> ids;
+        for (size_t k = 0; k < o.in.size(); ++k) ids.push_back(at(o.in, k));
+        st = b2vx_node_concat(graph_, ids.data(), static_cast<uint32_t>(ids.size()), o.desc.concat_axis, at(o.out, 0));
+        break;
+      }
       default: break;
     }
     if (st != B2VX_OK) {
@@ -995,6 +1017,31 @@ NBG::NBG(Graph* graph, const char* binary, size_t input_count, size_t output_cou
 std::shared_ptr<Operation> NBG::Clone(std::shared_ptr<Graph>& graph) const {
   return graph->CreateOperation<NBG>(reinterpret_cast<const char*>(impl_->blob_.data()), impl_->input_cnt_, impl_->output_cnt_);
 }
+
+Reshape::Reshape(Graph* graph, const std::vector<uint32_t>& target_shape)
+    : BuiltinOp(graph, B2VX_NODE_RESHAPE, 1, 1), size_(target_shape) {
+  b2vx_dims_desc& d = impl_->desc_.dims;
+  d.rank = static_cast<uint32_t>(target_shape.size() <= B2VX_MAX_RANK ? target_shape.size() : 0);   // rank 0 is refused when the node is added
+  for (uint32_t i = 0; i < d.rank; ++i) d.v[i] = target_shape[i];
+}
+std::shared_ptr<Operation> Reshape::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Reshape>(size_); }
+
+Transpose::Transpose(Graph* graph, const std::vector<uint32_t>& perm) : BuiltinOp(graph, B2VX_NODE_TRANSPOSE, 1, 1), perm_(perm) {
+  b2vx_dims_desc& d = impl_->desc_.dims;
+  d.rank = static_cast<uint32_t>(perm.size() <= B2VX_MAX_RANK ? perm.size() : 0);
+  for (uint32_t i = 0; i < d.rank; ++i) d.v[i] = perm[i];
+}
+std::shared_ptr<Operation> Transpose::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Transpose>(perm_); }
+
+Concat::Concat(Graph* graph, uint32_t axis, int input_cnt) : BuiltinOp(graph, B2VX_NODE_CONCAT, input_cnt, 1), axis_(axis) {
+  impl_->desc_.concat_axis = axis;
+}
+std::shared_ptr<Operation> Concat::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<Concat>(axis_, impl_->input_cnt_);
+}
+
+DataConvert::DataConvert(Graph* graph) : BuiltinOp(graph, B2VX_NODE_DATACONVERT, 1, 1) {}
+std::shared_ptr<Operation> DataConvert::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<DataConvert>(); }
 
 Relu6::Relu6(Graph* graph) : BuiltinOp(graph, B2VX_NODE_RELU6, 1, 1) {}
 std::shared_ptr<Operation> Relu6::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Relu6>(); }

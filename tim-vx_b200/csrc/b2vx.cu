@@ -76,13 +76,15 @@ struct TensorRec {
 
 struct NodeRec {
   int32_t kind;
-  uint32_t in[3];
+  uint32_t in[B2VX_MAX_NODE_INPUTS];   // unused slots hold B2VX_NO_TENSOR
   uint32_t out;
   union {
     b2vx_conv2d_desc conv;
     b2vx_fc_desc fc;
     b2vx_pool2d_desc pool;
     b2vx_softmax_desc softmax;
+    b2vx_dims_desc dims;      // Reshape: target shape; Transpose: permutation
+    uint32_t concat_axis;
   } p;
   uint32_t pad[4];
   bool removed = false;   // folded into its producer at compile
@@ -292,6 +294,46 @@ b2vx_status infer_node(b2vx_graph* g, NodeRec& n) {
         dims[i] = std::max(da, db);
       }
       return set_shape(g, n.out, dims, "add", false);
+    }
+    case B2VX_NODE_RESHAPE: {
+      // src/tim/vx/ops/reshape.cc:46-58: the target shape is the output's shape; element counts must agree
+      const b2vx_dims_desc& d = n.p.dims;
+      std::vector<uint32_t> dims(d.v, d.v + d.rank);
+      size_t want = 1;
+      for (uint32_t v : dims) want *= v;
+      if (want != x.elems()) return fail(g, B2VX_SHAPE_MISMATCH, "reshape: element count changes");
+      TensorRec& y = g->tensors[n.out];
+      if (y.has_shape) return y.elems() == want ? B2VX_OK : fail(g, B2VX_SHAPE_MISMATCH, "reshape: declared output size");
+      return set_shape(g, n.out, dims, "reshape", false);
+    }
+    case B2VX_NODE_TRANSPOSE: {
+      // vsi_nn_op_permute.c op_setup: out.size[i] = in.size[perm[i]]
+      const b2vx_dims_desc& d = n.p.dims;
+      if (d.rank != x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "transpose: permutation length != input rank");
+      std::vector<uint32_t> dims(d.rank);
+      uint32_t seen = 0;
+      for (uint32_t i = 0; i < d.rank; ++i) {
+        if (d.v[i] >= d.rank || (seen >> d.v[i]) & 1u) return fail(g, B2VX_INVALID_ARG, "transpose: not a permutation");
+        seen |= 1u << d.v[i];
+        dims[i] = x.d.dims[d.v[i]];
+      }
+      return set_shape(g, n.out, dims, "transpose", false);
+    }
+    case B2VX_NODE_CONCAT: {
+      // vsi_nn_op_concat.c op_setup: all dimensions but `axis` agree; the axis extents add up
+      const uint32_t axis = n.p.concat_axis;
+      if (axis >= x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "concat: axis outside the input rank");
+      std::vector<uint32_t> dims(x.d.dims, x.d.dims + x.d.rank);
+      dims[axis] = 0;
+      for (uint32_t id : n.in) {
+        if (id == B2VX_NO_TENSOR) continue;
+        const TensorRec& t = g->tensors[id];
+        if (!t.has_shape || t.d.rank != x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "concat: input ranks differ");
+        for (uint32_t i = 0; i < x.d.rank; ++i)
+          if (i != axis && t.d.dims[i] != x.d.dims[i]) return fail(g, B2VX_SHAPE_MISMATCH, "concat: input shapes differ off the axis");
+        dims[axis] += t.d.dims[axis];
+      }
+      return set_shape(g, n.out, dims, "concat", false);
     }
     default:
       return set_shape(g, n.out, std::vector<uint32_t>(x.d.dims, x.d.dims + x.d.rank), "unary", false);
@@ -1070,6 +1112,146 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   return B2VX_OK;
 }
 
+// Element strides of a tensor's channels-last storage per logical (WHCN-order) dimension.
+void cl_strides(const TensorRec& t, long long s[4]) {
+  s[0] = s[1] = s[2] = s[3] = 0;
+  switch (t.d.rank) {
+    case 4: s[3] = static_cast<long long>(t.H) * t.W * t.Cp;   // fall through
+    case 3: s[0] = t.Cp; s[1] = static_cast<long long>(t.W) * t.Cp; s[2] = 1; break;
+    case 2: s[0] = 1; s[1] = t.Cp; break;
+    default: s[0] = 1; break;
+  }
+}
+
+RelayoutParams relayout_base(const TensorRec& shape_of) {
+  RelayoutParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.rank = static_cast<int>(shape_of.d.rank);
+  p.total = 1;
+  for (int k = 0; k < 4; ++k) {
+    p.dims[k] = k < p.rank ? static_cast<int>(shape_of.d.dims[k]) : 1;
+    p.idims[k] = 1;
+    p.total *= p.dims[k];
+  }
+  p.elem = static_cast<int>(dtype_size(shape_of.d.dtype));
+  return p;
+}
+
+// Reshape, Transpose, DataConvert: one pass from the input's storage to the output's.
+b2vx_status plan_move(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& x = g->tensors[n.in[0]];
+  TensorRec& y = g->tensors[n.out];
+  if (x.d.rank > 4 || y.d.rank > 4) return fail(g, B2VX_UNSUPPORTED, "reshape/transpose/dataconvert: rank above 4");
+  RelayoutParams p = relayout_base(y);
+  cl_strides(y, p.ostride);
+  const char* name = "reshape";
+  if (n.kind == B2VX_NODE_TRANSPOSE) {
+    name = "transpose";
+    long long xs[4];
+    cl_strides(x, xs);
+    for (uint32_t k = 0; k < y.d.rank; ++k) p.istride[k] = xs[n.p.dims.v[k]];
+  } else if (n.kind == B2VX_NODE_RESHAPE) {
+    p.reshape = 1;
+    cl_strides(x, p.istride);
+    for (uint32_t k = 0; k < x.d.rank; ++k) p.idims[k] = static_cast<int>(x.d.dims[k]);
+  } else {
+    name = "dataconvert";
+    cl_strides(x, p.istride);
+  }
+  if (n.kind != B2VX_NODE_DATACONVERT) {
+    if (x.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "reshape/transpose: input and output dtype differ");
+  } else if (is_q8(x.d.dtype) && is_q8(y.d.dtype)) {
+    // requantize: every input byte through dequantize + quantize, once, on the host
+    std::vector<uint8_t> lut(256);
+    const OutQuant oq = out_quant(y);
+    for (int i = 0; i < 256; ++i) {
+      const int q = x.d.dtype == B2VX_DT_INT8 ? static_cast<int>(static_cast<int8_t>(i)) : i;
+      lut[i] = static_cast<uint8_t>(host_requant((static_cast<float>(q) - static_cast<float>(x.zp())) * x.scale(), oq) & 0xFF);
+    }
+    uint8_t* dlut = nullptr;
+    const b2vx_status st = upload(g, lut, &dlut);
+    if (st != B2VX_OK) return st;
+    // same shape, one byte per element: the two storages have the same layout, so the whole storage goes
+    // through the table 16 bytes at a time
+    const void* xp8 = cl_in(x);
+    void* yp8 = y.d_cl;
+    const size_t nbytes = y.cl_bytes;
+    Step s8;
+    s8.info = make_info("requantize_lut", idx, 0, x.bytes() + y.bytes());
+    s8.fn = [=](cudaStream_t st2) { launch_lut_q(xp8, dlut, yp8, nbytes, st2); return cudaGetLastError(); };
+    g->steps.push_back(std::move(s8));
+    return B2VX_OK;
+  } else if (x.d.dtype == B2VX_DT_FLOAT32 && is_q8(y.d.dtype)) {
+    p.convert = 2;
+    p.out = out_quant(y);
+  } else if (is_q8(x.d.dtype) && y.d.dtype == B2VX_DT_FLOAT32) {
+    p.convert = 3;
+    p.in_scale = x.scale();
+    p.in_zp = x.zp();
+    p.in_signed = x.d.dtype == B2VX_DT_INT8;
+  } else if (x.d.dtype == y.d.dtype && x.d.dtype == B2VX_DT_FLOAT32) {
+    p.convert = 0;
+  } else {
+    return fail(g, B2VX_UNSUPPORTED, "dataconvert: supported are 8-bit <-> 8-bit, float32 <-> 8-bit and float32 -> float32");
+  }
+  const void* xp = cl_in(x);
+  void* yp = y.d_cl;
+  Step s;
+  s.info = make_info(name, idx, 0, x.bytes() + y.bytes());
+  s.fn = [=](cudaStream_t st2) { launch_relayout(xp, yp, p, st2); return cudaGetLastError(); };
+  g->steps.push_back(std::move(s));
+  return B2VX_OK;
+}
+
+// Concat: one pass per input into its slice of the output.
+b2vx_status plan_concat(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  TensorRec& y = g->tensors[n.out];
+  if (y.d.rank > 4) return fail(g, B2VX_UNSUPPORTED, "concat: rank above 4");
+  const uint32_t axis = n.p.concat_axis;
+  long long ys[4];
+  cl_strides(y, ys);
+  long long offset = 0;   // along the axis, in elements of that dimension
+  for (uint32_t id : n.in) {
+    if (id == B2VX_NO_TENSOR) continue;
+    TensorRec& t = g->tensors[id];
+    if (t.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "concat: input and output dtype differ");
+    const bool convert = is_q8(t.d.dtype) && (t.scale() != y.scale() || t.zp() != y.zp());
+    const void* tp = cl_in(t);
+    const size_t es = dtype_size(y.d.dtype);
+    uint8_t* yp = static_cast<uint8_t*>(y.d_cl) + static_cast<size_t>(offset * ys[axis]) * es;
+    Step s;
+    const bool channel_axis = (y.d.rank == 3 || y.d.rank == 4) && axis == 2;
+    if (channel_axis && es == 1 && !convert && t.C % 16 == 0 && offset % 16 == 0) {
+      const int in16 = t.C / 16, in_pitch16 = t.Cp / 16, out_pitch16 = y.Cp / 16;
+      const long long pixels = static_cast<long long>(t.N) * t.H * t.W;
+      s.info = make_info("concat_c16", idx, 0, 2 * t.bytes());
+      s.fn = [=](cudaStream_t st2) { launch_concat_c16(tp, in_pitch16, in16, yp, out_pitch16, 0, pixels, st2); return cudaGetLastError(); };
+    } else {
+      RelayoutParams p = relayout_base(t);
+      for (int k = 0; k < 4; ++k) p.ostride[k] = ys[k];
+      cl_strides(t, p.istride);
+      if (convert) {
+        std::vector<uint8_t> lut(256);
+        const OutQuant oq = out_quant(y);
+        for (int i = 0; i < 256; ++i) {
+          const int q = t.d.dtype == B2VX_DT_INT8 ? static_cast<int>(static_cast<int8_t>(i)) : i;
+          lut[i] = static_cast<uint8_t>(host_requant((static_cast<float>(q) - static_cast<float>(t.zp())) * t.scale(), oq) & 0xFF);
+        }
+        uint8_t* dlut = nullptr;
+        const b2vx_status st = upload(g, lut, &dlut);
+        if (st != B2VX_OK) return st;
+        p.convert = 1;
+        p.lut = dlut;
+      }
+      s.info = make_info("concat", idx, 0, 2 * t.bytes());
+      s.fn = [=](cudaStream_t st2) { launch_relayout(tp, yp, p, st2); return cudaGetLastError(); };
+    }
+    g->steps.push_back(std::move(s));
+    offset += t.d.dims[axis];
+  }
+  return B2VX_OK;
+}
+
 b2vx_status plan_relu(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   TensorRec& x = g->tensors[n.in[0]];
   TensorRec& y = g->tensors[n.out];
@@ -1147,6 +1329,7 @@ b2vx_status add_node(b2vx_graph* g, int32_t kind, uint32_t i0, uint32_t i1, uint
   if (proto) n = *proto;
   else std::memset(&n, 0, sizeof(n));
   n.kind = kind;
+  for (uint32_t& id : n.in) id = B2VX_NO_TENSOR;
   n.in[0] = i0; n.in[1] = i1; n.in[2] = i2; n.out = out;
   n.removed = false;
   n.fuse_add = -1;
@@ -1360,6 +1543,38 @@ b2vx_status b2vx_node_relu(b2vx_graph* g, uint32_t x, uint32_t y) {
 b2vx_status b2vx_node_relu6(b2vx_graph* g, uint32_t x, uint32_t y) {
   return add_node(g, B2VX_NODE_RELU6, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
 }
+b2vx_status b2vx_node_reshape(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_dims_desc* shape) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (!shape || shape->rank == 0 || shape->rank > B2VX_MAX_RANK) return fail(g, B2VX_INVALID_ARG, "reshape: bad shape");
+  NodeRec n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.dims = *shape;
+  return add_node(g, B2VX_NODE_RESHAPE, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+}
+b2vx_status b2vx_node_transpose(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_dims_desc* perm) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (!perm || perm->rank == 0 || perm->rank > B2VX_MAX_RANK) return fail(g, B2VX_INVALID_ARG, "transpose: bad permutation");
+  NodeRec n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.dims = *perm;
+  return add_node(g, B2VX_NODE_TRANSPOSE, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+}
+b2vx_status b2vx_node_concat(b2vx_graph* g, const uint32_t* inputs, uint32_t n_inputs, uint32_t axis, uint32_t y) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (!inputs || n_inputs == 0 || n_inputs > B2VX_MAX_NODE_INPUTS) return fail(g, B2VX_INVALID_ARG, "concat: 1 to 16 inputs");
+  for (uint32_t i = 0; i < n_inputs; ++i)
+    if (!valid_id(g, inputs[i])) return fail(g, B2VX_INVALID_ARG, "concat: bad tensor id");
+  NodeRec n;
+  std::memset(&n, 0, sizeof(n));
+  n.p.concat_axis = axis;
+  const b2vx_status st = add_node(g, B2VX_NODE_CONCAT, inputs[0], B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+  if (st != B2VX_OK) return st;
+  for (uint32_t i = 0; i < n_inputs; ++i) g->nodes.back().in[i] = inputs[i];
+  return B2VX_OK;
+}
+b2vx_status b2vx_node_dataconvert(b2vx_graph* g, uint32_t x, uint32_t y) {
+  return add_node(g, B2VX_NODE_DATACONVERT, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
+}
 b2vx_status b2vx_node_softmax(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_softmax_desc* d) {
   if (!g || !d) return B2VX_INVALID_ARG;
   NodeRec n;
@@ -1472,10 +1687,16 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
     if (n.removed) continue;
     g->tensors[n.in[0]].is_activation = true;
     g->tensors[n.out].is_activation = true;
+    if (n.kind == B2VX_NODE_CONCAT) {
+      for (uint32_t id : n.in)
+        if (id != B2VX_NO_TENSOR) g->tensors[id].is_activation = true;
+    }
     if (n.kind == B2VX_NODE_ADD) g->tensors[n.in[1]].is_activation = true;
-    // 32-bit integer activations exist only between Add nodes (the reference's platform sample adds INT32 vectors)
-    else if (g->tensors[n.in[0]].d.dtype == B2VX_DT_INT32 || g->tensors[n.out].d.dtype == B2VX_DT_INT32)
-      return fail(g, B2VX_UNSUPPORTED, "int32 activations are supported by Add only");
+    // 32-bit integer activations exist only around Add (the reference's platform sample adds INT32 vectors) and
+    // the nodes that move elements without looking at them
+    else if (n.kind != B2VX_NODE_RESHAPE && n.kind != B2VX_NODE_TRANSPOSE && n.kind != B2VX_NODE_CONCAT &&
+             (g->tensors[n.in[0]].d.dtype == B2VX_DT_INT32 || g->tensors[n.out].d.dtype == B2VX_DT_INT32))
+      return fail(g, B2VX_UNSUPPORTED, "int32 activations are supported by Add, Reshape, Transpose and Concat only");
   }
   for (TensorRec& t : g->tensors) {
     if (!t.is_activation) continue;
@@ -1516,6 +1737,10 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
       case B2VX_NODE_RELU:
       case B2VX_NODE_RELU6: st = plan_relu(g, idx, n); break;
       case B2VX_NODE_SOFTMAX: st = plan_softmax(g, idx, n); break;
+      case B2VX_NODE_RESHAPE:
+      case B2VX_NODE_TRANSPOSE:
+      case B2VX_NODE_DATACONVERT: st = plan_move(g, idx, n); break;
+      case B2VX_NODE_CONCAT: st = plan_concat(g, idx, n); break;
       default: return fail(g, B2VX_UNSUPPORTED, "unknown node kind");
     }
     if (st != B2VX_OK) return st;

@@ -118,6 +118,34 @@ void launch_add_broadcast(const void* a, int a_signed, float sa, int za, const i
 // y[i] = lut[x[i]] over n bytes: Relu/Relu6 between any two 8-bit quantizations,
 // the 256-entry device table being built on the host with the reference's float sequence
 void launch_lut_q(const void* x, const uint8_t* lut, void* y, size_t n, cudaStream_t s);
+
+// Data movement between storages (Reshape, Transpose, Concat pieces, DataConvert).  The iteration space is a
+// logical shape of up to four dimensions, dimension 0 fastest; each element goes from
+//   in  + sum(coord_in[k]  * istride[k])      to      out + sum(coord[k] * ostride[k])
+// (strides in elements) where coord_in = coord, or, with `reshape`, the coordinates of the same dense
+// linear index under the input's own shape idims.
+struct RelayoutParams {
+  int rank;
+  int dims[4];
+  long long ostride[4];
+  long long istride[4];
+  int reshape;
+  int idims[4];
+  long long total;
+  // 0: raw copy of `elem`-byte elements; 1: bytes through the 256-entry table `lut`;
+  // 2: float32 -> 8-bit with `out` (requant); 3: 8-bit (in_signed) -> float32 with in_scale / in_zp
+  int convert;
+  int elem;
+  const uint8_t* lut;
+  OutQuant out;
+  float in_scale;
+  int in_zp;
+  int in_signed;
+};
+void launch_relayout(const void* in, void* out, const RelayoutParams& p, cudaStream_t s);
+// Concat of 8-bit channels-last tensors along the channel axis when every extent is a multiple of 16:
+// per pixel, in16 16-byte pieces go to out + pixel * out_pitch16 + off16.
+void launch_concat_c16(const void* in, int in_pitch16, int in16, void* out, int out_pitch16, int off16, long long pixels, cudaStream_t s);
 // upper < 0: relu, else clamp to [0, upper]
 void launch_relu_f32(const float* x, float upper, float* y, size_t n, cudaStream_t s);
 

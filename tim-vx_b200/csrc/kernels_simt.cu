@@ -961,6 +961,61 @@ __global__ void add_i32_kernel(const int* __restrict__ a, float sa, int za, cons
   y[i] = requant_wide(__fadd_rn(fa, fb), out);
 }
 
+// Element-by-element move between two storages under a logical shape (see RelayoutParams): the general
+// form behind Reshape, Transpose, Concat and DataConvert.  One element per thread, consecutive threads on
+// consecutive positions of logical dimension 0.
+__global__ void relayout_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, RelayoutParams p) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= p.total) return;
+  long long rem = i, o = 0, src = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (k < p.rank) {
+      const long long c = rem % p.dims[k];
+      rem /= p.dims[k];
+      o += c * p.ostride[k];
+      if (!p.reshape) src += c * p.istride[k];
+    }
+  }
+  if (p.reshape) {
+    rem = i;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      {   // unused dimensions have extent 1
+        const long long c = rem % p.idims[k];
+        rem /= p.idims[k];
+        src += c * p.istride[k];
+      }
+    }
+  }
+  switch (p.convert) {
+    case 0:
+      if (p.elem == 1) out[o] = in[src];
+      else reinterpret_cast<uint32_t*>(out)[o] = reinterpret_cast<const uint32_t*>(in)[src];
+      break;
+    case 1:
+      out[o] = __ldg(p.lut + in[src]);
+      break;
+    case 2:
+      out[o] = static_cast<uint8_t>(requant(reinterpret_cast<const float*>(in)[src], p.out) & 0xFF);
+      break;
+    default: {
+      const int q = p.in_signed ? static_cast<int>(static_cast<int8_t>(in[src])) : static_cast<int>(in[src]);
+      reinterpret_cast<float*>(out)[o] = __fmul_rn(__fsub_rn(__int2float_rn(q), __int2float_rn(p.in_zp)), p.in_scale);
+      break;
+    }
+  }
+}
+
+__global__ void concat_c16_kernel(const uint4* __restrict__ in, int in_pitch16, int in16, uint4* __restrict__ out, int out_pitch16,
+                                  int off16, long long total) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= total) return;
+  const long long pix = i / in16;
+  const int j = static_cast<int>(i - pix * in16);
+  out[pix * out_pitch16 + off16 + j] = in[pix * in_pitch16 + j];
+}
+
 // Any 8-bit -> 8-bit pointwise map (Relu, Relu6 with arbitrary input/output
 // quantization) as a 256-entry table built on the host with the reference's
 // float sequence; 16 elements per thread.
@@ -1549,6 +1604,18 @@ void launch_add_i32(const int* a, float sa, int za, const int* b, float sb, int 
 void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStream_t s) {
   if (n == 0) return;
   add_f32_kernel<<<grid_for(static_cast<long long>(n), kThreads), kThreads, 0, s>>>(a, b, y, n);
+}
+
+void launch_relayout(const void* in, void* out, const RelayoutParams& p, cudaStream_t s) {
+  if (p.total <= 0) return;
+  relayout_kernel<<<grid_for(p.total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), p);
+}
+
+void launch_concat_c16(const void* in, int in_pitch16, int in16, void* out, int out_pitch16, int off16, long long pixels, cudaStream_t s) {
+  const long long total = pixels * in16;
+  if (total <= 0) return;
+  concat_c16_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>(static_cast<const uint4*>(in), in_pitch16, in16, static_cast<uint4*>(out),
+                                                                   out_pitch16, off16, total);
 }
 
 void launch_lut_q(const void* x, const uint8_t* lut, void* y, size_t n, cudaStream_t s) {

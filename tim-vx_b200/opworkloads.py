@@ -13,6 +13,8 @@ convolution sweep fuses):
   gemm:<m>:<n>:<k>                       FullyConnected: uint8 [k, m] (zero point 128, scale 0.02)
                                          x int8 per-channel [k, n] -> uint8 [n, m]
   add:<elements>                         quantized Add of two uint8 tensors with different scales
+  concat:<c1>:<c2>:<hw>                  Concat along the channel axis of two uint8 tensors [hw, hw, c, batch]
+  transpose:<c>:<hw>                     Transpose {1,2,0,3} of a uint8 [c, hw, hw, batch] tensor (NHWC image -> WHCN)
 
 build(spec, batch, graph, rng) adds the tensors and the node to `graph` (a pyb2vx.Graph on either
 the CUDA library or the CPU oracle library) and returns a dict describing the work of one pass.
@@ -32,8 +34,12 @@ def parse(spec):
         return kind, nums
     if kind == "add" and len(nums) == 1:
         return kind, nums
-    raise ValueError("workload must be conv:k:cin:cout:hw:stride, convadd:k:cin:cout:hw:stride, gemm:m:n:k or add:elements, "
-                     "got %r" % spec)
+    if kind == "concat" and len(nums) == 3:
+        return kind, nums
+    if kind == "transpose" and len(nums) == 2:
+        return kind, nums
+    raise ValueError("workload must be conv:k:cin:cout:hw:stride, convadd:k:cin:cout:hw:stride, gemm:m:n:k, add:elements, "
+                     "concat:c1:c2:hw or transpose:c:hw, got %r" % spec)
 
 
 def _u8(rng, shape):
@@ -84,6 +90,24 @@ def build(spec, batch, g, rng):
         return {"inputs": [(x, _u8(rng, (m, k)))], "outputs": [y], "ops": 2 * m * n * k,
                 "bytes": m * k + n * k + m * n + 4 * n, "bound": "tensor" if m >= 512 else "hbm", "units": m,
                 "name": "FullyConnected M=%d N=%d K=%d" % (m, n, k)}
+    if kind == "concat":
+        c1, c2, hw = v
+        a = g.tensor(B.DT_UINT8, [hw, hw, c1, batch], B.ATTR_INPUT, scale=0.05, zero_point=0)
+        b = g.tensor(B.DT_UINT8, [hw, hw, c2, batch], B.ATTR_INPUT, scale=0.05, zero_point=0)
+        y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.05, zero_point=0)
+        g.concat([a, b], y, 2)
+        n = batch * hw * hw * (c1 + c2)
+        return {"inputs": [(a, _u8(rng, (batch, c1, hw, hw))), (b, _u8(rng, (batch, c2, hw, hw)))], "outputs": [y], "ops": 0,
+                "bytes": 2 * n, "bound": "hbm", "units": n,
+                "name": "Concat of %d + %d channels on %dx%d, batch %d" % (c1, c2, hw, hw, batch)}
+    if kind == "transpose":
+        c, hw = v
+        x = g.tensor(B.DT_UINT8, [c, hw, hw, batch], B.ATTR_INPUT, scale=0.0078125, zero_point=128)
+        y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.0078125, zero_point=128)
+        g.transpose(x, y, [1, 2, 0, 3])
+        n = batch * hw * hw * c
+        return {"inputs": [(x, _u8(rng, (batch, hw, hw, c)))], "outputs": [y], "ops": 0, "bytes": 2 * n, "bound": "hbm", "units": n,
+                "name": "Transpose {1,2,0,3} of a %dx%dx%d image, batch %d" % (hw, hw, c, batch)}
     n = v[0]
     c = 256
     assert n % c == 0, "add: element count must be a multiple of 256"

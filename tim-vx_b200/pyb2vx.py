@@ -28,6 +28,7 @@ PAD_NONE, PAD_AUTO, PAD_VALID, PAD_SAME = -1, 0, 1, 2
 POOL_MAX, POOL_AVG, POOL_AVG_ANDROID = 0, 1, 3
 ROUND_CEILING, ROUND_FLOOR = 0, 1
 NODE_CONV2D, NODE_FC, NODE_POOL2D, NODE_ADD, NODE_RELU, NODE_RELU6, NODE_SOFTMAX = 1, 2, 3, 4, 5, 6, 7
+NODE_RESHAPE, NODE_TRANSPOSE, NODE_CONCAT, NODE_DATACONVERT = 8, 9, 10, 11
 STATUS_NAMES = ["OK", "INVALID_ARG", "UNSUPPORTED", "SHAPE_MISMATCH", "QUANT_MISMATCH", "OOM", "CUDA_ERROR",
                 "DEVICE_TIMEOUT", "BAD_STATE"]
 
@@ -56,6 +57,18 @@ class Pool2dDesc(C.Structure):
 
 class SoftmaxDesc(C.Structure):
     _fields_ = [("beta", C.c_float), ("axis", C.c_int32)]
+
+
+class DimsDesc(C.Structure):
+    _fields_ = [("rank", C.c_uint32), ("v", C.c_uint32 * 8)]
+
+    @classmethod
+    def of(cls, values):
+        d = cls()
+        d.rank = len(values)
+        for i, v in enumerate(values):
+            d.v[i] = int(v)
+        return d
 
 
 class KernelInfo(C.Structure):
@@ -92,6 +105,10 @@ def load(path):
         "b2vx_node_relu": (st, [vp, u32, u32]),
         "b2vx_node_relu6": (st, [vp, u32, u32]),
         "b2vx_node_softmax": (st, [vp, u32, u32, C.POINTER(SoftmaxDesc)]),
+        "b2vx_node_reshape": (st, [vp, u32, u32, C.POINTER(DimsDesc)]),
+        "b2vx_node_transpose": (st, [vp, u32, u32, C.POINTER(DimsDesc)]),
+        "b2vx_node_concat": (st, [vp, C.POINTER(C.c_uint32), u32, u32, u32]),
+        "b2vx_node_dataconvert": (st, [vp, u32, u32]),
         "b2vx_graph_compile": (st, [vp]),
         "b2vx_graph_run": (st, [vp]),
         "b2vx_graph_run_async": (st, [vp]),
@@ -219,6 +236,21 @@ class Graph:
         d = SoftmaxDesc(beta, axis)
         self._check(self.lib.b2vx_node_softmax(self.g, x, y, C.byref(d)))
 
+    def reshape(self, x, y, shape):
+        d = DimsDesc.of(shape)
+        self._check(self.lib.b2vx_node_reshape(self.g, x, y, C.byref(d)))
+
+    def transpose(self, x, y, perm):
+        d = DimsDesc.of(perm)
+        self._check(self.lib.b2vx_node_transpose(self.g, x, y, C.byref(d)))
+
+    def concat(self, inputs, y, axis):
+        arr = (C.c_uint32 * len(inputs))(*inputs)
+        self._check(self.lib.b2vx_node_concat(self.g, arr, len(inputs), axis, y))
+
+    def dataconvert(self, x, y):
+        self._check(self.lib.b2vx_node_dataconvert(self.g, x, y))
+
     def compile(self):
         self._check(self.lib.b2vx_graph_compile(self.g))
 
@@ -325,6 +357,14 @@ def graph_from_case(lib, case, device=0):
             g.relu6(i[0], o)
         elif k == NODE_SOFTMAX:
             g.softmax(i[0], o, beta=n["beta"], axis=n["axis"])
+        elif k == NODE_RESHAPE:
+            g.reshape(i[0], o, n["dims"])
+        elif k == NODE_TRANSPOSE:
+            g.transpose(i[0], o, n["dims"])
+        elif k == NODE_CONCAT:
+            g.concat([v for v in i if v is not None], o, n["axis"])
+        elif k == NODE_DATACONVERT:
+            g.dataconvert(i[0], o)
         else:
             raise ValueError("unknown node kind %r" % k)
     expects = [(ids[e["tensor"]], unpack(e["data"], e["dtype"]), e["tol"]) for e in case["expect"]]
