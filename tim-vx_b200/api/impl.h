@@ -141,6 +141,9 @@ class OpImpl {
     uint32_t concat_axis;
   } desc_;
   std::vector<uint8_t> blob_;   // ops::NBG: the serialised graph this op stands for
+  // Conv2d / Pool2d declared with a front-end layout (CWHN activations, IcWHOc / OcIcWH / IcOcWH kernels):
+  // such an op is not executed as it stands; tim::transform::LayoutInference rewrites the graph.
+  bool foreign_layout_ = false;
 };
 
 // Node kind of ops::NBG inside this layer; it never reaches the C ABI: Compile expands the op into the

@@ -513,6 +513,10 @@ bool GraphImpl::EmitNodes() {
     auto out = [&](size_t i) -> uint32_t {
       return i < p->outputs_tensor_.size() && p->outputs_tensor_[i] ? p->outputs_tensor_[i]->GetId() : B2VX_NO_TENSOR;
     };
+    if (p->foreign_layout_) {
+      TVX_LOGE("an op declared with a CWHN / front-end kernel layout is not executed as it stands: run tim::transform::LayoutInference on the graph first");
+      return false;
+    }
     b2vx_status st = B2VX_UNSUPPORTED;
     switch (p->kind_) {
       case B2VX_NODE_CONV2D: st = b2vx_node_conv2d(graph_, in(0), in(1), in(2), out(0), &p->desc_.conv2d); break;
@@ -922,10 +926,8 @@ Conv2d::Conv2d(Graph* graph, int32_t weights, PadType padding, const std::array<
   }
   for (int i = 0; i < 4; ++i) d.pad[i] = pad_[i];
   d.multiplier = multiplier_;
-  if (input_layout != DataLayout::WHCN && input_layout != DataLayout::ANY)
-    TVX_LOGW("Conv2d: only WHCN input layout is executed; run layout inference first");
-  if (kernel_layout != DataLayout::WHIcOc && kernel_layout != DataLayout::ANY)
-    TVX_LOGW("Conv2d: only WHIcOc kernel layout is executed");
+  impl_->foreign_layout_ = (input_layout != DataLayout::WHCN && input_layout != DataLayout::ANY) ||
+                           (kernel_layout != DataLayout::WHIcOc && kernel_layout != DataLayout::ANY);
 }
 
 std::shared_ptr<Operation> Conv2d::Clone(std::shared_ptr<Graph>& graph) const {
@@ -986,6 +988,7 @@ Pool2d::Pool2d(Graph* graph, PoolType type, const std::array<uint32_t, 2>& input
 }
 
 void Pool2d::Init() {
+  impl_->foreign_layout_ = impl_->layout_ != DataLayout::WHCN && impl_->layout_ != DataLayout::ANY;
   b2vx_pool2d_desc& d = impl_->desc_.pool2d;
   d.type = static_cast<int32_t>(type_);
   d.pad_type = static_cast<int32_t>(padding_);
@@ -998,6 +1001,7 @@ void Pool2d::Init() {
 }
 
 std::shared_ptr<Operation> Pool2d::Clone(std::shared_ptr<Graph>& graph) const {
+  if (padding_ != PadType::AUTO) return graph->CreateOperation<Pool2d>(type_, padding_, ksize_, stride_, round_type_, impl_->layout_);
   return graph->CreateOperation<Pool2d>(type_, pad_, ksize_, stride_, round_type_, impl_->layout_);
 }
 

@@ -62,6 +62,7 @@ struct TensorRec {
   size_t cl_bytes = 0, io_bytes = 0;
   bool is_activation = false;
   bool cl_used = false;        // some kernel reads the channels-last copy (decides whether a graph input is converted)
+  bool io_direct = false;      // a graph output whose producer writes the WHCN copy itself (no conversion at the end)
 
   size_t elems() const {
     size_t n = 1;
@@ -1123,6 +1124,28 @@ void cl_strides(const TensorRec& t, long long s[4]) {
   }
 }
 
+// Element strides of the dense WHCN-order copy (dimension 0 fastest).
+void dense_strides(const TensorRec& t, long long s[4]) {
+  long long acc = 1;
+  for (uint32_t k = 0; k < 4; ++k) {
+    s[k] = k < t.d.rank ? acc : 0;
+    if (k < t.d.rank) acc *= t.d.dims[k];
+  }
+}
+
+// Lists the iteration dimensions by increasing output stride: consecutive threads then write neighbouring
+// elements.  `with_istride`: the input strides belong to the iteration dimensions and move with them.
+void sort_by_output_stride(RelayoutParams& p, bool with_istride) {
+  for (int a = 0; a < p.rank; ++a)
+    for (int b = a + 1; b < p.rank; ++b)
+      if (p.ostride[b] < p.ostride[a] || (p.ostride[b] == p.ostride[a] && p.dims[b] < p.dims[a])) {
+        std::swap(p.dims[a], p.dims[b]);
+        std::swap(p.ostride[a], p.ostride[b]);
+        std::swap(p.lstride[a], p.lstride[b]);
+        if (with_istride) std::swap(p.istride[a], p.istride[b]);
+      }
+}
+
 RelayoutParams relayout_base(const TensorRec& shape_of) {
   RelayoutParams p;
   std::memset(&p, 0, sizeof(p));
@@ -1143,21 +1166,34 @@ b2vx_status plan_move(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   TensorRec& y = g->tensors[n.out];
   if (x.d.rank > 4 || y.d.rank > 4) return fail(g, B2VX_UNSUPPORTED, "reshape/transpose/dataconvert: rank above 4");
   RelayoutParams p = relayout_base(y);
-  cl_strides(y, p.ostride);
+  // A graph input is read from its WHCN copy as the caller wrote it, and a graph output that nothing else
+  // reads is written in WHCN order, which saves the layout conversions before and after.
+  const bool x_dense = (x.d.attr & (B2VX_ATTR_INPUT | B2VX_ATTR_VARIABLE)) != 0 && x.d_io != nullptr && x.d_io != x.d_cl;
+  int consumers = 0;
+  for (const NodeRec& m : g->nodes) {
+    if (m.removed) continue;
+    for (uint32_t id : m.in) consumers += id == n.out;
+  }
+  const bool y_dense = (y.d.attr & B2VX_ATTR_OUTPUT) != 0 && consumers == 0 && y.d_io != nullptr && y.d_io != y.d_cl;
+  long long xs[4];
+  if (x_dense) dense_strides(x, xs);
+  else cl_strides(x, xs);
+  if (y_dense) dense_strides(y, p.ostride);
+  else cl_strides(y, p.ostride);
+  dense_strides(y, p.lstride);
   const char* name = "reshape";
   if (n.kind == B2VX_NODE_TRANSPOSE) {
     name = "transpose";
-    long long xs[4];
-    cl_strides(x, xs);
     for (uint32_t k = 0; k < y.d.rank; ++k) p.istride[k] = xs[n.p.dims.v[k]];
   } else if (n.kind == B2VX_NODE_RESHAPE) {
     p.reshape = 1;
-    cl_strides(x, p.istride);
+    for (int k = 0; k < 4; ++k) p.istride[k] = xs[k];
     for (uint32_t k = 0; k < x.d.rank; ++k) p.idims[k] = static_cast<int>(x.d.dims[k]);
   } else {
     name = "dataconvert";
-    cl_strides(x, p.istride);
+    for (int k = 0; k < 4; ++k) p.istride[k] = xs[k];
   }
+  sort_by_output_stride(p, !p.reshape);
   if (n.kind != B2VX_NODE_DATACONVERT) {
     if (x.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "reshape/transpose: input and output dtype differ");
   } else if (is_q8(x.d.dtype) && is_q8(y.d.dtype)) {
@@ -1194,8 +1230,9 @@ b2vx_status plan_move(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   } else {
     return fail(g, B2VX_UNSUPPORTED, "dataconvert: supported are 8-bit <-> 8-bit, float32 <-> 8-bit and float32 -> float32");
   }
-  const void* xp = cl_in(x);
-  void* yp = y.d_cl;
+  const void* xp = x_dense ? x.d_io : cl_in(x);
+  void* yp = y_dense ? y.d_io : y.d_cl;
+  if (y_dense) y.io_direct = true;
   Step s;
   s.info = make_info(name, idx, 0, x.bytes() + y.bytes());
   s.fn = [=](cudaStream_t st2) { launch_relayout(xp, yp, p, st2); return cudaGetLastError(); };
@@ -1230,6 +1267,7 @@ b2vx_status plan_concat(b2vx_graph* g, uint32_t idx, NodeRec& n) {
       RelayoutParams p = relayout_base(t);
       for (int k = 0; k < 4; ++k) p.ostride[k] = ys[k];
       cl_strides(t, p.istride);
+      sort_by_output_stride(p, true);
       if (convert) {
         std::vector<uint8_t> lut(256);
         const OutQuant oq = out_quant(y);
@@ -1764,7 +1802,7 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
   for (size_t i = 0; i < g->tensors.size(); ++i) {
     TensorRec& t = g->tensors[i];
     if (!t.is_activation || !(t.d.attr & B2VX_ATTR_OUTPUT)) continue;
-    if (t.d_io == t.d_cl) continue;
+    if (t.d_io == t.d_cl || t.io_direct) continue;
     const void* src = t.d_cl;
     void* dst = t.d_io;
     const int N = t.N, C = t.C, H = t.H, W = t.W, Cp = t.Cp, el = static_cast<int>(dtype_size(t.d.dtype));

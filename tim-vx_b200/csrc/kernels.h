@@ -120,7 +120,8 @@ void launch_add_broadcast(const void* a, int a_signed, float sa, int za, const i
 void launch_lut_q(const void* x, const uint8_t* lut, void* y, size_t n, cudaStream_t s);
 
 // Data movement between storages (Reshape, Transpose, Concat pieces, DataConvert).  The iteration space is a
-// logical shape of up to four dimensions, dimension 0 fastest; each element goes from
+// logical shape of up to four dimensions, dimension 0 fastest (the host lists the dimensions by increasing
+// output stride, so that consecutive threads write neighbouring bytes); each element goes from
 //   in  + sum(coord_in[k]  * istride[k])      to      out + sum(coord[k] * ostride[k])
 // (strides in elements) where coord_in = coord, or, with `reshape`, the coordinates of the same dense
 // linear index under the input's own shape idims.
@@ -130,6 +131,7 @@ struct RelayoutParams {
   long long ostride[4];
   long long istride[4];
   int reshape;
+  long long lstride[4];   // reshape: dense (WHCN-order) strides of the iteration dimensions, to form the linear index
   int idims[4];
   long long total;
   // 0: raw copy of `elem`-byte elements; 1: bytes through the 256-entry table `lut`;

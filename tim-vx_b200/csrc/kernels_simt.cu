@@ -967,25 +967,24 @@ __global__ void add_i32_kernel(const int* __restrict__ a, float sa, int za, cons
 __global__ void relayout_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, RelayoutParams p) {
   const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (i >= p.total) return;
-  long long rem = i, o = 0, src = 0;
+  long long rem = i, o = 0, src = 0, lin = 0;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     if (k < p.rank) {
       const long long c = rem % p.dims[k];
       rem /= p.dims[k];
       o += c * p.ostride[k];
-      if (!p.reshape) src += c * p.istride[k];
+      src += c * p.istride[k];
+      lin += c * p.lstride[k];
     }
   }
   if (p.reshape) {
-    rem = i;
+    src = 0;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      {   // unused dimensions have extent 1
-        const long long c = rem % p.idims[k];
-        rem /= p.idims[k];
-        src += c * p.istride[k];
-      }
+    for (int k = 0; k < 4; ++k) {   // unused dimensions have extent 1
+      const long long c = lin % p.idims[k];
+      lin /= p.idims[k];
+      src += c * p.istride[k];
     }
   }
   switch (p.convert) {
