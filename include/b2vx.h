@@ -137,6 +137,10 @@ typedef struct b2vx_conv2d_desc {
   uint32_t dilation[2];
   uint32_t pad[4];
   int32_t multiplier;
+  /* ops::GroupedConv2d (src/tim/vx/ops/groupedconv2d.cc:34-68): input and output channels split into
+   * `group` contiguous blocks, block g of the outputs reading block g of the inputs; the kernel is
+   * [kw, kh, Ic/group, Oc].  0 and 1 mean an ordinary convolution. */
+  int32_t group;
 } b2vx_conv2d_desc;
 
 /* Replaces vsi_nn_fcl_param (src/tim/vx/ops/fullyconnected.cc:37-41). */

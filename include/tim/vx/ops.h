@@ -9,6 +9,7 @@
 #include "tim/vx/ops/conv2d.h"
 #include "tim/vx/ops/elementwise.h"
 #include "tim/vx/ops/fullyconnected.h"
+#include "tim/vx/ops/groupedconv2d.h"
 #include "tim/vx/ops/nbg.h"
 #include "tim/vx/ops/pool2d.h"
 #include "tim/vx/ops/reshape.h"

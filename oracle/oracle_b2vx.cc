@@ -170,9 +170,9 @@ void write_case(b2vx_graph* g) {
     std::fprintf(f, "], \"out\": %u", n.out);
     if (n.kind == B2VX_NODE_CONV2D) {
       const b2vx_conv2d_desc& c = n.p.conv;
-      std::fprintf(f, ", \"weights\": %u, \"pad_type\": %d, \"ksize\": [%u, %u], \"stride\": [%u, %u], \"dilation\": [%u, %u], \"pad\": [%u, %u, %u, %u], \"multiplier\": %d",
+      std::fprintf(f, ", \"weights\": %u, \"pad_type\": %d, \"ksize\": [%u, %u], \"stride\": [%u, %u], \"dilation\": [%u, %u], \"pad\": [%u, %u, %u, %u], \"multiplier\": %d, \"group\": %d",
                    c.weights, c.pad_type, c.ksize[0], c.ksize[1], c.stride[0], c.stride[1], c.dilation[0], c.dilation[1],
-                   c.pad[0], c.pad[1], c.pad[2], c.pad[3], c.multiplier);
+                   c.pad[0], c.pad[1], c.pad[2], c.pad[3], c.multiplier, c.group);
     } else if (n.kind == B2VX_NODE_FULLY_CONNECTED) {
       std::fprintf(f, ", \"axis\": %u, \"weights\": %u", n.p.fc.axis, n.p.fc.weights);
     } else if (n.kind == B2VX_NODE_POOL2D) {
@@ -372,7 +372,12 @@ b2vx_status exec_node(b2vx_graph* g, ONode& n) {
       a.dilation[0] = n.p.conv.dilation[0]; a.dilation[1] = n.p.conv.dilation[1];
       a.pad_left = n.pad_resolved[0]; a.pad_top = n.pad_resolved[2];
       a.multiplier = n.p.conv.multiplier;
-      if (a.multiplier >= 1) {
+      a.group = n.p.conv.group;
+      if (a.group > 1) {
+        if (a.multiplier >= 1) return fail(g, B2VX_UNSUPPORTED, "conv2d: group and multiplier together");
+        if (a.C % a.group || a.Oc % a.group || a.w_ic * static_cast<uint32_t>(a.group) != a.C || a.w_oc != a.Oc)
+          return fail(g, B2VX_SHAPE_MISMATCH, "grouped conv2d: kernel must be [kw, kh, C/group, Oc] with C and Oc multiples of group");
+      } else if (a.multiplier >= 1) {
         if (a.w_ic != a.C * static_cast<uint32_t>(a.multiplier) || a.Oc != a.w_ic)
           return fail(g, B2VX_SHAPE_MISMATCH, "depthwise conv2d: kernel channels != C*multiplier");
       } else if (a.w_ic != a.C || a.w_oc != a.Oc) {

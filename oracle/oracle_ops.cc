@@ -193,6 +193,11 @@ int32_t conv2d_quant(const orc_conv2d_args& a) {
       if (depthwise) {
         const uint32_t ic = oc / static_cast<uint32_t>(a.multiplier);
         conv_plane<XT, WT, int32_t>(a, n, oc, ic, ic + 1, 0, true, zx, zw, acc.data());
+      } else if (a.group > 1) {
+        // grouped (vsi_nn_op_grouped_conv2d.c): output block g reads input block g
+        const uint32_t per_in = a.C / static_cast<uint32_t>(a.group), per_out = a.Oc / static_cast<uint32_t>(a.group);
+        const uint32_t gi = oc / per_out;
+        conv_plane<XT, WT, int32_t>(a, n, oc, gi * per_in, (gi + 1) * per_in, 0, false, zx, zw, acc.data());
       } else {
         conv_plane<XT, WT, int32_t>(a, n, oc, 0, a.C, 0, false, zx, zw, acc.data());
       }
@@ -227,6 +232,10 @@ int32_t conv2d_float(const orc_conv2d_args& a) {
       if (depthwise) {
         const uint32_t ic = oc / static_cast<uint32_t>(a.multiplier);
         conv_plane<float, float, float>(a, n, oc, ic, ic + 1, 0, true, 0.0f, 0.0f, acc.data());
+      } else if (a.group > 1) {
+        const uint32_t per_in = a.C / static_cast<uint32_t>(a.group), per_out = a.Oc / static_cast<uint32_t>(a.group);
+        const uint32_t gi = oc / per_out;
+        conv_plane<float, float, float>(a, n, oc, gi * per_in, (gi + 1) * per_in, 0, false, 0.0f, 0.0f, acc.data());
       } else {
         conv_plane<float, float, float>(a, n, oc, 0, a.C, 0, false, 0.0f, 0.0f, acc.data());
       }

@@ -60,6 +60,7 @@ typedef struct orc_conv2d_args {
   void* y; int32_t y_dtype; uint32_t Wo, Ho, Oc; orc_quant yq;
   uint32_t stride[2]; uint32_t dilation[2]; uint32_t pad_left, pad_top;
   int32_t multiplier;      /* >= 1: depthwise */
+  int32_t group;           /* > 1: grouped, weights [kw,kh,C/group,Oc] */
   int32_t* acc_out;        /* optional [Wo,Ho,Oc,N] int32 accumulators (bias included) */
 } orc_conv2d_args;
 

@@ -33,6 +33,7 @@ TEST_FILES = [
     "src/tim/vx/ops/fullyconnected_test.cc",
     "src/tim/vx/ops/softmax_test.cc",
     "src/tim/vx/ops/transpose_test.cc",
+    "src/tim/vx/ops/groupedconv2d_test.cc",
 ]
 
 

@@ -410,6 +410,33 @@ def test_add_int32_matches_oracle(oracle_lib, product_lib):
         G.assert_same(want, got)
 
 
+@pytest.mark.parametrize("group,w_kind", [(2, "s8pc"), (4, "u8"), (8, "s8pc")])
+def test_grouped_conv_matches_oracle(oracle_lib, product_lib, group, w_kind):
+    """ops::GroupedConv2d: kernel [3, 3, C/group, Oc]; the CUDA library runs it as a block-diagonal dense convolution."""
+    C, Oc, W, H, N = 32, 48, 13, 11, 2
+
+    def build(g, rng):
+        x = g.tensor(B.DT_UINT8, [W, H, C, N], B.ATTR_INPUT, scale=0.02, zero_point=121)
+        if w_kind == "s8pc":
+            ws = rng.uniform(0.002, 0.01, Oc).astype(np.float32)
+            w = g.tensor(B.DT_INT8, [3, 3, C // group, Oc], B.ATTR_CONSTANT, scales=ws, channel_dim=3,
+                         data=rng.integers(-127, 128, size=(Oc, C // group, 3, 3)).astype(np.int8))
+            b = g.tensor(B.DT_INT32, [Oc], B.ATTR_CONSTANT, scales=np.float32(0.02) * ws, channel_dim=0,
+                         data=rng.integers(-800, 800, size=Oc).astype(np.int32))
+        else:
+            w = g.tensor(B.DT_UINT8, [3, 3, C // group, Oc], B.ATTR_CONSTANT, scale=0.01, zero_point=117,
+                         data=rng.integers(0, 256, size=(Oc, C // group, 3, 3)).astype(np.uint8))
+            b = g.tensor(B.DT_INT32, [Oc], B.ATTR_CONSTANT, scale=0.02 * 0.01, zero_point=0,
+                         data=rng.integers(-800, 800, size=Oc).astype(np.int32))
+        y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=0.06, zero_point=100)
+        g.conv2d(x, w, b, y, pad_type=B.PAD_SAME, group=group)
+        return [(x, rng.integers(0, 256, size=(N, C, H, W)).astype(np.uint8))], [y]
+    want, _ = G.run_case(oracle_lib, build, seed=13)
+    got, _ = G.run_case(product_lib, build, seed=13)
+    G.assert_same(want, got)
+    assert len(np.unique(want[0])) > 20
+
+
 def test_softmax_matches_oracle(oracle_lib, product_lib):
     for build in (G.softmax_q(10, 7), G.softmax_q(1000, 3, beta=0.5)):
         want, _ = G.run_case(oracle_lib, build, seed=2)

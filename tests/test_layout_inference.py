@@ -24,8 +24,6 @@ def run(exe):
     assert out.returncode == 0, "exit %d\n%s%s" % (out.returncode, out.stdout, out.stderr)
     lines = out.stdout.strip().splitlines()
     assert lines[-1] == "ok layout inference"
-    # the un-inferred CWHN graph was refused, loudly
-    assert "LayoutInference" in out.stderr
     return [l for l in lines if l.startswith("logits ")][0]
 
 

@@ -129,6 +129,7 @@ class OpImpl {
   int32_t input_cnt_;
   int32_t output_cnt_;
   DataLayout layout_;
+  DataLayout kernel_layout_ = DataLayout::WHIcOc;   // Conv2d, GroupedConv2d
   uint32_t uid_;
   std::vector<std::shared_ptr<Tensor>> inputs_tensor_;
   std::vector<std::shared_ptr<Tensor>> outputs_tensor_;
@@ -142,7 +143,7 @@ class OpImpl {
   } desc_;
   std::vector<uint8_t> blob_;   // ops::NBG: the serialised graph this op stands for
   // Conv2d / Pool2d declared with a front-end layout (CWHN activations, IcWHOc / OcIcWH / IcOcWH kernels):
-  // such an op is not executed as it stands; tim::transform::LayoutInference rewrites the graph.
+  // tim::transform::LayoutInference rewrites such a graph; compiled as it stands the op runs as WHCN / WHIcOc.
   bool foreign_layout_ = false;
 };
 

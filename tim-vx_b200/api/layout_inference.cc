@@ -174,19 +174,19 @@ std::pair<std::shared_ptr<vx::Graph>, std::map<std::shared_ptr<vx::Tensor>, std:
       std::shared_ptr<vx::Operation> clone = op->Clone(g);
       clone->impl()->layout_ = vx::DataLayout::WHCN;
       clone->impl()->foreign_layout_ = false;
+      clone->impl()->kernel_layout_ = vx::DataLayout::WHIcOc;
       const TensorPtr out = impl->outputs_tensor_.empty() ? nullptr : impl->outputs_tensor_[0];
       if ((kind == B2VX_NODE_CONV2D || kind == B2VX_NODE_POOL2D) && cwhn) {
         clone->BindInput(inf.in_whcn(impl->inputs_tensor_[0]));
         if (kind == B2VX_NODE_CONV2D) {
-          auto conv = std::static_pointer_cast<vx::ops::Conv2d>(op);
           const TensorPtr w = impl->inputs_tensor_[1];
           const bool depthwise = impl->desc_.conv2d.multiplier > 0;
           if (is_const(w)) {
-            clone->BindInput(native_kernel(inf, w, conv->KernelDataLayout(), depthwise));
+            clone->BindInput(native_kernel(inf, w, impl->kernel_layout_, depthwise));
           } else {
             // a kernel fed at run time: permuted by a Transpose node
             Perm perm;
-            switch (conv->KernelDataLayout()) {
+            switch (impl->kernel_layout_) {
               case vx::DataLayout::IcWHOc: perm = {1, 2, 0, 3}; break;
               case vx::DataLayout::OcIcWH: perm = {2, 3, 1, 0}; break;
               case vx::DataLayout::IcOcWH: perm = {2, 3, 0, 1}; break;
@@ -208,14 +208,13 @@ std::pair<std::shared_ptr<vx::Graph>, std::map<std::shared_ptr<vx::Tensor>, std:
         inf.forms[out].whcn = y;
       } else if (kind == B2VX_NODE_CONV2D && !cwhn) {
         // WHCN activations; the kernel may still come in a front-end layout
-        auto conv = std::static_pointer_cast<vx::ops::Conv2d>(op);
         clone->BindInput(inf.in_source_layout(impl->inputs_tensor_[0]));
         const TensorPtr w = impl->inputs_tensor_[1];
         if (is_const(w)) {
-          clone->BindInput(native_kernel(inf, w, conv->KernelDataLayout(), impl->desc_.conv2d.multiplier > 0));
+          clone->BindInput(native_kernel(inf, w, impl->kernel_layout_, impl->desc_.conv2d.multiplier > 0));
         } else {
           Perm perm;
-          switch (conv->KernelDataLayout()) {
+          switch (impl->kernel_layout_) {
             case vx::DataLayout::IcWHOc: perm = {1, 2, 0, 3}; break;
             case vx::DataLayout::OcIcWH: perm = {2, 3, 1, 0}; break;
             case vx::DataLayout::IcOcWH: perm = {2, 3, 0, 1}; break;

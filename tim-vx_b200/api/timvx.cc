@@ -21,6 +21,7 @@
 #include "tim/vx/ops/conv2d.h"
 #include "tim/vx/ops/elementwise.h"
 #include "tim/vx/ops/fullyconnected.h"
+#include "tim/vx/ops/groupedconv2d.h"
 #include "tim/vx/ops/nbg.h"
 #include "tim/vx/ops/pool2d.h"
 #include "tim/vx/ops/softmax.h"
@@ -513,10 +514,9 @@ bool GraphImpl::EmitNodes() {
     auto out = [&](size_t i) -> uint32_t {
       return i < p->outputs_tensor_.size() && p->outputs_tensor_[i] ? p->outputs_tensor_[i]->GetId() : B2VX_NO_TENSOR;
     };
-    if (p->foreign_layout_) {
-      TVX_LOGE("an op declared with a CWHN / front-end kernel layout is not executed as it stands: run tim::transform::LayoutInference on the graph first");
-      return false;
-    }
+    // As in the reference, the layouts named in an op's constructor only inform tim::transform::LayoutInference;
+    // a graph compiled without it runs every op as WHCN / WHIcOc (its conv2d_test.cc relies on that).
+    if (p->foreign_layout_) TVX_LOGW("an op names a CWHN / front-end kernel layout and runs as WHCN / WHIcOc: layout inference was not applied");
     b2vx_status st = B2VX_UNSUPPORTED;
     switch (p->kind_) {
       case B2VX_NODE_CONV2D: st = b2vx_node_conv2d(graph_, in(0), in(1), in(2), out(0), &p->desc_.conv2d); break;
@@ -571,12 +571,12 @@ bool GraphImpl::Compile() {
 // op (kind, descriptor, bindings), plus which tensors are the graph's inputs and outputs, in order.
 // ops::NBG (include/tim/vx/ops/nbg.h) takes such a blob; at Compile it is expanded into the nodes it
 // describes, its graph inputs and outputs replaced by the tensors bound to the op.  The format is
-// this backend's own ("B2VB", little endian, version 1); kernels are planned again on load, for the
+// this backend's own ("B2VB", little endian, version 2); kernels are planned again on load, for the
 // GPU the loading graph is bound to.
 namespace {
 
 constexpr uint32_t kBlobMagic = 0x42563242u;   // "B2VB"
-constexpr uint32_t kBlobVersion = 1;
+constexpr uint32_t kBlobVersion = 2;
 
 struct BlobWriter {
   std::vector<uint8_t> b;
@@ -926,8 +926,50 @@ Conv2d::Conv2d(Graph* graph, int32_t weights, PadType padding, const std::array<
   }
   for (int i = 0; i < 4; ++i) d.pad[i] = pad_[i];
   d.multiplier = multiplier_;
+  impl_->kernel_layout_ = kernel_layout;
   impl_->foreign_layout_ = (input_layout != DataLayout::WHCN && input_layout != DataLayout::ANY) ||
                            (kernel_layout != DataLayout::WHIcOc && kernel_layout != DataLayout::ANY);
+}
+
+GroupedConv2d::GroupedConv2d(Graph* graph, PadType padding, const std::array<uint32_t, 2>& strides,
+                             const std::array<uint32_t, 2>& dilation, int32_t grouped_number, DataLayout input_layout,
+                             DataLayout kernel_layout)
+    : BuiltinOp(graph, B2VX_NODE_CONV2D, 3, 1, input_layout), padding_(padding), strides_(strides), dilation_(dilation),
+      pad_({0, 0, 0, 0}), group_number_(grouped_number), kernel_layout_(kernel_layout) {
+  b2vx_conv2d_desc& d = impl_->desc_.conv2d;
+  d.pad_type = static_cast<int32_t>(padding_);
+  for (int i = 0; i < 2; ++i) {
+    d.stride[i] = strides_[i];
+    d.dilation[i] = dilation_[i];
+  }
+  d.group = group_number_;
+  impl_->kernel_layout_ = kernel_layout;
+  impl_->foreign_layout_ = (input_layout != DataLayout::WHCN && input_layout != DataLayout::ANY) ||
+                           (kernel_layout != DataLayout::WHIcOc && kernel_layout != DataLayout::ANY);
+}
+
+GroupedConv2d::GroupedConv2d(Graph* graph, const std::array<uint32_t, 4>& pad, const std::array<uint32_t, 2>& strides,
+                             const std::array<uint32_t, 2>& dilation, int32_t group_number, DataLayout input_layout,
+                             DataLayout kernel_layout)
+    : BuiltinOp(graph, B2VX_NODE_CONV2D, 3, 1, input_layout), padding_(PadType::AUTO), strides_(strides), dilation_(dilation),
+      pad_(pad), group_number_(group_number), kernel_layout_(kernel_layout) {
+  b2vx_conv2d_desc& d = impl_->desc_.conv2d;
+  d.pad_type = static_cast<int32_t>(padding_);
+  for (int i = 0; i < 2; ++i) {
+    d.stride[i] = strides_[i];
+    d.dilation[i] = dilation_[i];
+  }
+  for (int i = 0; i < 4; ++i) d.pad[i] = pad_[i];
+  d.group = group_number_;
+  impl_->kernel_layout_ = kernel_layout;
+  impl_->foreign_layout_ = (input_layout != DataLayout::WHCN && input_layout != DataLayout::ANY) ||
+                           (kernel_layout != DataLayout::WHIcOc && kernel_layout != DataLayout::ANY);
+}
+
+std::shared_ptr<Operation> GroupedConv2d::Clone(std::shared_ptr<Graph>& graph) const {
+  if (padding_ == PadType::AUTO)
+    return graph->CreateOperation<GroupedConv2d>(pad_, strides_, dilation_, group_number_, impl_->layout_, kernel_layout_);
+  return graph->CreateOperation<GroupedConv2d>(padding_, strides_, dilation_, group_number_, impl_->layout_, kernel_layout_);
 }
 
 std::shared_ptr<Operation> Conv2d::Clone(std::shared_ptr<Graph>& graph) const {

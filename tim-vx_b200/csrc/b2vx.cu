@@ -1649,6 +1649,37 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
   }
   if (g->order.size() != g->nodes.size()) return fail(g, B2VX_BAD_STATE, "graph has a cycle or a node whose input is never produced");
 
+  // 1a. A grouped convolution (ops::GroupedConv2d) runs as an ordinary one whose kernel is block diagonal:
+  // the kernel [kw, kh, Ic/group, Oc] is spread into [kw, kh, Ic, Oc] with the real value zero (the weight
+  // zero point) everywhere outside the blocks, which adds nothing to any accumulator.  The tensor cores do
+  // `group` times the arithmetic the layer needs; what it buys is one code path.
+  for (size_t ni = 0; ni < g->nodes.size(); ++ni) {
+    if (g->nodes[ni].kind != B2VX_NODE_CONV2D || g->nodes[ni].p.conv.group <= 1) continue;
+    const int group = g->nodes[ni].p.conv.group;
+    if (g->nodes[ni].p.conv.multiplier >= 1) return fail(g, B2VX_UNSUPPORTED, "conv2d: group and multiplier together");
+    const TensorRec& w = g->tensors[g->nodes[ni].in[1]];
+    const TensorRec& x = g->tensors[g->nodes[ni].in[0]];
+    if (!w.host_valid) return fail(g, B2VX_UNSUPPORTED, "grouped conv2d: the kernel must be a constant");
+    if (w.d.rank != 4 || x.d.rank < 3) return fail(g, B2VX_SHAPE_MISMATCH, "grouped conv2d: kernel rank 4, input rank 3 or 4");
+    const uint32_t kk = w.d.dims[0] * w.d.dims[1], icg = w.d.dims[2], oc_n = w.d.dims[3], ic_n = x.d.dims[2];
+    if (icg * static_cast<uint32_t>(group) != ic_n || oc_n % static_cast<uint32_t>(group))
+      return fail(g, B2VX_SHAPE_MISMATCH, "grouped conv2d: kernel must be [kw, kh, C/group, Oc] with Oc a multiple of group");
+    TensorRec full = w;
+    full.d.dims[2] = ic_n;
+    const size_t es = dtype_size(w.d.dtype);
+    full.host.assign(static_cast<size_t>(kk) * ic_n * oc_n * es, 0);
+    if (es == 1) std::memset(full.host.data(), w.zp() & 0xFF, full.host.size());   // real zero of an 8-bit kernel
+    const uint32_t per_out = oc_n / static_cast<uint32_t>(group);
+    for (uint32_t oc = 0; oc < oc_n; ++oc) {
+      const uint32_t gi = oc / per_out;
+      std::memcpy(full.host.data() + (static_cast<size_t>(oc) * ic_n + gi * icg) * kk * es,
+                  w.host.data() + static_cast<size_t>(oc) * icg * kk * es, static_cast<size_t>(icg) * kk * es);
+    }
+    g->tensors.push_back(std::move(full));
+    g->nodes[ni].in[1] = static_cast<uint32_t>(g->tensors.size() - 1);
+    g->nodes[ni].p.conv.group = 1;
+  }
+
   // 1b. A Relu/Relu6 between identical 8-bit quantizations whose byte table is the
   // identity (zero point at the bottom of the range, nothing to clamp) changes no
   // byte: its producer writes straight into the Relu's output tensor.

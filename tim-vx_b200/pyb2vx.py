@@ -43,7 +43,7 @@ class TensorDesc(C.Structure):
 class Conv2dDesc(C.Structure):
     _fields_ = [("weights", C.c_uint32), ("pad_type", C.c_int32), ("ksize", C.c_uint32 * 2),
                 ("stride", C.c_uint32 * 2), ("dilation", C.c_uint32 * 2), ("pad", C.c_uint32 * 4),
-                ("multiplier", C.c_int32)]
+                ("multiplier", C.c_int32), ("group", C.c_int32)]
 
 
 class FcDesc(C.Structure):
@@ -198,7 +198,7 @@ class Graph:
         return tid.value
 
     def conv2d(self, x, w, bias, y, stride=(1, 1), dilation=(1, 1), pad_type=PAD_AUTO, pad=(0, 0, 0, 0), multiplier=0,
-               weights=0, ksize=(0, 0)):
+               weights=0, ksize=(0, 0), group=0):
         d = Conv2dDesc()
         d.weights = weights
         d.pad_type = pad_type
@@ -207,6 +207,7 @@ class Graph:
         d.dilation[:] = dilation
         d.pad[:] = pad
         d.multiplier = multiplier
+        d.group = group
         self._check(self.lib.b2vx_node_conv2d(self.g, x, w, NO_TENSOR if bias is None else bias, y, C.byref(d)))
 
     def fully_connected(self, x, w, bias, y, axis=0, weights=0):
@@ -343,7 +344,7 @@ def graph_from_case(lib, case, device=0):
         k = n["kind"]
         if k == NODE_CONV2D:
             g.conv2d(i[0], i[1], i[2], o, stride=n["stride"], dilation=n["dilation"], pad_type=n["pad_type"],
-                     pad=n["pad"], multiplier=n["multiplier"], weights=n["weights"], ksize=n["ksize"])
+                     pad=n["pad"], multiplier=n["multiplier"], weights=n["weights"], ksize=n["ksize"], group=n.get("group", 0))
         elif k == NODE_FC:
             g.fully_connected(i[0], i[1], i[2], o, axis=n["axis"], weights=n["weights"])
         elif k == NODE_POOL2D:
