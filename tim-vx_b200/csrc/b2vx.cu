@@ -522,11 +522,62 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
   }
 }
 
+// Element strides of a tensor's channels-last storage per logical (WHCN-order) dimension.
+void cl_strides(const TensorRec& t, long long s[4]) {
+  s[0] = s[1] = s[2] = s[3] = 0;
+  switch (t.d.rank) {
+    case 4: s[3] = static_cast<long long>(t.H) * t.W * t.Cp;   // fall through
+    case 3: s[0] = t.Cp; s[1] = static_cast<long long>(t.W) * t.Cp; s[2] = 1; break;
+    case 2: s[0] = 1; s[1] = t.Cp; break;
+    default: s[0] = 1; break;
+  }
+}
+
+// Element strides of the dense WHCN-order copy (dimension 0 fastest).
+void dense_strides(const TensorRec& t, long long s[4]) {
+  long long acc = 1;
+  for (uint32_t k = 0; k < 4; ++k) {
+    s[k] = k < t.d.rank ? acc : 0;
+    if (k < t.d.rank) acc *= t.d.dims[k];
+  }
+}
+
+// Lists the iteration dimensions by increasing output stride: consecutive threads then write neighbouring
+// elements.  `with_istride`: the input strides belong to the iteration dimensions and move with them.
+void sort_by_output_stride(RelayoutParams& p, bool with_istride) {
+  for (int a = 0; a < p.rank; ++a)
+    for (int b = a + 1; b < p.rank; ++b)
+      if (p.ostride[b] < p.ostride[a] || (p.ostride[b] == p.ostride[a] && p.dims[b] < p.dims[a])) {
+        std::swap(p.dims[a], p.dims[b]);
+        std::swap(p.ostride[a], p.ostride[b]);
+        std::swap(p.lstride[a], p.lstride[b]);
+        if (with_istride) std::swap(p.istride[a], p.istride[b]);
+      }
+}
+
+RelayoutParams relayout_base(const TensorRec& shape_of) {
+  RelayoutParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.rank = static_cast<int>(shape_of.d.rank);
+  p.total = 1;
+  for (int k = 0; k < 4; ++k) {
+    p.dims[k] = k < p.rank ? static_cast<int>(shape_of.d.dims[k]) : 1;
+    p.idims[k] = 1;
+    p.total *= p.dims[k];
+  }
+  p.elem = static_cast<int>(dtype_size(shape_of.d.dtype));
+  return p;
+}
+
 b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* label, TensorRec& x, TensorRec& w,
                              TensorRec* bias, TensorRec& y, int kw, int kh, const uint32_t stride[2],
                              const uint32_t dil[2], const uint32_t pad[4]) {
-  if (!w.host_valid) return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": weights must be a CONSTANT tensor with data");
-  if (bias && !bias->host_valid) return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": bias must be a CONSTANT tensor with data");
+  // float32 layers accept a kernel and a bias produced at run time (a graph input, or the Transpose that layout
+  // inference puts behind one); the quantized paths pack their weights when the graph is compiled
+  const bool runtime_ok = x.d.dtype == B2VX_DT_FLOAT32;
+  if (!w.host_valid && !(runtime_ok && w.is_activation)) return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": weights must be a CONSTANT tensor with data");
+  if (bias && !bias->host_valid && !(runtime_ok && bias->is_activation))
+    return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": bias must be a CONSTANT tensor with data");
   const ConvGeom geo = conv_geom(x, y, kw, kh, stride, dil, pad);
   const uint64_t P = static_cast<uint64_t>(y.N) * y.H * y.W;
   const uint64_t macs = P * y.C * static_cast<uint64_t>(kw) * kh * x.C;
@@ -538,13 +589,32 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     if (w.d.dtype != B2VX_DT_FLOAT32 || y.d.dtype != B2VX_DT_FLOAT32 || (bias && bias->d.dtype != B2VX_DT_FLOAT32))
       return fail(g, B2VX_UNSUPPORTED, std::string(label) + ": float32 input needs float32 weights, bias and output");
     float *dw = nullptr, *db = nullptr;
-    std::vector<float> wv(reinterpret_cast<const float*>(w.host.data()), reinterpret_cast<const float*>(w.host.data()) + w.elems());
-    b2vx_status st = upload(g, wv, &dw);
-    if (st != B2VX_OK) return st;
-    if (bias) {
+    b2vx_status st = B2VX_OK;
+    if (w.host_valid) {
+      std::vector<float> wv(reinterpret_cast<const float*>(w.host.data()), reinterpret_cast<const float*>(w.host.data()) + w.elems());
+      st = upload(g, wv, &dw);
+      if (st != B2VX_OK) return st;
+    } else {
+      // run-time kernel: every run first copies it from its storage into the dense [kw, kh, Ic, Oc] order the kernel reads
+      void* dense = nullptr;
+      st = dev_alloc(g, &dense, w.bytes());
+      if (st != B2VX_OK) return st;
+      dw = static_cast<float*>(dense);
+      RelayoutParams rp = relayout_base(w);
+      dense_strides(w, rp.ostride);
+      cl_strides(w, rp.istride);
+      const void* wp = cl_in(w);
+      Step sw;
+      sw.info = make_info("kernel_to_dense", node_index, 0, 2 * w.bytes());
+      sw.fn = [=](cudaStream_t st2) { launch_relayout(wp, dense, rp, st2); return cudaGetLastError(); };
+      g->steps.push_back(std::move(sw));
+    }
+    if (bias && bias->host_valid) {
       std::vector<float> bv(reinterpret_cast<const float*>(bias->host.data()), reinterpret_cast<const float*>(bias->host.data()) + bias->elems());
       st = upload(g, bv, &db);
       if (st != B2VX_OK) return st;
+    } else if (bias) {
+      db = static_cast<float*>(const_cast<void*>(cl_in(*bias)));   // rank 1: the storage is the dense vector
     }
     const float* xp = static_cast<const float*>(cl_in(x));
     float* yp = static_cast<float*>(y.d_cl);
@@ -1111,53 +1181,6 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   }
   g->steps.push_back(std::move(s));
   return B2VX_OK;
-}
-
-// Element strides of a tensor's channels-last storage per logical (WHCN-order) dimension.
-void cl_strides(const TensorRec& t, long long s[4]) {
-  s[0] = s[1] = s[2] = s[3] = 0;
-  switch (t.d.rank) {
-    case 4: s[3] = static_cast<long long>(t.H) * t.W * t.Cp;   // fall through
-    case 3: s[0] = t.Cp; s[1] = static_cast<long long>(t.W) * t.Cp; s[2] = 1; break;
-    case 2: s[0] = 1; s[1] = t.Cp; break;
-    default: s[0] = 1; break;
-  }
-}
-
-// Element strides of the dense WHCN-order copy (dimension 0 fastest).
-void dense_strides(const TensorRec& t, long long s[4]) {
-  long long acc = 1;
-  for (uint32_t k = 0; k < 4; ++k) {
-    s[k] = k < t.d.rank ? acc : 0;
-    if (k < t.d.rank) acc *= t.d.dims[k];
-  }
-}
-
-// Lists the iteration dimensions by increasing output stride: consecutive threads then write neighbouring
-// elements.  `with_istride`: the input strides belong to the iteration dimensions and move with them.
-void sort_by_output_stride(RelayoutParams& p, bool with_istride) {
-  for (int a = 0; a < p.rank; ++a)
-    for (int b = a + 1; b < p.rank; ++b)
-      if (p.ostride[b] < p.ostride[a] || (p.ostride[b] == p.ostride[a] && p.dims[b] < p.dims[a])) {
-        std::swap(p.dims[a], p.dims[b]);
-        std::swap(p.ostride[a], p.ostride[b]);
-        std::swap(p.lstride[a], p.lstride[b]);
-        if (with_istride) std::swap(p.istride[a], p.istride[b]);
-      }
-}
-
-RelayoutParams relayout_base(const TensorRec& shape_of) {
-  RelayoutParams p;
-  std::memset(&p, 0, sizeof(p));
-  p.rank = static_cast<int>(shape_of.d.rank);
-  p.total = 1;
-  for (int k = 0; k < 4; ++k) {
-    p.dims[k] = k < p.rank ? static_cast<int>(shape_of.d.dims[k]) : 1;
-    p.idims[k] = 1;
-    p.total *= p.dims[k];
-  }
-  p.elem = static_cast<int>(dtype_size(shape_of.d.dtype));
-  return p;
 }
 
 // Reshape, Transpose, DataConvert: one pass from the input's storage to the output's.
@@ -1759,6 +1782,12 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
     if (n.kind == B2VX_NODE_CONCAT) {
       for (uint32_t id : n.in)
         if (id != B2VX_NO_TENSOR) g->tensors[id].is_activation = true;
+    }
+    if (n.kind == B2VX_NODE_CONV2D || n.kind == B2VX_NODE_FULLY_CONNECTED) {
+      // a kernel or bias that is not a constant lives on the device like any other tensor
+      for (int k = 1; k <= 2; ++k)
+        if (n.in[k] != B2VX_NO_TENSOR && !g->tensors[n.in[k]].host_valid && !(g->tensors[n.in[k]].d.attr & B2VX_ATTR_CONSTANT))
+          g->tensors[n.in[k]].is_activation = true;
     }
     if (n.kind == B2VX_NODE_ADD) g->tensors[n.in[1]].is_activation = true;
     // 32-bit integer activations exist only around Add (the reference's platform sample adds INT32 vectors) and

@@ -961,32 +961,12 @@ __global__ void add_i32_kernel(const int* __restrict__ a, float sa, int za, cons
   y[i] = requant_wide(__fadd_rn(fa, fb), out);
 }
 
-// Element-by-element move between two storages under a logical shape (see RelayoutParams): the general
-// form behind Reshape, Transpose, Concat and DataConvert.  One element per thread, consecutive threads on
-// consecutive positions of logical dimension 0.
-__global__ void relayout_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, RelayoutParams p) {
-  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (i >= p.total) return;
-  long long rem = i, o = 0, src = 0, lin = 0;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    if (k < p.rank) {
-      const long long c = rem % p.dims[k];
-      rem /= p.dims[k];
-      o += c * p.ostride[k];
-      src += c * p.istride[k];
-      lin += c * p.lstride[k];
-    }
-  }
-  if (p.reshape) {
-    src = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {   // unused dimensions have extent 1
-      const long long c = lin % p.idims[k];
-      lin /= p.idims[k];
-      src += c * p.istride[k];
-    }
-  }
+// Move between two storages under a logical shape (see RelayoutParams): the general form behind Reshape,
+// Transpose, Concat and DataConvert.  A thread takes a run of up to 16 consecutive positions of iteration
+// dimension 0 (the one with the smallest output stride), so neighbouring threads write neighbouring runs and
+// the coordinates are worked out once per run.  IndexT: 32-bit when the element count allows.
+__device__ __forceinline__ void relayout_one(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, const RelayoutParams& p,
+                                             long long src, long long o) {
   switch (p.convert) {
     case 0:
       if (p.elem == 1) out[o] = in[src];
@@ -1003,6 +983,50 @@ __global__ void relayout_kernel(const uint8_t* __restrict__ in, uint8_t* __restr
       reinterpret_cast<float*>(out)[o] = __fmul_rn(__fsub_rn(__int2float_rn(q), __int2float_rn(p.in_zp)), p.in_scale);
       break;
     }
+  }
+}
+
+template <typename IndexT>
+__global__ void relayout_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, RelayoutParams p, int run, int runs0,
+                                long long n_threads) {
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (tid >= n_threads) return;
+  IndexT rem = static_cast<IndexT>(tid);
+  const int c0 = static_cast<int>(rem % static_cast<IndexT>(runs0)) * run;
+  rem /= static_cast<IndexT>(runs0);
+  long long o = c0 * p.ostride[0], src = c0 * p.istride[0], lin = c0 * p.lstride[0];
+#pragma unroll
+  for (int k = 1; k < 4; ++k) {
+    if (k < p.rank) {
+      const long long c = static_cast<long long>(rem % static_cast<IndexT>(p.dims[k]));
+      rem /= static_cast<IndexT>(p.dims[k]);
+      o += c * p.ostride[k];
+      src += c * p.istride[k];
+      lin += c * p.lstride[k];
+    }
+  }
+  const int count = min(run, p.dims[0] - c0);
+  if (count == 16 && p.convert == 0 && p.elem == 1 && !p.reshape && p.ostride[0] == 1 && p.istride[0] == 1 &&
+      ((reinterpret_cast<uintptr_t>(in + src) | reinterpret_cast<uintptr_t>(out + o)) & 15) == 0) {
+    // both sides contiguous along the run: one 16-byte copy
+    *reinterpret_cast<uint4*>(out + o) = *reinterpret_cast<const uint4*>(in + src);
+    return;
+  }
+  for (int e = 0; e < count; ++e) {
+    long long s = src;
+    if (p.reshape) {
+      IndexT l = static_cast<IndexT>(lin);
+      s = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {   // unused dimensions have extent 1
+        s += static_cast<long long>(l % static_cast<IndexT>(p.idims[k])) * p.istride[k];
+        l /= static_cast<IndexT>(p.idims[k]);
+      }
+    }
+    relayout_one(in, out, p, s, o);
+    o += p.ostride[0];
+    src += p.istride[0];
+    lin += p.lstride[0];
   }
 }
 
@@ -1607,7 +1631,13 @@ void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStre
 
 void launch_relayout(const void* in, void* out, const RelayoutParams& p, cudaStream_t s) {
   if (p.total <= 0) return;
-  relayout_kernel<<<grid_for(p.total, kThreads), kThreads, 0, s>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), p);
+  const int run = p.dims[0] < 16 ? p.dims[0] : 16;
+  const int runs0 = (p.dims[0] + run - 1) / run;
+  const long long n_threads = p.total / p.dims[0] * runs0;
+  const uint8_t* ip = static_cast<const uint8_t*>(in);
+  uint8_t* op = static_cast<uint8_t*>(out);
+  if (p.total < (1ll << 31)) relayout_kernel<unsigned><<<grid_for(n_threads, kThreads), kThreads, 0, s>>>(ip, op, p, run, runs0, n_threads);
+  else relayout_kernel<unsigned long long><<<grid_for(n_threads, kThreads), kThreads, 0, s>>>(ip, op, p, run, runs0, n_threads);
 }
 
 void launch_concat_c16(const void* in, int in_pitch16, int in16, void* out, int out_pitch16, int off16, long long pixels, cudaStream_t s) {
