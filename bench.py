@@ -403,6 +403,7 @@ def main():
 
     def feed(replica, count):
         r, rin, rout = replica
+        torch.cuda.set_device(local_rank)   # a new host thread starts on device 0
         for _ in range(count):
             r.set_input(rin.data_ptr())
             r.run()

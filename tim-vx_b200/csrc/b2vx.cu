@@ -150,6 +150,10 @@ b2vx_status fail(b2vx_graph* g, b2vx_status st, const std::string& msg) {
 
 bool valid_id(const b2vx_graph* g, uint32_t id) { return id < g->tensors.size(); }
 
+// Makes the graph's GPU current for the duration of a call.  A host thread that has not chosen a device yet
+// reports device 0; going back to it afterwards would create a context on GPU 0 in a process that works on
+// another GPU (and did, in worker threads of multi-GPU runs, at a cost of milliseconds per call), so the
+// previous device is restored only if this process already has a context there.
 struct DeviceGuard {
   int prev = -1;
   explicit DeviceGuard(int dev) {
@@ -158,7 +162,20 @@ struct DeviceGuard {
     else prev = -1;
   }
   ~DeviceGuard() {
-    if (prev >= 0) cudaSetDevice(prev);
+    if (prev < 0) return;
+    typedef int (*StateFn)(int, unsigned int*, int*);   // cuDevicePrimaryCtxGetState(CUdevice, unsigned*, int*)
+    static const StateFn state = [] {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuDevicePrimaryCtxGetState", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+          q != cudaDriverEntryPointSuccess)
+        fn = nullptr;
+      return reinterpret_cast<StateFn>(fn);
+    }();
+    unsigned int flags = 0;
+    int active = 1;
+    if (state && state(prev, &flags, &active) == 0 && !active) return;   // ordinal == CUdevice handle for cudart devices
+    cudaSetDevice(prev);
   }
 };
 
