@@ -91,6 +91,14 @@ struct GemmParams {
   int tmem_cols;
   int acc_stride;          // TMEM columns between accumulator buffers (BN rounded up to 32)
   int acc_shift;           // log2 of the number of accumulator buffers (2, 4 or 8 of them)
+  // Narrow tiles (at most four 16-column chunks): the sixteen epilogue warps split into four teams of four
+  // (one warp per TMEM lane quarter), each team takes every fourth tile of the CTA and all of its chunks, so
+  // that a warp's per-tile work (waits, row arithmetic) is spread over four chunks as it is with wide tiles.
+  int teams;
+  // The CTA's weight tile (all k-blocks of its N tile) stays in shared memory for the whole kernel, loaded once
+  // before the first tile; the ring then carries the A operand only.  For narrow layers, which are bound
+  // by the operand traffic from L2, this removes a third to two thirds of it.
+  int b_resident;
   uint32_t idesc;
   uint32_t layout_type;    // UMMA smem descriptor swizzle code
   uint32_t sbo;            // bytes between 8-row groups
@@ -272,6 +280,7 @@ struct SmemHeader {
   unsigned long long empty[kMaxStages];
   unsigned long long tmem_full[kMaxAccBuffers];
   unsigned long long tmem_empty[kMaxAccBuffers];
+  unsigned long long b_full;         // resident weights landed
   unsigned long long res_full[2];    // FUSE: residual tile landed / read by all epilogue warps
   unsigned long long res_empty[2];
   uint32_t tmem_base;
@@ -299,11 +308,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
   const uint32_t a_bytes = kBlockM * p.BK;
   const uint32_t b_bytes = static_cast<uint32_t>(p.BN) * p.BK;
-  const uint32_t sub_bytes = a_bytes + b_bytes;     // one k-block: whole swizzle atoms, see the host-side plan
+  const uint32_t sub_bytes = a_bytes + (p.b_resident ? 0u : b_bytes);   // one k-block: whole swizzle atoms, see the host-side plan
   const uint32_t stage_bytes = sub_bytes * p.group;
   const uint32_t ring_bytes = (p.stages * stage_bytes + 1023u) & ~1023u;
+  const uint32_t bres_bytes = p.b_resident ? ((static_cast<uint32_t>(p.num_kb) * b_bytes + 1023u) & ~1023u) : 0u;
+  const uint32_t bres_addr = tiles_addr + ring_bytes;                    // resident weights: k-block after k-block
   const uint32_t staging_bytes = (p.store_span || p.res_span) ? static_cast<uint32_t>(kBlockM) * p.BNd : 0u;   // per buffer, multiple of 4096
-  uint8_t* staging = tiles + ring_bytes;
+  uint8_t* staging = tiles + ring_bytes + bres_bytes;
   uint8_t* add_tab = staging + 2 * staging_bytes;                 // 64 KB when FUSE
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(add_tab + (FUSE ? 65536 : 0));
   volatile int* abort_flag = &hdr->abort_flag;
@@ -320,13 +331,14 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&hdr->full[s]), 2);     // A producer + B producer
+      mbar_init(smem_u32(&hdr->full[s]), p.b_resident ? 1 : 2);     // A producer (+ B producer)
       mbar_init(smem_u32(&hdr->empty[s]), 1);
     }
     for (int a = 0; a < kMaxAccBuffers; ++a) {
       mbar_init(smem_u32(&hdr->tmem_full[a]), 1);
-      mbar_init(smem_u32(&hdr->tmem_empty[a]), kEpilogueWarps);
+      mbar_init(smem_u32(&hdr->tmem_empty[a]), p.teams ? 4 : kEpilogueWarps);
     }
+    mbar_init(smem_u32(&hdr->b_full), 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&hdr->res_full[b]), 1);
       mbar_init(smem_u32(&hdr->res_empty[b]), kEpilogueWarps);
@@ -359,7 +371,25 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t tmem_base = hdr->tmem_base;
   TC_MARK(1);
 
-  if (warp == 0 || warp == 2) {
+  if (warp == 2 && p.b_resident) {
+    // ------------------------------------------------------------ resident weights: one load of every k-block
+    // Weights are constants of the graph, so this does not wait for earlier kernels of the stream.
+    if (elect_one()) {
+      const uint32_t full = smem_u32(&hdr->b_full);
+      mbar_arrive_expect_tx(full, static_cast<uint32_t>(p.num_kb) * b_bytes);
+      int tap = 0, cb = 0;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        const uint32_t dst = bres_addr + static_cast<uint32_t>(kb) * b_bytes;
+        if (p.conv) {
+          tma_load_2d(dst, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
+          if (++cb == p.cblocks) { cb = 0; ++tap; }
+        } else {
+          tma_load_2d(dst, &map_b, kb * p.BK, n_tile * p.BN, full);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 0 || warp == 2) {
     // ------------------------------------------------------------ TMA producers (warp 0: A, warp 2: B)
     // All lanes wait for the slot; one elected lane announces the bytes and issues the boxes of the
     // stage's k-blocks.
@@ -429,6 +459,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     bool ok = true;
     int j = 0;
     const int ksteps = p.BK >> 5;
+    if (p.b_resident && static_cast<int>(blockIdx.x) < num_tiles) {
+      ok = mbar_wait(smem_u32(&hdr->b_full), 0, abort_flag, p.status, 8);
+      ok = __all_sync(0xffffffffu, ok);
+    }
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
       const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
       ok = mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2);
@@ -449,7 +483,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           uint32_t acc_flag = accumulate;
           for (int gi = 0; gi < cnt; ++gi, a_addr += sub_bytes) {
             const uint64_t da = make_smem_desc(a_addr, p.sbo, p.layout_type);
-            const uint64_t db = make_smem_desc(a_addr + a_bytes, p.sbo, p.layout_type);
+            const uint64_t db = make_smem_desc(p.b_resident ? bres_addr + static_cast<uint32_t>(kb0 + gi) * b_bytes : a_addr + a_bytes,
+                                               p.sbo, p.layout_type);
             for (int k = 0; k < ksteps; ++k) {
               // advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
               tc_mma_i8(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc, acc_flag);
@@ -545,10 +580,14 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
     };
     bool alive = true;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
+    const int j_step = p.teams ? 4 : 1;                     // team mode: warp group col_group takes tiles j = col_group (mod 4)
+    const int c_first = p.teams ? 0 : col_group * 16;       // and all of their chunks
+    const int c_step = p.teams ? 16 : 64;
+    j = p.teams ? col_group : 0;
+    for (int tile = blockIdx.x + j * static_cast<int>(gridDim.x); tile < num_tiles; tile += j_step * static_cast<int>(gridDim.x), j += j_step) {
       const int m_tile = m_tile0 + j * m_step;
       const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
-      uint8_t* stage_out = staging + a * staging_bytes;
+      uint8_t* stage_out = staging + (j & 1) * staging_bytes;
       long long row;                 // direct-store path: output row (pixel index into D), -1 outside the tensor
       const int32_t* corr_row;       // border pixels of a padded convolution: their correction, this N tile
       locate(m_tile, row, corr_row);
@@ -607,18 +646,18 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       };
       {
         int acc_a[16], acc_b[16];
-        int c0 = col_group * 16;
+        int c0 = c_first;
         if (c0 < p.BNd) tc_ld_32x16(taddr + c0, acc_a);
         while (c0 < p.BNd) {
           tc_ld_wait(acc_a);
-          if (c0 + 64 < p.BNd) tc_ld_32x16(taddr + c0 + 64, acc_b);
+          if (c0 + c_step < p.BNd) tc_ld_32x16(taddr + c0 + c_step, acc_b);
           emit(acc_a, c0);
-          c0 += 64;
+          c0 += c_step;
           if (c0 >= p.BNd) break;
           tc_ld_wait(acc_b);
-          if (c0 + 64 < p.BNd) tc_ld_32x16(taddr + c0 + 64, acc_a);
+          if (c0 + c_step < p.BNd) tc_ld_32x16(taddr + c0 + c_step, acc_a);
           emit(acc_b, c0);
-          c0 += 64;
+          c0 += c_step;
         }
       }
       // accumulator buffer (and residual buffer) free again
@@ -775,6 +814,9 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.res_span = e.add_residual != nullptr ? p.store_span : 0;
   if (!tma_store || e.add_residual != nullptr) p.store_span = 0;
   const size_t add_table_bytes = e.add_residual != nullptr ? 65536 : 0;
+  static const bool no_teams = [] { const char* e2 = std::getenv("B2VX_TC_TEAMS"); return e2 && std::strcmp(e2, "0") == 0; }();
+  p.teams = (p.BNd <= 64 && p.store_span == 0 && !no_teams) ? 4 : 0;
+  if (p.teams) p.res_span = 0;   // four tiles in flight do not fit the two residual buffers: threads load their pieces
   if (p.res_span) {
     // The Add's table and two residual tiles leave less for the operand ring: three stages must remain,
     // with 64-byte K blocks if 128-byte ones do not fit (these layers are bound by their epilogue, not by
@@ -793,8 +835,13 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   // tile start keeps the alignment its swizzle pattern repeats on (8*BK bytes) relative to the 1024-byte
   // aligned start of the ring.  Several k-blocks share a stage (one barrier round trip) when they are
   // small: up to 64 KiB per stage.
-  const size_t sub_bytes = static_cast<size_t>(kBlockM + p.BN) * p.BK;
-  const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging - add_table_bytes;
+  // Resident weights: the whole [BN x K] tile of this CTA's N tile when it is small (B2VX_TC_BRES=0 disables).
+  static const bool no_bres = [] { const char* e2 = std::getenv("B2VX_TC_BRES"); return e2 && std::strcmp(e2, "0") == 0; }();
+  const size_t b_all = static_cast<size_t>(kblocks_per_tile) * p.BN * p.BK;
+  p.b_resident = (!no_bres && e.add_residual == nullptr && b_all <= 72 * 1024) ? 1 : 0;
+  const size_t bres = p.b_resident ? ((b_all + 1023) & ~static_cast<size_t>(1023)) : 0;
+  const size_t sub_bytes = static_cast<size_t>(kBlockM + (p.b_resident ? 0 : p.BN)) * p.BK;
+  const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging - add_table_bytes - bres;
   int group = static_cast<int>((64 * 1024) / sub_bytes);
   if (group > kblocks_per_tile) group = kblocks_per_tile;
   if (group > kMaxGroup) group = kMaxGroup;
@@ -812,6 +859,7 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.acc_stride = (p.BN + 31) & ~31;
   p.acc_shift = 1;
   while (p.acc_shift < 3 && (2 << p.acc_shift) * p.acc_stride <= 512) ++p.acc_shift;
+  if (p.teams && p.acc_shift < 2) p.teams = 0;   // a team per accumulator buffer needs four of them
   int cols = 32;
   while (cols < (1 << p.acc_shift) * p.acc_stride) cols <<= 1;
   p.tmem_cols = cols;
@@ -827,7 +875,7 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
     *why = "gemm_tc: cuTensorMapEncodeTiled failed for the weights";
     return false;
   }
-  size_t smem = ((static_cast<size_t>(stages) * stage_bytes + 1023) & ~static_cast<size_t>(1023)) + staging + add_table_bytes + sizeof(SmemHeader) + 1024;
+  size_t smem = ((static_cast<size_t>(stages) * stage_bytes + 1023) & ~static_cast<size_t>(1023)) + bres + staging + add_table_bytes + sizeof(SmemHeader) + 1024;
   if (smem < static_cast<size_t>(kMinDynSmem)) smem = kMinDynSmem;
   plan->smem = smem;
   // the attribute belongs to the function on one device: set it once per device of this process
