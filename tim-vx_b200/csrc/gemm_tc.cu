@@ -33,6 +33,15 @@
 //                            overlap tile i's epilogue with tile i+1's MMAs.
 //                            (B2VX_TC_STORE=tma: write the bytes swizzled into
 //                            a staging tile instead and store it with TMA.)
+//                            Tiles of at most 64 columns: four teams of four
+//                            warps, each team on its own tile with all chunks.
+//   warp 3      residual producer of a fused Add (template FUSE): the Add's
+//                            other operand, tile by tile, into the staging
+//                            memory by TMA; the epilogue looks every
+//                            (own byte, residual byte) pair up in the Add's
+//                            64 KB table, which sits in shared memory too.
+// Small weight tiles (BN x K up to 72 KB) are loaded once by warp 2 and stay in
+// shared memory; the ring then holds A only.
 // A stage holds up to `group` k-blocks so that small k-blocks share one
 // barrier round trip.  The grid is a multiple of the number of N tiles: a CTA
 // keeps one N tile for life (bias and scales staged in shared memory once) and
