@@ -55,6 +55,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -1076,7 +1077,11 @@ GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s) {
     double bytes_per_clk = 24.0 * sms / static_cast<double>(grid);
     if (bytes_per_clk > 64.0 || l2_resident) bytes_per_clk = 64.0;
     const double load = (rows + bn) * Kp / bytes_per_clk;
-    const double epi = 9.0 * data + 300.0;
+    // the epilogue takes the tile's 16-column chunks four at a time (one per column group), or, for tiles of at
+    // most four chunks, a team of warps takes a whole tile: 9 cycles per column of a full group of four chunks
+    const double chunks = data / 16.0;
+    const double chunk_groups = data <= 64 ? chunks / 4.0 : std::ceil(chunks / 4.0);
+    const double epi = 9.0 * 64.0 * chunk_groups + 300.0;
     const double mainloop = mma > load ? mma : load;
     const double steady = mainloop > epi ? mainloop : epi;
     const double time = mainloop + epi + (per_cta - 1.0) * steady;
