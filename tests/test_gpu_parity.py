@@ -101,6 +101,11 @@ CONV_CASES = {
     # wide first-layer filters: the row-of-8 im2col, with and without a weight zero point
     "stem5x5_c3_u8w": G.conv2d_q(31, 29, 3, 2, 5, 5, 24, w_kind="u8", in_q=(0.02, 114)),
     "stem8x6_c4_s1": G.conv2d_q(20, 17, 4, 1, 8, 6, 16, in_q=(0.03, 9)),
+    # weight tile resident in shared memory with several channel blocks per tap; narrow tiles on epilogue teams,
+    # with more tiles than accumulator buffers per CTA
+    "resident_c96_3x3_oc32": G.conv2d_q(33, 29, 96, 3, 3, 3, 32),
+    "resident_c160_5x5_oc16_u8w": G.conv2d_q(21, 17, 160, 2, 5, 5, 16, w_kind="u8"),
+    "teams_many_tiles_oc48": G.conv2d_q(120, 110, 16, 2, 3, 3, 48, relu=True),
 }
 
 
@@ -167,6 +172,9 @@ FC_CASES = {
     "fc_m3_u8zp": G.fc_q(512, 200, 3, w_kind="u8"),
     "fc_m9_u8zp": G.fc_q(1024, 64, 9, w_kind="u8"),
     "fc_m6_u8zp": G.fc_q(1024, 64, 6, w_kind="u8"),
+    # resident weight tile on the plain GEMM path, many row tiles
+    "fc_k512_n64_m3000": G.fc_q(512, 64, 3000),
+    "fc_k320_n48_m700_u8zp": G.fc_q(320, 48, 700, w_kind="u8"),
 }
 
 
