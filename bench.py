@@ -66,7 +66,7 @@ def load_samples(path):
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel's launches in one step,
 # from the ncu capture summarised in profiles/resnet50_b64_launch_list.md; keyed by (workload, batch).
-NCU_DRAM_TRAFFIC = {("resnet50", 64): 1176.5e6}   # 54 launches of gemm_i8_tc_kernel: 1144.9 MB read + 31.6 MB written
+NCU_DRAM_TRAFFIC = {("resnet50", 64): 1176.2e6}   # 54 launches of gemm_i8_tc_kernel: 1144.8 MB read + 31.4 MB written
 
 
 def measured_peaks():
