@@ -50,6 +50,21 @@ def test_resnet50_full_batch_tensor_core_equals_cuda_core(tmp_path, product_lib)
     assert np.array_equal(a, b)
 
 
+SWITCHES = [{"B2VX_TC_STORE": "tma"}, {"B2VX_TC_BRES": "0"}, {"B2VX_TC_TEAMS": "0"}, {"B2VX_FUSE_ADD": "0"},
+            {"B2VX_PDL": "0", "B2VX_CUDA_GRAPH": "0"}, {"B2VX_TC_BN": "64"}]
+
+
+@pytest.mark.parametrize("net,batch", [("resnet50", 8), ("mobilenetv2", 8)])
+def test_every_kernel_variant_gives_the_same_bytes(tmp_path, product_lib, net, batch):
+    """The per-process switches select other code paths of the GEMM kernel (staged TMA stores, weights through the
+    ring, one tile per sixteen epilogue warps, the Add as its own kernel, plain launches, narrow tiles): the
+    network's output must not change by a byte."""
+    want = run_net("gpu", net, batch, tmp_path)
+    for k, env in enumerate(SWITCHES):
+        got = run_net("gpu", net, batch, tmp_path, env=env, tag="_v%d" % k)
+        assert np.array_equal(got, want), env
+
+
 def _run_graph(lib, spec, batch, seed, inputs=None, env=None):
     old = {}
     for k, v in (env or {}).items():
