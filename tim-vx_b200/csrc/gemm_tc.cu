@@ -359,16 +359,6 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int n_tile = blockIdx.x % p.n_tiles;   // fixed per CTA: gridDim.x is a multiple of n_tiles
   // hence the j-th tile of this CTA is M tile m_tile0 + j * m_step (no division per tile)
   const int m_tile0 = blockIdx.x / p.n_tiles, m_step = gridDim.x / p.n_tiles;
-  for (int i = threadIdx.x; i < p.BNd; i += kThreadsTc) {
-    const int oc = n_tile * p.BNd + i;
-    hdr->bias[i] = oc < p.Ocp ? p.ep.bias_full[oc] : 0;
-    hdr->scale[i] = oc < p.Ocp ? p.ep.acc_scale[oc] : 0.0f;
-  }
-  if (FUSE) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.ep.add_table);   // a constant of the graph
-    uint4* dst = reinterpret_cast<uint4*>(add_tab);
-    for (int i = threadIdx.x; i < 4096; i += kThreadsTc) dst[i] = __ldg(src + i);
-  }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hdr->tmem_base)),
                  "r"(static_cast<uint32_t>(p.tmem_cols))
@@ -548,6 +538,20 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
   } else if (warp >= kFirstEpilogueWarp) {
     // ------------------------------------------------------------ epilogue
+    // The epilogue's constants (this N tile's folded bias and scales, the fused Add's table) are staged by the
+    // epilogue warps themselves, behind a barrier of their own: the producers and the MMA warp are already at
+    // work on the first tile meanwhile.
+    for (int i = threadIdx.x - kFirstEpilogueWarp * 32; i < p.BNd; i += kEpilogueThreads) {
+      const int oc = n_tile * p.BNd + i;
+      hdr->bias[i] = oc < p.Ocp ? p.ep.bias_full[oc] : 0;
+      hdr->scale[i] = oc < p.Ocp ? p.ep.acc_scale[oc] : 0.0f;
+    }
+    if (FUSE) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.ep.add_table);   // a constant of the graph
+      uint4* dst = reinterpret_cast<uint4*>(add_tab);
+      for (int i = threadIdx.x - kFirstEpilogueWarp * 32; i < 4096; i += kEpilogueThreads) dst[i] = __ldg(src + i);
+    }
+    epilogue_barrier();
     const int ew = warp - kFirstEpilogueWarp;     // 0..15
     const int quarter = warp & 3;                 // TMEM lanes [32*quarter, +32) belong to this warp
     const int col_group = ew >> 2;                // this warp takes 16-column chunks col_group, col_group+4, ...
