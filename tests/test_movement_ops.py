@@ -86,6 +86,10 @@ for _perm in itertools.permutations(range(4)):
 CASES.update({
     "transpose_u8_nhwc_image": transpose_case(B.DT_UINT8, [3, 32, 24, 2], [1, 2, 0, 3]),
     "transpose_f32_rank3": transpose_case(B.DT_FLOAT32, [7, 5, 3], [2, 0, 1]),
+    # large enough in both contiguous dimensions for the tiled byte transpose, with ragged tile edges
+    "transpose_u8_tiled_wh": transpose_case(B.DT_UINT8, [40, 50, 3, 2], [1, 0, 2, 3]),
+    "transpose_u8_tiled_nhwc64": transpose_case(B.DT_UINT8, [64, 19, 21, 2], [1, 2, 0, 3]),
+    "transpose_u8_tiled_rank2": transpose_case(B.DT_UINT8, [257, 131], [1, 0]),
     "transpose_i32_rank2": transpose_case(B.DT_INT32, [1, 3], [1, 0]),
     "transpose_s8_rank2": transpose_case(B.DT_INT8, [33, 17], [1, 0]),
     "reshape_u8_4d_to_2d": reshape_case(B.DT_UINT8, [5, 4, 3, 2], [60, 2]),

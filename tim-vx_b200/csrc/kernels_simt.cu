@@ -1030,6 +1030,37 @@ __global__ void relayout_kernel(const uint8_t* __restrict__ in, uint8_t* __restr
   }
 }
 
+// Byte transpose between a dimension that is contiguous in the output (iteration dimension 0) and one that is
+// contiguous in the input (dimension kb): 32 x 32 tiles through shared memory, so that both the reads and the
+// writes of a warp are 32 consecutive bytes.  The remaining dimensions are spread over blockIdx.z.
+__global__ void relayout_tiled_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, RelayoutParams p, int kb) {
+  __shared__ uint8_t tile[32][33];
+  long long ibase = 0, obase = 0;
+  unsigned rest = blockIdx.z;
+#pragma unroll
+  for (int k = 1; k < 4; ++k) {
+    if (k < p.rank && k != kb) {
+      const unsigned c = rest % static_cast<unsigned>(p.dims[k]);
+      rest /= static_cast<unsigned>(p.dims[k]);
+      ibase += c * p.istride[k];
+      obase += c * p.ostride[k];
+    }
+  }
+  const int a0 = blockIdx.x * 32, b0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    const int a = a0 + ty + i, b = b0 + tx;
+    if (a < p.dims[0] && b < p.dims[kb]) tile[ty + i][tx] = in[ibase + a * p.istride[0] + b];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    const int a = a0 + tx, b = b0 + ty + i;
+    if (a < p.dims[0] && b < p.dims[kb]) out[obase + a + b * p.ostride[kb]] = tile[tx][ty + i];
+  }
+}
+
 __global__ void concat_c16_kernel(const uint4* __restrict__ in, int in_pitch16, int in16, uint4* __restrict__ out, int out_pitch16,
                                   int off16, long long total) {
   const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -1631,6 +1662,21 @@ void launch_add_f32(const float* a, const float* b, float* y, size_t n, cudaStre
 
 void launch_relayout(const void* in, void* out, const RelayoutParams& p, cudaStream_t s) {
   if (p.total <= 0) return;
+  const uint8_t* ip0 = static_cast<const uint8_t*>(in);
+  uint8_t* op0 = static_cast<uint8_t*>(out);
+  if (p.convert == 0 && p.elem == 1 && !p.reshape && p.rank >= 2 && p.ostride[0] == 1 && p.istride[0] != 1 && p.dims[0] >= 16) {
+    int kb = -1;
+    for (int k = 1; k < p.rank; ++k)
+      if (p.istride[k] == 1 && p.dims[k] >= 16) kb = k;
+    long long others = 1;
+    for (int k = 1; k < p.rank; ++k)
+      if (k != kb) others *= p.dims[k];
+    if (kb > 0 && others <= 65535 && (p.dims[kb] + 31) / 32 <= 65535) {
+      const dim3 grid((p.dims[0] + 31) / 32, (p.dims[kb] + 31) / 32, static_cast<unsigned>(others));
+      relayout_tiled_kernel<<<grid, dim3(32, 8), 0, s>>>(ip0, op0, p, kb);
+      return;
+    }
+  }
   const int run = p.dims[0] < 16 ? p.dims[0] : 16;
   const int runs0 = (p.dims[0] + run - 1) / run;
   const long long n_threads = p.total / p.dims[0] * runs0;
