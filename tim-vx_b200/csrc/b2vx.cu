@@ -468,6 +468,9 @@ struct PackedContraction {
   std::vector<int32_t> tapc;       // [taps][Ocp]
   bool need_s = false;
   int rows = 0, Kp = 0;
+  // largest |accumulator * acc_scale| any output channel can reach, the accumulator being the true
+  // sum((x - zx)*(w - zw)) + bias with every product at the end of the input type's range that makes it largest
+  double real_max = 0.0;
 };
 
 // Weight element (kx,ky,ic,oc) of a WHIcOc kernel as a signed value together
@@ -500,6 +503,8 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
   const float sx = x.scale();
   std::vector<int64_t> tapsum(taps);
   const int32_t* b = bias ? reinterpret_cast<const int32_t*>(bias->host.data()) : nullptr;
+  const int x_lo = (x.d.dtype == B2VX_DT_INT8 ? -128 : 0) - zx, x_hi = (x.d.dtype == B2VX_DT_INT8 ? 127 : 255) - zx;
+  out->real_max = 0.0;
   for (int oc = 0; oc < Oc; ++oc) {
     const int zw = per_ch ? (w.zps.empty() ? 0 : w.zps[oc]) : w.zp();
     const float sw = per_ch ? w.scales[oc] : w.scale();
@@ -511,6 +516,7 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
   out->w8.assign(static_cast<size_t>(rows) * Kp, 0);
   for (int oc = 0; oc < Oc; ++oc) {
     std::fill(tapsum.begin(), tapsum.end(), 0);
+    int64_t pos = 0, neg = 0;
     int8_t* row = out->w8.data() + (static_cast<size_t>(oc / tile_data) * tile_rows + oc % tile_data) * Kp;
     for (int ic = 0; ic < C; ++ic) {
       for (int t = 0; t < taps; ++t) {
@@ -518,8 +524,14 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
         const int v = w_u8 ? static_cast<int>(w.host[src]) - 128 : static_cast<int>(reinterpret_cast<const int8_t*>(w.host.data())[src]);
         row[kidx(t, ic)] = static_cast<int8_t>(v);
         tapsum[t] += v;
+        const int64_t wr = v - out->dz[oc];   // the real weight minus its zero point
+        const int64_t p0 = wr * x_lo, p1 = wr * x_hi;
+        pos += p0 > p1 ? p0 : p1;
+        neg += p0 < p1 ? p0 : p1;
       }
     }
+    const double hi = static_cast<double>(pos + (b ? b[oc] : 0)), lo = static_cast<double>(neg + (b ? b[oc] : 0));
+    out->real_max = std::max(out->real_max, std::max(std::fabs(hi), std::fabs(lo)) * std::fabs(static_cast<double>(out->acc_scale[oc])));
     int64_t all = 0;
     for (int t = 0; t < taps; ++t) {
       // contribution of one fully in-bounds tap beyond the raw products:
@@ -807,11 +819,9 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     {
       // largest |acc * acc_scale / out scale| any input can produce: decides whether the epilogue may
       // use its fast rounding (valid below 2^21)
-      double bmax = 0.0, smax = 0.0;
-      for (int32_t b : pk.bias_full) bmax = std::max(bmax, std::fabs(static_cast<double>(b)));
-      for (float sc : pk.acc_scale) smax = std::max(smax, std::fabs(static_cast<double>(sc)));
-      // (twice the raw dot product's range: the S term of a weight zero point and the border corrections stay inside it)
-      const double tmax = (2.0 * static_cast<double>(Kp) * 255.0 * 128.0 + bmax) * smax / std::fabs(static_cast<double>(ep.out.scale));
+      // (bounded per output channel from the weights themselves; the integer the epilogue converts is that true
+      // accumulator: the S term of a weight zero point and the border corrections are already in it)
+      const double tmax = pk.real_max / std::fabs(static_cast<double>(ep.out.scale));
       ep.exact_only = !(tmax < 2097152.0);
     }
     void* fused_out = nullptr;
