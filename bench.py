@@ -17,7 +17,14 @@ Printed on rank 0, one JSON line:
             steps are shared by --e2e-threads host threads (default 3), each with its own
             replica of the graph, so that one replica's copies overlap the other's kernels
   roofline  the dominant kernel (the tcgen05 int8 GEMM over all its launches of one
-            step), per-kernel CUDA-event times measured live by b2vx_graph_profile
+            step), per-kernel CUDA-event times measured live by b2vx_graph_profile;
+            int8_peak_measured is the tensor pipe's dense int8 rate from an issue-rate
+            microbenchmark run on the spot (b2vx_measure_int8_peak)
+  sustained the same graph replayed back to back for at least two seconds, with the
+            median SM clock and power sampled meanwhile
+  configs   (N=1, default workload) one number each for the other benchmark
+            configurations: LeNet, the convolution sweep, MobileNetV2, the GEMM sweep,
+            the decode-like FullyConnected shapes and the 64 Mi-element Add
   cpu_baseline  the CPU oracle (a restatement, "port") on a bounded sample, rank 0, N=1
 
 --impl reference times that CPU oracle as the reference arm (the reference's own
@@ -64,9 +71,59 @@ def load_samples(path):
     return lib
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel's launches in one step,
-# from the ncu capture summarised in profiles/resnet50_b64_launch_list.md; keyed by (workload, batch).
-NCU_DRAM_TRAFFIC = {("resnet50", 64): 1176.2e6}   # 54 launches of gemm_i8_tc_kernel: 1144.8 MB read + 31.4 MB written
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "dram_traffic.json")
+
+
+def dram_traffic(workload, batch):
+    """DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel's launches in one step, as
+    recorded from an ncu capture by --traffic-from; None when no capture of this workload is on file."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            rec = json.load(f).get("%s:%d" % (workload, batch))
+        return rec
+    except (OSError, ValueError):
+        return None
+
+
+def record_traffic(args):
+    """--traffic-from <csv>: sums dram__bytes_read.sum and dram__bytes_write.sum per kernel over the launches listed
+    in an `ncu --csv --metrics dram__bytes_read.sum,dram__bytes_write.sum` log of one step of this workload and
+    stores the dominant kernel's total, with the commit the tree is at, in profiles/dram_traffic.json."""
+    import csv
+    unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    per = {}
+    with open(args.traffic_from) as f:
+        rows = [r for r in csv.reader(l for l in f if l.startswith('"'))]
+    hdr = rows[0]
+    ki, mi, ui, vi = hdr.index("Kernel Name"), hdr.index("Metric Name"), hdr.index("Metric Unit"), hdr.index("Metric Value")
+    launches = {}
+    for r in rows[1:]:
+        if r[mi] not in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            continue
+        name = r[ki].split("(")[0].split("::")[-1]
+        per[name] = per.get(name, 0.0) + float(r[vi].replace(",", "")) * unit.get(r[ui], 1.0)
+        if r[mi] == "dram__bytes_read.sum":
+            launches[name] = launches.get(name, 0) + 1
+    top = max(per, key=lambda n: per[n])
+    # both instantiations of the GEMM kernel count as one kernel
+    total = sum(v for n, v in per.items() if n.split("<")[0] == top.split("<")[0])
+    count = sum(v for n, v in launches.items() if n.split("<")[0] == top.split("<")[0])
+    try:
+        commit = subprocess.run(["git", "-C", ROOT, "rev-parse", "--short", "HEAD"], capture_output=True, text=True).stdout.strip()
+    except OSError:
+        commit = ""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            table = json.load(f)
+    except (OSError, ValueError):
+        table = {}
+    table["%s:%d" % (args.workload, args.batch)] = {"bytes": total, "kernel": top.split("<")[0], "launches": count, "commit": commit,
+                                                    "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one step"}
+    with open(TRAFFIC_FILE, "w") as f:
+        json.dump(table, f, indent=1, sort_keys=True)
+        f.write("\n")
+    print(json.dumps(table["%s:%d" % (args.workload, args.batch)]))
+    return 0
 
 
 def measured_peaks():
@@ -112,7 +169,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        mhz, mx, reasons = [], None, set()
+        mhz, mx, reasons, watts = [], None, set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             f = [v.strip() for v in line.split(",")]
@@ -121,14 +178,16 @@ class ClockSampler:
             try:
                 mhz.append(float(f[1]))
                 mx = float(f[2])
+                watts.append(float(f[3]))
             except ValueError:
                 continue
             for name, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         mhz.sort()
+        watts.sort()
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+                "samples": len(mhz), "power_w": watts[len(watts) // 2] if watts else None}
 
 
 
@@ -295,6 +354,115 @@ def cpu_baseline_subprocess(args):
     return {"value": None, "unit": None, "cores": 0, "kind": "port", "sample": "no output: %s" % out.stderr[-200:]}
 
 
+class ArgsView:
+    """The few fields make_workload reads, for the extra configurations."""
+
+    def __init__(self, workload, seed):
+        self.workload, self.seed = workload, seed
+
+
+def time_replays(blib, graph, stream, steps, flush):
+    """Milliseconds of `steps` replays of a compiled graph on `stream`, inputs resident; with `flush`, a buffer larger
+    than the L2 is rewritten before every replay and every replay has its own pair of events."""
+    import torch
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            assert blib.b2vx_graph_run_async(graph) == 0
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        flush.fill_(1)
+        a.record(stream)
+        assert blib.b2vx_graph_run_async(graph) == 0
+        b.record(stream)
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs)
+
+
+def kernel_table(blib, graph, B, iters, step_ms):
+    """Per-kernel times of one step: b2vx_graph_profile puts an event pair around every launch, which costs about
+    2 us apiece and breaks the overlap of consecutive kernels, so the event times add up to more than a step of the
+    timed region; a kernel's time inside the timed region is taken as its share of the event total times the step."""
+    assert blib.b2vx_graph_profile(graph, iters) == 0
+    n = C.c_uint32()
+    blib.b2vx_graph_kernel_count(graph, C.byref(n))
+    per = {}
+    for i in range(n.value):
+        k = B.KernelInfo()
+        blib.b2vx_graph_kernel_info(graph, i, C.byref(k))
+        name = k.name.decode().split("(")[0]
+        d = per.setdefault(name, {"launches": 0, "ms": 0.0, "ops": 0, "bytes": 0})
+        d["launches"] += 1
+        d["ms"] += k.last_ms
+        d["ops"] += k.ops
+        d["bytes"] += k.bytes
+    total = sum(d["ms"] for d in per.values()) or 1.0
+    for d in per.values():
+        d["ms_events"] = d["ms"]
+        d["ms"] = d["ms"] / total * step_ms
+    return per, n.value
+
+
+def roofline_of(t, hbm_gbs, int8_peak):
+    """Achieved rate of one kernel record (ops, bytes, ms) against the roofline min(int8 peak, intensity x HBM)."""
+    ai = t["ops"] / max(t["bytes"], 1)
+    ridge = int8_peak * 1e12 / (hbm_gbs * 1e9)
+    sec = max(t["ms"], 1e-9) / 1e3
+    if t["ops"] and ai >= ridge:
+        achieved = t["ops"] / sec / 1e12
+        return {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak}
+    achieved = t["bytes"] / sec / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs}
+
+
+# The benchmark configurations beside the headline one (workload, batch), timed at N=1 into "configs".
+EXTRA_CONFIGS = [("lenet", 1), ("lenet", 256),
+                 ("conv:3:64:64:56:1", 1), ("conv:3:64:64:56:1", 32), ("conv:3:64:64:56:1", 256),
+                 ("conv:1:64:64:56:1", 256), ("conv:3:64:64:56:2", 256),
+                 ("mobilenetv2", 64),
+                 ("gemm:1024:1024:1024", 1), ("gemm:2048:2048:2048", 1), ("gemm:4096:4096:4096", 1), ("gemm:8192:8192:8192", 1),
+                 ("gemm:1:4096:4096", 1), ("gemm:16:4096:4096", 1), ("gemm:1:8192:8192", 1), ("gemm:16:8192:8192", 1),
+                 ("add:67108864", 1)]
+
+
+def run_configs(blib, B, stream, seed, device, hbm_gbs, int8_peak, flush):
+    """One record per extra configuration: whole-graph value in the configuration's unit (layout conversion of the
+    graph's inputs and outputs included), and the dominant kernel's rate against its roofline."""
+    import torch
+    out = []
+    for spec, batch in EXTRA_CONFIGS:
+        rec = {"workload": spec, "batch": batch}
+        try:
+            wl = make_workload(ArgsView(spec, seed), False, batch, device)
+            g = wl.graph_handle()
+            assert blib.b2vx_graph_set_stream(g, C.c_void_p(stream.cuda_stream)) == 0
+            host_in = torch.empty(wl.in_bytes, dtype=torch.uint8).pin_memory()
+            wl.synthetic_input(seed, host_in.data_ptr())
+            wl.set_input(host_in.data_ptr())
+            for _ in range(3):
+                assert blib.b2vx_graph_run_async(g) == 0
+            assert blib.b2vx_graph_sync(g) == 0
+            steps = 10
+            ms = time_replays(blib, g, stream, steps, flush if wl.in_bytes + wl.out_bytes < 256 * 1024 * 1024 else None)
+            assert blib.b2vx_graph_sync(g) == 0
+            step_ms = ms / steps
+            per, launches = kernel_table(blib, g, B, 2, step_ms)
+            top = max(per, key=lambda n: per[n]["ms"])
+            roof = roofline_of(per[top], hbm_gbs, int8_peak)
+            rec.update({"metric": wl.metric, "value": wl.units / (step_ms / 1e3) * wl.scale, "unit": wl.unit, "ms_per_step": step_ms,
+                        "launches": launches, "kernel": top, "kernel_ms": per[top]["ms"], "bound": roof["bound"],
+                        "achieved": roof["achieved"], "achieved_unit": roof["unit"], "frac": roof["frac"]})
+            wl.close()
+        except Exception as e:   # noqa: BLE001 - one failing configuration must not lose the headline line
+            rec["error"] = str(e)[:200]
+        out.append(rec)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -311,12 +479,21 @@ def main():
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer loop (profiler captures)")
+    ap.add_argument("--no-configs", action="store_true", help="skip the extra configurations (N=1, default workload)")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained replay")
     ap.add_argument("--e2e-threads", type=int, default=3,
                     help="host threads (each with its own graph replica and pinned buffers) sharing the steps of the end-to-end loop")
+    ap.add_argument("--e2e-repeats", type=int, default=5, help="the end-to-end loop times this many rounds of --steps steps")
     ap.add_argument("--profile-iters", type=int, default=3)
+    ap.add_argument("--traffic-from", default=None,
+                    help="an ncu --csv log with dram__bytes_read.sum / dram__bytes_write.sum of one step of --workload at --batch: "
+                         "record the dominant kernel's DRAM traffic in profiles/dram_traffic.json and exit")
     args = ap.parse_args()
+    default_workload = args.workload is None and args.net == "resnet50" and args.batch == 64
     if args.workload is None:
         args.workload = args.net
+    if args.traffic_from:
+        return record_traffic(args)
     if args.impl == "reference":
         return run_reference(args)
 
@@ -350,8 +527,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    n_kernels = C.c_uint32()
-    blib.b2vx_graph_kernel_count(graph, C.byref(n_kernels))
+    # The tensor pipe's dense int8 rate, measured here and now on rank 0's GPU (well under a second)
+    int8_measured = None
+    if rank == 0:
+        tops, sms = C.c_double(0.0), C.c_int32(0)
+        if blib.b2vx_measure_int8_peak(local_rank, 5, C.byref(tops), C.byref(sms)) == 0 and tops.value > 0:
+            int8_measured = tops.value
+
     # A pass that touches less than the L2 (126 MB) would be served from cache on repeat: write a
     # buffer larger than L2 between timed passes and time each pass with its own pair of events.
     flush = None
@@ -367,31 +549,17 @@ def main():
         sampler.start()
         time.sleep(0.3)
     barrier()
-    if flush is None:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(args.steps):
-            assert blib.b2vx_graph_run_async(graph) == 0
-        e1.record(stream)
-        barrier()
-        elapsed = e0.elapsed_time(e1)
-    else:
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-        for a, b in evs:
-            flush.fill_(1)
-            a.record(stream)
-            assert blib.b2vx_graph_run_async(graph) == 0
-            b.record(stream)
-        barrier()
-        elapsed = sum(a.elapsed_time(b) for a, b in evs)
+    elapsed = time_replays(blib, graph, stream, args.steps, flush)
+    barrier()
     assert blib.b2vx_graph_sync(graph) == 0, "a kernel reported a device-side timeout"
     ms = torch.tensor([elapsed], device="cuda")
     # ---- end to end through the public calls, host buffers pinned
     # Every step copies its input from pinned host memory, runs, and copies its result back, all through the
     # synchronous public calls.  As in the reference's multi-thread sample, --e2e-threads host threads each own
     # a replica of the graph and their own pinned buffers and take the steps in turn, so one replica's copies
-    # overlap the other's kernels; 1 gives the strictly serial copy-run-copy loop.
-    e2e_steps = 0 if args.no_e2e else args.steps
+    # overlap the other's kernels; 1 gives the strictly serial copy-run-copy loop.  The threads are started and
+    # parked behind a barrier before the clock starts, and the timed region is --e2e-repeats rounds of --steps steps.
+    e2e_steps = 0 if args.no_e2e else args.steps * max(1, args.e2e_repeats)
     n_host = max(1, min(args.e2e_threads, e2e_steps)) if e2e_steps else 1
     replicas = [(wl, host_in, host_out)]
     for _ in range(1, n_host):
@@ -401,9 +569,11 @@ def main():
         rin.copy_(host_in)
         replicas.append((r, rin, rout))
 
-    def feed(replica, count):
+    def feed(replica, count, gate=None):
         r, rin, rout = replica
         torch.cuda.set_device(local_rank)   # a new host thread starts on device 0
+        if gate is not None:
+            gate.wait()
         for _ in range(count):
             r.set_input(rin.data_ptr())
             r.run()
@@ -411,71 +581,83 @@ def main():
 
     for rep in replicas if e2e_steps else []:
         feed(rep, 2)
-    barrier()
     counts = [e2e_steps // n_host + (1 if k < e2e_steps % n_host else 0) for k in range(n_host)]
-    threads = [threading.Thread(target=feed, args=(rep, cnt)) for rep, cnt in zip(replicas[1:], counts[1:])]
-    t0 = time.perf_counter()
+    gate = threading.Barrier(n_host)
+    threads = [threading.Thread(target=feed, args=(rep, cnt, gate)) for rep, cnt in zip(replicas[1:], counts[1:])]
     for t in threads:
         t.start()
+    barrier()
+    t0 = time.perf_counter()
     if e2e_steps:
-        feed(replicas[0], counts[0])
+        feed(replicas[0], counts[0], gate)
     for t in threads:
         t.join()
     torch.cuda.synchronize()
     e2e_ms = torch.tensor([1e3 * (time.perf_counter() - t0)], device="cuda")
     if n_host > 1:
         assert torch.equal(replicas[0][2], replicas[1][2]), "graph replicas disagree on the same input"
+    for r, _, _ in replicas[1:]:
+        r.close()
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(ms.item()), float(e2e_ms.item())
 
+    # ---- sustained: the same graph back to back for at least two seconds, clocks and power sampled meanwhile
+    sustained = None
+    if not args.no_sustained and flush is None:
+        step_ms = ms / args.steps
+        n_sus = max(args.steps, int(2200.0 / max(step_ms, 1e-3)))
+        sus_sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sus_sampler.start()
+        barrier()
+        sus_ms = torch.tensor([time_replays(blib, graph, stream, n_sus, None)], device="cuda")
+        barrier()
+        sus_clocks = sus_sampler.stop() if rank == 0 else None
+        if world > 1:
+            dist.all_reduce(sus_ms, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            sus_ms = float(sus_ms.item())
+            sustained = {"value": wl.units * world * n_sus / (sus_ms / 1e3) * wl.scale, "unit": wl.unit, "steps": n_sus,
+                         "seconds": sus_ms / 1e3, "ms_per_step": sus_ms / n_sus, "sm_mhz_median": sus_clocks["sm_mhz"],
+                         "power_w_median": sus_clocks.get("power_w"), "reasons": sus_clocks["reasons"],
+                         "ms_per_step_x_mhz": (sus_ms / n_sus) * sus_clocks["sm_mhz"] if sus_clocks["sm_mhz"] else None}
+
     if rank == 0:
         units = wl.units * world * args.steps
         value = units / (ms / 1e3) * wl.scale
-        e2e_value = units / (e2e_ms / 1e3) * wl.scale if e2e_steps else None
+        e2e_value = wl.units * world * e2e_steps / (e2e_ms / 1e3) * wl.scale if e2e_steps else None
         # ---- roofline of the dominant kernel, per-kernel CUDA events measured live
-        assert blib.b2vx_graph_profile(graph, args.profile_iters) == 0
-        per = {}
-        for i in range(n_kernels.value):
-            k = B.KernelInfo()
-            blib.b2vx_graph_kernel_info(graph, i, C.byref(k))
-            name = k.name.decode().split("(")[0]
-            d = per.setdefault(name, {"launches": 0, "ms": 0.0, "ops": 0, "bytes": 0})
-            d["launches"] += 1
-            d["ms"] += k.last_ms
-            d["ops"] += k.ops
-            d["bytes"] += k.bytes
-        total_ms = sum(d["ms"] for d in per.values()) or 1.0
-        top = max(per, key=lambda n: per[n]["ms"])
-        # Events between kernels cost about 2 us apiece and break the overlap of consecutive kernels, so
-        # the per-kernel times add up to more than a step of the timed region.  The kernel's time inside
-        # the timed region is taken as its share of the event-measured total times the measured step.
         step_ms = ms / args.steps
-        for d in per.values():
-            d["ms_events"] = d["ms"]
-            d["ms"] = d["ms"] / total_ms * step_ms
-        total_ms = step_ms
+        per, n_kernels = kernel_table(blib, graph, B, args.profile_iters, step_ms)
+        top = max(per, key=lambda n: per[n]["ms"])
         peaks = measured_peaks()
-        int8_peak = 2.0 * peaks["bf16_sustained"]
+        int8_assumed = 2.0 * peaks["bf16_sustained"]
+        int8_peak = int8_measured if int8_measured else int8_assumed
         t = per[top]
-        ai = t["ops"] / max(t["bytes"], 1)
-        ridge = int8_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
-        if t["ops"] and ai >= ridge:
-            achieved = t["ops"] / (t["ms"] / 1e3) / 1e12
-            roof = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak}
-        else:
-            achieved = t["bytes"] / (t["ms"] / 1e3) / 1e9
-            roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"]}
-        roof.update({"traffic": NCU_DRAM_TRAFFIC.get((args.workload, args.batch)), "kernel": top, "launches_per_step": t["launches"], "kernel_ms_per_step": t["ms"],
+        roof = roofline_of(t, peaks["hbm_gbs"], int8_peak)
+        traffic = dram_traffic(args.workload, args.batch)
+        roof.update({"traffic": traffic["bytes"] if traffic else None, "traffic_record": traffic,
+                     "kernel": top, "launches_per_step": t["launches"], "kernel_ms_per_step": t["ms"],
                      "kernel_ms_per_step_events": t["ms_events"],
                      "timing": "per-kernel CUDA events (b2vx_graph_profile) give the shares; kernel time = share x measured step",
-                     "share_of_step": t["ms"] / total_ms, "tops": t["ops"] / (t["ms"] / 1e3) / 1e12 if t["ms"] else None,
-                     "int8_peak_assumed": "2 x bf16_tflops_sustained (%s)" % peaks["source"],
+                     "share_of_step": t["ms"] / step_ms, "tops": t["ops"] / (t["ms"] / 1e3) / 1e12 if t["ms"] else None,
+                     "algorithmic_bytes": t["bytes"], "algorithmic_ops": t["ops"],
+                     "int8_peak_measured": int8_measured,
+                     "int8_peak_measured_how": "tcgen05.mma.kind::i8 issue-rate microbenchmark on every SM, operands in shared memory, best of 5 x 10 ms",
+                     "int8_peak_assumed": int8_assumed,
+                     "frac_of_int8_peak": (t["ops"] / (t["ms"] / 1e3) / 1e12) / int8_peak if t["ms"] and t["ops"] else None,
+                     "frac_of_hbm": (t["bytes"] / (t["ms"] / 1e3) / 1e9) / peaks["hbm_gbs"] if t["ms"] else None,
                      "peak_source": peaks["source"],
                      "per_kernel_ms": {n: round(d["ms"], 4) for n, d in sorted(per.items(), key=lambda kv: -kv[1]["ms"])},
                      "per_kernel_ms_events": {n: round(d["ms_events"], 4) for n, d in sorted(per.items(), key=lambda kv: -kv[1]["ms"])}})
+        configs = None
+        if world == 1 and default_workload and not args.no_configs:
+            cfg_flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+            configs = run_configs(blib, B, stream, args.seed, local_rank, peaks["hbm_gbs"], int8_peak, cfg_flush)
+            del cfg_flush
         cpu = None if (args.no_cpu_baseline or world > 1) else cpu_baseline_subprocess(args)
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -486,9 +668,10 @@ def main():
                        "l2": ("a 192 MB buffer is rewritten between timed passes (L2 flush); each pass has its own events"
                               if flush is not None else "the per-step working set exceeds the 126 MB L2")},
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
-                    "ms_per_step": e2e_ms / args.steps if e2e_steps else None, "host_threads": n_host},
-            "gpu_launches": n_kernels.value * args.steps,
-            "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
+                    "ms_per_step": e2e_ms / e2e_steps if e2e_steps else None, "host_threads": n_host,
+                    "steps": e2e_steps, "repeats": max(1, args.e2e_repeats) if e2e_steps else 0},
+            "gpu_launches": n_kernels * args.steps,
+            "roofline": roof, "sustained": sustained, "cpu_baseline": cpu, "clocks": clocks, "configs": configs,
         }
         print(json.dumps(line))
     wl.close()

@@ -301,6 +301,13 @@ b2vx_status b2vx_conv2d_first_layer_noalloc(const b2vx_conv2d_noalloc_desc* d, c
                                             const int32_t* bias_full, const float* acc_scale, void* y_cl,
                                             void* cuda_stream, char* err, size_t err_len);
 
+/* Measurement aid with no counterpart in the reference: the dense int8 rate of
+ * the tensor pipe of GPU `device_id`, in TOP/s (2 x multiply-accumulate), from
+ * an issue-rate microbenchmark (tcgen05.mma.kind::i8 on operands resident in
+ * shared memory, no epilogue, every SM, about 10 ms per repetition, best of
+ * `reps`).  It is the denominator of the "fraction of int8 peak" figures. */
+b2vx_status b2vx_measure_int8_peak(int32_t device_id, int32_t reps, double* tops_out, int32_t* sm_count_out);
+
 /* Pinned host memory for callers that want asynchronous tensor_write/read. */
 b2vx_status b2vx_host_alloc(void** out, size_t bytes);
 void b2vx_host_free(void* p);

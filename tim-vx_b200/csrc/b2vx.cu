@@ -2064,6 +2064,27 @@ b2vx_status b2vx_graph_profile(b2vx_graph* g, uint32_t iters) {
   return b2vx_graph_sync(g);
 }
 
+b2vx_status b2vx_measure_int8_peak(int32_t device_id, int32_t reps, double* tops_out, int32_t* sm_count_out) {
+  if (!tops_out || reps < 1 || reps > 100) return B2VX_INVALID_ARG;
+  *tops_out = 0.0;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device_id < 0 || device_id >= count) return B2VX_INVALID_ARG;
+  DeviceGuard guard(device_id);
+  if (!gemm_tc_available()) return B2VX_UNSUPPORTED;
+  int* d_status = nullptr;
+  if (cudaMalloc(reinterpret_cast<void**>(&d_status), sizeof(int)) != cudaSuccess) return B2VX_OOM;
+  cudaMemset(d_status, 0, sizeof(int));
+  int sms = 0, h_status = 0;
+  const double tops = gemm_tc_measure_int8_peak(reps, &sms, d_status);
+  cudaMemcpy(&h_status, d_status, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(d_status);
+  if (h_status != 0) return B2VX_DEVICE_TIMEOUT;
+  if (tops <= 0.0) return B2VX_CUDA_ERROR;
+  *tops_out = tops;
+  if (sm_count_out) *sm_count_out = sms;
+  return B2VX_OK;
+}
+
 b2vx_status b2vx_host_alloc(void** out, size_t bytes) {
   if (!out) return B2VX_INVALID_ARG;
   if (cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {

@@ -723,6 +723,60 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
+// ---- issue-rate microbenchmark of the int8 tensor pipe ----------------------------------------
+// One CTA per SM; operands (pseudo-random bytes) stay in shared memory, one thread issues `iters` rounds of
+// four M=128, N=256, K=32 tcgen05.mma.kind::i8 (one 128-byte K block) into two alternating accumulators and
+// commits every round to an mbarrier it waits on two rounds later, so the pipe always has work queued.  No
+// loads from global memory and no epilogue: what is timed is the rate at which the tensor pipe retires MMAs.
+__global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int* status) {
+  extern __shared__ uint8_t peak_smem[];
+  __shared__ unsigned long long bars[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const uint32_t base = (smem_u32(peak_smem) + 1023u) & ~1023u;
+  uint8_t* tiles = peak_smem + (base - smem_u32(peak_smem));
+  uint32_t h = 0x9E3779B9u * (threadIdx.x + 1u) + blockIdx.x;
+  for (uint32_t i = threadIdx.x; i < (128u + 256u) * 128u / 4u; i += blockDim.x) {
+    h = h * 1664525u + 1013904223u;
+    reinterpret_cast<uint32_t*>(tiles)[i] = h;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars[0]), 1);
+    mbar_init(smem_u32(&bars[1]), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the operand bytes were written with ordinary stores
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint32_t idesc = (2u << 4) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+    const uint64_t da = make_smem_desc(base, 8u * 128u, 2u), db = make_smem_desc(base + 128u * 128u, 8u * 128u, 2u);
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      const int b = it & 1;
+      if (it >= 2) ok = mbar_wait(smem_u32(&bars[b]), ((it - 2) >> 1) & 1, &abort_flag, status, 9);
+      if (!ok) break;
+      tc_fence_after();
+      for (int k = 0; k < 4; ++k) tc_mma_i8(tmem + b * 256, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc, 1);
+      tc_commit(smem_u32(&bars[b]));
+    }
+    for (int it = max(0, iters - 2); it < iters && ok; ++it) ok = mbar_wait(smem_u32(&bars[it & 1]), (it >> 1) & 1, &abort_flag, status, 9);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1102,6 +1156,34 @@ GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s) {
     best.rows = best.data + extra;
   }
   return best;
+}
+
+// Dense int8 tensor-pipe rate of the current device in TOP/s (2 * MAC): best of `reps` launches of the
+// microbenchmark above on every SM; *sm_count receives the number of SMs used.  Returns 0 on failure.
+double gemm_tc_measure_int8_peak(int reps, int* sm_count, int* status) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0.0;
+  const size_t smem = (128 + 256) * 128 + 1024;
+  if (cudaFuncSetAttribute(int8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMinDynSmem)) != cudaSuccess) return 0.0;
+  (void)smem;
+  cudaEvent_t e0, e1;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return 0.0;
+  const int iters = 20000;   // x 4 MMAs of 128 x 256 x 32: about 10 ms per launch
+  double best = 0.0;
+  for (int r = 0; r < reps + 1; ++r) {
+    cudaEventRecord(e0, 0);
+    int8_peak_kernel<<<sms, 128, kMinDynSmem, 0>>>(iters, status);   // kMinDynSmem keeps it to one CTA per SM
+    cudaEventRecord(e1, 0);
+    if (cudaEventSynchronize(e1) != cudaSuccess) { best = 0.0; break; }
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    const double tops = 2.0 * 128.0 * 256.0 * 128.0 * iters * sms / (ms * 1e-3) / 1e12;
+    if (r > 0 && tops > best) best = tops;   // the first launch warms up
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (sm_count) *sm_count = sms;
+  return cudaGetLastError() == cudaSuccess ? best : 0.0;
 }
 
 size_t gemm_tc_plan_bytes(void) { return sizeof(GemmTcPlan); }

@@ -221,6 +221,9 @@ void gemm_tc_plan_destroy(GemmTcPlan* p);
 cudaError_t gemm_tc_launch(const GemmTcPlan* p, cudaStream_t s);
 // 1 when this build and device can run the tensor-core path.
 int gemm_tc_available(void);
+// Measured dense int8 rate of the tensor pipe on the current device, TOP/s (issue-rate microbenchmark: operands in
+// shared memory, no epilogue); 0 when it cannot run.  status: device int for the bounded waits, as for the GEMM.
+double gemm_tc_measure_int8_peak(int reps, int* sm_count, int* status);
 
 }  // namespace b2vx
 #endif  // B2VX_KERNELS_H_

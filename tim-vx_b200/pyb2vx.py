@@ -118,10 +118,13 @@ def load(path):
         "b2vx_graph_kernel_count": (st, [vp, C.POINTER(u32)]),
         "b2vx_graph_kernel_info": (st, [vp, u32, C.POINTER(KernelInfo)]),
         "b2vx_graph_profile": (st, [vp, u32]),
+        "b2vx_measure_int8_peak": (st, [C.c_int32, C.c_int32, C.POINTER(C.c_double), C.POINTER(C.c_int32)]),
         "b2vx_host_alloc": (st, [C.POINTER(vp), C.c_size_t]),
         "b2vx_host_free": (None, [vp]),
     }
     for name, (res, args) in sigs.items():
+        if name == "b2vx_measure_int8_peak" and not hasattr(lib, name):
+            continue   # a measurement of the GPU: the CPU oracle library has no such entry
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
