@@ -251,6 +251,8 @@ class OpWorkload:
             self.metric, self.unit, self.scale = "quantized_add_gbytes_per_sec", "GB/s", 3.0 / 1e9
         elif kind in ("concat", "transpose"):
             self.metric, self.unit, self.scale = kind + "_gbytes_per_sec", "GB/s", 2.0 / 1e9   # each element read and written once
+        elif kind == "fcchain":
+            self.metric, self.unit, self.scale = "fullyconnected_chain_gbytes_per_sec", "GB/s", self.w["bytes"] / self.units / 1e9
         else:
             self.metric = "conv2d_int8_tops" if kind in ("conv", "convadd") else "fullyconnected_int8_tops"
             self.unit, self.scale = "TOP/s", self.ops / self.units / 1e12
@@ -287,7 +289,12 @@ class OpWorkload:
 def make_workload(args, oracle, batch, device):
     if ":" in args.workload:
         import pyb2vx as B
-        return OpWorkload(B.ORACLE_LIB if oracle else B.PRODUCT_LIB, args.workload, batch, args.seed, device)
+        lib_path = B.PRODUCT_LIB
+        if oracle:   # the CPU baseline / reference arm: the one place outside tests/ that runs the oracle
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import oracle_paths
+            lib_path = oracle_paths.ORACLE_LIB
+        return OpWorkload(lib_path, args.workload, batch, args.seed, device)
     return NetWorkload(SAMPLES_ORACLE_LIB if oracle else SAMPLES_LIB, args.workload, batch, args.seed, device)
 
 
@@ -426,6 +433,7 @@ EXTRA_CONFIGS = [("lenet", 1), ("lenet", 256),
                  ("mobilenetv2", 64),
                  ("gemm:1024:1024:1024", 1), ("gemm:2048:2048:2048", 1), ("gemm:4096:4096:4096", 1), ("gemm:8192:8192:8192", 1),
                  ("gemm:1:4096:4096", 1), ("gemm:16:4096:4096", 1), ("gemm:1:8192:8192", 1), ("gemm:16:8192:8192", 1),
+                 ("fcchain:1:4096:12", 1), ("fcchain:16:4096:12", 1), ("fcchain:1:8192:4", 1), ("fcchain:16:8192:4", 1),
                  ("add:67108864", 1)]
 
 
@@ -471,7 +479,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None,
                     help="resnet50 (default), mobilenetv2, lenet, or one operator: conv:k:cin:cout:hw:stride, "
-                         "convadd:k:cin:cout:hw:stride, gemm:m:n:k, add:elements, concat:c1:c2:hw, transpose:c:hw "
+                         "convadd:k:cin:cout:hw:stride, gemm:m:n:k, fcchain:m:n:layers, add:elements, concat:c1:c2:hw, transpose:c:hw "
                          "(tim-vx_b200/opworkloads.py)")
     ap.add_argument("--net", default="resnet50", help="older spelling of --workload for the networks")
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")

@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 
 import graph_cases as G
+import oracle_paths
 import pyb2vx as B
 
 pytestmark = pytest.mark.gpu
@@ -39,7 +40,7 @@ def test_reference_vectors(product_lib, reference_cases, conv_kernel):
     and GPU vs the oracle output recorded in the fixture (bit for bit for integers)."""
     failures = []
     for case in reference_cases:
-        g, inputs, expects, recorded = B.graph_from_case(product_lib, case)
+        g, inputs, expects, recorded = oracle_paths.graph_from_case(product_lib, case)
         try:
             g.compile()
             for tid, arr in inputs:
@@ -199,6 +200,26 @@ def test_small_m_fc_on_tensor_cores_matches_oracle(oracle_lib, product_lib, name
     G.assert_same(want, got)
 
 
+SMALL_M = ["fc_1024_m1", "fc_1024_m16", "fc_2048_1000", "fc_k500_n10", "fc_k800_from4d", "fc_m16_n30", "fc_m3_u8zp",
+           "fc_m6_u8zp", "fc_m7_n1001", "fc_m8_n30", "fc_m9_u8zp", "fc_u8_zp"]
+
+
+@pytest.mark.parametrize("name", SMALL_M)
+@pytest.mark.parametrize("fc_mma", ["0", "1"])
+def test_small_m_fc_both_kernels_match_oracle(oracle_lib, product_lib, name, fc_mma):
+    """Every few-row shape on the dp4a kernel (B2VX_FC_MMA=0; up to 16 rows) and on the mma.sync kernel (=1): ragged
+    channel counts, K that is not a multiple of 64, a weight zero point, one to sixteen rows."""
+    want, _ = G.run_case(oracle_lib, FC_CASES[name], seed=3)
+    os.environ["B2VX_FC_MMA"] = fc_mma
+    os.environ.pop("B2VX_CONV_KERNEL", None)
+    try:
+        got, kernels = G.run_case(product_lib, FC_CASES[name], seed=3)
+    finally:
+        os.environ.pop("B2VX_FC_MMA", None)
+    assert any(k["name"] == "fc_small_m" for k in kernels), [k["name"] for k in kernels]
+    G.assert_same(want, got)
+
+
 def test_small_m_fc_kernel_is_taken(product_lib):
     _, kernels = G.run_case(product_lib, FC_CASES["fc_1024_m1"], seed=3)
     assert [k["name"] for k in kernels if k["name"].startswith(("fc_", "gemm_"))] == ["fc_small_m"], [k["name"] for k in kernels]
@@ -212,6 +233,9 @@ POOL_CASES = {
     "avg_pad": G.pool_q(10, 10, 32, 1, B.POOL_AVG, (3, 3), (2, 2), pad=(1, 1, 1, 1)),
     "avg_android_pad": G.pool_q(10, 10, 32, 1, B.POOL_AVG_ANDROID, (3, 3), (2, 2), pad=(1, 1, 1, 1)),
     "avg_s8": G.pool_q(8, 8, 16, 1, B.POOL_AVG, (2, 2), (2, 2), in_q=(0.1, -5), dtype=B.DT_INT8),
+    # L2: sqrt of the mean square over the taps inside the input (parity unpinned: the reference holds no vector)
+    "l2_3x3_pad": G.pool_q(10, 10, 32, 2, B.POOL_L2, (3, 3), (2, 2), pad=(1, 1, 1, 1), in_q=(0.05, 120), out_q=(0.03, 0)),
+    "l2_global_s8": G.pool_q(7, 7, 48, 2, B.POOL_L2, (7, 7), (7, 7), in_q=(0.1, -5), out_q=(0.08, -128), dtype=B.DT_INT8),
 }
 
 
@@ -235,6 +259,33 @@ ELTWISE_CASES = {
 def test_elementwise_matches_oracle(oracle_lib, product_lib, name):
     want, _ = G.run_case(oracle_lib, ELTWISE_CASES[name], seed=21)
     got, _ = G.run_case(product_lib, ELTWISE_CASES[name], seed=21)
+    G.assert_same(want, got)
+
+
+def _addn_case(n_in, dims, dtype=B.DT_UINT8):
+    def build(g, rng):
+        ins = []
+        for k in range(n_in):
+            if dtype == B.DT_FLOAT32:
+                t = g.tensor(dtype, dims, B.ATTR_INPUT)
+                a = rng.normal(size=dims[::-1]).astype(np.float32)
+            else:
+                t = g.tensor(dtype, dims, B.ATTR_INPUT, scale=0.01 + 0.007 * k, zero_point=100 + 9 * k if dtype == B.DT_UINT8 else -3 + k)
+                a = rng.integers(0, 256, size=dims[::-1]).astype(np.uint8).view(np.int8 if dtype == B.DT_INT8 else np.uint8)
+            ins.append((t, a))
+        y = g.tensor(dtype, [], B.ATTR_OUTPUT, **({} if dtype == B.DT_FLOAT32 else dict(scale=0.05, zero_point=120 if dtype == B.DT_UINT8 else 5)))
+        g.addn([t for t, _ in ins], y)
+        return ins, [y]
+    return build
+
+
+@pytest.mark.parametrize("n_in,dims,dtype", [(2, [14, 14, 24, 2], B.DT_UINT8), (3, [14, 14, 24, 2], B.DT_UINT8), (5, [7, 5, 40, 3], B.DT_INT8),
+                                             (16, [33], B.DT_UINT8), (4, [9, 3, 5], B.DT_FLOAT32)])
+def test_addn_matches_oracle(oracle_lib, product_lib, n_in, dims, dtype):
+    """ops::AddN: two inputs run the Add kernels, more the n-input kernel (the sum stays float32 until the end)."""
+    want, _ = G.run_case(oracle_lib, _addn_case(n_in, dims, dtype), seed=5)
+    got, kernels = G.run_case(product_lib, _addn_case(n_in, dims, dtype), seed=5)
+    assert any(k["name"] == ("addn" if n_in > 2 else ("add_q" if dtype != B.DT_FLOAT32 else "add_f32")) for k in kernels), [k["name"] for k in kernels]
     G.assert_same(want, got)
 
 

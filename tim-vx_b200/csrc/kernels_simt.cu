@@ -541,6 +541,7 @@ __global__ void pool_q_kernel(const uint8_t* __restrict__ x, int type, float in_
   const int n = static_cast<int>(t / g.Ho);
   int sum[4] = {0, 0, 0, 0};
   int mx[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // type 2 (L2): squares of the real values, added in tap order
   int count = 0;
   for (int ky = 0; ky < g.kh; ++ky) {
     const int hi = ho * g.sy - g.pt + ky;
@@ -557,6 +558,10 @@ __global__ void pool_q_kernel(const uint8_t* __restrict__ x, int type, float in_
         const int v = XS ? static_cast<int>(static_cast<int8_t>(b)) : static_cast<int>(b);
         sum[j] += v - in_zp;
         mx[j] = max(mx[j], v);
+        if (type == 2) {
+          const float real = __fmul_rn(__int2float_rn(v - in_zp), in_scale);
+          sq[j] = __fadd_rn(sq[j], __fmul_rn(real, real));
+        }
       }
     }
   }
@@ -565,7 +570,9 @@ __global__ void pool_q_kernel(const uint8_t* __restrict__ x, int type, float in_
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     int q;
-    if (type == 0) {
+    if (type == 2) {
+      q = requant(count ? __fsqrt_rn(__fdiv_rn(sq[j], __int2float_rn(count))) : 0.0f, out);
+    } else if (type == 0) {
       q = count ? mx[j] : in_zp;
       if (!same_quant) q = requant(__fmul_rn(__fsub_rn(__int2float_rn(q), __int2float_rn(in_zp)), in_scale), out);
     } else {
@@ -748,7 +755,7 @@ __global__ void pool_f32_kernel(const float* __restrict__ x, int type, ConvGeom 
   const long long t = p / g.Wo;
   const int ho = static_cast<int>(t % g.Ho);
   const int n = static_cast<int>(t / g.Ho);
-  float sum = 0.0f, mx = -INFINITY;
+  float sum = 0.0f, mx = -INFINITY, sq = 0.0f;
   int count = 0;
   for (int ky = 0; ky < g.kh; ++ky) {
     const int hi = ho * g.sy - g.pt + ky;
@@ -759,12 +766,13 @@ __global__ void pool_f32_kernel(const float* __restrict__ x, int type, ConvGeom 
       const float v = x[((static_cast<size_t>(n) * g.H + hi) * g.W + wi) * g.Cp + c];
       sum = __fadd_rn(sum, v);
       mx = fmaxf(mx, v);
+      sq = __fadd_rn(sq, __fmul_rn(v, v));
       ++count;
     }
   }
   const float div = type == 1 ? static_cast<float>(g.kw * g.kh) : static_cast<float>(count);
   float r = 0.0f;
-  if (count) r = type == 0 ? mx : __fdiv_rn(sum, div);
+  if (count) r = type == 0 ? mx : (type == 2 ? __fsqrt_rn(__fdiv_rn(sq, __int2float_rn(count))) : __fdiv_rn(sum, div));
   y[static_cast<size_t>(p) * g.Cp + c] = r;
 }
 
@@ -1550,7 +1558,7 @@ void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int i
                    OutQuant out, void* y, cudaStream_t s) {
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* yp = static_cast<uint8_t*>(y);
-  if (g.kw * g.kh <= 256 && g.dx == 1 && g.dy == 1) {
+  if (type != 2 && g.kw * g.kh <= 256 && g.dx == 1 && g.dy == 1) {   // (L2 pooling runs the general kernel)
     const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * (g.Cp / 16);
     if (total == 0) return;
     if (g.kw * g.kh >= 32 && total <= 148LL * 2048 / 32 * 8) {
@@ -1608,6 +1616,36 @@ void launch_add_q(const void* a, int a_signed, float sa, int za, const void* b, 
   uint4* py = static_cast<uint4*>(y);
   if (fast) launch_pdl(add_q_kernel<true>, dim3(grid), dim3(256), 0, s, pa, pb, p, py, n16);
   else launch_pdl(add_q_kernel<false>, dim3(grid), dim3(256), 0, s, pa, pb, p, py, n16);
+}
+
+// AddN: one element per thread (the op is rare on the path; the two-input case runs the tuned Add kernels).
+template <int ELEM>
+__global__ void __launch_bounds__(256) addn_kernel(AddNParams p, void* __restrict__ y, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  float r = 0.0f;
+#pragma unroll 1
+  for (int k = 0; k < p.n_in; ++k) {
+    float v;
+    if (ELEM == 4) {
+      v = static_cast<const float*>(p.x[k])[i];
+    } else {
+      const int q = p.is_signed[k] ? static_cast<int>(static_cast<const int8_t*>(p.x[k])[i]) : static_cast<int>(static_cast<const uint8_t*>(p.x[k])[i]);
+      v = __fmul_rn(__int2float_rn(q - p.zp[k]), p.scale[k]);
+    }
+    r = k == 0 ? v : __fadd_rn(r, v);
+  }
+  if (ELEM == 4) static_cast<float*>(y)[i] = r;
+  else static_cast<uint8_t*>(y)[i] = static_cast<uint8_t>(requant(r, p.out) & 0xFF);
+}
+
+void launch_addn(const AddNParams& p, int elem, void* y, size_t n, cudaStream_t s) {
+  if (n == 0) return;
+  const unsigned grid = grid_for(static_cast<long long>(n), 256);
+  if (elem == 4) launch_pdl(addn_kernel<4>, dim3(grid), dim3(256), 0, s, p, y, n);
+  else launch_pdl(addn_kernel<1>, dim3(grid), dim3(256), 0, s, p, y, n);
 }
 
 void launch_add_q_lut(const void* a, const void* b, const uint8_t* table, void* y, size_t n, cudaStream_t s) {
@@ -1720,6 +1758,115 @@ void launch_im2col(const void* x, int Cs, int Kp, int zx, const ConvGeom& g, voi
                                                              static_cast<uint8_t*>(col));
 }
 
+// The same shapes with 9 to 16 rows (and large ones with fewer): weight streaming through the warp-level
+// integer MMA, mma.sync m16n8k32: the sixteen input rows are the MMA's M, eight output channels its N.
+// A block of eight warps owns 32 output channels (four n-tiles per warp, so that the input fragments
+// are loaded once for four MMAs) and splits K in 64-byte pieces among its warps.  K is a reduction
+// dimension, so any assignment of bytes to the MMA's k positions is right as long as both operands use
+// the same one: a lane's 16-byte load of a weight row (k bytes 16q .. 16q+15 of the piece, q = lane % 4)
+// feeds two MMAs, words (0,1) and (2,3), and the same words of the two input rows it loads are the A
+// fragments.  All HBM traffic is 128-bit loads of 128 contiguous bytes per row and step.  (Tried and dropped:
+// 16-byte asynchronous copies into a six-deep ring in shared memory, 1.4 times slower.)  Partial sums of the
+// eight warps meet in shared memory; the requantization is the exact sequence.
+// HAS_DZ: weights keep a zero point dz, removed as dz * sum(x) from an MMA against all-ones bytes.
+template <bool XS>
+__device__ __forceinline__ void mma_m16n8k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (XS)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool XS, bool HAS_DZ>
+__global__ void __launch_bounds__(256, 2) fc_mma16_kernel(const uint8_t* __restrict__ A, const int8_t* __restrict__ B, int M, int Kp,
+                                                          int Oc, int Ocp, ContractEpilogue ep, uint8_t* __restrict__ D, int ldd) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int NT = 4;                              // n-tiles of eight channels per warp
+  __shared__ int partial[8][16][NT * 8 + 1];
+  __shared__ int s_sum[8][16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q = lane & 3, r = lane >> 2;             // k quarter of a piece; row (and channel within an n-tile)
+  const int c0 = blockIdx.x * (NT * 8);
+  int acc[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+  int accs[4] = {0, 0, 0, 0};
+  const bool row_lo = r < M, row_hi = r + 8 < M;
+  const uint8_t* a_lo = A + static_cast<size_t>(row_lo ? r : 0) * Kp + q * 16;
+  const uint8_t* a_hi = A + static_cast<size_t>(row_hi ? r + 8 : 0) * Kp + q * 16;
+  const int8_t* b_row[NT];
+  bool b_ok[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const int ch = c0 + 8 * t + r;
+    b_ok[t] = ch < Ocp;
+    b_row[t] = B + static_cast<size_t>(b_ok[t] ? ch : 0) * Kp + q * 16;
+  }
+  // Every warp takes one contiguous eighth of K (in whole pieces), so that its successive loads of a weight row
+  // are neighbours in memory; two pieces (128 bytes per row) per step, all ten loads issued before the first MMA.
+  const int pieces = (Kp + 63) >> 6;
+  const int per_warp = (pieces + 7) >> 3;
+  const int p_begin = warp * per_warp, p_end = min(pieces, p_begin + per_warp);
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+  for (int p0 = p_begin; p0 < p_end; p0 += 2) {
+    uint4 w[2][NT], xl[2], xh[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int k = (p0 + u) * 64;
+      const bool k_ok = p0 + u < p_end && k + q * 16 < Kp;
+#pragma unroll
+      for (int t = 0; t < NT; ++t) w[u][t] = (k_ok && b_ok[t]) ? __ldcs(reinterpret_cast<const uint4*>(b_row[t] + k)) : zero4;
+      xl[u] = (k_ok && row_lo) ? __ldg(reinterpret_cast<const uint4*>(a_lo + k)) : zero4;
+      xh[u] = (k_ok && row_hi) ? __ldg(reinterpret_cast<const uint4*>(a_hi + k)) : zero4;
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        mma_m16n8k32<XS>(acc[t], xl[u].x, xh[u].x, xl[u].y, xh[u].y, w[u][t].x, w[u][t].y);
+        mma_m16n8k32<XS>(acc[t], xl[u].z, xh[u].z, xl[u].w, xh[u].w, w[u][t].z, w[u][t].w);
+      }
+      if (HAS_DZ) {
+        mma_m16n8k32<XS>(accs, xl[u].x, xh[u].x, xl[u].y, xh[u].y, 0x01010101u, 0x01010101u);
+        mma_m16n8k32<XS>(accs, xl[u].z, xh[u].z, xl[u].w, xh[u].w, 0x01010101u, 0x01010101u);
+      }
+    }
+  }
+  // accumulator layout: c0, c1 = (row r, channels 2q, 2q+1), c2, c3 = (row r + 8, the same channels)
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    partial[warp][r][8 * t + 2 * q] = acc[t][0];
+    partial[warp][r][8 * t + 2 * q + 1] = acc[t][1];
+    partial[warp][r + 8][8 * t + 2 * q] = acc[t][2];
+    partial[warp][r + 8][8 * t + 2 * q + 1] = acc[t][3];
+  }
+  if (HAS_DZ && q == 0) {
+    s_sum[warp][r] = accs[0];
+    s_sum[warp][r + 8] = accs[2];
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < 16 * NT * 8; o += 256) {
+    const int m = o / (NT * 8), c = o - m * (NT * 8);
+    const int oc = c0 + c;
+    if (m >= M || oc >= Oc) continue;
+    int total = 0, sx = 0;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) {
+      total += partial[w8][m][c];
+      if (HAS_DZ) sx += s_sum[w8][m];
+    }
+    if (HAS_DZ) total -= ep.dz_uniform * sx;
+    const float real = __fmul_rn(__int2float_rn(total + ep.bias_full[oc]), ep.acc_scale[oc]);
+    D[static_cast<size_t>(m) * ldd + oc] = static_cast<uint8_t>(requant(real, ep.out) & 0xFF);
+  }
+}
+
 template <int CH, int MT>
 static void launch_fc_small_m_t(const void* A, int a_signed, const int8_t* B, int M, int Kp, int Oc, int Ocp,
                                 const ContractEpilogue& e, void* D, int ldd, cudaStream_t s) {
@@ -1739,6 +1886,23 @@ static void launch_fc_small_m_t(const void* A, int a_signed, const int8_t* B, in
 void launch_fc_small_m(const void* A, int a_signed, const int8_t* B, int M, int Kp, int Oc, int Ocp, const ContractEpilogue& e,
                        void* D, int ldd, cudaStream_t s) {
   if (M <= 0 || Ocp <= 0) return;
+  // B2VX_FC_MMA=0 keeps every shape on the dp4a kernel; 1 sends every shape to the MMA kernel (tuning aids)
+  static const int fc_mma = [] { const char* v = std::getenv("B2VX_FC_MMA"); return v ? std::atoi(v) : -1; }();
+  const bool use_mma = fc_mma == 1 || (fc_mma != 0 && M > 1);
+  if (use_mma && M <= 16) {
+    const uint8_t* a = static_cast<const uint8_t*>(A);
+    uint8_t* d = static_cast<uint8_t*>(D);
+    const unsigned grid = static_cast<unsigned>((Ocp + 31) / 32);
+    const bool dz = e.dz_uniform != 0;
+    if (a_signed) {
+      if (dz) launch_pdl(fc_mma16_kernel<true, true>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+      else launch_pdl(fc_mma16_kernel<true, false>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+    } else {
+      if (dz) launch_pdl(fc_mma16_kernel<false, true>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+      else launch_pdl(fc_mma16_kernel<false, false>, dim3(grid), dim3(256), 0, s, a, B, M, Kp, Oc, Ocp, e, d, ldd);
+    }
+    return;
+  }
   if (M <= 1) launch_fc_small_m_t<4, 1>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);
   else if (M <= 4) launch_fc_small_m_t<4, 4>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);
   else if (M <= 8) launch_fc_small_m_t<4, 8>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);

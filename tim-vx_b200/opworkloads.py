@@ -12,6 +12,10 @@ convolution sweep fuses):
                                          Relu: the tail of a ResNet bottleneck block
   gemm:<m>:<n>:<k>                       FullyConnected: uint8 [k, m] (zero point 128, scale 0.02)
                                          x int8 per-channel [k, n] -> uint8 [n, m]
+  fcchain:<m>:<n>:<layers>               `layers` FullyConnected nodes of n x n weights in a row on m rows (the
+                                         decode-like shapes as they occur in use: every layer streams its own
+                                         weights, together more than the L2 holds, and the cost of launching the
+                                         graph is shared by the layers)
   add:<elements>                         quantized Add of two uint8 tensors with different scales
   concat:<c1>:<c2>:<hw>                  Concat along the channel axis of two uint8 tensors [hw, hw, c, batch]
   transpose:<c>:<hw>                     Transpose {1,2,0,3} of a uint8 [c, hw, hw, batch] tensor (NHWC image -> WHCN)
@@ -32,13 +36,15 @@ def parse(spec):
         return kind, nums
     if kind == "gemm" and len(nums) == 3:
         return kind, nums
+    if kind == "fcchain" and len(nums) == 3:
+        return kind, nums
     if kind == "add" and len(nums) == 1:
         return kind, nums
     if kind == "concat" and len(nums) == 3:
         return kind, nums
     if kind == "transpose" and len(nums) == 2:
         return kind, nums
-    raise ValueError("workload must be conv:k:cin:cout:hw:stride, convadd:k:cin:cout:hw:stride, gemm:m:n:k, add:elements, "
+    raise ValueError("workload must be conv:k:cin:cout:hw:stride, convadd:k:cin:cout:hw:stride, gemm:m:n:k, fcchain:m:n:layers, add:elements, "
                      "concat:c1:c2:hw or transpose:c:hw, got %r" % spec)
 
 
@@ -90,6 +96,22 @@ def build(spec, batch, g, rng):
         return {"inputs": [(x, _u8(rng, (m, k)))], "outputs": [y], "ops": 2 * m * n * k,
                 "bytes": m * k + n * k + m * n + 4 * n, "bound": "tensor" if m >= 512 else "hbm", "units": m,
                 "name": "FullyConnected M=%d N=%d K=%d" % (m, n, k)}
+    if kind == "fcchain":
+        m, n, layers = v
+        x = g.tensor(B.DT_UINT8, [n, m], B.ATTR_INPUT, scale=0.02, zero_point=128)
+        cur = x
+        for i in range(layers):
+            ws = (rng.uniform(0.001, 0.01, n) / np.sqrt(n / 64.0)).astype(np.float32)
+            wd = rng.integers(-127, 128, size=(n, n)).astype(np.int8)
+            w = g.tensor(B.DT_INT8, [n, n], B.ATTR_CONSTANT, scales=ws, channel_dim=1, data=wd)
+            b = g.tensor(B.DT_INT32, [n], B.ATTR_CONSTANT, scales=np.float32(0.02) * ws, channel_dim=0,
+                         data=rng.integers(-1000, 1001, size=n).astype(np.int32))
+            y = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT if i == layers - 1 else B.ATTR_TRANSIENT, scale=0.02, zero_point=128)
+            g.fully_connected(cur, w, b, y, axis=0, weights=n)
+            cur = y
+        return {"inputs": [(x, _u8(rng, (m, n)))], "outputs": [cur], "ops": 2 * m * n * n * layers,
+                "bytes": layers * (2 * m * n + n * n + 4 * n), "bound": "hbm", "units": m * layers,
+                "name": "%d FullyConnected layers in a row, M=%d N=K=%d" % (layers, m, n)}
     if kind == "concat":
         c1, c2, hw = v
         a = g.tensor(B.DT_UINT8, [hw, hw, c1, batch], B.ATTR_INPUT, scale=0.05, zero_point=0)
@@ -126,6 +148,9 @@ def cpu_sample(spec):
     if kind == "gemm":
         m = min(v[0], 64)
         return "gemm:%d:%d:%d" % (m, v[1], v[2]), "%d of the %d rows per step" % (m, v[0])
+    if kind == "fcchain":
+        n = min(v[1], 2048)
+        return "fcchain:%d:%d:%d" % (v[0], n, min(v[2], 2)), "%d layers of %d x %d weights per step" % (min(v[2], 2), n, n)
     if kind == "add":
         n = min(v[0], 1 << 24)
         return "add:%d" % n, "%d of the %d elements per step" % (n, v[0])
