@@ -16,8 +16,10 @@
 // the status word, which every call clears before its kernels run.
 #include <cuda_runtime.h>
 
+#include <climits>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "b2vx.h"
 #include "kernels.h"
@@ -33,9 +35,10 @@ static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 static __device__ __align__(256) int g_status[64];
 
 struct PerDevice {
-  bool ready;
-  unsigned char* scratch;   // device address of g_scratch on this device
-  int* status;              // device address of g_status on this device
+  std::once_flag once;      // first calls on one GPU from several threads: one of them does the set-up, the others wait
+  cudaError_t error = cudaSuccess;
+  unsigned char* scratch = nullptr;   // device address of g_scratch on this device
+  int* status = nullptr;              // device address of g_status on this device
 };
 PerDevice g_dev[kMaxDevices];
 
@@ -47,15 +50,16 @@ b2vx_status fail(char* err, size_t err_len, b2vx_status st, const char* msg) {
 // Once per device, with that device current: resolve the device addresses of the static arrays.
 b2vx_status setup(int dev, char* err, size_t err_len) {
   PerDevice& d = g_dev[dev];
-  if (d.ready) return B2VX_OK;
-  void* p = nullptr;
-  cudaError_t e = cudaGetSymbolAddress(&p, g_scratch);
-  if (e != cudaSuccess) return fail(err, err_len, B2VX_CUDA_ERROR, cudaGetErrorString(e));
-  d.scratch = static_cast<unsigned char*>(p);
-  e = cudaGetSymbolAddress(&p, g_status);
-  if (e != cudaSuccess) return fail(err, err_len, B2VX_CUDA_ERROR, cudaGetErrorString(e));
-  d.status = static_cast<int*>(p);
-  d.ready = true;
+  std::call_once(d.once, [&d] {
+    void* p = nullptr;
+    d.error = cudaGetSymbolAddress(&p, g_scratch);
+    if (d.error != cudaSuccess) return;
+    d.scratch = static_cast<unsigned char*>(p);
+    d.error = cudaGetSymbolAddress(&p, g_status);
+    if (d.error != cudaSuccess) return;
+    d.status = static_cast<int*>(p);
+  });
+  if (d.error != cudaSuccess) return fail(err, err_len, B2VX_CUDA_ERROR, cudaGetErrorString(d.error));
   return B2VX_OK;
 }
 
@@ -69,6 +73,15 @@ extern "C" b2vx_status b2vx_conv2d_first_layer_noalloc(const b2vx_conv2d_noalloc
   if (d->n == 0 || d->h == 0 || d->w == 0 || d->c == 0 || d->c >= 16 || d->kw == 0 || d->kh == 0 || d->oc == 0 || d->oc > 256)
     return fail(err, err_len, B2VX_INVALID_ARG, "need 1 <= c < 16, 1 <= oc <= 256 and non-empty shapes");
   if (!(d->out_scale > 0.0f)) return fail(err, err_len, B2VX_INVALID_ARG, "out_scale must be positive");
+  // every extent is turned into an int below: refuse what would not survive that (or the sums built from it)
+  const uint32_t lim = static_cast<uint32_t>(INT_MAX / 4);
+  if (d->n > lim || d->h > lim || d->w > lim || d->kw > lim || d->kh > lim || d->stride[0] > lim || d->stride[1] > lim ||
+      d->dilation[0] > lim || d->dilation[1] > lim || d->pad[0] > lim || d->pad[1] > lim || d->pad[2] > lim || d->pad[3] > lim)
+    return fail(err, err_len, B2VX_INVALID_ARG, "an extent, stride, dilation or padding is out of range");
+  if (static_cast<long long>(d->kw) * d->kh * d->c > 65536)
+    return fail(err, err_len, B2VX_INVALID_ARG, "filter too large (kw*kh*c must be at most 65536)");
+  if (d->in_zero_point < 0 || d->in_zero_point > 255 || d->out_zero_point < 0 || d->out_zero_point > 255)
+    return fail(err, err_len, B2VX_INVALID_ARG, "zero points of uint8 tensors must lie in 0..255");
   const int sx = d->stride[0] ? d->stride[0] : 1, sy = d->stride[1] ? d->stride[1] : 1;
   const int dx = d->dilation[0] ? d->dilation[0] : 1, dy = d->dilation[1] ? d->dilation[1] : 1;
   const long long span_w = static_cast<long long>(d->w) + d->pad[0] + d->pad[1] - (static_cast<long long>(d->kw - 1) * dx + 1);
@@ -109,6 +122,9 @@ extern "C" b2vx_status b2vx_conv2d_first_layer_noalloc(const b2vx_conv2d_noalloc
   ep.out.zp = d->out_zero_point;
   ep.out.lo = 0;
   ep.out.hi = 255;
+  // The scales are device memory, which this call may not read back to bound |accumulator * scale / out_scale| the
+  // way the graph's planner does; the exact requantization is right for any scales.
+  ep.exact_only = 1;
   alignas(64) unsigned char plan_storage[1024];
   if (gemm_tc_plan_bytes() > sizeof(plan_storage)) return fail(err, err_len, B2VX_BAD_STATE, "plan storage too small");
   char why[160] = {0};
