@@ -55,6 +55,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -132,6 +133,8 @@ struct GemmParams {
   int res_span;
   int dz;                  // weight zero point left after the shift into int8; != 0: column BNd of the accumulator is S
   int exact_only;          // requantize with the exact sequence only (the fast form's range check failed)
+  long long wait_limit;    // cycles after which a barrier wait gives up (kWaitLimitCycles)
+  uint32_t tx_extra;       // test aid: bytes added to what the A producer announces, so that its barrier never completes
 #ifdef B2VX_TC_TRACE
   long long* trace;        // clock64 stamps of CTA 0, [3 roles][64 iterations][2], then 8 marks
 #endif
@@ -167,7 +170,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Returns false when the CTA is aborting.  Polls back off: a wait that is not over after
 // a few tries is a long one (a control warp waiting for the epilogue, say), and a warp that keeps
 // polling takes issue slots from the warps it is waiting for; sleeps grow from 64 ns to 1 us.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          long long limit = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   unsigned sleep_ns = 32;
@@ -176,7 +180,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (int i = 0; i < 4; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - start > kWaitLimitCycles) {
+    if (clock64() - start > limit) {
       *abort_flag = 1;
       atomicCAS(status, 0, code);
       return false;
@@ -415,12 +419,12 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
         const int cnt = min(p.group, p.num_kb - kb0);
         const uint32_t full = smem_u32(&hdr->full[s]);
-        ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, is_a ? 1 : 5);
+        ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1, abort_flag, p.status, is_a ? 1 : 5, p.wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (is_a) TC_TRACE(0, it, 0);
         if (elect_one()) {
-          mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (is_a ? p.a_tx_bytes : b_bytes));
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (is_a ? p.a_tx_bytes : b_bytes) + (is_a ? p.tx_extra : 0u));
           uint32_t dst = tiles_addr + s * stage_bytes;
           int t_tap = tap, t_cb = cb, t_ky = ky, t_kx = kx;
           for (int gi = 0; gi < cnt; ++gi, dst += sub_bytes) {
@@ -460,19 +464,19 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     int j = 0;
     const int ksteps = p.BK >> 5;
     if (p.b_resident && static_cast<int>(blockIdx.x) < num_tiles) {
-      ok = mbar_wait(smem_u32(&hdr->b_full), 0, abort_flag, p.status, 8);
+      ok = mbar_wait(smem_u32(&hdr->b_full), 0, abort_flag, p.status, 8, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
     }
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
       const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
-      ok = mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2);
+      ok = mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + a * p.acc_stride;
       uint32_t accumulate = 0;
       for (int kb0 = 0; kb0 < p.num_kb; kb0 += p.group, ++it) {
-        ok = mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3);
+        ok = mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, p.status, 3, p.wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         TC_TRACE(1, it, 0);
@@ -516,7 +520,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       int m_tile = m_tile0, j = 0;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, m_tile += m_step, ++j) {
         const uint32_t b = j & 1, ph = (j >> 1) & 1;
-        ok = mbar_wait(smem_u32(&hdr->res_empty[b]), ph ^ 1, abort_flag, p.status, 6);
+        ok = mbar_wait(smem_u32(&hdr->res_empty[b]), ph ^ 1, abort_flag, p.status, 6, p.wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (elect_one()) {
@@ -605,14 +609,14 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       long long row;                 // direct-store path: output row (pixel index into D), -1 outside the tensor
       const int32_t* corr_row;       // border pixels of a padded convolution: their correction, this N tile
       locate(m_tile, row, corr_row);
-      if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4);
+      if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4, p.wait_limit);
       alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
       if (!alive) {
         if (span_b) epilogue_barrier();
         continue;
       }
       if (span_r) {
-        alive = mbar_wait(smem_u32(&hdr->res_full[j & 1]), (j >> 1) & 1, abort_flag, p.status, 7);
+        alive = mbar_wait(smem_u32(&hdr->res_full[j & 1]), (j >> 1) & 1, abort_flag, p.status, 7, p.wait_limit);
         alive = __all_sync(0xffffffffu, alive);
         if (!alive) continue;
       }
@@ -935,6 +939,8 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
             (static_cast<uint32_t>(p.BN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
   p.ep = e;
   p.exact_only = e.exact_only;
+  p.wait_limit = kWaitLimitCycles;
+  p.tx_extra = 0;
   p.D = static_cast<uint8_t*>(D);
   p.status = status;
   const uint64_t bdims[2] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(Np)};
@@ -1237,6 +1243,18 @@ cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
     cudaMemset(mp->params.trace, 0, (3 * 64 * 2 + 8) * sizeof(long long));
   }
 #endif
+  // Test aid: B2VX_TEST_STALL=<n> makes the first n launches of the process announce 16 bytes more than their loads
+  // deliver and give up after about a millisecond, so that the path "a barrier wait ran out -> status word ->
+  // B2VX_DEVICE_TIMEOUT" can be exercised without harming the GPU: every real load lands, the kernel leaves
+  // through its common exit.  (Use with B2VX_CUDA_GRAPH=0: a captured launch would keep the stall.)
+  static std::atomic<int> stall_left([] { const char* v = std::getenv("B2VX_TEST_STALL"); return v ? std::atoi(v) : 0; }());
+  GemmTcPlan stalled;
+  if (stall_left.load(std::memory_order_relaxed) > 0 && stall_left.fetch_sub(1) > 0) {
+    stalled = *plan;
+    stalled.params.wait_limit = 2000000LL;
+    stalled.params.tx_extra = 16;
+    plan = &stalled;
+  }
   cudaError_t launched;
   const bool extra = plan->params.dz != 0 || plan->params.ep.border_corr != nullptr;
   const bool fuse = plan->params.ep.add_residual != nullptr;
