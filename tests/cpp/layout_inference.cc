@@ -95,6 +95,7 @@ struct Weights {
   std::vector<uint8_t> dw;     // IcWHOc [1, 3, 3, OC]
   std::vector<uint8_t> fc;     // [K, CLASSES] with K counted over the NHWC-flattened pooled tensor
   std::vector<int32_t> conv_b, dw_b, fc_b;
+  std::vector<uint8_t> channel_offset;   // [OC]: the constant operand of an Add
 };
 
 // element (i0, i1, i2, i3) of a dense tensor with dimension 0 fastest
@@ -136,14 +137,20 @@ static std::vector<uint8_t> run_network(const std::shared_ptr<Context>& ctx, con
   auto fw = g->CreateTensor(TensorSpec(DataType::UINT8, ShapeType({PW * PH * OC, CLASSES}), TensorAttribute::CONSTANT, quant(0.005f, 128)), fc_w.data());
   auto fb = g->CreateTensor(TensorSpec(DataType::INT32, ShapeType({CLASSES}), TensorAttribute::CONSTANT, quant(0.06f * 0.005f, 0)), wts.fc_b.data());
   auto transient = [&](float s, int32_t z) { return g->CreateTensor(TensorSpec(DataType::UINT8, {}, TensorAttribute::TRANSIENT, quant(s, z))); };
-  auto t1 = transient(0.05f, 20), t2 = transient(0.05f, 20), t3 = transient(0.07f, 90), t4 = transient(0.06f, 50), t5 = transient(0.06f, 50);
+  auto t1 = transient(0.05f, 20), t2a = transient(0.05f, 20), t2 = transient(0.05f, 20), t3 = transient(0.07f, 90), t4 = transient(0.06f, 50), t5 = transient(0.06f, 50);
   auto logits = g->CreateTensor(TensorSpec(DataType::UINT8, ShapeType({CLASSES, N}), TensorAttribute::OUTPUT, quant(0.1f, 128)));
   const std::array<uint32_t, 2> one = {1, 1}, three = {3, 3}, two = {2, 2};
   const std::array<uint32_t, 4> nopad = {0, 0, 0, 0};
   auto conv = g->CreateOperation<ops::Conv2d>(static_cast<int32_t>(OC), PadType::SAME, three, one, one, nopad, 0, act, ker);
   (*conv).BindInputs({input, cw, cb}).BindOutput(t1);
   auto relu = g->CreateOperation<ops::Relu>();
-  (*relu).BindInput(t1).BindOutput(t2);
+  (*relu).BindInput(t1).BindOutput(t2a);
+  // an elementwise op with a constant operand that has all four dimensions (one value per channel): layout
+  // inference has to permute the constant together with the activation it is added to
+  auto per_channel = g->CreateTensor(TensorSpec(DataType::UINT8, nhwc ? ShapeType({OC, 1, 1, 1}) : ShapeType({1, 1, OC, 1}), TensorAttribute::CONSTANT,
+                                                quant(0.03f, 100)), wts.channel_offset.data());
+  auto addc = g->CreateOperation<ops::Add>();
+  (*addc).BindInputs({t2a, per_channel}).BindOutput(t2);
   auto dw = g->CreateOperation<ops::Conv2d>(static_cast<int32_t>(OC), PadType::SAME, three, one, one, nopad, 1, act, ker);
   (*dw).BindInputs({t2, dwt, db}).BindOutput(t3);
   auto add = g->CreateOperation<ops::Add>();
@@ -181,6 +188,7 @@ int main() {
   w.fc.resize((W / 2) * (H / 2) * OC * CLASSES); for (auto& v : w.fc) v = next_byte();
   w.conv_b.resize(OC); for (auto& v : w.conv_b) v = static_cast<int32_t>(next_byte()) * 16 - 2000;
   w.dw_b.resize(OC); for (auto& v : w.dw_b) v = static_cast<int32_t>(next_byte()) * 4 - 500;
+  w.channel_offset.resize(OC); for (auto& v : w.channel_offset) v = next_byte();
   w.fc_b.resize(CLASSES); for (auto& v : w.fc_b) v = static_cast<int32_t>(next_byte()) * 8 - 1000;
   std::vector<uint8_t> image(C * W * H * N);
   for (auto& v : image) v = next_byte();

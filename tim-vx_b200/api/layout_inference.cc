@@ -93,6 +93,33 @@ struct Inference {
 
 bool is_const(const TensorPtr& t) { return t && t->IsConstTensor(); }
 
+size_t element_count(const TensorPtr& t) {
+  size_t n = 1;
+  for (uint32_t v : t->GetShape()) n *= v;
+  return n;
+}
+
+// A rank-4 constant operand of an op that runs in WHCN: its elements (and the channel dimension of a per-channel
+// quantization) permuted CWHN -> WHCN on the host, as the reference's layout inference permutes the constant inputs of
+// an elementwise op together with the others.
+TensorPtr constant_whcn(Inference& inf, const TensorPtr& t) {
+  Forms& f = inf.forms[t];
+  if (f.whcn) return f.whcn;
+  vx::TensorSpec spec(t->GetSpec());
+  const vx::ShapeType shape = spec.GetShapeType();
+  const std::vector<uint8_t>& data = static_cast<vx::TensorImpl*>(t.get())->ConstData();
+  const std::vector<uint8_t> moved = permute_data(data, shape, kCWHN2WHCN, data.size() / std::max<size_t>(1, element_count(t)));
+  spec.SetShape(permuted(shape, kCWHN2WHCN));
+  vx::Quantization q = spec.GetQuantization();
+  if (q.Type() == vx::QuantType::SYMMETRIC_PER_CHANNEL && q.ChannelDim() >= 0 && q.ChannelDim() < 4) {
+    for (int32_t i = 0; i < 4; ++i)
+      if (static_cast<int32_t>(kCWHN2WHCN[i]) == q.ChannelDim()) { q.SetChannelDim(i); break; }
+    spec.SetQuantization(q);
+  }
+  f.whcn = inf.graph->CreateTensor(spec, moved.data());
+  return f.whcn;
+}
+
 // A constant kernel in WHIcOc, permuted on the host; depthwise kernels end as [W, H, C*multiplier, 1].
 TensorPtr native_kernel(Inference& inf, const TensorPtr& w, vx::DataLayout layout, bool depthwise) {
   Perm perm;
@@ -233,11 +260,17 @@ std::pair<std::shared_ptr<vx::Graph>, std::map<std::shared_ptr<vx::Tensor>, std:
         // layout-agnostic ops follow their inputs into WHCN when every non-constant input is there already
         const bool agnostic = kind == B2VX_NODE_RELU || kind == B2VX_NODE_RELU6 || kind == B2VX_NODE_ADD || kind == B2VX_NODE_DATACONVERT;
         bool all_whcn = agnostic;
-        for (const TensorPtr& t : impl->inputs_tensor_)
-          if (t && !is_const(t)) all_whcn = all_whcn && inf.forms[t].whcn != nullptr;   // a WHCN form exists for rank-4 tensors only
         for (const TensorPtr& t : impl->inputs_tensor_) {
           if (!t) continue;
-          if (is_const(t)) clone->BindInput(inf.constant(t));
+          if (!is_const(t)) all_whcn = all_whcn && inf.forms[t].whcn != nullptr;   // a WHCN form exists for rank-4 tensors only
+          // a constant operand goes along when it has all four dimensions (it is permuted) or a single element (any
+          // layout); one of lower rank would broadcast against other dimensions after the permutation, so such an op
+          // stays in the source layout
+          else all_whcn = all_whcn && (t->GetShape().size() == 4 || element_count(t) == 1);
+        }
+        for (const TensorPtr& t : impl->inputs_tensor_) {
+          if (!t) continue;
+          if (is_const(t)) clone->BindInput(all_whcn && t->GetShape().size() == 4 ? constant_whcn(inf, t) : inf.constant(t));
           else clone->BindInput(all_whcn ? inf.in_whcn(t) : inf.in_source_layout(t));
         }
         for (const TensorPtr& o : impl->outputs_tensor_) {
