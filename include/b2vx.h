@@ -97,7 +97,8 @@ enum {
   B2VX_NODE_RESHAPE = 8,
   B2VX_NODE_TRANSPOSE = 9,
   B2VX_NODE_CONCAT = 10,
-  B2VX_NODE_DATACONVERT = 11
+  B2VX_NODE_DATACONVERT = 11,
+  B2VX_NODE_ADDN = 12
 };
 
 /* most tensors one node reads (Concat) */
@@ -229,6 +230,14 @@ b2vx_status b2vx_node_reshape(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_
 b2vx_status b2vx_node_transpose(b2vx_graph* g, uint32_t x, uint32_t y, const b2vx_dims_desc* perm);
 b2vx_status b2vx_node_concat(b2vx_graph* g, const uint32_t* inputs, uint32_t n_inputs, uint32_t axis, uint32_t y);
 b2vx_status b2vx_node_dataconvert(b2vx_graph* g, uint32_t x, uint32_t y);
+/* ops::AddN (src/tim/vx/ops/addn.cc -> vsi_nn_op_addn.c:124-205, which chains
+ * n-1 Add nodes): y = x0 + x1 + ... over 2 to 16 tensors of one shape, all
+ * int8/uint8 (any scales) or all float32.  The inputs are dequantized, summed in
+ * float32 from left to right, and the sum is quantized once with the output's
+ * parameters; with two inputs this is exactly the Add node.  (The reference's
+ * intermediate sums of quantized inputs are float16 on hardware without the SP
+ * unit; float16 is outside this backend, the sums here stay float32.) */
+b2vx_status b2vx_node_addn(b2vx_graph* g, const uint32_t* inputs, uint32_t n_inputs, uint32_t y);
 
 /* ---- compile / run: vsi_nn_SetupGraph + vsi_nn_VerifyGraph
  *      (src/tim/vx/graph.cc:328-383) and vsi_nn_RunGraph (graph.cc:389-391).
@@ -283,9 +292,12 @@ b2vx_status b2vx_graph_profile(b2vx_graph* g, uint32_t iters);
  * y_cl is complete.  A problem whose im2col matrix (N*Ho*Wo*Kp bytes) exceeds
  * the array is refused with B2VX_INVALID_ARG and a message in err.
  *
- * The first call on a GPU resolves the array's device address; make that call
- * before any stream capture.  All calls on one GPU share the array: calls whose
- * kernels overlap on the GPU (other streams, other threads) race. */
+ * The first call on a GPU resolves the array's device address (once, also when
+ * several threads make their first call together); make that call before any
+ * stream capture.  All calls on one GPU share the array: calls whose kernels
+ * overlap on the GPU (other streams, other threads) race.  Extents, strides,
+ * dilations and paddings above INT_MAX/4, filters with kw*kh*c > 65536 and zero
+ * points outside 0..255 are refused with B2VX_INVALID_ARG. */
 #define B2VX_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u)
 typedef struct b2vx_conv2d_noalloc_desc {
   uint32_t n, h, w, c;

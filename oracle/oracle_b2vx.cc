@@ -287,6 +287,16 @@ b2vx_status infer_node(b2vx_graph* g, ONode& n) {
       for (uint32_t i = 2; i < x.d.rank; ++i) dims.push_back(x.d.dims[i]);
       return set_shape(g, n.out, dims, "pool2d", true);
     }
+    case B2VX_NODE_ADDN: {
+      for (uint32_t id : n.in) {
+        if (id == B2VX_NO_TENSOR) continue;
+        const OTensor& t = g->tensors[id];
+        if (!t.has_shape || t.d.rank != x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "addn: input shapes differ");
+        for (uint32_t i = 0; i < x.d.rank; ++i)
+          if (t.d.dims[i] != x.d.dims[i]) return fail(g, B2VX_SHAPE_MISMATCH, "addn: input shapes differ");
+      }
+      return set_shape(g, n.out, std::vector<uint32_t>(x.d.dims, x.d.dims + x.d.rank), "addn");
+    }
     case B2VX_NODE_ADD: {
       const OTensor& b = g->tensors[n.in[1]];
       if (!b.has_shape) return fail(g, B2VX_SHAPE_MISMATCH, "add: input shape unknown");
@@ -426,6 +436,20 @@ b2vx_status exec_node(b2vx_graph* g, ONode& n) {
       }
       rc = orc_add(x.data.data(), x.d.dtype, ad, x.quant(), b.data.data(), b.d.dtype, bd, b.quant(),
                    y.data.data(), y.d.dtype, y.d.dims, y.quant(), rank);
+      break;
+    }
+    case B2VX_NODE_ADDN: {
+      const void* ptrs[B2VX_MAX_NODE_INPUTS];
+      int32_t dts[B2VX_MAX_NODE_INPUTS];
+      orc_quant qs[B2VX_MAX_NODE_INPUTS];
+      uint32_t cnt = 0;
+      for (uint32_t id : n.in) {
+        if (id == B2VX_NO_TENSOR) continue;
+        OTensor& t = g->tensors[id];
+        ptrs[cnt] = t.data.data(); dts[cnt] = t.d.dtype; qs[cnt] = t.quant();
+        ++cnt;
+      }
+      rc = orc_addn(ptrs, dts, qs, cnt, y.data.data(), y.d.dtype, y.quant(), y.elems());
       break;
     }
     case B2VX_NODE_RELU:
@@ -712,6 +736,16 @@ b2vx_status b2vx_node_concat(b2vx_graph* g, const uint32_t* inputs, uint32_t n_i
   std::memset(&n, 0, sizeof(n));
   n.p.concat_axis = axis;
   b2vx_status st = add_node(g, B2VX_NODE_CONCAT, inputs[0], B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, &n);
+  if (st != B2VX_OK) return st;
+  for (uint32_t i = 0; i < n_inputs; ++i) g->nodes.back().in[i] = inputs[i];
+  return B2VX_OK;
+}
+b2vx_status b2vx_node_addn(b2vx_graph* g, const uint32_t* inputs, uint32_t n_inputs, uint32_t y) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (!inputs || n_inputs < 2 || n_inputs > B2VX_MAX_NODE_INPUTS) return fail(g, B2VX_INVALID_ARG, "addn: 2 to 16 inputs");
+  for (uint32_t i = 0; i < n_inputs; ++i)
+    if (!valid_id(g, inputs[i])) return fail(g, B2VX_INVALID_ARG, "addn: bad tensor id");
+  b2vx_status st = add_node(g, B2VX_NODE_ADDN, inputs[0], B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
   if (st != B2VX_OK) return st;
   for (uint32_t i = 0; i < n_inputs; ++i) g->nodes.back().in[i] = inputs[i];
   return B2VX_OK;

@@ -323,7 +323,7 @@ int32_t orc_fully_connected(const orc_fc_args* a) {
 int32_t orc_pool2d(const orc_pool2d_args* a) {
   const bool is_float = a->dtype == DT_FLOAT32;
   if (!is_float && !is_quant_dtype(a->dtype)) return -1;
-  if (a->type != 0 && a->type != 1 && a->type != 3) return -1;
+  if (a->type < 0 || a->type > 3) return -1;
   const bool same_quant = is_float || (a->xq.scale == a->yq.scale && a->xq.zp == a->yq.zp);
   const int64_t planes = static_cast<int64_t>(a->N) * a->C;
 #pragma omp parallel for schedule(static)
@@ -333,7 +333,7 @@ int32_t orc_pool2d(const orc_pool2d_args* a) {
     for (uint32_t ho = 0; ho < a->Ho; ++ho) {
       for (uint32_t wo = 0; wo < a->Wo; ++wo) {
         int32_t count = 0, qsum = 0, qmax = std::numeric_limits<int32_t>::min();
-        float fsum = 0.0f, fmax = -std::numeric_limits<float>::infinity();
+        float fsum = 0.0f, fmax = -std::numeric_limits<float>::infinity(), fsq = 0.0f;
         for (uint32_t ky = 0; ky < a->ksize[1]; ++ky) {
           int64_t hi = static_cast<int64_t>(ho) * a->stride[1] - a->pad_top + ky;
           if (hi < 0 || hi >= static_cast<int64_t>(a->H)) continue;
@@ -346,16 +346,28 @@ int32_t orc_pool2d(const orc_pool2d_args* a) {
               float v = static_cast<const float*>(a->x)[idx];
               fsum += v;
               fmax = std::max(fmax, v);
+              const float sq = v * v;
+              fsq = fsq + sq;
             } else {
               int32_t v = load_q(a->x, a->dtype, idx);
               qsum += v - a->xq.zp;
               qmax = std::max(qmax, v);
+              const float real = orc_affine_to_fp32(v, a->xq.scale, a->xq.zp);
+              const float sq = real * real;
+              fsq = fsq + sq;
             }
           }
         }
         const size_t o = obase + static_cast<size_t>(ho) * a->Wo + wo;
         const float div = a->type == 1 ? static_cast<float>(a->ksize[0] * a->ksize[1]) : static_cast<float>(count);
-        if (is_float) {
+        if (a->type == 2) {
+          // L2: sqrt(mean of x^2) over the taps inside the input, in float (squares added in tap order).  The
+          // reference only lowers the type (src/tim/vx/type_utils.cc:99-100, VX_NN_POOLING_L2); it holds neither a
+          // formula nor a vector for it: parity unpinned.
+          const float r = count ? std::sqrt(fsq / static_cast<float>(count)) : 0.0f;
+          if (is_float) static_cast<float*>(a->y)[o] = r;
+          else store_q(a->y, a->dtype, o, orc_fp32_to_affine(r, a->yq.scale, a->yq.zp, a->dtype));
+        } else if (is_float) {
           float r = a->type == 0 ? (count ? fmax : 0.0f) : (count ? fsum / div : 0.0f);
           static_cast<float*>(a->y)[o] = r;
         } else if (a->type == 0) {
@@ -407,6 +419,27 @@ int32_t orc_add(const void* a, int32_t a_dtype, const uint32_t* a_dims, orc_quan
       bi += c * bstride[d];
     }
     float r = to_real(a, a_dtype, ai, aq) + to_real(b, b_dtype, bi, bq);
+    if (y_dtype == DT_FLOAT32) static_cast<float*>(y)[i] = r;
+    else store_q(y, y_dtype, static_cast<size_t>(i), orc_fp32_to_affine(r, yq.scale, yq.zp, y_dtype));
+  }
+  return 0;
+}
+
+// ops::AddN (src/tim/vx/internal/src/ops/vsi_nn_op_addn.c:124-205: a chain of n-1 Add nodes): every Add
+// dequantizes its inputs and adds them in float; the intermediate sums stay float32 here and only the
+// last one is quantized, with the output's parameters.
+int32_t orc_addn(const void* const* x, const int32_t* dtypes, const orc_quant* q, uint32_t n,
+                 void* y, int32_t y_dtype, orc_quant yq, uint64_t elems) {
+  if (n < 2) return -1;
+  auto to_real = [](const void* p, int32_t dt, size_t i, const orc_quant& qq) -> float {
+    if (dt == DT_FLOAT32) return static_cast<const float*>(p)[i];
+    int32_t v = dt == DT_INT32 ? static_cast<const int32_t*>(p)[i] : load_q(p, dt, i);
+    return orc_affine_to_fp32(v, qq.scale, qq.zp);
+  };
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < static_cast<int64_t>(elems); ++i) {
+    float r = to_real(x[0], dtypes[0], static_cast<size_t>(i), q[0]);
+    for (uint32_t k = 1; k < n; ++k) r = r + to_real(x[k], dtypes[k], static_cast<size_t>(i), q[k]);
     if (y_dtype == DT_FLOAT32) static_cast<float*>(y)[i] = r;
     else store_q(y, y_dtype, static_cast<size_t>(i), orc_fp32_to_affine(r, yq.scale, yq.zp, y_dtype));
   }

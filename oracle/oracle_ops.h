@@ -98,6 +98,10 @@ int32_t orc_pool2d(const orc_pool2d_args* a);
 int32_t orc_add(const void* a, int32_t a_dtype, const uint32_t* a_dims, orc_quant aq,
                 const void* b, int32_t b_dtype, const uint32_t* b_dims, orc_quant bq,
                 void* y, int32_t y_dtype, const uint32_t* y_dims, orc_quant yq, uint32_t rank);
+// ops::AddN: the sum of n same-shaped tensors, dequantized, added in float32 from left to right and quantized once
+// (src/tim/vx/internal/src/ops/vsi_nn_op_addn.c:124-205 chains n-1 Add nodes; see b2vx.h for the intermediate type).
+int32_t orc_addn(const void* const* x, const int32_t* dtypes, const orc_quant* q, uint32_t n,
+                 void* y, int32_t y_dtype, orc_quant yq, uint64_t elems);
 /* upper < 0: plain relu; otherwise clamp to [0, upper] */
 int32_t orc_relu(const void* x, int32_t x_dtype, orc_quant xq, void* y, int32_t y_dtype,
                  orc_quant yq, uint64_t n, float upper);

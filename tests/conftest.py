@@ -9,6 +9,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "tim-vx_b200"))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 def pytest_configure(config):
@@ -23,9 +24,9 @@ def _ensure(path, make_dir):
 
 @pytest.fixture(scope="session")
 def oracle_lib():
-    import pyb2vx
-    _ensure(pyb2vx.ORACLE_LIB, os.path.join(ROOT, "oracle"))
-    return pyb2vx.load(pyb2vx.ORACLE_LIB)
+    import oracle_paths
+    _ensure(oracle_paths.ORACLE_LIB, os.path.join(ROOT, "oracle"))
+    return oracle_paths.load(oracle_paths.ORACLE_LIB)
 
 
 @pytest.fixture(scope="session")

@@ -6,6 +6,7 @@ import re
 
 import numpy as np
 
+import oracle_paths
 import pyb2vx as B
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -49,7 +50,7 @@ def test_product_has_no_cpu_fallback():
 
 
 def _ops():
-    lib = C.CDLL(B.ORACLE_OPS_LIB)
+    lib = C.CDLL(oracle_paths.ORACLE_OPS_LIB)
     lib.orc_rint.restype = C.c_double
     lib.orc_rint.argtypes = [C.c_double]
     lib.orc_fp32_to_affine.restype = C.c_int32
@@ -120,3 +121,25 @@ def test_oracle_rejects_mismatched_shapes(oracle_lib):
     else:
         raise AssertionError("shape mismatch accepted")
     g.close()
+
+
+def test_oracle_l2_pool_is_root_mean_square_of_the_valid_taps(oracle_lib):
+    """Pool2d L2 as this repository defines it (the reference lowers the type but states no formula): the oracle against
+    a float64 numpy restatement, within one quantization step."""
+    import graph_cases as G
+    W = H = 10
+    C, N, k, stride, pad = 16, 2, 3, 2, 1
+    in_q, out_q = (0.05, 120), (0.03, 0)
+    out, _ = G.run_case(oracle_lib, G.pool_q(W, H, C, N, B.POOL_L2, (k, k), (stride, stride), pad=(pad, pad, pad, pad), in_q=in_q, out_q=out_q), seed=9)
+    rng = np.random.default_rng(9)
+    x = G._act(rng, [W, H, C, N]).astype(np.float64)
+    real = (x - in_q[1]) * in_q[0]
+    Ho = (H + 2 * pad - k) // stride + 1
+    want = np.zeros((N, C, Ho, Ho))
+    for ho in range(Ho):
+        for wo in range(Ho):
+            h0, w0 = ho * stride - pad, wo * stride - pad
+            patch = real[:, :, max(h0, 0):min(h0 + k, H), max(w0, 0):min(w0 + k, W)]
+            want[:, :, ho, wo] = np.sqrt((patch ** 2).mean(axis=(2, 3)))
+    q = np.clip(np.rint(want / out_q[0]) + out_q[1], 0, 255)
+    assert np.abs(out[0].astype(np.float64) - q).max() <= 1

@@ -14,13 +14,13 @@ hardware's exp/accumulation and cannot be pinned by a different machine.
 import numpy as np
 import pytest
 
-import pyb2vx
+import oracle_paths
 
 FLOAT_EXACT_TOL = 1e-5
 
 
 def check_case(lib, case):
-    g, inputs, expects, _ = pyb2vx.graph_from_case(lib, case)
+    g, inputs, expects, _ = oracle_paths.graph_from_case(lib, case)
     try:
         g.compile()
         for tid, arr in inputs:
@@ -69,7 +69,7 @@ def test_oracle_matches_reference_vectors(oracle_lib, reference_cases):
 def test_recorded_oracle_outputs_are_reproduced(oracle_lib, reference_cases):
     """The outputs stored in the fixture are what the oracle produces today (bit for bit)."""
     for case in reference_cases[::7]:
-        g, inputs, _, recorded = pyb2vx.graph_from_case(oracle_lib, case)
+        g, inputs, _, recorded = oracle_paths.graph_from_case(oracle_lib, case)
         g.compile()
         for tid, arr in inputs:
             g.write(tid, arr)

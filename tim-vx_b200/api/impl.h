@@ -145,11 +145,19 @@ class OpImpl {
   // Conv2d / Pool2d declared with a front-end layout (CWHN activations, IcWHOc / OcIcWH / IcOcWH kernels):
   // tim::transform::LayoutInference rewrites such a graph; compiled as it stands the op runs as WHCN / WHIcOc.
   bool foreign_layout_ = false;
+  // Operation::SetRoundingPolicy, defaults as in include/tim/vx/operation.h of the reference
+  OverflowPolicy overflow_policy_ = OverflowPolicy::SATURATE;
+  RoundingPolicy rounding_policy_ = RoundingPolicy::RTNE;
+  RoundType down_scale_size_rounding_ = RoundType::FLOOR;
+  uint32_t accumulator_bits_ = 0;
+  const char* name_ = "";       // declared-only ops: the class name, for the message Compile gives
 };
 
 // Node kind of ops::NBG inside this layer; it never reaches the C ABI: Compile expands the op into the
 // nodes and tensors of its blob.
 constexpr uint32_t kNodeKindNbg = 0x4E4247u;
+// Node kind of the op classes that are declared for source compatibility only; `name_` says which.
+constexpr uint32_t kNodeKindDeclaredOnly = 0x4E4F4Eu;
 
 class GraphImpl : public Graph {
  public:

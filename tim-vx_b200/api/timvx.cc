@@ -13,6 +13,11 @@
 
 #include "impl.h"
 #include "tim/vx/builtin_op.h"
+#include "tim/vx/ops/addn.h"
+#include "tim/vx/ops/instancenormalization.h"
+#include "tim/vx/ops/relational_operations.h"
+#include "tim/vx/ops/resize.h"
+#include "tim/vx/ops/roi_align.h"
 #include "tim/vx/ops/concat.h"
 #include "tim/vx/ops/reshape.h"
 #include "tim/vx/ops/simple_operations.h"
@@ -517,6 +522,10 @@ bool GraphImpl::EmitNodes() {
     // As in the reference, the layouts named in an op's constructor only inform tim::transform::LayoutInference;
     // a graph compiled without it runs every op as WHCN / WHIcOc (its conv2d_test.cc relies on that).
     if (p->foreign_layout_) TVX_LOGW("an op names a CWHN / front-end kernel layout and runs as WHCN / WHIcOc: layout inference was not applied");
+    if (p->overflow_policy_ != OverflowPolicy::SATURATE || p->rounding_policy_ != RoundingPolicy::RTNE) {
+      TVX_LOGE("SetRoundingPolicy: this backend saturates and rounds to nearest even; OverflowPolicy::WRAP and RoundingPolicy::TO_ZERO are not supported");
+      return false;
+    }
     b2vx_status st = B2VX_UNSUPPORTED;
     switch (p->kind_) {
       case B2VX_NODE_CONV2D: st = b2vx_node_conv2d(graph_, in(0), in(1), in(2), out(0), &p->desc_.conv2d); break;
@@ -537,7 +546,16 @@ bool GraphImpl::EmitNodes() {
         st = b2vx_node_concat(graph_, ids.data(), static_cast<uint32_t>(ids.size()), p->desc_.concat_axis, out(0));
         break;
       }
+      case B2VX_NODE_ADDN: {
+        std::vector<uint32_t> ids;
+        for (size_t k = 0; k < p->inputs_tensor_.size(); ++k) ids.push_back(in(k));
+        st = b2vx_node_addn(graph_, ids.data(), static_cast<uint32_t>(ids.size()), out(0));
+        break;
+      }
       case kNodeKindNbg: st = ExpandBlob(p) ? B2VX_OK : B2VX_INVALID_ARG; break;
+      case kNodeKindDeclaredOnly:
+        TVX_LOGE("ops::%s is declared for source compatibility only; this backend does not execute it", p->name_);
+        return false;
       default: break;
     }
     if (st != B2VX_OK) {
@@ -615,6 +633,10 @@ struct BlobReader {
 
 bool GraphImpl::CompileToBinary(void* buf, size_t* size) {
   if (!size) return false;
+  if (op_vector_.empty()) {   // as vsi_nn_GenerateNBG on a graph without nodes (src/tim/vx/graph_test.cc:32-38 expects false)
+    TVX_LOGE("CompileToBinary: the graph has no operation");
+    return false;
+  }
   std::map<const Tensor*, uint32_t> index;
   std::vector<std::shared_ptr<Tensor>> tensors;
   auto add = [&](const std::shared_ptr<Tensor>& t) {
@@ -808,6 +830,12 @@ bool GraphImpl::ExpandBlob(const OpImpl* op) {
         st = b2vx_node_concat(graph_, ids.data(), static_cast<uint32_t>(ids.size()), o.desc.concat_axis, at(o.out, 0));
         break;
       }
+      case B2VX_NODE_ADDN: {
+        std::vector<uint32_t> ids;
+        for (size_t k = 0; k < o.in.size(); ++k) ids.push_back(at(o.in, k));
+        st = b2vx_node_addn(graph_, ids.data(), static_cast<uint32_t>(ids.size()), at(o.out, 0));
+        break;
+      }
       default: break;
     }
     if (st != B2VX_OK) {
@@ -869,7 +897,17 @@ Operation& Operation::BindOutputs(const std::vector<std::shared_ptr<Tensor>>& te
   return *this;
 }
 
-Operation& Operation::SetRoundingPolicy(OverflowPolicy, RoundingPolicy, RoundType, uint32_t) { return *this; }
+// BuiltinOpImpl::SetRoundingPolicy (src/tim/vx/builtin_op_impl.cc:65-74) writes the four values into the node's
+// vx_param.  This backend saturates and rounds to nearest even, always; the values are kept, and Compile refuses a
+// graph with an op that asked for anything else instead of quietly computing something the caller did not order.
+Operation& Operation::SetRoundingPolicy(OverflowPolicy overflow_policy, RoundingPolicy rounding_policy,
+                                        RoundType down_scale_size_rounding, uint32_t accumulator_bits) {
+  impl_->overflow_policy_ = overflow_policy;
+  impl_->rounding_policy_ = rounding_policy;
+  impl_->down_scale_size_rounding_ = down_scale_size_rounding;
+  impl_->accumulator_bits_ = accumulator_bits;
+  return *this;
+}
 
 const std::vector<std::shared_ptr<Tensor>> Operation::ConstantInputsTensor() const {
   if (IsAllInputsConst()) return impl_->inputs_tensor_;
@@ -1047,6 +1085,67 @@ std::shared_ptr<Operation> Pool2d::Clone(std::shared_ptr<Graph>& graph) const {
   return graph->CreateOperation<Pool2d>(type_, pad_, ksize_, stride_, round_type_, impl_->layout_);
 }
 
+// ---- declared-only ops (see the headers): one- and two-input families, then the three the reference's
+// layout inference tests build
+#define B2VX_DECLARED_ONLY_OP(NAME, INPUTS)                                                          \
+  NAME::NAME(Graph* graph) : BuiltinOp(graph, kNodeKindDeclaredOnly, INPUTS, 1) { impl_->name_ = #NAME; } \
+  std::shared_ptr<Operation> NAME::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<NAME>(); }
+B2VX_DECLARED_ONLY_OP(Neg, 1)
+B2VX_DECLARED_ONLY_OP(Abs, 1)
+B2VX_DECLARED_ONLY_OP(Sin, 1)
+B2VX_DECLARED_ONLY_OP(Exp, 1)
+B2VX_DECLARED_ONLY_OP(Log, 1)
+B2VX_DECLARED_ONLY_OP(Sqrt, 1)
+B2VX_DECLARED_ONLY_OP(Rsqrt, 1)
+B2VX_DECLARED_ONLY_OP(Square, 1)
+B2VX_DECLARED_ONLY_OP(LogicalNot, 1)
+B2VX_DECLARED_ONLY_OP(Floor, 1)
+B2VX_DECLARED_ONLY_OP(Ceil, 1)
+B2VX_DECLARED_ONLY_OP(Round, 1)
+B2VX_DECLARED_ONLY_OP(Cast, 1)
+B2VX_DECLARED_ONLY_OP(Rcp, 1)
+B2VX_DECLARED_ONLY_OP(Cos, 1)
+B2VX_DECLARED_ONLY_OP(Tan, 1)
+B2VX_DECLARED_ONLY_OP(ATan, 1)
+B2VX_DECLARED_ONLY_OP(ATanh, 1)
+B2VX_DECLARED_ONLY_OP(ACosh, 1)
+B2VX_DECLARED_ONLY_OP(Greater, 2)
+B2VX_DECLARED_ONLY_OP(GreaterOrEqual, 2)
+B2VX_DECLARED_ONLY_OP(Less, 2)
+B2VX_DECLARED_ONLY_OP(LessOrEqual, 2)
+B2VX_DECLARED_ONLY_OP(NotEqual, 2)
+B2VX_DECLARED_ONLY_OP(Equal, 2)
+#undef B2VX_DECLARED_ONLY_OP
+
+InstanceNormalization::InstanceNormalization(Graph* graph, float eps, DataLayout input_layout)
+    : BuiltinOp(graph, kNodeKindDeclaredOnly, 3, 1, input_layout), eps_(eps) { impl_->name_ = "InstanceNormalization"; }
+std::shared_ptr<Operation> InstanceNormalization::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<InstanceNormalization>(eps_, impl_->layout_);
+}
+
+Resize::Resize(Graph* graph, ResizeType type, float factor, bool align_corners, bool half_pixel_centers, int target_height,
+               int target_width, DataLayout layout)
+    : BuiltinOp(graph, kNodeKindDeclaredOnly, 1, 1, layout), type_(type), factor_(factor), align_corners_(align_corners),
+      half_pixel_centers_(half_pixel_centers), target_height_(target_height), target_width_(target_width) { impl_->name_ = "Resize"; }
+std::shared_ptr<Operation> Resize::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<Resize>(type_, factor_, align_corners_, half_pixel_centers_, target_height_, target_width_, impl_->layout_);
+}
+
+RoiAlign::RoiAlign(Graph* graph, int32_t output_height, int32_t output_width, float height_ratio, float width_ratio,
+                   int32_t height_sample_num, int32_t width_sample_num, DataLayout input_layout)
+    : BuiltinOp(graph, kNodeKindDeclaredOnly, 3, 1, input_layout), output_height_(output_height), output_width_(output_width),
+      height_ratio_(height_ratio), width_ratio_(width_ratio), height_sample_num_(height_sample_num),
+      width_sample_num_(width_sample_num) { impl_->name_ = "RoiAlign"; }
+std::shared_ptr<Operation> RoiAlign::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<RoiAlign>(output_height_, output_width_, height_ratio_, width_ratio_, height_sample_num_,
+                                          width_sample_num_, impl_->layout_);
+}
+
+AddN::AddN(Graph* graph, uint32_t num_inputs) : BuiltinOp(graph, B2VX_NODE_ADDN, static_cast<int>(num_inputs), 1) {}
+std::shared_ptr<Operation> AddN::Clone(std::shared_ptr<Graph>& graph) const {
+  return graph->CreateOperation<AddN>(static_cast<uint32_t>(impl_->input_cnt_));
+}
+
 Add::Add(Graph* graph) : BuiltinOp(graph, B2VX_NODE_ADD, 2, 1) {}
 std::shared_ptr<Operation> Add::Clone(std::shared_ptr<Graph>& graph) const { return graph->CreateOperation<Add>(); }
 
@@ -1056,9 +1155,16 @@ std::shared_ptr<Operation> Relu::Clone(std::shared_ptr<Graph>& graph) const { re
 NBG::NBG(Graph* graph, const char* binary, size_t input_count, size_t output_count)
     : BuiltinOp(graph, kNodeKindNbg, static_cast<int>(input_count), static_cast<int>(output_count)) {
   // the blob states its own length in its header (the reference's constructor takes no size either)
+  // and nothing of it is trusted before the first eight bytes say it is a blob of this backend and this version:
+  // a vendor-format NBG file, which the reference's API takes here, leaves the op empty and Compile fails cleanly
+  uint32_t magic = 0, version = 0;
   uint64_t total = 0;
-  if (binary) std::memcpy(&total, binary + 8, sizeof(total));
-  if (binary && total >= 32 && total < (1ull << 40)) impl_->blob_.assign(binary, binary + total);
+  if (binary) {
+    std::memcpy(&magic, binary, sizeof(magic));
+    std::memcpy(&version, binary + 4, sizeof(version));
+  }
+  if (binary && magic == kBlobMagic && version == kBlobVersion) std::memcpy(&total, binary + 8, sizeof(total));
+  if (total >= 32 && total < (1ull << 40)) impl_->blob_.assign(binary, binary + total);
 }
 std::shared_ptr<Operation> NBG::Clone(std::shared_ptr<Graph>& graph) const {
   return graph->CreateOperation<NBG>(reinterpret_cast<const char*>(impl_->blob_.data()), impl_->input_cnt_, impl_->output_cnt_);

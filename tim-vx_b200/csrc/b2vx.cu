@@ -337,6 +337,16 @@ b2vx_status infer_node(b2vx_graph* g, NodeRec& n) {
       }
       return set_shape(g, n.out, dims, "transpose", false);
     }
+    case B2VX_NODE_ADDN: {
+      for (uint32_t id : n.in) {
+        if (id == B2VX_NO_TENSOR) continue;
+        const TensorRec& t = g->tensors[id];
+        if (!t.has_shape || t.d.rank != x.d.rank) return fail(g, B2VX_SHAPE_MISMATCH, "addn: input shapes differ");
+        for (uint32_t i = 0; i < x.d.rank; ++i)
+          if (t.d.dims[i] != x.d.dims[i]) return fail(g, B2VX_SHAPE_MISMATCH, "addn: input shapes differ");
+      }
+      return set_shape(g, n.out, std::vector<uint32_t>(x.d.dims, x.d.dims + x.d.rank), "addn", false);
+    }
     case B2VX_NODE_CONCAT: {
       // vsi_nn_op_concat.c op_setup: all dimensions but `axis` agree; the axis extents add up
       const uint32_t axis = n.p.concat_axis;
@@ -761,7 +771,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     // (B2VX_FC_SMALL_M=0, read when the graph is created, keeps such shapes on the tensor-core kernel)
     // Measured at N = K = 4096: faster than the 128-row tile up to 8 rows (1.8x at one row); at 16 rows the
     // dp4a rate bounds it and the tensor-core kernel is level or better.
-    if (g->fc_small_m && mode == IDENTITY && M <= 8 && (!any_dz || x.C == x.Cp)) {
+    if (g->fc_small_m && mode == IDENTITY && M <= 16 && (!any_dz || x.C == x.Cp)) {
       pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, 1, y.Cp, y.Cp, 0, &pk);
       int8_t* dw8s = nullptr; int32_t* dbias_s = nullptr; float* dscale_s = nullptr;
       b2vx_status sts = upload(g, pk.w8, &dw8s);
@@ -1084,8 +1094,8 @@ b2vx_status plan_pool(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   TensorRec& x = g->tensors[n.in[0]];
   TensorRec& y = g->tensors[n.out];
   const b2vx_pool2d_desc& c = n.p.pool;
-  if (c.type != B2VX_POOL_MAX && c.type != B2VX_POOL_AVG && c.type != B2VX_POOL_AVG_ANDROID)
-    return fail(g, B2VX_UNSUPPORTED, "pool2d: only MAX, AVG and AVG_ANDROID are supported");
+  if (c.type != B2VX_POOL_MAX && c.type != B2VX_POOL_AVG && c.type != B2VX_POOL_L2 && c.type != B2VX_POOL_AVG_ANDROID)
+    return fail(g, B2VX_UNSUPPORTED, "pool2d: the type must be MAX, AVG, L2 or AVG_ANDROID");
   if (x.d.dtype != y.d.dtype) return fail(g, B2VX_UNSUPPORTED, "pool2d: input and output dtype must match");
   const uint32_t one[2] = {1, 1};
   const ConvGeom geo = conv_geom(x, y, c.ksize[0], c.ksize[1], c.stride, one, n.pad);
@@ -1206,6 +1216,42 @@ b2vx_status plan_add(b2vx_graph* g, uint32_t idx, NodeRec& n) {
   } else {
     return fail(g, B2VX_UNSUPPORTED, "add: operands must be all int8/uint8, all int32 or all float32");
   }
+  g->steps.push_back(std::move(s));
+  return B2VX_OK;
+}
+
+// ops::AddN: two inputs are an Add; more run the one-element-per-thread kernel over the channels-last storages
+// (all operands have one shape, hence one storage layout).
+b2vx_status plan_addn(b2vx_graph* g, uint32_t idx, NodeRec& n) {
+  uint32_t cnt = 0;
+  for (uint32_t id : n.in) cnt += id != B2VX_NO_TENSOR ? 1u : 0u;
+  if (cnt == 2) return plan_add(g, idx, n);
+  TensorRec& y = g->tensors[n.out];
+  const bool f32 = y.d.dtype == B2VX_DT_FLOAT32;
+  if (!f32 && !is_q8(y.d.dtype)) return fail(g, B2VX_UNSUPPORTED, "addn: operands must be all int8/uint8 or all float32");
+  AddNParams p;
+  std::memset(&p, 0, sizeof(p));
+  uint64_t abytes = y.bytes();
+  for (uint32_t id : n.in) {
+    if (id == B2VX_NO_TENSOR) continue;
+    TensorRec& t = g->tensors[id];
+    if (f32 ? t.d.dtype != B2VX_DT_FLOAT32 : !is_q8(t.d.dtype)) return fail(g, B2VX_UNSUPPORTED, "addn: operands must be all int8/uint8 or all float32");
+    if (t.cl_bytes != y.cl_bytes) return fail(g, B2VX_SHAPE_MISMATCH, "addn: operand storage differs from the output's");
+    p.x[p.n_in] = cl_in(t);
+    p.scale[p.n_in] = f32 ? 1.0f : t.scale();
+    p.zp[p.n_in] = f32 ? 0 : t.zp();
+    p.is_signed[p.n_in] = t.d.dtype == B2VX_DT_INT8;
+    ++p.n_in;
+    abytes += t.bytes();
+  }
+  p.out = out_quant(y);
+  p.out_signed = y.d.dtype == B2VX_DT_INT8;
+  void* yp = y.d_cl;
+  const size_t nel = f32 ? y.cl_bytes / 4 : y.cl_bytes;
+  const int elem = f32 ? 4 : 1;
+  Step s;
+  s.info = make_info("addn", idx, 0, abytes);
+  s.fn = [=](cudaStream_t st2) { launch_addn(p, elem, yp, nel, st2); return cudaGetLastError(); };
   g->steps.push_back(std::move(s));
   return B2VX_OK;
 }
@@ -1660,6 +1706,16 @@ b2vx_status b2vx_node_concat(b2vx_graph* g, const uint32_t* inputs, uint32_t n_i
   for (uint32_t i = 0; i < n_inputs; ++i) g->nodes.back().in[i] = inputs[i];
   return B2VX_OK;
 }
+b2vx_status b2vx_node_addn(b2vx_graph* g, const uint32_t* inputs, uint32_t n_inputs, uint32_t y) {
+  if (!g) return B2VX_INVALID_ARG;
+  if (!inputs || n_inputs < 2 || n_inputs > B2VX_MAX_NODE_INPUTS) return fail(g, B2VX_INVALID_ARG, "addn: 2 to 16 inputs");
+  for (uint32_t i = 0; i < n_inputs; ++i)
+    if (!valid_id(g, inputs[i])) return fail(g, B2VX_INVALID_ARG, "addn: bad tensor id");
+  const b2vx_status st = add_node(g, B2VX_NODE_ADDN, inputs[0], B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
+  if (st != B2VX_OK) return st;
+  for (uint32_t i = 0; i < n_inputs; ++i) g->nodes.back().in[i] = inputs[i];
+  return B2VX_OK;
+}
 b2vx_status b2vx_node_dataconvert(b2vx_graph* g, uint32_t x, uint32_t y) {
   return add_node(g, B2VX_NODE_DATACONVERT, x, B2VX_NO_TENSOR, B2VX_NO_TENSOR, y, nullptr);
 }
@@ -1806,7 +1862,7 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
     if (n.removed) continue;
     g->tensors[n.in[0]].is_activation = true;
     g->tensors[n.out].is_activation = true;
-    if (n.kind == B2VX_NODE_CONCAT) {
+    if (n.kind == B2VX_NODE_CONCAT || n.kind == B2VX_NODE_ADDN) {
       for (uint32_t id : n.in)
         if (id != B2VX_NO_TENSOR) g->tensors[id].is_activation = true;
     }
@@ -1866,6 +1922,7 @@ b2vx_status b2vx_graph_compile(b2vx_graph* g) {
       case B2VX_NODE_TRANSPOSE:
       case B2VX_NODE_DATACONVERT: st = plan_move(g, idx, n); break;
       case B2VX_NODE_CONCAT: st = plan_concat(g, idx, n); break;
+      case B2VX_NODE_ADDN: st = plan_addn(g, idx, n); break;
       default: return fail(g, B2VX_UNSUPPORTED, "unknown node kind");
     }
     if (st != B2VX_OK) return st;

@@ -98,7 +98,7 @@ void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* w
 void launch_conv_f32(const float* x, const float* w, const float* bias, int multiplier, int w_ic,
                      const ConvGeom& g, float* y, cudaStream_t s);
 
-// ---- pooling: type 0 max, 1 avg (divide by kw*kh), 3 avg over valid taps ----
+// ---- pooling: type 0 max, 1 avg (divide by kw*kh), 2 L2 (sqrt of the mean square over valid taps), 3 avg over valid taps ----
 void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int in_zp, int same_quant,
                    const ConvGeom& g, OutQuant out, void* y, cudaStream_t s);
 void launch_pool_f32(const float* x, int type, const ConvGeom& g, float* y, cudaStream_t s);
@@ -115,6 +115,18 @@ void launch_add_i32(const int* a, float sa, int za, const int* b, float sb, int 
 // (a dimension of 1 repeats along the output's), elem = 1 (quantized) or 4 (float32).
 void launch_add_broadcast(const void* a, int a_signed, float sa, int za, const int a_dims[5], const void* b, int b_signed, float sb,
                           int zb, const int b_dims[5], OutQuant out, const int y_dims[5], int elem, void* y, cudaStream_t s);
+// ops::AddN over n_in (2..16) same-shaped channels-last tensors of n elements each: dequantize, add in float32 from
+// left to right, quantize once.  elem = 1: int8/uint8 inputs and output; 4: float32 throughout.
+struct AddNParams {
+  const void* x[16];
+  float scale[16];
+  int zp[16];
+  int is_signed[16];
+  int n_in;
+  OutQuant out;
+  int out_signed;
+};
+void launch_addn(const AddNParams& p, int elem, void* y, size_t n, cudaStream_t s);
 // y[i] = lut[x[i]] over n bytes: Relu/Relu6 between any two 8-bit quantizations,
 // the 256-entry device table being built on the host with the reference's float sequence
 void launch_lut_q(const void* x, const uint8_t* lut, void* y, size_t n, cudaStream_t s);

@@ -1,23 +1,18 @@
 """ctypes binding of the b2vx C ABI (include/b2vx.h) for tests and benchmarks.
 
-The same binding drives two libraries that export the identical ABI:
-``tim-vx_b200/csrc/libb2vx.so`` (the CUDA product) and
-``oracle/_build/libb2vx_oracle.so`` (the CPU oracle, test infrastructure).
+The binding drives any library that exports the ABI: ``tim-vx_b200/csrc/libb2vx.so``
+(the CUDA product, PRODUCT_LIB) and, from the tests, the CPU oracle's library.
 Nothing here computes anything: tensors go in and out as numpy arrays in
 tim::vx order (shape listed fastest dimension first, i.e. the reversed numpy
 shape of a C-contiguous array).
 """
-import base64
 import ctypes as C
 import os
-import zlib
 
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PRODUCT_LIB = os.path.join(ROOT, "tim-vx_b200", "csrc", "libb2vx.so")
-ORACLE_LIB = os.path.join(ROOT, "oracle", "_build", "libb2vx_oracle.so")
-ORACLE_OPS_LIB = os.path.join(ROOT, "oracle", "_build", "liboracle_ops.so")
 
 NO_TENSOR = 0xFFFFFFFF
 DT_INT8, DT_UINT8, DT_INT32, DT_FLOAT32 = 1, 2, 5, 9
@@ -25,10 +20,10 @@ NP_DTYPE = {DT_INT8: np.int8, DT_UINT8: np.uint8, DT_INT32: np.int32, DT_FLOAT32
 Q_NONE, Q_ASYM, Q_PER_CHANNEL = 0, 1, 2
 ATTR_CONSTANT, ATTR_TRANSIENT, ATTR_VARIABLE, ATTR_INPUT, ATTR_OUTPUT = 1, 2, 4, 8, 16
 PAD_NONE, PAD_AUTO, PAD_VALID, PAD_SAME = -1, 0, 1, 2
-POOL_MAX, POOL_AVG, POOL_AVG_ANDROID = 0, 1, 3
+POOL_MAX, POOL_AVG, POOL_L2, POOL_AVG_ANDROID = 0, 1, 2, 3
 ROUND_CEILING, ROUND_FLOOR = 0, 1
 NODE_CONV2D, NODE_FC, NODE_POOL2D, NODE_ADD, NODE_RELU, NODE_RELU6, NODE_SOFTMAX = 1, 2, 3, 4, 5, 6, 7
-NODE_RESHAPE, NODE_TRANSPOSE, NODE_CONCAT, NODE_DATACONVERT = 8, 9, 10, 11
+NODE_RESHAPE, NODE_TRANSPOSE, NODE_CONCAT, NODE_DATACONVERT, NODE_ADDN = 8, 9, 10, 11, 12
 STATUS_NAMES = ["OK", "INVALID_ARG", "UNSUPPORTED", "SHAPE_MISMATCH", "QUANT_MISMATCH", "OOM", "CUDA_ERROR",
                 "DEVICE_TIMEOUT", "BAD_STATE"]
 
@@ -109,6 +104,7 @@ def load(path):
         "b2vx_node_transpose": (st, [vp, u32, u32, C.POINTER(DimsDesc)]),
         "b2vx_node_concat": (st, [vp, C.POINTER(C.c_uint32), u32, u32, u32]),
         "b2vx_node_dataconvert": (st, [vp, u32, u32]),
+        "b2vx_node_addn": (st, [vp, C.POINTER(C.c_uint32), u32, u32]),
         "b2vx_graph_compile": (st, [vp]),
         "b2vx_graph_run": (st, [vp]),
         "b2vx_graph_run_async": (st, [vp]),
@@ -252,6 +248,10 @@ class Graph:
         arr = (C.c_uint32 * len(inputs))(*inputs)
         self._check(self.lib.b2vx_node_concat(self.g, arr, len(inputs), axis, y))
 
+    def addn(self, inputs, y):
+        arr = (C.c_uint32 * len(inputs))(*inputs)
+        self._check(self.lib.b2vx_node_addn(self.g, arr, len(inputs), y))
+
     def dataconvert(self, x, y):
         self._check(self.lib.b2vx_node_dataconvert(self.g, x, y))
 
@@ -310,68 +310,3 @@ class Graph:
     def profile(self, iters=5):
         self._check(self.lib.b2vx_graph_profile(self.g, iters))
         return self.kernels()
-
-
-# ----------------------------------------------------------------------------
-# Fixture cases (tests/golden/reference_cases.json)
-
-def unpack(b64, dtype):
-    return np.frombuffer(zlib.decompress(base64.b64decode(b64)), dtype=NP_DTYPE[dtype])
-
-
-def graph_from_case(lib, case, device=0):
-    """Rebuild the graph of one fixture case.  Returns (graph, inputs, expectations):
-    inputs is a list of (tensor id, array) to write before running, expectations a
-    list of (tensor id, expected array, tolerance)."""
-    g = Graph(lib, device)
-    ids = []
-    inputs = []
-    for t in case["tensors"]:
-        declared = t["declared_rank"] > 0
-        dims = t["dims"] if declared else []
-        kw = {}
-        if t["quant_type"] == Q_PER_CHANNEL:
-            kw = dict(scales=t["scales"], zero_points=t["zero_points"] or None, channel_dim=t["channel_dim"])
-        elif t["quant_type"] == Q_ASYM:
-            kw = dict(scale=t["scale"], zero_point=t["zero_point"], channel_dim=t["channel_dim"])
-        data = None
-        if t["data"] is not None and (t["attr"] & ATTR_CONSTANT):
-            data = unpack(t["data"], t["dtype"])
-        tid = g.tensor(t["dtype"], dims, t["attr"], data=data, **kw)
-        ids.append(tid)
-        if t["data"] is not None and (t["attr"] & ATTR_INPUT):
-            inputs.append((tid, unpack(t["data"], t["dtype"])))
-    for n in case["nodes"]:
-        i = [ids[v] if v != NO_TENSOR else None for v in n["in"]]
-        o = ids[n["out"]]
-        k = n["kind"]
-        if k == NODE_CONV2D:
-            g.conv2d(i[0], i[1], i[2], o, stride=n["stride"], dilation=n["dilation"], pad_type=n["pad_type"],
-                     pad=n["pad"], multiplier=n["multiplier"], weights=n["weights"], ksize=n["ksize"], group=n.get("group", 0))
-        elif k == NODE_FC:
-            g.fully_connected(i[0], i[1], i[2], o, axis=n["axis"], weights=n["weights"])
-        elif k == NODE_POOL2D:
-            g.pool2d(i[0], o, n["type"], n["ksize"], n["stride"], pad_type=n["pad_type"], pad=n["pad"],
-                     round_type=n["round_type"])
-        elif k == NODE_ADD:
-            g.add(i[0], i[1], o)
-        elif k == NODE_RELU:
-            g.relu(i[0], o)
-        elif k == NODE_RELU6:
-            g.relu6(i[0], o)
-        elif k == NODE_SOFTMAX:
-            g.softmax(i[0], o, beta=n["beta"], axis=n["axis"])
-        elif k == NODE_RESHAPE:
-            g.reshape(i[0], o, n["dims"])
-        elif k == NODE_TRANSPOSE:
-            g.transpose(i[0], o, n["dims"])
-        elif k == NODE_CONCAT:
-            g.concat([v for v in i if v is not None], o, n["axis"])
-        elif k == NODE_DATACONVERT:
-            g.dataconvert(i[0], o)
-        else:
-            raise ValueError("unknown node kind %r" % k)
-    expects = [(ids[e["tensor"]], unpack(e["data"], e["dtype"]), e["tol"]) for e in case["expect"]]
-    oracle_out = {ids[t["id"]]: unpack(t["data"], t["dtype"]) for t in case["tensors"]
-                  if t["data"] is not None and (t["attr"] & ATTR_OUTPUT)}
-    return g, inputs, expects, oracle_out
