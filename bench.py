@@ -414,6 +414,41 @@ def kernel_table(blib, graph, B, iters, step_ms):
     return per, n.value
 
 
+def layer_table(blib, B, graph, stream, args, wl, int8_measured):
+    """One line per kernel launch of a step.  A launch's ceiling time is max(ops / int8 peak, algorithmic bytes / HBM copy
+    rate); its time inside a step is its event time scaled by step / sum of event times (the events serialise launches
+    that overlap in the replayed graph and add about 2 us apiece)."""
+    peaks = measured_peaks()
+    int8_peak = int8_measured if int8_measured else 2.0 * peaks["bf16_sustained"]
+    for _ in range(max(3, args.warmup)):
+        assert blib.b2vx_graph_run_async(graph) == 0
+    assert blib.b2vx_graph_sync(graph) == 0
+    step_ms = time_replays(blib, graph, stream, args.steps, None) / args.steps
+    assert blib.b2vx_graph_profile(graph, max(3, args.profile_iters)) == 0
+    n = C.c_uint32()
+    blib.b2vx_graph_kernel_count(graph, C.byref(n))
+    rows = []
+    for i in range(n.value):
+        k = B.KernelInfo()
+        blib.b2vx_graph_kernel_info(graph, i, C.byref(k))
+        rows.append((k.name.decode(), -1 if k.node_index == 0xFFFFFFFF else k.node_index, k.last_ms, k.ops, k.bytes))
+    total = sum(r[2] for r in rows) or 1.0
+    print("# %s, batch %d: step %.4f ms, %d launches, sum of event times %.4f ms; int8 peak %.0f TOP/s (%s), HBM %.0f GB/s (%s)"
+          % (args.workload, args.batch, step_ms, len(rows), total, int8_peak, "measured" if int8_measured else "assumed",
+             peaks["hbm_gbs"], peaks["source"]))
+    print("# %3s %-44s %5s %9s %9s %9s %8s %8s %6s" % ("i", "kernel", "node", "event_us", "step_us", "ceil_us", "TOP/s", "GB/s", "frac"))
+    ceil_total = 0.0
+    for i, (name, node, ms, ops, nbytes) in enumerate(rows):
+        us = ms / total * step_ms * 1e3
+        ceil_us = max(ops / (int8_peak * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)) * 1e6
+        ceil_total += ceil_us
+        print("%5d %-44s %5d %9.2f %9.2f %9.2f %8.1f %8.1f %6.3f" % (i, name[:44], node, ms * 1e3, us, ceil_us, ops / (us * 1e-6) / 1e12 if us else 0.0,
+                                                                       nbytes / (us * 1e-6) / 1e9 if us else 0.0, ceil_us / us if us else 0.0))
+    print("# sum of ceilings %.1f us = %.3f of the step" % (ceil_total, ceil_total / (step_ms * 1e3)))
+    wl.close()
+    return 0
+
+
 def roofline_of(t, hbm_gbs, int8_peak):
     """Achieved rate of one kernel record (ops, bytes, ms) against the roofline min(int8 peak, intensity x HBM)."""
     ai = t["ops"] / max(t["bytes"], 1)
@@ -493,6 +528,9 @@ def main():
                     help="host threads (each with its own graph replica and pinned buffers) sharing the steps of the end-to-end loop")
     ap.add_argument("--e2e-repeats", type=int, default=5, help="the end-to-end loop times this many rounds of --steps steps")
     ap.add_argument("--profile-iters", type=int, default=3)
+    ap.add_argument("--layer-table", action="store_true",
+                    help="print one line per kernel launch of a step (event time, share-scaled time, achieved rate, roofline "
+                         "ceiling time and the ratio of the two) instead of the JSON line")
     ap.add_argument("--traffic-from", default=None,
                     help="an ncu --csv log with dram__bytes_read.sum / dram__bytes_write.sum of one step of --workload at --batch: "
                          "record the dominant kernel's DRAM traffic in profiles/dram_traffic.json and exit")
@@ -547,6 +585,9 @@ def main():
     flush = None
     if in_bytes + out_bytes < 256 * 1024 * 1024 and ":" in args.workload:
         flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+    if args.layer_table:
+        return layer_table(blib, B, graph, stream, args, wl, int8_measured)
 
     # ---- device-resident timing
     for _ in range(args.warmup):
