@@ -67,15 +67,24 @@
 #include "requant.cuh"
 
 // Build with -DB2VX_TC_TRACE to record, for CTA 0, when each role passed its waits (a debugging aid
-// for pipeline stalls; the normal build contains none of it).
+// for pipeline stalls; the normal build contains none of it).  -DB2VX_TRACE_WARP=<4..19> picks the epilogue
+// warp whose per-tile stamps (loop top, accumulator ready, residual ready, chunks done) are printed.
+// -DB2VX_ABL_NOREQ / -DB2VX_ABL_NOLUT build an epilogue without its requantization / without the fused Add's
+// table look-ups: wrong outputs, for measuring what each part costs.
 #ifdef B2VX_TC_TRACE
 #define TC_TRACE(role, idx, slot) \
   do { if (p.trace && blockIdx.x == 0 && (idx) < 64) p.trace[((role) * 64 + (idx)) * 2 + (slot)] = clock64(); } while (0)
 #define TC_MARK(k) \
   do { if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[384 + (k)] = clock64(); } while (0)
+#ifndef B2VX_TRACE_WARP
+#define B2VX_TRACE_WARP 4
+#endif
+#define TC_EPI(j, k) \
+  do { if (p.trace && blockIdx.x == 0 && threadIdx.x == B2VX_TRACE_WARP * 32 && (j) < 16) p.trace[400 + (j) * 8 + (k)] = clock64(); } while (0)
 #else
 #define TC_TRACE(role, idx, slot) do { } while (0)
 #define TC_MARK(k) do { } while (0)
+#define TC_EPI(j, k) do { } while (0)
 #endif
 
 namespace b2vx {
@@ -136,7 +145,7 @@ struct GemmParams {
   long long wait_limit;    // cycles after which a barrier wait gives up (kWaitLimitCycles)
   uint32_t tx_extra;       // test aid: bytes added to what the A producer announces, so that its barrier never completes
 #ifdef B2VX_TC_TRACE
-  long long* trace;        // clock64 stamps of CTA 0, [3 roles][64 iterations][2], then 8 marks
+  long long* trace;        // clock64 stamps of CTA 0, [3 roles][64 iterations][2], 16 marks, then [16 tiles][8] of one epilogue warp
 #endif
 };
 
@@ -214,6 +223,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
+}
+// Plain (untiled) bulk copy global -> shared: both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -295,6 +310,7 @@ struct SmemHeader {
   unsigned long long tmem_full[kMaxAccBuffers];
   unsigned long long tmem_empty[kMaxAccBuffers];
   unsigned long long b_full;         // resident weights landed
+  unsigned long long tab_full;       // FUSE: the Add's table landed
   unsigned long long res_full[2];    // FUSE: residual tile landed / read by all epilogue warps
   unsigned long long res_empty[2];
   uint32_t tmem_base;
@@ -353,6 +369,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(smem_u32(&hdr->tmem_empty[a]), p.teams ? 4 : kEpilogueWarps);
     }
     mbar_init(smem_u32(&hdr->b_full), 1);
+    mbar_init(smem_u32(&hdr->tab_full), 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&hdr->res_full[b]), 1);
       mbar_init(smem_u32(&hdr->res_empty[b]), kEpilogueWarps);
@@ -509,6 +526,16 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ------------------------------------------------------------ residual producer (FUSE)
     // The residual tile of the Add (same rows and columns as the output tile) is brought into the
     // staging memory by TMA, two tiles deep, so that the epilogue reads it from shared memory.
+    // First of all the Add's 64 KB table (a constant of the graph, so no waiting for earlier kernels): four bulk copies
+    // that land while the first tiles are loaded and multiplied; the epilogue warps wait for them before their first
+    // look-up.  (Copied by the epilogue threads themselves with ordinary loads, the table kept them from their first
+    // tile for about five microseconds of every launch.)
+    if (elect_one()) {
+      const uint32_t full = smem_u32(&hdr->tab_full);
+      mbar_arrive_expect_tx(full, 65536u);
+      for (int q = 0; q < 4; ++q) bulk_load(smem_u32(add_tab) + q * 16384u, p.ep.add_table + q * 16384, 16384u, full);
+    }
+    __syncwarp();
     if (p.res_span) {
       pdl_wait();   // the residual is an earlier kernel's output
       const int span = p.res_span;
@@ -542,18 +569,12 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
   } else if (warp >= kFirstEpilogueWarp) {
     // ------------------------------------------------------------ epilogue
-    // The epilogue's constants (this N tile's folded bias and scales, the fused Add's table) are staged by the
-    // epilogue warps themselves, behind a barrier of their own: the producers and the MMA warp are already at
-    // work on the first tile meanwhile.
+    // The epilogue's constants (this N tile's folded bias and scales) are staged by the epilogue warps themselves,
+    // behind a barrier of their own: the producers and the MMA warp are already at work on the first tile meanwhile.
     for (int i = threadIdx.x - kFirstEpilogueWarp * 32; i < p.BNd; i += kEpilogueThreads) {
       const int oc = n_tile * p.BNd + i;
       hdr->bias[i] = oc < p.Ocp ? p.ep.bias_full[oc] : 0;
       hdr->scale[i] = oc < p.Ocp ? p.ep.acc_scale[oc] : 0.0f;
-    }
-    if (FUSE) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.ep.add_table);   // a constant of the graph
-      uint4* dst = reinterpret_cast<uint4*>(add_tab);
-      for (int i = threadIdx.x - kFirstEpilogueWarp * 32; i < 4096; i += kEpilogueThreads) dst[i] = __ldg(src + i);
     }
     epilogue_barrier();
     const int ew = warp - kFirstEpilogueWarp;     // 0..15
@@ -598,6 +619,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
     };
     bool alive = true;
+    bool table_ready = !FUSE;
     const int j_step = p.teams ? 4 : 1;                     // team mode: warp group col_group takes tiles j = col_group (mod 4)
     const int c_first = p.teams ? 0 : col_group * 16;       // and all of their chunks
     const int c_step = p.teams ? 16 : 64;
@@ -609,17 +631,26 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       long long row;                 // direct-store path: output row (pixel index into D), -1 outside the tensor
       const int32_t* corr_row;       // border pixels of a padded convolution: their correction, this N tile
       locate(m_tile, row, corr_row);
+      TC_EPI(j, 0);
       if (alive) alive = mbar_wait(smem_u32(&hdr->tmem_full[a]), aph, abort_flag, p.status, 4, p.wait_limit);
       alive = __all_sync(0xffffffffu, alive);   // the TMEM loads below are warp-wide
       if (!alive) {
         if (span_b) epilogue_barrier();
         continue;
       }
+      TC_EPI(j, 1);
       if (span_r) {
         alive = mbar_wait(smem_u32(&hdr->res_full[j & 1]), (j >> 1) & 1, abort_flag, p.status, 7, p.wait_limit);
         alive = __all_sync(0xffffffffu, alive);
         if (!alive) continue;
       }
+      if (!table_ready) {   // first tile of a fused Add: the table's bulk copies
+        alive = mbar_wait(smem_u32(&hdr->tab_full), 0, abort_flag, p.status, 10, p.wait_limit);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) continue;
+        table_ready = true;
+      }
+      TC_EPI(j, 2);
       if (warp == kFirstEpilogueWarp && lane == 0) TC_TRACE(2, j, 0);
       tc_fence_after();
       const uint32_t taddr = tmem_base + a * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -646,8 +677,17 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             res16 = __ldg(reinterpret_cast<const uint4*>(p.ep.add_residual + row * p.ldd + cbase));
           }
         }
+#ifdef B2VX_ABL_NOREQ
+        uint4 out16 = make_uint4(acc[0] ^ acc[4] ^ acc[8] ^ acc[12], acc[1] ^ acc[5] ^ acc[9] ^ acc[13], acc[2] ^ acc[6] ^ acc[10] ^ acc[14],
+                                 acc[3] ^ acc[7] ^ acc[11] ^ acc[15]);
+#else
         uint4 out16 = requant_chunk16<EXTRA>(acc, &hdr->bias[c0], &hdr->scale[c0], rc, sub,
                                              (corr_row && cbase + 16 <= p.Ocp) ? corr_row + c0 : nullptr);
+#endif
+#ifdef B2VX_ABL_NOLUT
+        if (FUSE) { out16.x ^= res16.x; out16.y ^= res16.y; out16.z ^= res16.z; out16.w ^= res16.w; }
+        else
+#endif
         if (FUSE) {
           out16.x = add_lut_word(out16.x, res16.x, add_tab);
           out16.y = add_lut_word(out16.y, res16.y, add_tab);
@@ -678,6 +718,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           c0 += c_step;
         }
       }
+      TC_EPI(j, 3);
       // accumulator buffer (and residual buffer) free again
       tc_fence_before();
       __syncwarp();
@@ -1239,8 +1280,8 @@ cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
 #ifdef B2VX_TC_TRACE
   GemmTcPlan* mp = const_cast<GemmTcPlan*>(plan);
   if (!mp->params.trace) {
-    cudaMalloc(reinterpret_cast<void**>(&mp->params.trace), (3 * 64 * 2 + 8) * sizeof(long long));
-    cudaMemset(mp->params.trace, 0, (3 * 64 * 2 + 8) * sizeof(long long));
+    cudaMalloc(reinterpret_cast<void**>(&mp->params.trace), (3 * 64 * 2 + 16 + 128) * sizeof(long long));
+    cudaMemset(mp->params.trace, 0, (3 * 64 * 2 + 16 + 128) * sizeof(long long));
   }
 #endif
   // Test aid: B2VX_TEST_STALL=<n> makes the first n launches of the process announce 16 bytes more than their loads
@@ -1269,7 +1310,7 @@ cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
     static int launches = 0;
     if (++launches == 3) {
       cudaStreamSynchronize(s);
-      long long h[3 * 64 * 2 + 8];
+      long long h[3 * 64 * 2 + 16 + 128];
       cudaMemcpy(h, plan->params.trace, sizeof(h), cudaMemcpyDeviceToHost);
       const long long t0 = h[0];
       const GemmParams& p = plan->params;
@@ -1280,6 +1321,9 @@ cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
         std::fprintf(stderr, "it %2d  prodA slot-free %7lld issued %7lld | mma data-in %7lld committed %7lld | epi acc-ready %7lld done %7lld\n",
                      i, h[(0 * 64 + i) * 2] - t0, h[(0 * 64 + i) * 2 + 1] - t0, h[(1 * 64 + i) * 2] - t0,
                      h[(1 * 64 + i) * 2 + 1] - t0, h[(2 * 64 + i) * 2] - t0, h[(2 * 64 + i) * 2 + 1] - t0);
+      for (int i = 0; i < 12; ++i)
+        std::fprintf(stderr, "epi warp %d tile %2d  top %7lld accumulator ready %7lld residual ready %7lld chunks done %7lld\n", B2VX_TRACE_WARP, i,
+                     h[400 + i * 8] - t0, h[400 + i * 8 + 1] - t0, h[400 + i * 8 + 2] - t0, h[400 + i * 8 + 3] - t0);
     }
   }
 #endif
