@@ -456,7 +456,9 @@ ConvGeom conv_geom(const TensorRec& x, const TensorRec& y, int kw, int kh, const
 }
 
 // vsi_nn_QuantCheck (src/tim/vx/internal/src/utils/vsi_nn_dtype_util.c:368-441):
-// only same-dtype, same-quantization-kind triples are checked; the bias scale
+// only same-dtype, same-quantization-kind triples are checked (so per-channel weights
+// under a per-tensor input, whose quantization kinds differ, pass unchecked there and
+// here: no per-channel comparison of bias scales exists to mirror); the bias scale
 // has to equal s_in*s_w within max(min(.)*1e-5, 1e-8)
 // (src/tim/vx/internal/src/quantization/vsi_nn_asymmetric_affine.c:59-112).
 bool quant_check(const TensorRec& x, const TensorRec& w, const TensorRec* b) {
