@@ -229,6 +229,13 @@ POOL_CASES = {
     "max2x2": G.pool_q(24, 24, 20, 2, B.POOL_MAX, (2, 2), (2, 2)),
     "max3x3s2_ceil": G.pool_q(112, 112, 64, 1, B.POOL_MAX, (3, 3), (2, 2), pad=(0, 1, 0, 1), round_type=B.ROUND_CEILING),
     "max_requant": G.pool_q(9, 9, 16, 1, B.POOL_MAX, (3, 3), (1, 1), pad=(1, 1, 1, 1), out_q=(0.07, 10)),
+    # the 2 x 2-outputs-per-thread kernel: padding on every side, odd output extents (a thread's second row / column missing),
+    # signed bytes, a 2x2 window on odd inputs, ceiling mode with windows hanging over the right and bottom edges
+    "max3x3s2_pad1": G.pool_q(28, 28, 48, 2, B.POOL_MAX, (3, 3), (2, 2), pad=(1, 1, 1, 1)),
+    "max3x3s2_odd": G.pool_q(15, 13, 32, 3, B.POOL_MAX, (3, 3), (2, 2), pad=(1, 0, 0, 1)),
+    "max3x3s2_s8": G.pool_q(11, 9, 16, 2, B.POOL_MAX, (3, 3), (2, 2), pad=(2, 2, 2, 2), in_q=(0.1, -5), dtype=B.DT_INT8),
+    "max2x2s2_odd_ceil": G.pool_q(9, 7, 32, 2, B.POOL_MAX, (2, 2), (2, 2), round_type=B.ROUND_CEILING),
+    "max3x3s2_tiny": G.pool_q(3, 3, 16, 1, B.POOL_MAX, (3, 3), (2, 2), pad=(1, 1, 1, 1)),
     "avg7x7_global": G.pool_q(7, 7, 2048, 2, B.POOL_AVG, (7, 7), (7, 7), out_q=(0.04, 7)),
     "avg_pad": G.pool_q(10, 10, 32, 1, B.POOL_AVG, (3, 3), (2, 2), pad=(1, 1, 1, 1)),
     "avg_android_pad": G.pool_q(10, 10, 32, 1, B.POOL_AVG_ANDROID, (3, 3), (2, 2), pad=(1, 1, 1, 1)),

@@ -3,6 +3,8 @@
 // Softmax, im2col and the float32 variants.  All work on channels-last
 // storage (kernels.h) with 128-bit or 32-bit accesses along the channel axis.
 #include <cmath>
+#include <cstdlib>
+#include <cstring>
 
 #include "kernels.h"
 #include "pdl.cuh"
@@ -671,6 +673,90 @@ __global__ void __launch_bounds__(256) pool_q16_kernel(const uint8_t* __restrict
     o[k] = word;
   }
   *reinterpret_cast<uint4*>(y + static_cast<size_t>(p) * g.Cp + ch * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Max pooling whose output keeps the input's quantization, K x K window with stride S (3x3 / 2 and 2x2 / 2 are the
+// common ones): a thread produces a 2 x 2 block of outputs for 16 channels from the (K + S) x (K + S) input patch the
+// four windows share, row by row: one horizontal maximum per output column and input row, handed to the output rows whose
+// window contains that row.  25 loads and about 130 byte-SIMD maxima for four 3x3 / 2 outputs, where one output per thread
+// costs 9 loads and 36 maxima each.  Taps outside the image are skipped by clamping their coordinates into the window's
+// valid part (a repeated tap does not change a maximum; every window of an existing output has a valid tap).
+template <bool XS, int K, int S>
+__global__ void __launch_bounds__(256) pool_max2x2_kernel(const uint8_t* __restrict__ x, ConvGeom g, uint8_t* __restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int P = K + S;   // patch extent
+  const int chunks = g.Cp >> 4;
+  const int wo2n = (g.Wo + 1) >> 1, ho2n = (g.Ho + 1) >> 1;
+  const long long total = static_cast<long long>(g.N) * ho2n * wo2n * chunks;
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= total) return;
+  const int ch = static_cast<int>(i % chunks);
+  const long long p = i / chunks;
+  const int wo = static_cast<int>(p % wo2n) * 2;
+  const long long t = p / wo2n;
+  const int ho = static_cast<int>(t % ho2n) * 2;
+  const int n = static_cast<int>(t / ho2n);
+  const int w0 = wo * S - g.pl, h0 = ho * S - g.pt;
+  const bool has_w1 = wo + 1 < g.Wo, has_h1 = ho + 1 < g.Ho;
+  // columns of the patch, each clamped into the valid part of the window(s) it belongs to
+  int col[P];
+#pragma unroll
+  for (int c = 0; c < P; ++c) {
+    // window 0 holds patch columns [0, K), window 1 [S, S + K); a column of window 1 only (c >= K) is clamped into window
+    // 1's range, which starts at w0 + S
+    const int lo = c >= K ? max(w0 + S, 0) : max(w0, 0);
+    col[c] = min(max(w0 + c, lo), g.W - 1);
+  }
+  const uint32_t flip = XS ? 0x80808080u : 0u;
+  const uint8_t* img = x + static_cast<size_t>(n) * g.H * g.W * g.Cp + ch * 16;
+  uint32_t o[2][2][4];   // [output row][output column][word]; bytes biased to unsigned
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o[a][b][k] = 0u;
+#pragma unroll
+  for (int r = 0; r < P; ++r) {
+    const int lo = r >= K ? max(h0 + S, 0) : max(h0, 0);
+    const int hr = min(max(h0 + r, lo), g.H - 1);
+    const uint8_t* rowp = img + static_cast<size_t>(hr) * g.W * g.Cp;
+    uint4 v[P];
+#pragma unroll
+    for (int c = 0; c < P; ++c) v[c] = __ldg(reinterpret_cast<const uint4*>(rowp + static_cast<size_t>(col[c]) * g.Cp));
+    uint32_t m[2][4];
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      m[b][0] = m[b][1] = m[b][2] = m[b][3] = 0u;
+#pragma unroll
+      for (int c = b * S; c < b * S + K; ++c) {
+        m[b][0] = __vmaxu4(m[b][0], v[c].x ^ flip);
+        m[b][1] = __vmaxu4(m[b][1], v[c].y ^ flip);
+        m[b][2] = __vmaxu4(m[b][2], v[c].z ^ flip);
+        m[b][3] = __vmaxu4(m[b][3], v[c].w ^ flip);
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      if (r >= a * S && r < a * S + K) {   // (known at compile time: the loops are unrolled)
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) o[a][b][k] = __vmaxu4(o[a][b][k], m[b][k]);
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < 2; ++a) {
+    if (a == 1 && !has_h1) break;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      if (b == 1 && !has_w1) break;
+      const size_t pix = (static_cast<size_t>(n) * g.Ho + ho + a) * g.Wo + wo + b;
+      *reinterpret_cast<uint4*>(y + pix * g.Cp + ch * 16) = make_uint4(o[a][b][0] ^ flip, o[a][b][1] ^ flip, o[a][b][2] ^ flip, o[a][b][3] ^ flip);
+    }
+  }
 }
 
 // Large windows with few outputs (global average pooling): one warp per (output pixel, 16-channel
@@ -1565,6 +1651,22 @@ void launch_pool_q(const void* x, int is_signed, int type, float in_scale, int i
       // few outputs, many taps each: a warp per output chunk
       if (is_signed) launch_pdl(pool_q16_warp_kernel<true>, dim3(grid_for(total * 32, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
       else launch_pdl(pool_q16_warp_kernel<false>, dim3(grid_for(total * 32, 256)), dim3(256), 0, s, xp, type, in_scale, in_zp, same_quant, g, out, yp);
+      return;
+    }
+    // Max pooling that keeps the quantization, 3x3 or 2x2 window, stride 2, padding smaller than the window: 2 x 2 outputs per
+    // thread (B2VX_POOL_2X2=0: one output per thread as for every other pooling)
+    static const bool no_2x2 = [] { const char* e = std::getenv("B2VX_POOL_2X2"); return e && std::strcmp(e, "0") == 0; }();
+    if (!no_2x2 && type == 0 && same_quant && g.kw == g.kh && (g.kw == 3 || g.kw == 2) && g.sx == 2 && g.sy == 2 && g.pl < g.kw && g.pt < g.kh &&
+        (g.Wo - 1) * 2 - g.pl <= g.W - 1 && (g.Ho - 1) * 2 - g.pt <= g.H - 1) {   // every window holds a tap of the image
+      const long long blocks4 = static_cast<long long>(g.N) * ((g.Ho + 1) / 2) * ((g.Wo + 1) / 2) * (g.Cp / 16);
+      const dim3 grid4(grid_for(blocks4, 256));
+      if (g.kw == 3) {
+        if (is_signed) launch_pdl(pool_max2x2_kernel<true, 3, 2>, grid4, dim3(256), 0, s, xp, g, yp);
+        else launch_pdl(pool_max2x2_kernel<false, 3, 2>, grid4, dim3(256), 0, s, xp, g, yp);
+      } else {
+        if (is_signed) launch_pdl(pool_max2x2_kernel<true, 2, 2>, grid4, dim3(256), 0, s, xp, g, yp);
+        else launch_pdl(pool_max2x2_kernel<false, 2, 2>, grid4, dim3(256), 0, s, xp, g, yp);
+      }
       return;
     }
     const dim3 grid(grid_for(total, 256));
