@@ -951,7 +951,8 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   // Resident weights: the whole [BN x K] tile of this CTA's N tile when it is small (B2VX_TC_BRES=0 disables).
   static const bool no_bres = [] { const char* e2 = std::getenv("B2VX_TC_BRES"); return e2 && std::strcmp(e2, "0") == 0; }();
   const size_t b_all = static_cast<size_t>(kblocks_per_tile) * p.BN * p.BK;
-  p.b_resident = (!no_bres && e.add_residual == nullptr && b_all <= 72 * 1024) ? 1 : 0;
+  // (beside a fused Add's table and residual tiles only up to 32 KB)
+  p.b_resident = (!no_bres && b_all <= (e.add_residual != nullptr ? 32u : 72u) * 1024) ? 1 : 0;
   const size_t bres = p.b_resident ? ((b_all + 1023) & ~static_cast<size_t>(1023)) : 0;
   const size_t sub_bytes = static_cast<size_t>(kBlockM + (p.b_resident ? 0 : p.BN)) * p.BK;
   const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging - add_table_bytes - bres;
