@@ -390,6 +390,28 @@ def time_replays(blib, graph, stream, steps, flush):
     return sum(a.elapsed_time(b) for a, b in evs)
 
 
+def time_replays_streams(blib, lanes, steps):
+    """Milliseconds of `steps` replays shared round-robin by the graph replicas in `lanes` ((graph handle, torch stream)
+    pairs), each replica on its own stream with its own resident input: kernels of different replicas overlap wherever
+    one leaves SMs idle (a layer with fewer tiles than SMs, the tail of a launch, its prologue).  Timed from an event all
+    streams wait for to an event that waits for all streams."""
+    import torch
+    main = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(main)
+    for _, st in lanes:
+        st.wait_event(e0)
+    for i in range(steps):
+        assert blib.b2vx_graph_run_async(lanes[i % len(lanes)][0]) == 0
+    for _, st in lanes:
+        done = torch.cuda.Event()
+        done.record(st)
+        main.wait_event(done)
+    e1.record(main)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
 def kernel_table(blib, graph, B, iters, step_ms):
     """Per-kernel times of one step: b2vx_graph_profile puts an event pair around every launch, which costs about
     2 us apiece and breaks the overlap of consecutive kernels, so the event times add up to more than a step of the
@@ -524,7 +546,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer loop (profiler captures)")
     ap.add_argument("--no-configs", action="store_true", help="skip the extra configurations (N=1, default workload)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained replay")
-    ap.add_argument("--e2e-threads", type=int, default=3,
+    ap.add_argument("--streams", type=int, default=2,
+                    help="graph replicas replayed concurrently, each on its own CUDA stream with its own resident batch (the device-resident "
+                         "value; 1 = one graph back to back, which the line also reports as single_stream)")
+    ap.add_argument("--e2e-threads", type=int, default=4,
                     help="host threads (each with its own graph replica and pinned buffers) sharing the steps of the end-to-end loop")
     ap.add_argument("--e2e-repeats", type=int, default=5, help="the end-to-end loop times this many rounds of --steps steps")
     ap.add_argument("--profile-iters", type=int, default=3)
@@ -598,10 +623,32 @@ def main():
         sampler.start()
         time.sleep(0.3)
     barrier()
-    elapsed = time_replays(blib, graph, stream, args.steps, flush)
+    single_elapsed = time_replays(blib, graph, stream, args.steps, flush)
     barrier()
     assert blib.b2vx_graph_sync(graph) == 0, "a kernel reported a device-side timeout"
+    # ---- the same with --streams replicas in flight (not for the L2-flushed single-operator passes)
+    n_lanes = max(1, args.streams) if flush is None else 1
+    lanes, lane_workloads = [(graph, stream)], []
+    for _ in range(1, n_lanes):
+        r = make_workload(args, False, args.batch, local_rank)
+        rs = torch.cuda.Stream()
+        assert blib.b2vx_graph_set_stream(r.graph_handle(), C.c_void_p(rs.cuda_stream)) == 0
+        r.set_input(host_in.data_ptr())
+        for _ in range(max(2, args.warmup)):
+            assert blib.b2vx_graph_run_async(r.graph_handle()) == 0
+        assert blib.b2vx_graph_sync(r.graph_handle()) == 0
+        lanes.append((r.graph_handle(), rs))
+        lane_workloads.append(r)
+    elapsed = single_elapsed
+    if n_lanes > 1:
+        time_replays_streams(blib, lanes, len(lanes))   # one untimed round
+        barrier()
+        elapsed = time_replays_streams(blib, lanes, args.steps)
+        barrier()
+        for g, _ in lanes:
+            assert blib.b2vx_graph_sync(g) == 0, "a kernel reported a device-side timeout"
     ms = torch.tensor([elapsed], device="cuda")
+    single_ms = torch.tensor([single_elapsed], device="cuda")
     # ---- end to end through the public calls, host buffers pinned
     # Every step copies its input from pinned host memory, runs, and copies its result back, all through the
     # synchronous public calls.  As in the reference's multi-thread sample, --e2e-threads host threads each own
@@ -650,8 +697,9 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(single_ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(ms.item()), float(e2e_ms.item())
+    ms, single_ms, e2e_ms = float(ms.item()), float(single_ms.item()), float(e2e_ms.item())
 
     # ---- sustained: the same graph back to back for at least two seconds, clocks and power sampled meanwhile
     sustained = None
@@ -662,14 +710,15 @@ def main():
         if rank == 0:
             sus_sampler.start()
         barrier()
-        sus_ms = torch.tensor([time_replays(blib, graph, stream, n_sus, None)], device="cuda")
+        sus_ms = torch.tensor([time_replays_streams(blib, lanes, n_sus) if n_lanes > 1 else time_replays(blib, graph, stream, n_sus, None)],
+                              device="cuda")
         barrier()
         sus_clocks = sus_sampler.stop() if rank == 0 else None
         if world > 1:
             dist.all_reduce(sus_ms, op=dist.ReduceOp.MAX)
         if rank == 0:
             sus_ms = float(sus_ms.item())
-            sustained = {"value": wl.units * world * n_sus / (sus_ms / 1e3) * wl.scale, "unit": wl.unit, "steps": n_sus,
+            sustained = {"value": wl.units * world * n_sus / (sus_ms / 1e3) * wl.scale, "unit": wl.unit, "steps": n_sus, "streams": n_lanes,
                          "seconds": sus_ms / 1e3, "ms_per_step": sus_ms / n_sus, "sm_mhz_median": sus_clocks["sm_mhz"],
                          "power_w_median": sus_clocks.get("power_w"), "reasons": sus_clocks["reasons"],
                          "ms_per_step_x_mhz": (sus_ms / n_sus) * sus_clocks["sm_mhz"] if sus_clocks["sm_mhz"] else None}
@@ -678,8 +727,9 @@ def main():
         units = wl.units * world * args.steps
         value = units / (ms / 1e3) * wl.scale
         e2e_value = wl.units * world * e2e_steps / (e2e_ms / 1e3) * wl.scale if e2e_steps else None
-        # ---- roofline of the dominant kernel, per-kernel CUDA events measured live
-        step_ms = ms / args.steps
+        # ---- roofline of the dominant kernel, per-kernel CUDA events measured live; a kernel's time is its share of the
+        # single-stream step (with several replicas in flight kernels overlap and a per-kernel time is not defined)
+        step_ms = single_ms / args.steps
         per, n_kernels = kernel_table(blib, graph, B, args.profile_iters, step_ms)
         top = max(per, key=lambda n: per[n]["ms"])
         peaks = measured_peaks()
@@ -714,15 +764,22 @@ def main():
             "dtype": "u8", "data": "synthetic",
             "config": {"workload": wl.describe,
                        "parallelism": "batch-sharded replicas, no collective", "units_per_step": wl.units * world,
+                       "streams": n_lanes,
+                       "step": "one replay of one graph replica over its resident batch; the %d replicas of a GPU, each on its own CUDA "
+                               "stream, take the steps in turn and overlap" % n_lanes if n_lanes > 1 else "one replay of the graph",
                        "l2": ("a 192 MB buffer is rewritten between timed passes (L2 flush); each pass has its own events"
                               if flush is not None else "the per-step working set exceeds the 126 MB L2")},
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                     "ms_per_step": e2e_ms / e2e_steps if e2e_steps else None, "host_threads": n_host,
                     "steps": e2e_steps, "repeats": max(1, args.e2e_repeats) if e2e_steps else 0},
             "gpu_launches": n_kernels * args.steps,
+            "single_stream": {"value": wl.units * world * args.steps / (single_ms / 1e3) * wl.scale, "unit": wl.unit,
+                              "ms_per_step": single_ms / args.steps},
             "roofline": roof, "sustained": sustained, "cpu_baseline": cpu, "clocks": clocks, "configs": configs,
         }
         print(json.dumps(line))
+    for r in lane_workloads:
+        r.close()
     wl.close()
     if world > 1:
         dist.destroy_process_group()
