@@ -93,7 +93,11 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kFirstEpilogueWarp = 4;
-constexpr int kEpilogueWarps = 16;
+#ifndef B2VX_EPI_WARPS
+#define B2VX_EPI_WARPS 16
+#endif
+constexpr int kEpilogueWarps = B2VX_EPI_WARPS;   // a multiple of four: one warp per TMEM lane quarter in every column group
+constexpr int kGroups = kEpilogueWarps / 4;      // column groups of a wide tile, or teams on narrow tiles
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kThreadsTc = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
 constexpr int kMaxStages = 8;
@@ -620,9 +624,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     };
     bool alive = true;
     bool table_ready = !FUSE;
-    const int j_step = p.teams ? 4 : 1;                     // team mode: warp group col_group takes tiles j = col_group (mod 4)
+    const int j_step = p.teams ? kGroups : 1;               // team mode: warp group col_group takes tiles j = col_group (mod kGroups)
     const int c_first = p.teams ? 0 : col_group * 16;       // and all of their chunks
-    const int c_step = p.teams ? 16 : 64;
+    const int c_step = p.teams ? 16 : kGroups * 16;
     j = p.teams ? col_group : 0;
     for (int tile = blockIdx.x + j * static_cast<int>(gridDim.x); tile < num_tiles; tile += j_step * static_cast<int>(gridDim.x), j += j_step) {
       const int m_tile = m_tile0 + j * m_step;
@@ -928,7 +932,7 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   if (!tma_store || e.add_residual != nullptr) p.store_span = 0;
   const size_t add_table_bytes = e.add_residual != nullptr ? 65536 : 0;
   static const bool no_teams = [] { const char* e2 = std::getenv("B2VX_TC_TEAMS"); return e2 && std::strcmp(e2, "0") == 0; }();
-  p.teams = (p.BNd <= 64 && p.store_span == 0 && !no_teams) ? 4 : 0;
+  p.teams = (p.BNd <= 64 && p.store_span == 0 && !no_teams) ? kGroups : 0;
   if (p.teams) p.res_span = 0;   // four tiles in flight do not fit the two residual buffers: threads load their pieces
   if (p.res_span) {
     // The Add's table and two residual tiles leave less for the operand ring: three stages must remain,
@@ -973,7 +977,7 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.acc_stride = (p.BN + 31) & ~31;
   p.acc_shift = 1;
   while (p.acc_shift < 3 && (2 << p.acc_shift) * p.acc_stride <= 512) ++p.acc_shift;
-  if (p.teams && p.acc_shift < 2) p.teams = 0;   // a team per accumulator buffer needs four of them
+  if (p.teams && (1 << p.acc_shift) < kGroups) p.teams = 0;   // every team's tile needs an accumulator buffer
   int cols = 32;
   while (cols < (1 << p.acc_shift) * p.acc_stride) cols <<= 1;
   p.tmem_cols = cols;
