@@ -137,6 +137,14 @@ struct GemmParams {
   int kw, sx, sy, dx, dy, pl, pt;
   int cblocks, Cp;
   uint32_t a_tx_bytes;     // bytes one A box delivers (rows in the box x BK)
+  // Halo mode of the implicit convolution (stride 1, weights resident): the ring's stage is the tile's input patch
+  // with its halo for one channel block, loaded once ((TW + kw - 1) x (TH + kh - 1) pixels of BK bytes, TW = 8,
+  // TN = 1), and the kh * kw taps are MMAs on shifted views of it: descriptor start = patch + (ky * halo_w + kx) * BK,
+  // distance between 8-row groups = halo_w * BK.  The 64-byte swizzle is a function of the absolute shared-memory
+  // address on both sides (TMA write, MMA read), so a view may start on any pixel.
+  int halo, halo_w;
+  uint32_t a_stage_bytes;  // halo mode: bytes of a stage (the patch, rounded up to 1 KB)
+  int num_kb_b;            // k-blocks of the weight tile (kh * kw * cblocks; == num_kb unless halo)
   // output through shared memory + TMA store: the tile is staged as BN/store_span column blocks of
   // [128 rows][store_span bytes], 16-byte chunks XOR-swizzled the way the store's tensor map expects.
   // store_span == 0: BN is not a multiple of 32, threads store their 16-byte pieces directly.
@@ -272,6 +280,17 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
+// The same with the accumulate flag known when compiling (no predicate set-up per instruction).
+template <int ACCUMULATE>
+__device__ __forceinline__ void tc_mma_i8_const(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "n"(ACCUMULATE)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, int (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -340,12 +359,12 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
-  const uint32_t a_bytes = kBlockM * p.BK;
+  const uint32_t a_bytes = p.halo ? p.a_stage_bytes : static_cast<uint32_t>(kBlockM) * p.BK;
   const uint32_t b_bytes = static_cast<uint32_t>(p.BN) * p.BK;
   const uint32_t sub_bytes = a_bytes + (p.b_resident ? 0u : b_bytes);   // one k-block: whole swizzle atoms, see the host-side plan
   const uint32_t stage_bytes = sub_bytes * p.group;
   const uint32_t ring_bytes = (p.stages * stage_bytes + 1023u) & ~1023u;
-  const uint32_t bres_bytes = p.b_resident ? ((static_cast<uint32_t>(p.num_kb) * b_bytes + 1023u) & ~1023u) : 0u;
+  const uint32_t bres_bytes = p.b_resident ? ((static_cast<uint32_t>(p.num_kb_b) * b_bytes + 1023u) & ~1023u) : 0u;
   const uint32_t bres_addr = tiles_addr + ring_bytes;                    // resident weights: k-block after k-block
   const uint32_t staging_bytes = (p.store_span || p.res_span) ? static_cast<uint32_t>(kBlockM) * p.BNd : 0u;   // per buffer, multiple of 4096
   uint8_t* staging = tiles + ring_bytes + bres_bytes;
@@ -401,9 +420,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // Weights are constants of the graph, so this does not wait for earlier kernels of the stream.
     if (elect_one()) {
       const uint32_t full = smem_u32(&hdr->b_full);
-      mbar_arrive_expect_tx(full, static_cast<uint32_t>(p.num_kb) * b_bytes);
+      mbar_arrive_expect_tx(full, static_cast<uint32_t>(p.num_kb_b) * b_bytes);
       int tap = 0, cb = 0;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
+      for (int kb = 0; kb < p.num_kb_b; ++kb) {
         const uint32_t dst = bres_addr + static_cast<uint32_t>(kb) * b_bytes;
         if (p.conv) {
           tma_load_2d(dst, &map_b, tap * p.Cp + cb * p.BK, n_tile * p.BN, full);
@@ -503,18 +522,46 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         TC_TRACE(1, it, 0);
         tc_fence_after();
         const int cnt = min(p.group, p.num_kb - kb0);
-        if (elect_one()) {
-          uint32_t a_addr = tiles_addr + s * stage_bytes;
-          uint32_t acc_flag = accumulate;
-          for (int gi = 0; gi < cnt; ++gi, a_addr += sub_bytes) {
-            const uint64_t da = make_smem_desc(a_addr, p.sbo, p.layout_type);
-            const uint64_t db = make_smem_desc(p.b_resident ? bres_addr + static_cast<uint32_t>(kb0 + gi) * b_bytes : a_addr + a_bytes,
-                                               p.sbo, p.layout_type);
-            for (int k = 0; k < ksteps; ++k) {
-              // advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
-              tc_mma_i8(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc, acc_flag);
-              acc_flag = 1;
+        if (p.halo) {
+          // one stage = the input patch of channel block kb0: every tap is a shifted view of it.  The issuing thread
+          // shares its scheduler with four epilogue warps, so every instruction here costs several cycles: descriptors
+          // are built once per stage and advanced by additions to their address field (16-byte units).
+          if (elect_one()) {
+            const uint64_t da0 = make_smem_desc(tiles_addr + s * stage_bytes, static_cast<uint32_t>(p.halo_w) * p.BK, p.layout_type);
+            uint64_t db = make_smem_desc(bres_addr + static_cast<uint32_t>(kb0) * b_bytes, p.sbo, p.layout_type);
+            const uint64_t db_step = static_cast<uint64_t>((static_cast<uint32_t>(p.cblocks) * b_bytes) >> 4);
+            const uint32_t px16 = static_cast<uint32_t>(p.BK) >> 4;           // one pixel of the patch, in 16-byte units
+            const int taps_h = p.num_kb_b / (p.cblocks * p.kw);
+            bool first = accumulate == 0;
+            for (int ky = 0; ky < taps_h; ++ky) {
+              uint64_t da = da0 + static_cast<uint64_t>(static_cast<uint32_t>(ky * p.halo_w) * px16);
+              for (int kx = 0; kx < p.kw; ++kx, da += px16, db += db_step) {
+                if (first) {
+                  tc_mma_i8_const<0>(tmem_d, da, db, p.idesc);
+                  first = false;
+                } else {
+                  tc_mma_i8_const<1>(tmem_d, da, db, p.idesc);
+                }
+                for (int k = 1; k < ksteps; ++k) tc_mma_i8_const<1>(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc);
+              }
             }
+            tc_commit(smem_u32(&hdr->empty[s]));
+          }
+        } else if (elect_one()) {
+          uint64_t da = make_smem_desc(tiles_addr + s * stage_bytes, p.sbo, p.layout_type);
+          uint64_t db = make_smem_desc(p.b_resident ? bres_addr + static_cast<uint32_t>(kb0) * b_bytes : tiles_addr + s * stage_bytes + a_bytes,
+                                       p.sbo, p.layout_type);
+          const uint64_t da_step = static_cast<uint64_t>(sub_bytes >> 4), db_step = static_cast<uint64_t>((p.b_resident ? b_bytes : sub_bytes) >> 4);
+          bool first = accumulate == 0;
+          for (int gi = 0; gi < cnt; ++gi, da += da_step, db += db_step) {
+            // k steps advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
+            if (first) {
+              tc_mma_i8_const<0>(tmem_d, da, db, p.idesc);
+              first = false;
+            } else {
+              tc_mma_i8_const<1>(tmem_d, da, db, p.idesc);
+            }
+            for (int k = 1; k < ksteps; ++k) tc_mma_i8_const<1>(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc);
           }
           tc_commit(smem_u32(&hdr->empty[s]));
         }
@@ -893,8 +940,11 @@ namespace {
 // Everything of a plan that does not depend on how A is addressed: N tiling, K block / swizzle mode,
 // output staging, stage count, TMEM columns, instruction descriptor, the B tensor map.
 // Kspan is the K extent one tap (or the whole GEMM) covers, used to pick BK.
+// halo_w, halo_h: extent in pixels of the input patch (tile + halo) the caller would load per channel block if the plan
+// turns out to allow the halo mode of the implicit convolution (0: not asked for).
 bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int taps, int ldd,
-                 const ContractEpilogue& e, void* D, int* status, const char** why, const GemmTcTiling* tiling) {
+                 const ContractEpilogue& e, void* D, int* status, const char** why, const GemmTcTiling* tiling, int halo_w = 0,
+                 int halo_h = 0) {
   GemmParams& p = plan->params;
   p.Ocp = ldd;
   p.ldd = ldd;
@@ -958,9 +1008,17 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   // (beside a fused Add's table and residual tiles only up to 32 KB)
   p.b_resident = (!no_bres && b_all <= (e.add_residual != nullptr ? 32u : 72u) * 1024) ? 1 : 0;
   const size_t bres = p.b_resident ? ((b_all + 1023) & ~static_cast<size_t>(1023)) : 0;
-  const size_t sub_bytes = static_cast<size_t>(kBlockM + (p.b_resident ? 0 : p.BN)) * p.BK;
+  // Halo mode: weights resident, 64-byte K blocks (the swizzle mode whose shifted views were verified on the device);
+  // B2VX_TC_HALO=0 keeps one shifted TMA box per tap.
+  static const bool no_halo = [] { const char* e2 = std::getenv("B2VX_TC_HALO"); return e2 && std::strcmp(e2, "0") == 0; }();
+  p.halo = (halo_w > 0 && !no_halo && p.b_resident && p.BK == 64 && e.add_residual == nullptr) ? 1 : 0;
+  p.halo_w = p.halo ? halo_w : 0;
+  p.a_stage_bytes = p.halo ? static_cast<uint32_t>((static_cast<size_t>(halo_w) * halo_h * p.BK + 1023) & ~static_cast<size_t>(1023)) : 0u;
+  p.num_kb_b = kblocks_per_tile;
+  const size_t sub_bytes = p.halo ? p.a_stage_bytes : static_cast<size_t>(kBlockM + (p.b_resident ? 0 : p.BN)) * p.BK;
   const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging - add_table_bytes - bres;
   int group = static_cast<int>((64 * 1024) / sub_bytes);
+  if (p.halo) group = 1;
   if (group > kblocks_per_tile) group = kblocks_per_tile;
   if (group > kMaxGroup) group = kMaxGroup;
   if (group < 1) group = 1;
@@ -1093,7 +1151,14 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   std::memset(&plan->map_d, 0, sizeof(plan->map_d));
   const char* why = "";
   const int Kp = g.kh * g.kw * g.Cp;
-  if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.kh * g.kw, g.Ocp, e, D, status, &why, tiling)) {
+  // Halo mode (see GemmParams): a tile is 8 x 16 output pixels of one image.  Asked for when the convolution has more
+  // than one tap, stride and dilation 1, and tiles of that shape waste at most 15 % of their rows on this output size.
+  int halo_w = 0, halo_h = 0;
+  if (g.kh * g.kw > 1 && g.sx == 1 && g.sy == 1 && g.dx == 1 && g.dy == 1 && g.kw <= 16 && g.kh <= 16) {
+    const double covered = static_cast<double>((g.Wo + 7) / 8 * 8) * ((g.Ho + 15) / 16 * 16);
+    if (static_cast<double>(g.Wo) * g.Ho >= 0.85 * covered) { halo_w = 8 + g.kw - 1; halo_h = 16 + g.kh - 1; }
+  }
+  if (!finish_plan(plan, B, x_signed, Np, Kp, g.Cp, g.kh * g.kw, g.Ocp, e, D, status, &why, tiling, halo_w, halo_h)) {
     delete plan;
     return fail(why);
   }
@@ -1113,6 +1178,7 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
       if (eff > best + 1e-9 || (eff > best - 1e-9 && tw > bw)) { best = eff; bw = tw; bh = th; bn = tn; }
     }
   }
+  if (p.halo) { bw = 8; bh = 16; bn = 1; }
   p.conv = 1;
   p.TW = bw; p.TH = bh; p.TN = bn;
   p.tiles_w = (g.Wo + bw - 1) / bw;
@@ -1124,11 +1190,11 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   p.kw = g.kw; p.sx = g.sx; p.sy = g.sy; p.dx = g.dx; p.dy = g.dy; p.pl = g.pl; p.pt = g.pt;
   p.Cp = g.Cp;
   p.cblocks = (g.Cp + p.BK - 1) / p.BK;
-  p.num_kb = g.kh * g.kw * p.cblocks;
-  p.a_tx_bytes = static_cast<uint32_t>(bw * bh * bn) * p.BK;
+  p.num_kb = p.halo ? p.cblocks : g.kh * g.kw * p.cblocks;   // stages per tile: one patch per channel block, or one box per tap and block
+  p.a_tx_bytes = p.halo ? static_cast<uint32_t>(halo_w * halo_h) * p.BK : static_cast<uint32_t>(bw * bh * bn) * p.BK;
   const uint64_t dims[4] = {static_cast<uint64_t>(g.Cp), static_cast<uint64_t>(g.W), static_cast<uint64_t>(g.H), static_cast<uint64_t>(g.N)};
-  const uint32_t box[4] = {static_cast<uint32_t>(p.BK), static_cast<uint32_t>((bw - 1) * g.sx + 1),
-                           static_cast<uint32_t>((bh - 1) * g.sy + 1), static_cast<uint32_t>(bn)};
+  const uint32_t box[4] = {static_cast<uint32_t>(p.BK), static_cast<uint32_t>(p.halo ? halo_w : (bw - 1) * g.sx + 1),
+                           static_cast<uint32_t>(p.halo ? halo_h : (bh - 1) * g.sy + 1), static_cast<uint32_t>(bn)};
   const uint32_t estr[4] = {1, static_cast<uint32_t>(g.sx), static_cast<uint32_t>(g.sy), 1};
   bool ok = encode_u8(&plan->map_a, X, 4, dims, box, estr, swizzle_of(p.BK));
   if (ok && (p.store_span || p.res_span)) {
