@@ -824,7 +824,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 // four M=128, N=256, K=32 tcgen05.mma.kind::i8 (one 128-byte K block) into two alternating accumulators and
 // commits every round to an mbarrier it waits on two rounds later, so the pipe always has work queued.  No
 // loads from global memory and no epilogue: what is timed is the rate at which the tensor pipe retires MMAs.
-__global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int* status) {
+// n, span: the instruction's N and the operands' swizzle span in bytes (256 and 128 for the peak; other values show what
+// narrower instructions and narrower spans deliver: B2VX_PEAK_N / B2VX_PEAK_SPAN at the host entry).
+__global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int n, int span, int* status) {
   extern __shared__ uint8_t peak_smem[];
   __shared__ unsigned long long bars[2];
   __shared__ uint32_t tmem_slot;
@@ -852,15 +854,20 @@ __global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int* statu
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   if (threadIdx.x == 0) {
-    const uint32_t idesc = (2u << 4) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
-    const uint64_t da = make_smem_desc(base, 8u * 128u, 2u), db = make_smem_desc(base + 128u * 128u, 8u * 128u, 2u);
+    const uint32_t idesc = (2u << 4) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+    const uint32_t layout = span == 128 ? 2u : (span == 64 ? 4u : 6u);
+    const uint64_t da = make_smem_desc(base, 8u * span, layout), db = make_smem_desc(base + 128u * 128u, 8u * span, layout);
+    const int ksteps = span >> 5;
     bool ok = true;
     for (int it = 0; it < iters && ok; ++it) {
       const int b = it & 1;
       if (it >= 2) ok = mbar_wait(smem_u32(&bars[b]), ((it - 2) >> 1) & 1, &abort_flag, status, 9);
       if (!ok) break;
       tc_fence_after();
-      for (int k = 0; k < 4; ++k) tc_mma_i8(tmem + b * 256, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc, 1);
+      for (int k = 0; k < 4; ++k) {
+        const int kk = k & (ksteps - 1);   // four instructions per round whatever the span (ksteps is 1, 2 or 4)
+        tc_mma_i8(tmem + b * 256, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, 1);
+      }
       tc_commit(smem_u32(&bars[b]));
     }
     for (int it = max(0, iters - 2); it < iters && ok; ++it) ok = mbar_wait(smem_u32(&bars[it & 1]), (it >> 1) & 1, &abort_flag, status, 9);
@@ -1247,6 +1254,9 @@ GemmTcTiling gemm_tc_choose_tiling(long long M, int Ocp, int Kp, int with_s) {
     const double per_cta = static_cast<double>((tiles + grid - 1) / grid);
     // cycles per tile: tensor pipe (8192 MAC/clk), operand bytes (HBM share per SM when all SMs load,
     // more when few do), epilogue issue slots
+    // (Measured with B2VX_PEAK_N: 4395 / 2572 / 1341 TOP/s at N = 256 / 128 / 64: an M = 128, K = 32 instruction takes
+    // 134 / 115 / 110 cycles, i.e. at least about 110 whatever its N.  A model with that floor chose no better tilings on
+    // the networks, whose narrow layers are bound elsewhere, so the term that was tuned on them stays.)
     const double mma = static_cast<double>(Kp) * bn / 64.0;
     // operands of a layer that fits the L2 several times over (a previous layer's output and a small
     // weight matrix) are served by the L2 at its per-SM rate; otherwise by the CTA's share of HBM
@@ -1287,15 +1297,19 @@ double gemm_tc_measure_int8_peak(int reps, int* sm_count, int* status) {
   cudaEvent_t e0, e1;
   if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return 0.0;
   const int iters = 20000;   // x 4 MMAs of 128 x 256 x 32: about 10 ms per launch
+  // diagnostic: another instruction width (a multiple of 16 up to 256) or operand swizzle span (32, 64, 128 bytes)
+  int n = 256, span = 128;
+  if (const char* v = std::getenv("B2VX_PEAK_N")) { const int t = std::atoi(v); if (t >= 16 && t <= 256 && t % 16 == 0) n = t; }
+  if (const char* v = std::getenv("B2VX_PEAK_SPAN")) { const int t = std::atoi(v); if (t == 32 || t == 64 || t == 128) span = t; }
   double best = 0.0;
   for (int r = 0; r < reps + 1; ++r) {
     cudaEventRecord(e0, 0);
-    int8_peak_kernel<<<sms, 128, kMinDynSmem, 0>>>(iters, status);   // kMinDynSmem keeps it to one CTA per SM
+    int8_peak_kernel<<<sms, 128, kMinDynSmem, 0>>>(iters, n, span, status);   // kMinDynSmem keeps it to one CTA per SM
     cudaEventRecord(e1, 0);
     if (cudaEventSynchronize(e1) != cudaSuccess) { best = 0.0; break; }
     float ms = 0.0f;
     cudaEventElapsedTime(&ms, e0, e1);
-    const double tops = 2.0 * 128.0 * 256.0 * 128.0 * iters * sms / (ms * 1e-3) / 1e12;
+    const double tops = 2.0 * 128.0 * n * 128.0 * iters * sms / (ms * 1e-3) / 1e12;
     if (r > 0 && tops > best) best = tops;   // the first launch warms up
   }
   cudaEventDestroy(e0);
