@@ -6,7 +6,10 @@
 // A: activations, u8 or s8, K-contiguous: either a matrix [M][Kp] (a
 //    channels-last tensor seen as pixels x channels, or an im2col matrix), or —
 //    convolution mode — the channels-last input itself as a 4-D tensor
-//    (C, W, H, N), one filter tap per k-block fetched as a shifted TMA box.
+//    (C, W, H, N), one filter tap per k-block fetched as a shifted TMA box, or
+//    — halo mode, stride 1 with resident weights — the tile's input patch
+//    fetched once per channel block and every tap an MMA on a shifted view of
+//    it (GemmParams::halo).
 // B: weights shifted into int8, [Np][Kp] K-contiguous.
 // Both are "K-major" operands, which is what TMA tiled loads with a 32/64/128
 // byte swizzle and tcgen05.mma.kind::i8 consume directly; accumulation is int32
@@ -36,10 +39,10 @@
 //                            Tiles of at most 64 columns: four teams of four
 //                            warps, each team on its own tile with all chunks.
 //   warp 3      residual producer of a fused Add (template FUSE): the Add's
-//                            other operand, tile by tile, into the staging
-//                            memory by TMA; the epilogue looks every
-//                            (own byte, residual byte) pair up in the Add's
-//                            64 KB table, which sits in shared memory too.
+//                            64 KB table by four bulk copies first, then the
+//                            Add's other operand, tile by tile, into the
+//                            staging memory by TMA; the epilogue looks every
+//                            (own byte, residual byte) pair up in the table.
 // Small weight tiles (BN x K up to 72 KB) are loaded once by warp 2 and stay in
 // shared memory; the ring then holds A only.
 // A stage holds up to `group` k-blocks so that small k-blocks share one
