@@ -107,7 +107,14 @@ CONV_CASES = {
     "resident_c96_3x3_oc32": G.conv2d_q(33, 29, 96, 3, 3, 3, 32),
     "resident_c160_5x5_oc16_u8w": G.conv2d_q(21, 17, 160, 2, 5, 5, 16, w_kind="u8"),
     "teams_many_tiles_oc48": G.conv2d_q(120, 110, 16, 2, 3, 3, 48, relu=True),
+    # halo mode of the implicit convolution (stride 1, resident weights, 64-byte channel blocks): three channel blocks per
+    # patch; a 5x5 window with a weight zero point on an output whose right and bottom tiles are ragged; signed bytes
+    "halo_c192_3x3_oc32": G.conv2d_q(24, 32, 192, 2, 3, 3, 32),
+    "halo_c64_5x5_oc16_u8w_ragged": G.conv2d_q(63, 47, 64, 2, 5, 5, 16, w_kind="u8"),
+    "halo_c64_3x3_s8": G.conv2d_q(40, 48, 64, 1, 3, 3, 64, x_dtype=B.DT_INT8, w_kind="s8", in_q=(0.5, -1), out_q=(1.5, -3), out_dtype=B.DT_INT8),
 }
+
+HALO_CASES = ["cfg2_3x3_n1", "cfg2_3x3_n3", "halo_c192_3x3_oc32", "halo_c64_5x5_oc16_u8w_ragged", "halo_c64_3x3_s8"]
 
 
 @pytest.mark.parametrize("name", sorted(CONV_CASES))
@@ -120,12 +127,21 @@ def test_conv2d_matches_oracle(oracle_lib, product_lib, conv_kernel, name):
         assert not any(n.startswith("gemm_i8_tc") for n in names)
 
 
+@pytest.mark.parametrize("name", HALO_CASES)
+def test_halo_mode_is_taken(product_lib, name):
+    if os.environ.get("B2VX_TC_HALO") == "0":
+        pytest.skip("halo mode switched off by the environment")
+    os.environ.pop("B2VX_CONV_KERNEL", None)
+    _, kernels = G.run_case(product_lib, CONV_CASES[name], seed=11)
+    assert any(k["name"].startswith("gemm_i8_tc(halo") for k in kernels), [k["name"] for k in kernels]
+
+
 def test_padded_conv_with_zero_point_is_implicit(product_lib):
     """The benchmark's 3x3 SAME convolution (input zero point 128) runs as an implicit GEMM: no im2col pass."""
     os.environ.pop("B2VX_CONV_KERNEL", None)
     _, kernels = G.run_case(product_lib, CONV_CASES["cfg2_3x3_n3"], seed=1)
     names = [k["name"] for k in kernels]
-    assert "gemm_i8_tc(implicit)" in names and not any(n.startswith("im2col") for n in names), names
+    assert ("gemm_i8_tc(halo)" in names or "gemm_i8_tc(implicit)" in names) and not any(n.startswith("im2col") for n in names), names
 
 
 def test_uint8_weight_zero_point_runs_on_tensor_cores(product_lib):

@@ -96,6 +96,7 @@ struct NodeRec {
 struct Step {
   b2vx_kernel_info info;
   std::function<cudaError_t(cudaStream_t)> fn;
+  const void* tag = nullptr;   // identifies a step to code that runs after the list was edited (steps are inserted in front of others)
 };
 
 }  // namespace
@@ -920,6 +921,18 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       if (!pl) return fail(g, B2VX_UNSUPPORTED, lbl + ": " + err);
       g->gemm_plans.push_back(pl);
       *plan_holder = pl;
+      if (implicit && gemm_tc_plan_is_halo(pl)) {
+        // "gemm_i8_tc(implicit...)" -> "gemm_i8_tc(halo...)": one input patch per tile instead of one box per tap
+        for (Step& st : g->steps) {
+          if (st.tag != plan_holder.get()) continue;
+          std::string name = st.info.name;
+          const size_t at = name.find("implicit");
+          if (at != std::string::npos) {
+            name.replace(at, 8, "halo");
+            std::snprintf(st.info.name, sizeof(st.info.name), "%s", name.c_str());
+          }
+        }
+      }
       return B2VX_OK;
     });
     Step s_gemm;
@@ -931,6 +944,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
       s_gemm.info = make_info(kname.c_str(), node_index, 2 * macs, abytes + (fused_out ? y.bytes() : 0));
     }
     s_gemm.fn = [=](cudaStream_t st2) -> cudaError_t { return gemm_tc_launch(*plan_holder, st2); };
+    s_gemm.tag = plan_holder.get();
     g->steps.push_back(std::move(s_gemm));
     return B2VX_OK;
   }

@@ -1364,6 +1364,8 @@ GemmTcPlan* gemm_tc_plan_build_in(void* storage, size_t storage_bytes, const voi
 
 void gemm_tc_plan_destroy(GemmTcPlan* p) { delete p; }
 
+int gemm_tc_plan_is_halo(const GemmTcPlan* p) { return p && p->params.halo ? 1 : 0; }
+
 cudaError_t gemm_tc_launch(const GemmTcPlan* plan, cudaStream_t s) {
 #ifdef B2VX_TC_TRACE
   GemmTcPlan* mp = const_cast<GemmTcPlan*>(plan);

@@ -230,6 +230,8 @@ GemmTcPlan* gemm_tc_plan_build_in(void* storage, size_t storage_bytes, const voi
                                   int Np, int Kp, void* D, int ldd, const ContractEpilogue& e, int* status, char* err,
                                   size_t err_len);
 void gemm_tc_plan_destroy(GemmTcPlan* p);
+// 1 when an implicit-convolution plan loads one input patch per tile and runs the taps on shifted views of it.
+int gemm_tc_plan_is_halo(const GemmTcPlan* p);
 cudaError_t gemm_tc_launch(const GemmTcPlan* p, cudaStream_t s);
 // 1 when this build and device can run the tensor-core path.
 int gemm_tc_available(void);
