@@ -101,6 +101,21 @@ def test_full_size_gemm_rows_match_oracle(oracle_lib, product_lib, n):
     assert len(np.unique(full[0])) > 50
 
 
+@pytest.mark.parametrize("m", [4096, 4000])
+def test_pair_mode_gemm_equals_one_tile_at_a_time(oracle_lib, product_lib, m):
+    """K = 4096 with several tiles per CTA: two M tiles share every weight block (pair mode).  Same bytes as the kernel
+    working on one tile at a time (B2VX_TC_PAIR=0), whole matrix, CTAs with odd and even tile counts and a ragged last
+    M tile; the oracle on the first rows."""
+    spec = "gemm:%d:4096:4096" % m
+    pair, xs, kernels = _run_graph(product_lib, spec, 1, seed=12)
+    assert any(k.startswith("gemm_i8_tc") for k in kernels)
+    single, _, _ = _run_graph(product_lib, spec, 1, seed=12, inputs=xs, env={"B2VX_TC_PAIR": "0"})
+    assert np.array_equal(pair[0], single[0])
+    rows = 40
+    part, _, _ = _run_graph(oracle_lib, "gemm:%d:4096:4096" % rows, 1, seed=12, inputs=[xs[0][:rows]])
+    assert np.array_equal(pair[0][:rows], part[0])
+
+
 def test_decode_like_gemm_matches_oracle(oracle_lib, product_lib):
     for m in (1, 16):
         spec = "gemm:%d:4096:4096" % m

@@ -44,7 +44,8 @@
 //                            staging memory by TMA; the epilogue looks every
 //                            (own byte, residual byte) pair up in the table.
 // Small weight tiles (BN x K up to 72 KB) are loaded once by warp 2 and stay in
-// shared memory; the ring then holds A only.
+// shared memory; the ring then holds A only.  Long K loops with many tiles per
+// CTA run two M tiles at once on one stream of weight blocks (GemmParams::pair).
 // A stage holds up to `group` k-blocks so that small k-blocks share one
 // barrier round trip.  The grid is a multiple of the number of N tiles: a CTA
 // keeps one N tile for life (bias and scales staged in shared memory once) and
@@ -148,6 +149,12 @@ struct GemmParams {
   int halo, halo_w;
   uint32_t a_stage_bytes;  // halo mode: bytes of a stage (the patch, rounded up to 1 KB)
   int num_kb_b;            // k-blocks of the weight tile (kh * kw * cblocks; == num_kb unless halo)
+  // Pair mode (plain GEMM with a long K loop): a CTA works on two of its M tiles at once, one per accumulator buffer,
+  // and every stage holds [A of the first | A of the second | B], so the weight block is fetched once for 256 rows:
+  // 64 instead of 96 bytes per 128 x 256 x 128 block of multiply-accumulates, which the SM's read port from L2
+  // (about 56 bytes per clock) could not feed.  The price: both accumulators are in use, so a pair's epilogue does
+  // not overlap the next pair's main loop; chosen only where the main loop is many times longer.
+  int pair;
   // output through shared memory + TMA store: the tile is staged as BN/store_span column blocks of
   // [128 rows][store_span bytes], 16-byte chunks XOR-swizzled the way the store's tensor map expects.
   // store_span == 0: BN is not a multiple of 32, threads store their 16-byte pieces directly.
@@ -294,6 +301,21 @@ __device__ __forceinline__ void tc_mma_i8_const(uint32_t tmem_d, uint64_t desc_a
       : "memory");
 }
 
+// The issue loops keep a descriptor as its two 32-bit halves: only the low half (start address in 16-byte units, bits
+// 0-13) changes from one instruction to the next, by additions that never carry out of that field (shared-memory
+// addresses stay below 256 KB), so advancing a descriptor is one 32-bit addition.
+template <int ACCUMULATE>
+__device__ __forceinline__ void tc_mma_i8_halves(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACCUMULATE)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, int (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -364,7 +386,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
   const uint32_t a_bytes = p.halo ? p.a_stage_bytes : static_cast<uint32_t>(kBlockM) * p.BK;
   const uint32_t b_bytes = static_cast<uint32_t>(p.BN) * p.BK;
-  const uint32_t sub_bytes = a_bytes + (p.b_resident ? 0u : b_bytes);   // one k-block: whole swizzle atoms, see the host-side plan
+  const uint32_t sub_bytes = (p.pair ? 2u : 1u) * a_bytes + (p.b_resident ? 0u : b_bytes);   // one k-block: whole swizzle atoms, see the host-side plan
+  const uint32_t b_off = (p.pair ? 2u : 1u) * a_bytes;   // B behind the A block(s) of a k-block
   const uint32_t stage_bytes = sub_bytes * p.group;
   const uint32_t ring_bytes = (p.stages * stage_bytes + 1023u) & ~1023u;
   const uint32_t bres_bytes = p.b_resident ? ((static_cast<uint32_t>(p.num_kb_b) * b_bytes + 1023u) & ~1023u) : 0u;
@@ -448,7 +471,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     pdl_wait();
     bool ok = true;
     int m_tile = m_tile0;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, m_tile += m_step) {
+    const int tstep = p.pair ? 2 : 1;   // pair mode: tiles j and j + 1 of this CTA go through the ring together
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += tstep * gridDim.x, m_tile += tstep * m_step) {
+      const bool two = p.pair && tile + static_cast<int>(gridDim.x) < num_tiles;
       int w0 = 0, h0 = 0, n0 = 0;
       if (p.conv) {
         // tile -> first output pixel (tw, th, tn), turned into input coordinates of tap (0,0).
@@ -467,13 +492,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (!ok) break;
         if (is_a) TC_TRACE(0, it, 0);
         if (elect_one()) {
-          mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (is_a ? p.a_tx_bytes : b_bytes) + (is_a ? p.tx_extra : 0u));
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(cnt) * (is_a ? p.a_tx_bytes * (two ? 2u : 1u) : b_bytes) + (is_a ? p.tx_extra : 0u));
           uint32_t dst = tiles_addr + s * stage_bytes;
           int t_tap = tap, t_cb = cb, t_ky = ky, t_kx = kx;
           for (int gi = 0; gi < cnt; ++gi, dst += sub_bytes) {
             if (p.conv) {
               if (is_a) tma_load_4d(dst, &map_a, t_cb * p.BK, w0 + t_kx * p.dx, h0 + t_ky * p.dy, n0, full);
-              else tma_load_2d(dst + a_bytes, &map_b, t_tap * p.Cp + t_cb * p.BK, n_tile * p.BN, full);
+              else tma_load_2d(dst + b_off, &map_b, t_tap * p.Cp + t_cb * p.BK, n_tile * p.BN, full);
               if (++t_cb == p.cblocks) {
                 t_cb = 0;
                 ++t_tap;
@@ -481,8 +506,9 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               }
             } else if (is_a) {
               tma_load_2d(dst, &map_a, (kb0 + gi) * p.BK, m_tile * kBlockM, full);
+              if (two) tma_load_2d(dst + a_bytes, &map_a, (kb0 + gi) * p.BK, (m_tile + m_step) * kBlockM, full);
             } else {
-              tma_load_2d(dst + a_bytes, &map_b, (kb0 + gi) * p.BK, n_tile * p.BN, full);
+              tma_load_2d(dst + b_off, &map_b, (kb0 + gi) * p.BK, n_tile * p.BN, full);
             }
           }
         }
@@ -510,9 +536,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       ok = mbar_wait(smem_u32(&hdr->b_full), 0, abort_flag, p.status, 8, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
     }
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++j) {
+    const int tstep = p.pair ? 2 : 1;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += tstep * gridDim.x, j += tstep) {
       const uint32_t a = j & ((1 << p.acc_shift) - 1), aph = (j >> p.acc_shift) & 1;
+      // pair mode (two accumulator buffers): tile j fills buffer 0 and tile j + 1, when the CTA has one, buffer 1
+      const bool two = p.pair && tile + static_cast<int>(gridDim.x) < num_tiles;
       ok = mbar_wait(smem_u32(&hdr->tmem_empty[a]), aph ^ 1, abort_flag, p.status, 2, p.wait_limit);
+      if (ok && two) ok = mbar_wait(smem_u32(&hdr->tmem_empty[a + 1]), aph ^ 1, abort_flag, p.status, 2, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -531,40 +561,63 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           // are built once per stage and advanced by additions to their address field (16-byte units).
           if (elect_one()) {
             const uint64_t da0 = make_smem_desc(tiles_addr + s * stage_bytes, static_cast<uint32_t>(p.halo_w) * p.BK, p.layout_type);
-            uint64_t db = make_smem_desc(bres_addr + static_cast<uint32_t>(kb0) * b_bytes, p.sbo, p.layout_type);
-            const uint64_t db_step = static_cast<uint64_t>((static_cast<uint32_t>(p.cblocks) * b_bytes) >> 4);
+            const uint64_t db0 = make_smem_desc(bres_addr + static_cast<uint32_t>(kb0) * b_bytes, p.sbo, p.layout_type);
+            const uint32_t a_hi = static_cast<uint32_t>(da0 >> 32), b_hi = static_cast<uint32_t>(db0 >> 32);
+            uint32_t b_lo = static_cast<uint32_t>(db0);
+            const uint32_t db_step = (static_cast<uint32_t>(p.cblocks) * b_bytes) >> 4;
             const uint32_t px16 = static_cast<uint32_t>(p.BK) >> 4;           // one pixel of the patch, in 16-byte units
             const int taps_h = p.num_kb_b / (p.cblocks * p.kw);
             bool first = accumulate == 0;
             for (int ky = 0; ky < taps_h; ++ky) {
-              uint64_t da = da0 + static_cast<uint64_t>(static_cast<uint32_t>(ky * p.halo_w) * px16);
-              for (int kx = 0; kx < p.kw; ++kx, da += px16, db += db_step) {
+              uint32_t a_lo = static_cast<uint32_t>(da0) + static_cast<uint32_t>(ky * p.halo_w) * px16;
+              for (int kx = 0; kx < p.kw; ++kx, a_lo += px16, b_lo += db_step) {
                 if (first) {
-                  tc_mma_i8_const<0>(tmem_d, da, db, p.idesc);
+                  tc_mma_i8_halves<0>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
                   first = false;
                 } else {
-                  tc_mma_i8_const<1>(tmem_d, da, db, p.idesc);
+                  tc_mma_i8_halves<1>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
                 }
-                for (int k = 1; k < ksteps; ++k) tc_mma_i8_const<1>(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc);
+                for (int k = 1; k < ksteps; ++k) tc_mma_i8_halves<1>(tmem_d, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, p.idesc);
               }
             }
             tc_commit(smem_u32(&hdr->empty[s]));
           }
         } else if (elect_one()) {
-          uint64_t da = make_smem_desc(tiles_addr + s * stage_bytes, p.sbo, p.layout_type);
-          uint64_t db = make_smem_desc(p.b_resident ? bres_addr + static_cast<uint32_t>(kb0) * b_bytes : tiles_addr + s * stage_bytes + a_bytes,
-                                       p.sbo, p.layout_type);
-          const uint64_t da_step = static_cast<uint64_t>(sub_bytes >> 4), db_step = static_cast<uint64_t>((p.b_resident ? b_bytes : sub_bytes) >> 4);
+          const uint64_t da0 = make_smem_desc(tiles_addr + s * stage_bytes, p.sbo, p.layout_type);
+          const uint64_t db0 = make_smem_desc(p.b_resident ? bres_addr + static_cast<uint32_t>(kb0) * b_bytes : tiles_addr + s * stage_bytes + b_off,
+                                              p.sbo, p.layout_type);
+          const uint32_t a_hi = static_cast<uint32_t>(da0 >> 32), b_hi = static_cast<uint32_t>(db0 >> 32);
+          uint32_t a_lo = static_cast<uint32_t>(da0), b_lo = static_cast<uint32_t>(db0);
+          const uint32_t da_step = sub_bytes >> 4, db_step = (p.b_resident ? b_bytes : sub_bytes) >> 4;
+          const uint32_t a2 = a_bytes >> 4;            // pair mode: the second tile's A block follows the first's
+          const uint32_t tmem_d2 = tmem_d + p.acc_stride;
           bool first = accumulate == 0;
-          for (int gi = 0; gi < cnt; ++gi, da += da_step, db += db_step) {
-            // k steps advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
-            if (first) {
-              tc_mma_i8_const<0>(tmem_d, da, db, p.idesc);
-              first = false;
-            } else {
-              tc_mma_i8_const<1>(tmem_d, da, db, p.idesc);
+          if (two) {
+            for (int gi = 0; gi < cnt; ++gi, a_lo += da_step, b_lo += db_step) {
+              // k steps advance 32 bytes along K inside the swizzle span: +2 in 16-byte units
+              if (first) {
+                tc_mma_i8_halves<0>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+                tc_mma_i8_halves<0>(tmem_d2, a_lo + a2, a_hi, b_lo, b_hi, p.idesc);
+                first = false;
+              } else {
+                tc_mma_i8_halves<1>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+                tc_mma_i8_halves<1>(tmem_d2, a_lo + a2, a_hi, b_lo, b_hi, p.idesc);
+              }
+              for (int k = 1; k < ksteps; ++k) {
+                tc_mma_i8_halves<1>(tmem_d, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, p.idesc);
+                tc_mma_i8_halves<1>(tmem_d2, a_lo + a2 + 2u * k, a_hi, b_lo + 2u * k, b_hi, p.idesc);
+              }
             }
-            for (int k = 1; k < ksteps; ++k) tc_mma_i8_const<1>(tmem_d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), p.idesc);
+          } else {
+            for (int gi = 0; gi < cnt; ++gi, a_lo += da_step, b_lo += db_step) {
+              if (first) {
+                tc_mma_i8_halves<0>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+                first = false;
+              } else {
+                tc_mma_i8_halves<1>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+              }
+              for (int k = 1; k < ksteps; ++k) tc_mma_i8_halves<1>(tmem_d, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, p.idesc);
+            }
           }
           tc_commit(smem_u32(&hdr->empty[s]));
         }
@@ -573,7 +626,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         TC_TRACE(1, it, 1);
         if (++s == static_cast<uint32_t>(p.stages)) { s = 0; ph ^= 1; }
       }
-      if (ok && elect_one()) tc_commit(smem_u32(&hdr->tmem_full[a]));
+      if (ok && elect_one()) {
+        tc_commit(smem_u32(&hdr->tmem_full[a]));
+        if (two) tc_commit(smem_u32(&hdr->tmem_full[a + 1]));
+      }
       __syncwarp();
     }
   } else if (FUSE && warp == 3) {
@@ -954,7 +1010,7 @@ namespace {
 // turns out to allow the halo mode of the implicit convolution (0: not asked for).
 bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int taps, int ldd,
                  const ContractEpilogue& e, void* D, int* status, const char** why, const GemmTcTiling* tiling, int halo_w = 0,
-                 int halo_h = 0) {
+                 int halo_h = 0, bool want_pair = false) {
   GemmParams& p = plan->params;
   p.Ocp = ldd;
   p.ldd = ldd;
@@ -1025,7 +1081,13 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   p.halo_w = p.halo ? halo_w : 0;
   p.a_stage_bytes = p.halo ? static_cast<uint32_t>((static_cast<size_t>(halo_w) * halo_h * p.BK + 1023) & ~static_cast<size_t>(1023)) : 0u;
   p.num_kb_b = kblocks_per_tile;
-  const size_t sub_bytes = p.halo ? p.a_stage_bytes : static_cast<size_t>(kBlockM + (p.b_resident ? 0 : p.BN)) * p.BK;
+  // Pair mode (see GemmParams): asked for by the caller where the K loop is long and every CTA has several tiles; needs
+  // the weights in the ring, exactly two accumulator buffers (tiles wider than 128 columns) and no fused Add.
+  // B2VX_TC_PAIR=0 disables.
+  const char* pair_env = std::getenv("B2VX_TC_PAIR");   // read per plan, so that one process can build both forms
+  const bool no_pair = pair_env && std::strcmp(pair_env, "0") == 0;
+  p.pair = (want_pair && !no_pair && !p.halo && !p.b_resident && !p.teams && e.add_residual == nullptr && p.BN > 128) ? 1 : 0;
+  const size_t sub_bytes = p.halo ? p.a_stage_bytes : static_cast<size_t>((p.pair ? 2 : 1) * kBlockM + (p.b_resident ? 0 : p.BN)) * p.BK;
   const size_t ring_budget = kSmemBudget - 2048 - sizeof(SmemHeader) - staging - add_table_bytes - bres;
   int group = static_cast<int>((64 * 1024) / sub_bytes);
   if (p.halo) group = 1;
@@ -1117,7 +1179,16 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   std::memset(&p, 0, sizeof(p));
   std::memset(&plan->map_d, 0, sizeof(plan->map_d));
   const char* why = "";
-  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why, tiling)) {
+  // pair mode where the main loop dwarfs the epilogue (K of 4096 or more) and there are at least two tiles per SM
+  int sms = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const long long tiles_256 = static_cast<long long>((M + kBlockM - 1) / kBlockM) * ((Np + 255) / 256);
+  const bool want_pair = Kp >= 4096 && tiles_256 >= 2LL * sms;
+  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why, tiling, 0, 0, want_pair)) {
     delete plan;
     return fail(why);
   }
