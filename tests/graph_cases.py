@@ -82,10 +82,10 @@ def conv2d_q(W, H, C, N, kw, kh, Oc, stride=(1, 1), dilation=(1, 1), pad_type=B.
 
 
 def depthwise_q(W, H, C, N, kw, kh, multiplier=1, stride=(1, 1), pad_type=B.PAD_SAME, w_kind="u8", in_q=(0.03, 120),
-                out_q=(0.06, 0), relu6=True):
+                out_q=(0.06, 0), relu6=True, x_dtype=B.DT_UINT8, pad=(0, 0, 0, 0)):
     def build(g, rng):
         Oc = C * multiplier
-        x = g.tensor(B.DT_UINT8, [W, H, C, N], B.ATTR_INPUT, scale=in_q[0], zero_point=in_q[1])
+        x = g.tensor(x_dtype, [W, H, C, N], B.ATTR_INPUT, scale=in_q[0], zero_point=in_q[1])
         wshape = [kw, kh, Oc, 1]
         if w_kind == "s8pc":
             ws = rng.uniform(0.001, 0.01, Oc).astype(np.float32)
@@ -99,12 +99,12 @@ def depthwise_q(W, H, C, N, kw, kh, multiplier=1, stride=(1, 1), pad_type=B.PAD_
             bq = dict(scale=float(np.float32(in_q[0]) * np.float32(0.02)), zero_point=0)
         b = g.tensor(B.DT_INT32, [Oc], B.ATTR_CONSTANT, data=rng.integers(-500, 501, size=Oc).astype(np.int32), **bq)
         y = g.tensor(B.DT_UINT8, [], B.ATTR_TRANSIENT if relu6 else B.ATTR_OUTPUT, scale=out_q[0], zero_point=out_q[1])
-        g.conv2d(x, w, b, y, stride=stride, pad_type=pad_type, multiplier=multiplier)
+        g.conv2d(x, w, b, y, stride=stride, pad_type=pad_type, pad=pad, multiplier=multiplier)
         z = y
         if relu6:
             z = g.tensor(B.DT_UINT8, [], B.ATTR_OUTPUT, scale=out_q[0], zero_point=out_q[1])
             g.relu6(y, z)
-        return [(x, _act(rng, [W, H, C, N]))], [z]
+        return [(x, _act(rng, [W, H, C, N], x_dtype))], [z]
     return build
 
 

@@ -164,6 +164,21 @@ DEPTHWISE_CASES = {
     "dw_mult2": G.depthwise_q(9, 9, 6, 2, 3, 3, multiplier=2),
     "dw_s8pc": G.depthwise_q(14, 14, 64, 2, 3, 3, w_kind="s8pc"),
     "dw5x5": G.depthwise_q(11, 13, 16, 1, 5, 5, relu6=False),
+    # strip form (3x3, stride 1 or 2): whole images per tile with an odd batch, ragged widths and channel counts,
+    # one 16-channel chunk, VALID and explicit one-sided padding, signed input bytes, wide rows
+    "dw_7x7_c960_n3": G.depthwise_q(7, 7, 960, 3, 3, 3),
+    "dw_7x7_c16_n9": G.depthwise_q(7, 7, 16, 9, 3, 3),
+    "dw_14x14_c384_s2_n3": G.depthwise_q(14, 14, 384, 3, 3, 3, stride=(2, 2)),
+    "dw_13x9_c144": G.depthwise_q(13, 9, 144, 2, 3, 3),
+    "dw_56x56_c144_s2": G.depthwise_q(56, 56, 144, 1, 3, 3, stride=(2, 2)),
+    "dw_112x112_c32": G.depthwise_q(112, 112, 32, 1, 3, 3),
+    "dw_valid_s1": G.depthwise_q(19, 11, 40, 2, 3, 3, pad_type=B.PAD_VALID),
+    "dw_valid_s2": G.depthwise_q(19, 12, 40, 2, 3, 3, stride=(2, 2), pad_type=B.PAD_VALID),
+    "dw_pad_1002": G.depthwise_q(21, 10, 48, 2, 3, 3, pad_type=B.PAD_AUTO, pad=(1, 0, 0, 2)),
+    "dw_s8_input": G.depthwise_q(17, 17, 72, 2, 3, 3, x_dtype=B.DT_INT8, in_q=(0.03, -8), w_kind="s8pc"),
+    "dw_s8_input_s2": G.depthwise_q(17, 18, 24, 2, 3, 3, stride=(2, 2), x_dtype=B.DT_INT8, in_q=(0.03, 5)),
+    "dw_1x1_image": G.depthwise_q(1, 1, 64, 5, 3, 3),
+    "dw_3x40_c8": G.depthwise_q(40, 3, 8, 1, 3, 3),
 }
 
 
@@ -172,6 +187,19 @@ def test_depthwise_matches_oracle(oracle_lib, product_lib, name):
     want, _ = G.run_case(oracle_lib, DEPTHWISE_CASES[name], seed=5)
     got, _ = G.run_case(product_lib, DEPTHWISE_CASES[name], seed=5)
     G.assert_same(want, got)
+
+
+def test_strip_form_equals_sixteen_channel_form(product_lib):
+    """B2VX_DW_STRIP=0 selects the kernel that owns sixteen channels of two pixels per thread: same bytes."""
+    for name in ("dw3x3_s1", "dw3x3_s2", "dw_13x9_c144", "dw_7x7_c960_n3"):
+        got, kernels = G.run_case(product_lib, DEPTHWISE_CASES[name], seed=5)
+        assert any(k["name"] == "depthwise_q16" for k in kernels), [k["name"] for k in kernels]
+        os.environ["B2VX_DW_STRIP"] = "0"
+        try:
+            other, _ = G.run_case(product_lib, DEPTHWISE_CASES[name], seed=5)
+        finally:
+            os.environ.pop("B2VX_DW_STRIP", None)
+        G.assert_same(got, other)
 
 
 FC_CASES = {

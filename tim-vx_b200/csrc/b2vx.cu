@@ -1065,13 +1065,25 @@ b2vx_status plan_conv(b2vx_graph* g, uint32_t idx, NodeRec& n) {
     }
     const double tmax = (static_cast<double>(taps) * 255.0 * 255.0 + bmax) * smax / std::fabs(static_cast<double>(oq.scale));
     const int exact_only = !(tmax < 2097152.0);
-    uint32_t* dwt = nullptr; int32_t* dbf = nullptr;
+    uint32_t* dwt = nullptr; int32_t* dbf = nullptr; uint32_t* dwv = nullptr;
     st = upload(g, wtab, &dwt);
     if (st == B2VX_OK) st = upload(g, bfull, &dbf);
+    if (st == B2VX_OK && kh == 3 && kw == 3) {
+      // strip form of the kernel: window rows 0 and 1 of a column as the two halves of one word, row 2 as in wtab
+      std::vector<uint32_t> wv(static_cast<size_t>(6) * y.Cp, 0u);
+      for (int oc = 0; oc < y.C; ++oc)
+        for (int kx = 0; kx < 3; ++kx) {
+          const uint32_t r0 = static_cast<uint32_t>(wd[static_cast<size_t>(kx) * y.Cp + oc]) & 0xFFFFu;
+          const uint32_t r1 = static_cast<uint32_t>(wd[static_cast<size_t>(3 + kx) * y.Cp + oc]) & 0xFFFFu;
+          wv[static_cast<size_t>(kx) * y.Cp + oc] = r0 | (r1 << 16);
+          wv[static_cast<size_t>(3 + kx) * y.Cp + oc] = wtab[static_cast<size_t>(6 + kx) * y.Cp + oc];
+        }
+      st = upload(g, wv, &dwv);
+    }
     if (st != B2VX_OK) return st;
     Step s16;
     s16.info = make_info("depthwise_q16", idx, 2 * macs, abytes);
-    s16.fn = [=](cudaStream_t st2) { launch_depthwise_q16(xcl, xs, zx, dwt, dbf, dsc, geo, oq, exact_only, ycl, st2); return cudaGetLastError(); };
+    s16.fn = [=](cudaStream_t st2) { launch_depthwise_q16(xcl, xs, zx, dwt, dwv, dbf, dsc, geo, oq, exact_only, ycl, st2); return cudaGetLastError(); };
     g->steps.push_back(std::move(s16));
     return B2VX_OK;
   }

@@ -90,7 +90,10 @@ void launch_depthwise_q(const void* x, int x_signed, int zx, const int16_t* wd, 
 // The multiplier-1 case, 16 channels x 2 pixels per thread with the weights in shared memory:
 // wtab [kh*kw][Ocp] words, each w - zw as a 16-bit half in position (channel & 1);
 // bias_full = bias - zx' * sum_taps (w - zw) with zx' = zx (+128 for int8 input).  Needs kh*kw <= 64.
-void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* wtab, const int32_t* bias_full,
+// wtab_v (3x3 windows; else null) selects, for strides 1 and 2 without dilation, the form with 4 channels x 8 pixels
+// per thread: [6][Ocp] words, row kx < 3 = the halves (w[0][kx] - zw, w[1][kx] - zw) of a channel, row 3 + kx = wtab's
+// row of tap (2, kx).
+void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* wtab, const uint32_t* wtab_v, const int32_t* bias_full,
                           const float* acc_scale, const ConvGeom& g, OutQuant out, int exact_only, void* y, cudaStream_t s);
 
 // ---- float32 convolution (dense or depthwise), accumulation order ic,ky,kx --

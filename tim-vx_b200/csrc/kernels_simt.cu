@@ -304,6 +304,7 @@ __global__ void depthwise_q_kernel(const uint8_t* __restrict__ x, int zx, const 
 struct DwParams {
   ConvGeom g;
   const uint32_t* wtab;      // [taps][Ocp] words
+  const uint32_t* wtab_v;    // 3x3 windows: [6][Ocp] words for the strip form (see depthwise_strip_kernel), else null
   const int32_t* bias_full;  // [Ocp]
   const float* acc_scale;    // [Ocp]
   OutQuant out;
@@ -487,6 +488,177 @@ __global__ void __launch_bounds__(256, (KH == 3 ? 3 : 2)) depthwise_q16s_kernel(
   if (wo < g.Wo) *reinterpret_cast<uint4*>(out) = requant_chunk16<false>(acc0, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
   if (two && wo + 8 < g.Wo)
     *reinterpret_cast<uint4*>(out + 8 * g.Ocp) = requant_chunk16<false>(acc1, p.bias_full + c0, p.acc_scale + c0, rc, 0, nullptr);
+}
+
+// The 3x3 form for strides 1 and 2: a thread owns FOUR channels (one 32-bit word of a pixel) of a strip of eight
+// horizontally adjacent output pixels.  Its 36 weight words and its bias / scale live in registers, every input word of the strip's
+// three rows is read from shared memory once (10 or 17 32-bit loads per row) and feeds up to three outputs, so
+// the arithmetic runs at 9.4 or 5.6 multiply-accumulates per shared-memory load instead of 5.3 per 128-bit load,
+// and a warp's load is one or two 128-byte wavefronts instead of four.  (The 16-channel form above spends more
+// shared-memory cycles than issue slots.)  A block's 256 threads are CW = 4, 8 or 16 channel words x 64, 32 or 16
+// strips, the strips laid out as NI images x SEG strips per row x TH rows (powers of two, chosen by the launcher).
+// Consecutive strips of a warp are consecutive rows; the patch's row pitch is chosen so that their words fall in
+// different banks.
+#ifndef B2VX_DW_BLOCKS
+#define B2VX_DW_BLOCKS 4   // resident blocks per SM the strip kernel is compiled for (64 registers per thread)
+#endif
+struct DwStripGeom {
+  int ck_shift;    // 16-channel chunks per slab: 1 << ck_shift
+  int seg_shift;   // strips per tile row
+  int th_shift;    // tile rows
+  int ni_shift;    // images per tile (more than one only when a tile covers a whole image)
+  int IH, IW;      // input patch of one image
+  int pitch;       // bytes between patch rows
+  int tiles_w;     // tiles per output row
+  int iw_recip;    // 65536 / IW + 1: (pixel * iw_recip) >> 16 = pixel / IW for pixel < 256
+  int step_h, step_w;   // (256 / CK) / IW and (256 / CK) % IW: how a thread's patch pixel advances per staging round
+};
+
+__device__ __forceinline__ uint4 requant16_packed(f32x2 (&real)[8], const RequantConsts& rc) {
+  uint32_t wh[4], wl[4];
+#pragma unroll
+  for (int g4 = 0; g4 < 4; ++g4) {
+    uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+    f2_unpack_bits(f2_fma(real[2 * g4], rc.inv_hi2, rc.magic2), h0, h1);
+    f2_unpack_bits(f2_fma(real[2 * g4 + 1], rc.inv_hi2, rc.magic2), h2, h3);
+    f2_unpack_bits(f2_fma(real[2 * g4], rc.inv_lo2, rc.magic2), l0, l1);
+    f2_unpack_bits(f2_fma(real[2 * g4 + 1], rc.inv_lo2, rc.magic2), l2, l3);
+    wh[g4] = sat_pack4(h0, h1, h2, h3);
+    wl[g4] = sat_pack4(l0, l1, l2, l3);
+  }
+  uint32_t differ = (wh[0] ^ wl[0]) | (wh[1] ^ wl[1]) | (wh[2] ^ wl[2]) | (wh[3] ^ wl[3]);
+  asm volatile("" : "+r"(differ));   // keeps the one test per sixteen values (see requant_chunk16)
+  if (differ != 0u || rc.exact_only) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t m = 0xFFu << (8 * (i & 3));
+      if (((wh[i >> 2] ^ wl[i >> 2]) & m) != 0u || rc.exact_only) {
+        float lo, hi;
+        f2_unpack(real[i >> 1], lo, hi);
+        const uint32_t q = (static_cast<uint32_t>(requant((i & 1) ? hi : lo, rc.oq)) ^ rc.out_flip) & 0xFFu;
+        wh[i >> 2] = (wh[i >> 2] & ~m) | (q << (8 * (i & 3)));
+      }
+    }
+  }
+  return make_uint4(wh[0] ^ rc.out_flip, wh[1] ^ rc.out_flip, wh[2] ^ rc.out_flip, wh[3] ^ rc.out_flip);
+}
+
+// Four pixels x four channels: acc[4 * pixel + channel] already holds the folded bias; one word per pixel comes back.
+// The arithmetic is requant_chunk16's (same two-sided rounding, same exact path for the rare disagreement).
+__device__ __forceinline__ uint4 requant_4x4(const int (&acc)[16], const float4& s4, const RequantConsts& rc) {
+  f32x2 real[8];
+  const f32x2 s01 = f2_pack(s4.x, s4.y), s23 = f2_pack(s4.z, s4.w);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    real[2 * j] = f2_mul(f2_pack(__int2float_rn(acc[4 * j + 0]), __int2float_rn(acc[4 * j + 1])), s01);
+    real[2 * j + 1] = f2_mul(f2_pack(__int2float_rn(acc[4 * j + 2]), __int2float_rn(acc[4 * j + 3])), s23);
+  }
+  return requant16_packed(real, rc);
+}
+
+// Grid: x = tile column + tiles_w * tile row, y = group of NI images, z = channel slab.
+template <int S, bool XS, int CKS>
+__global__ void __launch_bounds__(256, B2VX_DW_BLOCKS) depthwise_strip_kernel(const uint8_t* __restrict__ x, DwParams p, DwStripGeom t,
+                                                                 uint8_t* __restrict__ y) {
+  extern __shared__ uint4 dw_smem[];               // [NI][IH] patch rows of t.pitch bytes: [IW][CK] 16-channel chunks
+  const ConvGeom& g = p.g;
+  constexpr int CK = 1 << CKS, CW = 4 * CK, PXB = 16 * CK;   // chunks, words and bytes of a pixel of the slab
+  const int TH = 1 << t.th_shift, SEG = 1 << t.seg_shift, NI = 1 << t.ni_shift;
+  const unsigned tile_h = blockIdx.x / static_cast<unsigned>(t.tiles_w), tile_w = blockIdx.x - tile_h * t.tiles_w;
+  const int n0 = blockIdx.y << t.ni_shift;
+  const int c_slab = blockIdx.z * PXB;
+  const int slab_chunks = min(PXB, g.Ocp - c_slab) >> 4;
+  const int ho0 = tile_h << t.th_shift, wo0 = tile_w << (3 + t.seg_shift);
+  const int hi0 = ho0 * S - g.pt, wi0 = wo0 * S - g.pl;
+  pdl_trigger();
+  const int cw = threadIdx.x & (CW - 1);
+  const int strip = threadIdx.x >> (2 + CKS);
+  const bool active = (cw >> 2) < slab_chunks;
+  pdl_wait();   // the input is the first thing another kernel produced
+  uint8_t* const xsm = reinterpret_cast<uint8_t*>(dw_smem);
+  {
+    const uint4 zx4 = make_uint4(p.zx_word, p.zx_word, p.zx_word, p.zx_word);
+    const int chunk = threadIdx.x & (CK - 1);
+    const int units = t.IH * t.IW * CK;
+    const unsigned pix0 = threadIdx.x >> CKS;
+    const int ih0 = static_cast<int>((pix0 * static_cast<unsigned>(t.iw_recip)) >> 16);   // pix0 / IW (pix0 < 256)
+    const int iw0 = static_cast<int>(pix0) - ih0 * t.IW;
+    const bool chunk_ok = chunk < slab_chunks;
+    const uint32_t img_bytes = static_cast<uint32_t>(g.H) * g.W * g.Cp;
+    for (int ni = 0; ni < NI; ++ni) {
+      const bool img_ok = chunk_ok && n0 + ni < g.N;
+      const uint8_t* img = x + static_cast<size_t>(img_ok ? n0 + ni : 0) * img_bytes + c_slab + 16 * chunk;
+      uint8_t* dst = xsm + ni * t.IH * t.pitch + 16 * chunk;
+      int ih = ih0, iw = iw0;
+#pragma unroll 4
+      for (int u = threadIdx.x; u < units; u += 256) {
+        const int hi = hi0 + ih, wi = wi0 + iw;
+        uint4 v = zx4;
+        if (img_ok && static_cast<unsigned>(hi) < static_cast<unsigned>(g.H) && static_cast<unsigned>(wi) < static_cast<unsigned>(g.W)) {
+          v = __ldg(reinterpret_cast<const uint4*>(img + static_cast<uint32_t>(hi * g.W + wi) * static_cast<uint32_t>(g.Cp)));
+          if (XS) { v.x ^= 0x80808080u; v.y ^= 0x80808080u; v.z ^= 0x80808080u; v.w ^= 0x80808080u; }
+        }
+        *reinterpret_cast<uint4*>(dst + ih * t.pitch + iw * PXB) = v;
+        ih += t.step_h; iw += t.step_w;
+        if (iw >= t.IW) { iw -= t.IW; ++ih; }
+      }
+    }
+  }
+  // this thread's constants, requested while the block's copies land (they stay in L1/L2 between blocks);
+  // threads past the last channel read the last words and never use them
+  uint4 wp[3], ws[3];                             // per window column: rows 0 and 1 as a pair, row 2 alone
+  const int c0 = min(c_slab + 4 * cw, g.Ocp - 4);
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    wp[k] = __ldg(reinterpret_cast<const uint4*>(p.wtab_v + static_cast<size_t>(k) * g.Ocp + c0));
+    ws[k] = __ldg(reinterpret_cast<const uint4*>(p.wtab_v + static_cast<size_t>(3 + k) * g.Ocp + c0));
+  }
+  const int4 b4 = __ldg(reinterpret_cast<const int4*>(p.bias_full + c0));
+  const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.acc_scale + c0));
+  __syncthreads();
+  if (!active) return;
+  const int r = strip & (TH - 1);
+  const int sgm = (strip >> t.th_shift) & (SEG - 1);
+  const int ni = strip >> (t.th_shift + t.seg_shift);
+  const int n = n0 + ni, ho = ho0 + r, wo = wo0 + 8 * sgm;
+  if (n >= g.N || ho >= g.Ho || wo >= g.Wo) return;
+  int acc[2][16];
+  const uint8_t* rowp = xsm + (ni * t.IH + r * S) * t.pitch + (8 * sgm * S) * PXB + 4 * cw;
+  const uint8_t* rowp1 = rowp + t.pitch;
+  const uint8_t* rowp2 = rowp1 + t.pitch;
+#pragma unroll
+  for (int ic = 0; ic < 7 * S + 3; ++ic) {
+    const uint32_t x0 = *reinterpret_cast<const uint32_t*>(rowp + ic * PXB);
+    const uint32_t x1 = *reinterpret_cast<const uint32_t*>(rowp1 + ic * PXB);
+    const uint32_t x2 = *reinterpret_cast<const uint32_t*>(rowp2 + ic * PXB);
+    // rows 0 and 1 of this column, byte-interleaved: [r0.c0 r1.c0 r0.c1 r1.c1] and [r0.c2 r1.c2 r0.c3 r1.c3], so that one
+    // dp2a against the pair (w[0][kx], w[1][kx]) of a channel does two multiply-accumulates
+    const uint32_t p01 = __byte_perm(x0, x1, 0x5140), p23 = __byte_perm(x0, x1, 0x7362);
+#pragma unroll
+    for (int kx = 0; kx < 3; ++kx) {
+      if (ic - kx >= 0 && (ic - kx) % S == 0 && (ic - kx) / S < 8) {
+        const int j = (ic - kx) / S;
+        int* a = &acc[j >> 2][4 * (j & 3)];
+        const bool first = kx == 0;   // an output's first product starts from the folded bias
+        a[0] = dp2a_su<0>(wp[kx].x, p01, first ? b4.x : a[0]);
+        a[1] = dp2a_su<1>(wp[kx].y, p01, first ? b4.y : a[1]);
+        a[2] = dp2a_su<0>(wp[kx].z, p23, first ? b4.z : a[2]);
+        a[3] = dp2a_su<1>(wp[kx].w, p23, first ? b4.w : a[3]);
+        a[0] = dp2a_su<0>(ws[kx].x, x2, a[0]);
+        a[1] = dp2a_su<0>(ws[kx].y, x2, a[1]);
+        a[2] = dp2a_su<1>(ws[kx].z, x2, a[2]);
+        a[3] = dp2a_su<1>(ws[kx].w, x2, a[3]);
+      }
+    }
+  }
+  const RequantConsts rc = make_requant_consts(p.out, p.exact_only);
+  uint8_t* out = y + ((static_cast<size_t>(n) * g.Ho + ho) * g.Wo + wo) * g.Ocp + c_slab + 4 * cw;
+  const uint4 q0 = requant_4x4(acc[0], s4, rc);
+  const uint4 q1 = requant_4x4(acc[1], s4, rc);
+  const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (wo + j < g.Wo) *reinterpret_cast<uint32_t*>(out + j * g.Ocp) = q[j];
 }
 
 // ---------------------------------------------------------------- float32 conv
@@ -1568,12 +1740,57 @@ void launch_depthwise_q(const void* x, int x_signed, int zx, const int16_t* wd, 
                                                                           static_cast<uint8_t*>(y));
 }
 
-void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* wtab, const int32_t* bias_full,
+namespace {
+constexpr int kDwStripSmem = 72 * 1024;
+
+// Tile shape of the strip form for one layer: the candidate (channel chunks per slab, strips per row, rows, images
+// per tile) with the lowest estimated instruction count over the whole layer.  A block always runs its 256 threads
+// through the arithmetic of 32 outputs each (about 540 instructions) and stages its patch at about 15 instructions
+// per 16-byte unit, so the estimate is blocks * (540 + 15 * units / 256); ties go to the wider slab.
+bool choose_dw_strip(const ConvGeom& g, DwStripGeom* best, double* best_cost) {
+  const int S = g.sx, nchunks = g.Ocp / 16;
+  bool found = false;
+  for (int cs = 2; cs >= 0; --cs) {
+    const int CK = 1 << cs, strips = 64 >> cs, slabs = (nchunks + CK - 1) / CK, px_bytes = 64 >> (2 - cs);
+    for (int ss = 0; ss <= 3; ++ss) {
+      const int SEG = 1 << ss, TW = 8 * SEG;
+      if (SEG > strips || (ss > 0 && 8 * (SEG / 2) >= g.Wo)) continue;   // a row of strips no wider than needed
+      for (int ts = 0; (SEG << ts) <= strips; ++ts) {
+        const int TH = 1 << ts;
+        if (ts > 0 && (TH / 2) >= g.Ho) continue;
+        const int NI = strips / (SEG * TH);
+        if (NI > 1 && (TH < g.Ho || TW < g.Wo)) continue;                 // several images only as whole images
+        int ns = 0;
+        while ((1 << ns) < NI) ++ns;
+        const int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;
+        // rows of a warp's consecutive strips (S patch rows apart) should start px_bytes apart modulo 128
+        int pitch = IW * px_bytes;
+        for (int k = 0; k < 8 && (S * pitch) % 128 != px_bytes % 128; ++k) pitch += 16;
+        if ((S * pitch) % 128 != px_bytes % 128) pitch = IW * px_bytes;
+        if (static_cast<size_t>(NI) * IH * pitch > static_cast<size_t>(kDwStripSmem) || IW > 255) continue;
+        if ((g.N + NI - 1) / NI > 65535 || slabs > 65535) continue;
+        const double blocks = static_cast<double>((g.Wo + TW - 1) / TW) * ((g.Ho + TH - 1) / TH) * ((g.N + NI - 1) / NI) * slabs;
+        const double cost = blocks * (540.0 + 15.0 * (static_cast<double>(NI) * IH * IW * CK) / 256.0);
+        if (!found || cost < *best_cost) {
+          found = true;
+          *best_cost = cost;
+          best->ck_shift = cs; best->seg_shift = ss; best->th_shift = ts; best->ni_shift = ns;
+          best->IH = IH; best->IW = IW; best->pitch = pitch;
+        }
+      }
+    }
+  }
+  return found;
+}
+}  // namespace
+
+void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* wtab, const uint32_t* wtab_v, const int32_t* bias_full,
                           const float* acc_scale, const ConvGeom& g, OutQuant out, int exact_only, void* y, cudaStream_t s) {
   if (static_cast<long long>(g.N) * g.Ho * g.Wo == 0) return;
   DwParams p;
   p.g = g;
   p.wtab = wtab;
+  p.wtab_v = wtab_v;
   p.bias_full = bias_full;
   p.acc_scale = acc_scale;
   p.out = out;
@@ -1588,6 +1805,39 @@ void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* w
   const size_t smem = static_cast<size_t>(g.kh) * g.kw * (p.slab / 4) * sizeof(uint4);
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* yp = static_cast<uint8_t*>(y);
+  // 3x3 windows at stride 1 or 2: the strip form (B2VX_DW_STRIP=0 keeps the 16-channel form below)
+  static const bool no_strip = [] { const char* e = std::getenv("B2VX_DW_STRIP"); return e && std::strcmp(e, "0") == 0; }();
+  if (!no_strip && wtab_v != nullptr && g.kh == 3 && g.kw == 3 && g.dx == 1 && g.dy == 1 && g.sx == g.sy && (g.sx == 1 || g.sx == 2)) {
+    DwStripGeom best{};
+    double best_cost = 0.0;
+    if (choose_dw_strip(g, &best, &best_cost)) {
+      const int CK = 1 << best.ck_shift, TH = 1 << best.th_shift, TW = 8 << best.seg_shift, NI = 1 << best.ni_shift;
+      const size_t smem_t = static_cast<size_t>(NI) * best.IH * best.pitch;
+      best.tiles_w = (g.Wo + TW - 1) / TW;
+      best.iw_recip = 65536 / best.IW + 1;
+      best.step_h = (256 / CK) / best.IW;
+      best.step_w = (256 / CK) % best.IW;
+      const dim3 grid_t(static_cast<unsigned>(best.tiles_w * ((g.Ho + TH - 1) / TH)), static_cast<unsigned>((g.N + NI - 1) / NI),
+                        static_cast<unsigned>((g.Ocp / 16 + CK - 1) / CK));
+      using StripFn = void (*)(const uint8_t*, DwParams, DwStripGeom, uint8_t*);
+      static const StripFn fns[2][2][3] = {
+          {{depthwise_strip_kernel<1, false, 0>, depthwise_strip_kernel<1, false, 1>, depthwise_strip_kernel<1, false, 2>},
+           {depthwise_strip_kernel<1, true, 0>, depthwise_strip_kernel<1, true, 1>, depthwise_strip_kernel<1, true, 2>}},
+          {{depthwise_strip_kernel<2, false, 0>, depthwise_strip_kernel<2, false, 1>, depthwise_strip_kernel<2, false, 2>},
+           {depthwise_strip_kernel<2, true, 0>, depthwise_strip_kernel<2, true, 1>, depthwise_strip_kernel<2, true, 2>}}};
+      static bool attr_set_t[64] = {false};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev < 0 || dev >= 64 || !attr_set_t[dev]) {
+        for (int a = 0; a < 2; ++a)
+          for (int b = 0; b < 2; ++b)
+            for (int c = 0; c < 3; ++c) cudaFuncSetAttribute(fns[a][b][c], cudaFuncAttributeMaxDynamicSharedMemorySize, kDwStripSmem);
+        if (dev >= 0 && dev < 64) attr_set_t[dev] = true;
+      }
+      launch_pdl(fns[g.sx - 1][x_signed ? 1 : 0][best.ck_shift], grid_t, dim3(256), smem_t, s, xp, p, best, yp);
+      return;
+    }
+  }
   {
     // staged form when the input patch of a TH x TW output tile fits comfortably in shared memory
     const int tw_shift = g.Wo <= 8 ? 3 : 4;
