@@ -51,7 +51,7 @@ def test_resnet50_full_batch_tensor_core_equals_cuda_core(tmp_path, product_lib)
 
 
 SWITCHES = [{"B2VX_TC_STORE": "tma"}, {"B2VX_TC_BRES": "0"}, {"B2VX_TC_TEAMS": "0"}, {"B2VX_FUSE_ADD": "0"},
-            {"B2VX_PDL": "0", "B2VX_CUDA_GRAPH": "0"}, {"B2VX_TC_BN": "64"}, {"B2VX_POOL_2X2": "0"}, {"B2VX_TC_HALO": "0"}, {"B2VX_DW_STRIP": "0"}]
+            {"B2VX_PDL": "0", "B2VX_CUDA_GRAPH": "0"}, {"B2VX_TC_BN": "64"}, {"B2VX_POOL_2X2": "0"}, {"B2VX_TC_HALO": "0"}, {"B2VX_DW_STRIP": "0"}, {"B2VX_DW_PIPE": "1"}]
 
 
 @pytest.mark.parametrize("net,batch", [("resnet50", 8), ("mobilenetv2", 8)])

@@ -202,6 +202,37 @@ def test_strip_form_equals_sixteen_channel_form(product_lib):
         G.assert_same(got, other)
 
 
+@pytest.mark.parametrize("name", sorted(n for n in DEPTHWISE_CASES if n not in ("dw_mult2", "dw5x5")))
+def test_pipelined_depthwise_matches_oracle(oracle_lib, product_lib, name):
+    """B2VX_DW_PIPE=1 sends every 3x3 stride-1/2 layer through the persistent, double-buffered form that large
+    layers take by default (a block walks over several tiles of its channel slab)."""
+    want, _ = G.run_case(oracle_lib, DEPTHWISE_CASES[name], seed=6)
+    os.environ["B2VX_DW_PIPE"] = "1"
+    try:
+        got, _ = G.run_case(product_lib, DEPTHWISE_CASES[name], seed=6)
+    finally:
+        os.environ.pop("B2VX_DW_PIPE", None)
+    G.assert_same(want, got)
+
+
+def test_pipelined_depthwise_many_tiles_per_block(oracle_lib, product_lib):
+    """Enough tiles that every persistent block takes several (both buffers in use, last round ragged).  The first
+    case is large enough to take the pipelined form by itself; the others are sent there."""
+    cases = [(G.depthwise_q(56, 56, 32, 120, 3, 3), None),
+             (G.depthwise_q(57, 55, 16, 500, 3, 3, stride=(2, 2)), "1"),
+             (G.depthwise_q(28, 28, 24, 200, 3, 3, x_dtype=B.DT_INT8, in_q=(0.03, 3)), "1")]
+    for case, pipe in cases:
+        want, _ = G.run_case(oracle_lib, case, seed=8)
+        for env in (pipe, "0"):
+            if env is not None:
+                os.environ["B2VX_DW_PIPE"] = env
+            try:
+                got, _ = G.run_case(product_lib, case, seed=8)
+            finally:
+                os.environ.pop("B2VX_DW_PIPE", None)
+            G.assert_same(want, got)
+
+
 FC_CASES = {
     "fc_1024_m16": G.fc_q(1024, 1024, 16),
     "fc_1024_m1": G.fc_q(1024, 1024, 1),

@@ -512,6 +512,8 @@ struct DwStripGeom {
   int tiles_w;     // tiles per output row
   int iw_recip;    // 65536 / IW + 1: (pixel * iw_recip) >> 16 = pixel / IW for pixel < 256
   int step_h, step_w;   // (256 / CK) / IW and (256 / CK) % IW: how a thread's patch pixel advances per staging round
+  int tiles_h, n_groups;   // pipelined form: tile rows per image, groups of NI images
+  int patch_bytes;         // pipelined form: NI * IH * pitch rounded up to 128
 };
 
 __device__ __forceinline__ uint4 requant16_packed(f32x2 (&real)[8], const RequantConsts& rc) {
@@ -659,6 +661,143 @@ __global__ void __launch_bounds__(256, B2VX_DW_BLOCKS) depthwise_strip_kernel(co
 #pragma unroll
   for (int j = 0; j < 8; ++j)
     if (wo + j < g.Wo) *reinterpret_cast<uint32_t*>(out + j * g.Ocp) = q[j];
+}
+
+// The strip form as a pipeline: a block stays on one channel slab, keeps its weights in registers and walks over
+// that slab's tiles (grid x = blocks per slab, z = slab).  The patch of the next tile is copied with 16-byte
+// asynchronous copies into the second of two buffers while the block computes the current one, so the copy
+// latency that a one-tile block pays in full is hidden.  Signed input bytes arrive as they are and are biased by
+// 128 when they are read from shared memory.
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+
+template <int S, bool XS, int CKS>
+__global__ void __launch_bounds__(256, 3) depthwise_strip_pipe_kernel(const uint8_t* __restrict__ x, DwParams p, DwStripGeom t,
+                                                                      uint8_t* __restrict__ y) {
+  extern __shared__ uint4 dw_smem[];               // two patches of t.patch_bytes
+  const ConvGeom& g = p.g;
+  constexpr int CK = 1 << CKS, CW = 4 * CK, PXB = 16 * CK;
+  const int TH = 1 << t.th_shift, SEG = 1 << t.seg_shift, NI = 1 << t.ni_shift;
+  const int c_slab = blockIdx.z * PXB;
+  const int slab_chunks = min(PXB, g.Ocp - c_slab) >> 4;
+  pdl_trigger();
+  const int cw = threadIdx.x & (CW - 1);
+  const int strip = threadIdx.x >> (2 + CKS);
+  const bool active = (cw >> 2) < slab_chunks;
+  const int r = strip & (TH - 1);
+  const int sgm = (strip >> t.th_shift) & (SEG - 1);
+  const int ni_s = strip >> (t.th_shift + t.seg_shift);
+  const uint32_t row_off = (ni_s * t.IH + r * S) * t.pitch + (8 * sgm * S) * PXB + 4 * cw;
+  // staging role of this thread
+  const int chunk = threadIdx.x & (CK - 1);
+  const int units = t.IH * t.IW * CK;
+  const unsigned pix0 = threadIdx.x >> CKS;
+  const int ih0 = static_cast<int>((pix0 * static_cast<unsigned>(t.iw_recip)) >> 16);
+  const int iw0 = static_cast<int>(pix0) - ih0 * t.IW;
+  const bool chunk_ok = chunk < slab_chunks;
+  const uint32_t img_bytes = static_cast<uint32_t>(g.H) * g.W * g.Cp;
+  const uint32_t zraw = p.zx_word ^ p.x_flip;       // the zero point as the input stores it
+  const uint4 zx4 = make_uint4(zraw, zraw, zraw, zraw);
+  const uint32_t smem0 = static_cast<uint32_t>(__cvta_generic_to_shared(dw_smem));
+  uint8_t* const xsm = reinterpret_cast<uint8_t*>(dw_smem);
+  const unsigned tiles_xy = static_cast<unsigned>(t.tiles_w) * t.tiles_h;
+  const unsigned T = tiles_xy * t.n_groups;
+
+  auto locate = [&](unsigned L, int& n0, int& ho0, int& wo0) {
+    const unsigned ng = L / tiles_xy, txy = L - ng * tiles_xy;
+    const unsigned th = txy / static_cast<unsigned>(t.tiles_w), tw = txy - th * t.tiles_w;
+    n0 = ng << t.ni_shift;
+    ho0 = th << t.th_shift;
+    wo0 = tw << (3 + t.seg_shift);
+  };
+  auto stage = [&](unsigned L, uint32_t buf_off) {
+    int n0, ho0, wo0;
+    locate(L, n0, ho0, wo0);
+    const int hi0 = ho0 * S - g.pt, wi0 = wo0 * S - g.pl;
+    for (int ni = 0; ni < NI; ++ni) {
+      const bool img_ok = chunk_ok && n0 + ni < g.N;
+      const uint8_t* img = x + static_cast<size_t>(img_ok ? n0 + ni : 0) * img_bytes + c_slab + 16 * chunk;
+      const uint32_t dst = buf_off + ni * t.IH * t.pitch + 16 * chunk;
+      int ih = ih0, iw = iw0;
+#pragma unroll 2
+      for (int u = threadIdx.x; u < units; u += 256) {
+        const int hi = hi0 + ih, wi = wi0 + iw;
+        const uint32_t d = dst + ih * t.pitch + iw * PXB;
+        if (img_ok && static_cast<unsigned>(hi) < static_cast<unsigned>(g.H) && static_cast<unsigned>(wi) < static_cast<unsigned>(g.W))
+          cp_async16(smem0 + d, img + static_cast<uint32_t>(hi * g.W + wi) * static_cast<uint32_t>(g.Cp));
+        else
+          *reinterpret_cast<uint4*>(xsm + d) = zx4;
+        ih += t.step_h; iw += t.step_w;
+        if (iw >= t.IW) { iw -= t.IW; ++ih; }
+      }
+    }
+  };
+
+  pdl_wait();   // the input is the first thing another kernel produced
+  unsigned L = blockIdx.x;
+  if (L < T) stage(L, 0u);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  uint4 wp[3], ws[3];
+  const int c0 = min(c_slab + 4 * cw, g.Ocp - 4);
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    wp[k] = __ldg(reinterpret_cast<const uint4*>(p.wtab_v + static_cast<size_t>(k) * g.Ocp + c0));
+    ws[k] = __ldg(reinterpret_cast<const uint4*>(p.wtab_v + static_cast<size_t>(3 + k) * g.Ocp + c0));
+  }
+  const int4 b4 = __ldg(reinterpret_cast<const int4*>(p.bias_full + c0));
+  const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.acc_scale + c0));
+  const RequantConsts rc = make_requant_consts(p.out, p.exact_only);
+  uint32_t cur = 0u, nxt = static_cast<uint32_t>(t.patch_bytes);
+  for (; L < T; L += gridDim.x) {
+    if (L + gridDim.x < T) stage(L + gridDim.x, nxt);     // that buffer was read two tiles ago; a barrier has passed since
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // this thread's copies of the current tile have landed
+    __syncthreads();                                       // ... and everybody else's
+    int n0, ho0, wo0;
+    locate(L, n0, ho0, wo0);
+    const int n = n0 + ni_s, ho = ho0 + r, wo = wo0 + 8 * sgm;
+    if (active && n < g.N && ho < g.Ho && wo < g.Wo) {
+      int acc[2][16];
+      const uint8_t* rowp = xsm + cur + row_off;
+      const uint8_t* rowp1 = rowp + t.pitch;
+      const uint8_t* rowp2 = rowp1 + t.pitch;
+#pragma unroll
+      for (int ic = 0; ic < 7 * S + 3; ++ic) {
+        uint32_t x0 = *reinterpret_cast<const uint32_t*>(rowp + ic * PXB);
+        uint32_t x1 = *reinterpret_cast<const uint32_t*>(rowp1 + ic * PXB);
+        uint32_t x2 = *reinterpret_cast<const uint32_t*>(rowp2 + ic * PXB);
+        if (XS) { x0 ^= 0x80808080u; x1 ^= 0x80808080u; x2 ^= 0x80808080u; }
+        const uint32_t p01 = __byte_perm(x0, x1, 0x5140), p23 = __byte_perm(x0, x1, 0x7362);
+#pragma unroll
+        for (int kx = 0; kx < 3; ++kx) {
+          if (ic - kx >= 0 && (ic - kx) % S == 0 && (ic - kx) / S < 8) {
+            const int j = (ic - kx) / S;
+            int* a = &acc[j >> 2][4 * (j & 3)];
+            const bool first = kx == 0;
+            a[0] = dp2a_su<0>(wp[kx].x, p01, first ? b4.x : a[0]);
+            a[1] = dp2a_su<1>(wp[kx].y, p01, first ? b4.y : a[1]);
+            a[2] = dp2a_su<0>(wp[kx].z, p23, first ? b4.z : a[2]);
+            a[3] = dp2a_su<1>(wp[kx].w, p23, first ? b4.w : a[3]);
+            a[0] = dp2a_su<0>(ws[kx].x, x2, a[0]);
+            a[1] = dp2a_su<0>(ws[kx].y, x2, a[1]);
+            a[2] = dp2a_su<1>(ws[kx].z, x2, a[2]);
+            a[3] = dp2a_su<1>(ws[kx].w, x2, a[3]);
+          }
+        }
+      }
+      uint8_t* out = y + ((static_cast<size_t>(n) * g.Ho + ho) * g.Wo + wo) * g.Ocp + c_slab + 4 * cw;
+      const uint4 q0 = requant_4x4(acc[0], s4, rc);
+      const uint4 q1 = requant_4x4(acc[1], s4, rc);
+      const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (wo + j < g.Wo) *reinterpret_cast<uint32_t*>(out + j * g.Ocp) = q[j];
+    }
+    __syncthreads();                                       // the current buffer may be overwritten from here on
+    const uint32_t tmp = cur; cur = nxt; nxt = tmp;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- float32 conv
@@ -1806,7 +1945,8 @@ void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* w
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* yp = static_cast<uint8_t*>(y);
   // 3x3 windows at stride 1 or 2: the strip form (B2VX_DW_STRIP=0 keeps the 16-channel form below)
-  static const bool no_strip = [] { const char* e = std::getenv("B2VX_DW_STRIP"); return e && std::strcmp(e, "0") == 0; }();
+  const char* strip_env = std::getenv("B2VX_DW_STRIP");   // read per launch, so that one process can run both forms
+  const bool no_strip = strip_env && std::strcmp(strip_env, "0") == 0;
   if (!no_strip && wtab_v != nullptr && g.kh == 3 && g.kw == 3 && g.dx == 1 && g.dy == 1 && g.sx == g.sy && (g.sx == 1 || g.sx == 2)) {
     DwStripGeom best{};
     double best_cost = 0.0;
@@ -1825,14 +1965,46 @@ void launch_depthwise_q16(const void* x, int x_signed, int zx, const uint32_t* w
            {depthwise_strip_kernel<1, true, 0>, depthwise_strip_kernel<1, true, 1>, depthwise_strip_kernel<1, true, 2>}},
           {{depthwise_strip_kernel<2, false, 0>, depthwise_strip_kernel<2, false, 1>, depthwise_strip_kernel<2, false, 2>},
            {depthwise_strip_kernel<2, true, 0>, depthwise_strip_kernel<2, true, 1>, depthwise_strip_kernel<2, true, 2>}}};
+      static const StripFn pipe_fns[2][2][3] = {
+          {{depthwise_strip_pipe_kernel<1, false, 0>, depthwise_strip_pipe_kernel<1, false, 1>, depthwise_strip_pipe_kernel<1, false, 2>},
+           {depthwise_strip_pipe_kernel<1, true, 0>, depthwise_strip_pipe_kernel<1, true, 1>, depthwise_strip_pipe_kernel<1, true, 2>}},
+          {{depthwise_strip_pipe_kernel<2, false, 0>, depthwise_strip_pipe_kernel<2, false, 1>, depthwise_strip_pipe_kernel<2, false, 2>},
+           {depthwise_strip_pipe_kernel<2, true, 0>, depthwise_strip_pipe_kernel<2, true, 1>, depthwise_strip_pipe_kernel<2, true, 2>}}};
+      static int sms_of[64] = {0};
       static bool attr_set_t[64] = {false};
       int dev = 0;
       cudaGetDevice(&dev);
       if (dev < 0 || dev >= 64 || !attr_set_t[dev]) {
         for (int a = 0; a < 2; ++a)
           for (int b = 0; b < 2; ++b)
-            for (int c = 0; c < 3; ++c) cudaFuncSetAttribute(fns[a][b][c], cudaFuncAttributeMaxDynamicSharedMemorySize, kDwStripSmem);
-        if (dev >= 0 && dev < 64) attr_set_t[dev] = true;
+            for (int c = 0; c < 3; ++c) {
+              cudaFuncSetAttribute(fns[a][b][c], cudaFuncAttributeMaxDynamicSharedMemorySize, kDwStripSmem);
+              cudaFuncSetAttribute(pipe_fns[a][b][c], cudaFuncAttributeMaxDynamicSharedMemorySize, kDwStripSmem);
+            }
+        if (dev >= 0 && dev < 64) {
+          cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev);
+          attr_set_t[dev] = true;
+        }
+      }
+      // Pipelined form (two patches per block, three blocks per SM) when both patches fit and the layer is large;
+      // B2VX_DW_PIPE=0 keeps one tile per block, =1 pipelines every layer whose patches fit.
+      const char* pipe_env = std::getenv("B2VX_DW_PIPE");   // read per launch plan: "0" never, "1" whenever it fits
+      const bool no_pipe = pipe_env && std::strcmp(pipe_env, "0") == 0, force_pipe = pipe_env && std::strcmp(pipe_env, "1") == 0;
+      best.tiles_h = (g.Ho + TH - 1) / TH;
+      best.n_groups = (g.N + NI - 1) / NI;
+      best.patch_bytes = static_cast<int>((smem_t + 127) & ~static_cast<size_t>(127));
+      const int sms = (dev >= 0 && dev < 64 && sms_of[dev] > 0) ? sms_of[dev] : 148;
+      // (measured on MobileNetV2 at batch 64: the pipeline wins from about four tiles per resident block on, below
+      // that the one-tile blocks, which the hardware schedules one by one, finish sooner)
+      const long long all_tiles = static_cast<long long>(grid_t.x) * grid_t.y * grid_t.z;
+      if (!no_pipe && 2 * static_cast<size_t>(best.patch_bytes) <= static_cast<size_t>(kDwStripSmem) && (force_pipe || all_tiles >= 12LL * sms)) {
+        const long long tiles = static_cast<long long>(grid_t.x) * grid_t.y;
+        long long gx = (3LL * sms) / grid_t.z;
+        if (gx < 1) gx = 1;
+        if (gx > tiles) gx = tiles;
+        const dim3 grid_p(static_cast<unsigned>(gx), 1, grid_t.z);
+        launch_pdl(pipe_fns[g.sx - 1][x_signed ? 1 : 0][best.ck_shift], grid_p, dim3(256), 2 * static_cast<size_t>(best.patch_bytes), s, xp, p, best, yp);
+        return;
       }
       launch_pdl(fns[g.sx - 1][x_signed ? 1 : 0][best.ck_shift], grid_t, dim3(256), smem_t, s, xp, p, best, yp);
       return;
