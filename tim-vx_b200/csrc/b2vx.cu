@@ -490,7 +490,7 @@ struct PackedContraction {
 // with the zero point that still has to be subtracted from it: u8 weights are
 // shifted by 128 into int8 (dz = zw-128), s8 weights are kept (dz = zw).
 // K index by k_order: 0 tap*Cs + ic; 1 ic*taps + tap (the kernel tensor's own order, used with the
-// WHCN im2col); 2 (ky*C + ic)*8 + kx (filter rows padded to 8 taps, used with the row-of-8 im2col).  Rows come in n_tiles tiles of tile_rows rows: output channel oc is row
+// WHCN im2col); 2 / 3 (ky*C + ic)*8 + kx / (ky*C + ic)*4 + kx (filter rows padded to 8 / 4 taps, used with the row-of-8 / row-of-4 im2col).  Rows come in n_tiles tiles of tile_rows rows: output channel oc is row
 // (oc / tile_data) * tile_rows + oc % tile_data; when some dz != 0 and tile_rows > tile_data, row
 // tile_data of every tile is the all-ones row (its dot product with an input row is S).
 void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* bias, int kw, int kh, int C, int Cs,
@@ -502,7 +502,7 @@ void pack_contraction(const TensorRec& x, const TensorRec& w, const TensorRec* b
   const bool per_ch = w.d.quant_type == B2VX_QUANT_SYMMETRIC_PER_CHANNEL;
   auto kidx = [&](int t, int ic) -> size_t {
     if (k_order == 1) return static_cast<size_t>(ic) * taps + t;
-    if (k_order == 2) return (static_cast<size_t>(t / kw) * C + ic) * 8 + t % kw;
+    if (k_order == 2 || k_order == 3) return (static_cast<size_t>(t / kw) * C + ic) * (k_order == 2 ? 8 : 4) + t % kw;
     return static_cast<size_t>(t) * Cs + ic;
   };
   out->rows = rows;
@@ -718,7 +718,9 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     //             zero point the border pixels get a per-class correction in the epilogue;
     //   whcn      first layers with < 16 channels: im2col straight from the WHCN graph input, K = (c,ky,kx);
     //   im2col    everything else: explicit matrix in scratch memory, padding filled with zx.
+    //   whcn8     the same with filter rows of 2..8 taps padded to 4 or 8, K = (ky,c,kx'): whole input words per piece;
     enum { IDENTITY, IMPLICIT, WHCN, WHCN8, IM2COL } mode;
+    const int padk = kw <= 4 ? 4 : 8;   // whcn8 mode: bytes per (pixel, ky, c)
     static const bool allow_strided = [] { const char* e = std::getenv("B2VX_IMPLICIT_STRIDED"); return !(e && e[0] == '0'); }();
     const bool strided = geo.sx != 1 || geo.sy != 1;
     // Border classes of an implicit convolution: output rows (columns) grouped by which ky (kx) fall
@@ -750,9 +752,9 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     }
     if (identity_1x1 || identity_full) mode = IDENTITY;
     else if (x.C >= 16 && (!need_border || classes_ok) && (!strided || allow_strided)) mode = IMPLICIT;
-    else if (x.C < 16 && (x.d.attr & B2VX_ATTR_INPUT) && x.d_io != nullptr && kw >= 5 && kw <= 8 && geo.dx == 1 && geo.dy == 1 &&
-             static_cast<size_t>(x.C) * kh * im2col_whcn8_pitch(geo) + 16 <= 40u * 1024u)
-      mode = WHCN8;  // wide filter rows: 8 consecutive input bytes per (pixel, ky, c)
+    else if (x.C < 16 && (x.d.attr & B2VX_ATTR_INPUT) && x.d_io != nullptr && kw >= 2 && kw <= 8 && geo.dx == 1 && geo.dy == 1 &&
+             static_cast<size_t>(x.C) * kh * im2col_whcn8_pitch(geo, padk) + 16 <= 40u * 1024u)
+      mode = WHCN8;  // filter rows of up to 8 (or 4) taps: 8 (or 4) consecutive input bytes per (pixel, ky, c)
     else if (x.C < 16 && (x.d.attr & B2VX_ATTR_INPUT) && x.d_io != nullptr &&
              static_cast<size_t>(x.C) * kh * ((geo.Wo - 1) * geo.sx + (kw - 1) * geo.dx + 1) + 4u * round_up(taps * x.C, 16) <= 40u * 1024u)
       mode = WHCN;   // the staging rows of one output row fit in shared memory
@@ -767,7 +769,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     else if (mode == WHCN8) {
       // rows of the matrix are read by TMA in 64- or 128-byte pieces: a pitch that is a multiple of 64
       // keeps every piece on whole 32-byte sectors
-      Cs = x.C; Kp = round_up(kh * x.C * 8, 16); if (Kp > 64) Kp = round_up(Kp, 64); M = static_cast<int>(P);
+      Cs = x.C; Kp = round_up(kh * x.C * padk, 16); if (Kp > 64) Kp = round_up(Kp, 64); M = static_cast<int>(P);
     }
     else { Cs = x.C < 16 ? x.C : x.Cp; Kp = round_up(taps * Cs, 16); M = static_cast<int>(P); }
     // Few rows (decode-like FullyConnected, 1x1 on a handful of pixels): weight streaming on CUDA cores.
@@ -797,7 +799,7 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     }
     const GemmTcTiling tiling = gemm_tc_choose_tiling(M, y.Cp, Kp, any_dz ? 1 : 0);
     const int Np = tiling.n_tiles * tiling.rows;
-    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, tiling.n_tiles, tiling.data, tiling.rows, mode == WHCN ? 1 : (mode == WHCN8 ? 2 : 0), &pk);
+    pack_contraction(x, w, bias, kw, kh, x.C, Cs, Kp, y.C, y.Cp, tiling.n_tiles, tiling.data, tiling.rows, mode == WHCN ? 1 : (mode == WHCN8 ? (padk == 8 ? 2 : 3) : 0), &pk);
     ep.dz_uniform = any_dz ? dz_value : 0;
     if (mode == IMPLICIT && need_border) {
       // correction of class (r, c) = minus the folded contribution of every tap that is out of bounds there
@@ -882,9 +884,9 @@ b2vx_status plan_contraction(b2vx_graph* g, uint32_t node_index, const char* lab
     if (mode == WHCN8) {
       const void* xio = x.d_io;
       Step s_col;
-      s_col.info = make_info("im2col_whcn8", node_index, 0, x.elems() + static_cast<uint64_t>(M) * Kp);
+      s_col.info = make_info(padk == 8 ? "im2col_whcn8" : "im2col_whcn4", node_index, 0, x.elems() + static_cast<uint64_t>(M) * Kp);
       s_col.fn = [=](cudaStream_t st2) {
-        launch_im2col_whcn8(xio, Kp, zx, geo, g->scratch, st2);
+        launch_im2col_whcn8(xio, Kp, zx, geo, padk, g->scratch, st2);
         return cudaGetLastError();
       };
       g->steps.push_back(std::move(s_col));

@@ -194,11 +194,11 @@ void launch_im2col(const void* x, int Cs, int Kp, int zx, const ConvGeom& g, voi
 // The same matrix straight from a WHCN tensor [N][C][H][W] with few channels (network inputs):
 // K index = (c*kh + ky)*kw + kx, the kernel tensor's own element order.
 void launch_im2col_whcn(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s);
-// The same for filters up to 8 wide (dilation 1) with K index = (ky*C + c)*8 + kx: every (pixel, ky, c)
-// contributes 8 consecutive input bytes, slot kx >= kw carrying a don't-care byte (zero weight).
-// Shared memory needed per block: C * kh * im2col_whcn8_pitch(g) + 16 bytes.
-void launch_im2col_whcn8(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s);
-int im2col_whcn8_pitch(const ConvGeom& g);
+// The same for filters up to padk = 8 or 4 wide (dilation 1) with K index = (ky*C + c)*padk + kx: every (pixel, ky, c)
+// contributes padk consecutive input bytes, slot kx >= kw carrying a don't-care byte (zero weight).
+// Shared memory needed per block: C * kh * im2col_whcn8_pitch(g, padk) + 16 bytes.
+void launch_im2col_whcn8(const void* x, int Kp, int zx, const ConvGeom& g, int padk, void* col, cudaStream_t s);
+int im2col_whcn8_pitch(const ConvGeom& g, int padk);
 
 // ---- int8 GEMM on tcgen05 tensor cores --------------------------------------
 // D[M][ldd] (u8/s8) = requant(A[M][Kp] (u8 or s8) * B[Np][Kp]^T (s8)), K-major

@@ -1642,6 +1642,7 @@ __global__ void im2col_whcn_kernel(const uint8_t* __restrict__ x, int Kp, int zx
 // gathered bytes.  The byte in the padding slot (kx >= kw) belongs to the neighbouring pixel; its
 // weight is zero.  One block per output row (n, ho); staged rows have pitch `pitch` (a multiple of 4,
 // at least 8 bytes beyond the last input column used).
+template <int PADK>
 __global__ void __launch_bounds__(256) im2col_whcn8_kernel(const uint8_t* __restrict__ x, int Kp, int zx, ConvGeom g, int pitch,
                                                            uint8_t* __restrict__ col) {
   pdl_wait();
@@ -1695,16 +1696,28 @@ __global__ void __launch_bounds__(256) im2col_whcn8_kernel(const uint8_t* __rest
   for (int q = threadIdx.x; q < g.Wo * chunks; q += 256, wo += step_wo, ch += step_ch) {
     if (ch >= chunks) { ch -= chunks; ++wo; }
     uint32_t w4[4] = {0, 0, 0, 0};
+    if (PADK == 8) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = 2 * ch + h;
-      if (r < rows) {
-        const int byte = r * pitch + wo * g.sx + shift0;
-        const uint32_t* wp = sm_words + (byte >> 2);
-        const uint32_t sh = (byte & 3) * 8;
-        const uint32_t a0 = wp[0], a1 = wp[1], a2 = wp[2];
-        w4[2 * h] = __funnelshift_r(a0, a1, sh);
-        w4[2 * h + 1] = __funnelshift_r(a1, a2, sh);
+      for (int h = 0; h < 2; ++h) {
+        const int r = 2 * ch + h;
+        if (r < rows) {
+          const int byte = r * pitch + wo * g.sx + shift0;
+          const uint32_t* wp = sm_words + (byte >> 2);
+          const uint32_t sh = (byte & 3) * 8;
+          const uint32_t a0 = wp[0], a1 = wp[1], a2 = wp[2];
+          w4[2 * h] = __funnelshift_r(a0, a1, sh);
+          w4[2 * h + 1] = __funnelshift_r(a1, a2, sh);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const int r = 4 * ch + h;
+        if (r < rows) {
+          const int byte = r * pitch + wo * g.sx + shift0;
+          const uint32_t* wp = sm_words + (byte >> 2);
+          w4[h] = __funnelshift_r(wp[0], wp[1], (byte & 3) * 8);
+        }
       }
     }
     *reinterpret_cast<uint4*>(out + static_cast<size_t>(wo) * Kp + ch * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
@@ -2433,19 +2446,22 @@ void launch_fc_small_m(const void* A, int a_signed, const int8_t* B, int M, int 
   else launch_fc_small_m_t<4, 16>(A, a_signed, B, M, Kp, Oc, Ocp, e, D, ldd, s);
 }
 
-void launch_im2col_whcn8(const void* x, int Kp, int zx, const ConvGeom& g, void* col, cudaStream_t s) {
+void launch_im2col_whcn8(const void* x, int Kp, int zx, const ConvGeom& g, int padk, void* col, cudaStream_t s) {
   if (g.N == 0 || g.Ho == 0 || g.Wo == 0) return;
-  const int pitch = im2col_whcn8_pitch(g);
+  const int pitch = im2col_whcn8_pitch(g, padk);
   const size_t smem = static_cast<size_t>(g.C) * g.kh * pitch + 16;
   dim3 grid(g.Ho, g.N);
-  launch_pdl(im2col_whcn8_kernel, dim3(grid), dim3(256), smem, s, static_cast<const uint8_t*>(x), Kp, zx, g, pitch,
-             static_cast<uint8_t*>(col));
+  if (padk == 8)
+    launch_pdl(im2col_whcn8_kernel<8>, dim3(grid), dim3(256), smem, s, static_cast<const uint8_t*>(x), Kp, zx, g, pitch,
+               static_cast<uint8_t*>(col));
+  else
+    launch_pdl(im2col_whcn8_kernel<4>, dim3(grid), dim3(256), smem, s, static_cast<const uint8_t*>(x), Kp, zx, g, pitch,
+               static_cast<uint8_t*>(col));
 }
-
-int im2col_whcn8_pitch(const ConvGeom& g) {
-  // up to 3 bytes of alignment lead, the 8-byte read of the last pixel, the third word of the funnel
-  // shift; 4 mod 64 spreads consecutive row pairs over the banks
-  const int need = 3 + (g.Wo - 1) * g.sx + 8 + 4;
+int im2col_whcn8_pitch(const ConvGeom& g, int padk) {
+  // up to 3 bytes of alignment lead, the padk-byte read of the last pixel, the last word of the funnel
+  // shift; 4 mod 64 spreads consecutive rows over the banks
+  const int need = 3 + (g.Wo - 1) * g.sx + padk + 4;
   int pitch = (need + 3) & ~3;
   while ((pitch & 63) != 4) pitch += 4;
   return pitch;
