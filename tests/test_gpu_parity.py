@@ -76,6 +76,9 @@ CONV_CASES = {
     "cfg2_3x3_n1": G.conv2d_q(56, 56, 64, 1, 3, 3, 64, relu=True),
     "cfg2_3x3_n3": G.conv2d_q(56, 56, 64, 3, 3, 3, 64, relu=True),
     "cfg2_1x1": G.conv2d_q(56, 56, 64, 2, 1, 1, 64, relu=True),
+    # more than eight 128-row tiles per SM with a short K: tiles of 65-128 columns also go one per warp group
+    "many_tiles_16_96_u8": G.conv2d_q(448, 400, 16, 1, 1, 1, 96, w_kind="u8", relu=True),
+    "many_tiles_64_128": G.conv2d_q(224, 224, 64, 4, 1, 1, 128, in_q=(0.02, 3)),
     "cfg2_3x3_s2": G.conv2d_q(56, 56, 64, 2, 3, 3, 64, stride=(2, 2), relu=True),
     # channel counts that need padding, odd sizes, ragged tiles
     "c24_oc40": G.conv2d_q(13, 11, 24, 2, 3, 3, 40),

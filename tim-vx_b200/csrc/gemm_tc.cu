@@ -1010,7 +1010,7 @@ namespace {
 // turns out to allow the halo mode of the implicit convolution (0: not asked for).
 bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp, int Kspan, int taps, int ldd,
                  const ContractEpilogue& e, void* D, int* status, const char** why, const GemmTcTiling* tiling, int halo_w = 0,
-                 int halo_h = 0, bool want_pair = false) {
+                 int halo_h = 0, bool want_pair = false, bool wide_teams = false) {
   GemmParams& p = plan->params;
   p.Ocp = ldd;
   p.ldd = ldd;
@@ -1048,7 +1048,9 @@ bool finish_plan(GemmTcPlan* plan, const int8_t* B, int a_signed, int Np, int Kp
   if (!tma_store || e.add_residual != nullptr) p.store_span = 0;
   const size_t add_table_bytes = e.add_residual != nullptr ? 65536 : 0;
   static const bool no_teams = [] { const char* e2 = std::getenv("B2VX_TC_TEAMS"); return e2 && std::strcmp(e2, "0") == 0; }();
-  p.teams = (p.BNd <= 64 && p.store_span == 0 && !no_teams) ? kGroups : 0;
+  // (wide_teams: the caller found the launch bound by its epilogue, short K and many tiles per CTA, so tiles of up to 128
+  // columns also go one per warp group: four tiles in flight instead of four passes over every tile)
+  p.teams = ((p.BNd <= 64 || (wide_teams && p.BN <= 128)) && p.store_span == 0 && !no_teams) ? kGroups : 0;
   if (p.teams) p.res_span = 0;   // four tiles in flight do not fit the two residual buffers: threads load their pieces
   if (p.res_span) {
     // The Add's table and two residual tiles leave less for the operand ring: three stages must remain,
@@ -1188,7 +1190,8 @@ GemmTcPlan* gemm_tc_plan_create(const void* A, int a_signed, const int8_t* B, in
   }
   const long long tiles_256 = static_cast<long long>((M + kBlockM - 1) / kBlockM) * ((Np + 255) / 256);
   const bool want_pair = Kp >= 4096 && tiles_256 >= 2LL * sms;
-  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why, tiling, 0, 0, want_pair)) {
+  const bool wide_teams = Kp <= 128 && static_cast<long long>((M + kBlockM - 1) / kBlockM) >= 8LL * sms;
+  if (!finish_plan(plan, B, a_signed, Np, Kp, Kp, 1, ldd, e, D, status, &why, tiling, 0, 0, want_pair, wide_teams)) {
     delete plan;
     return fail(why);
   }
