@@ -83,6 +83,16 @@ CONV_CASES = {
     # channel counts that need padding, odd sizes, ragged tiles
     "c24_oc40": G.conv2d_q(13, 11, 24, 2, 3, 3, 40),
     "c3_stem7x7": G.conv2d_q(32, 32, 3, 2, 7, 7, 64, stride=(2, 2), pad_type=B.PAD_AUTO, pad=(3, 3, 3, 3)),
+    # first layers (graph inputs with few channels) at strides 2 and 4: channel counts 1-8, filter rows of 2-8 taps, odd and
+    # even left padding, a weight zero point (ones row), signed input
+    "stem_3x3_s2_c3_u8": G.conv2d_q(224, 224, 3, 2, 3, 3, 32, stride=(2, 2), w_kind="u8", relu=True),
+    "stem_7x7_s2_c3": G.conv2d_q(75, 61, 3, 3, 7, 7, 64, stride=(2, 2), pad_type=B.PAD_AUTO, pad=(3, 3, 3, 3), relu=True),
+    "stem_5x5_s2_c1": G.conv2d_q(28, 28, 1, 2, 5, 5, 20, stride=(2, 2), in_q=(0.02, 7)),
+    "stem_8x3_s2_c8_nopad": G.conv2d_q(40, 21, 8, 2, 8, 3, 24, stride=(2, 2), pad_type=B.PAD_VALID),
+    "stem_2x2_s2_c4_s8in": G.conv2d_q(30, 30, 4, 2, 2, 2, 16, stride=(2, 2), pad_type=B.PAD_VALID, x_dtype=B.DT_INT8, in_q=(0.02, -5)),
+    "stem_6x6_s2_pad2": G.conv2d_q(33, 35, 2, 1, 6, 6, 48, stride=(2, 2), pad_type=B.PAD_AUTO, pad=(2, 2, 2, 2), w_kind="u8"),
+    "stem_4x4_s4_c3": G.conv2d_q(64, 48, 3, 2, 4, 4, 96, stride=(4, 4), pad_type=B.PAD_VALID),
+    "stem_7x1_s2": G.conv2d_q(50, 9, 3, 1, 7, 1, 16, stride=(2, 2), pad_type=B.PAD_AUTO, pad=(3, 3, 0, 0)),
     "c1_5x5_valid": G.conv2d_q(28, 28, 1, 2, 5, 5, 20, pad_type=B.PAD_VALID, w_kind="u8z128", in_q=(1 / 255.0, 0), out_q=(0.05, 128)),
     "u8_weights_zp": G.conv2d_q(10, 9, 20, 2, 3, 3, 50, w_kind="u8", out_q=(0.3, 121)),
     "u8_weights_1x1": G.conv2d_q(7, 7, 96, 3, 1, 1, 24, w_kind="u8", out_q=(0.2, 130)),
