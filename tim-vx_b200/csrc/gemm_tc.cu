@@ -568,16 +568,33 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t px16 = static_cast<uint32_t>(p.BK) >> 4;           // one pixel of the patch, in 16-byte units
             const int taps_h = p.num_kb_b / (p.cblocks * p.kw);
             bool first = accumulate == 0;
-            for (int ky = 0; ky < taps_h; ++ky) {
-              uint32_t a_lo = static_cast<uint32_t>(da0) + static_cast<uint32_t>(ky * p.halo_w) * px16;
-              for (int kx = 0; kx < p.kw; ++kx, a_lo += px16, b_lo += db_step) {
-                if (first) {
-                  tc_mma_i8_halves<0>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
-                  first = false;
-                } else {
-                  tc_mma_i8_halves<1>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+            if (p.kw == 3 && taps_h == 3) {
+              // The 3x3 window written out (halo mode always has 64-byte channel blocks: a pixel is four 16-byte units,
+              // two k steps): eighteen instructions whose descriptors differ by constants, no loop control between them.
+              uint32_t a_row = static_cast<uint32_t>(da0);
+              const uint32_t row16 = static_cast<uint32_t>(p.halo_w) * 4u;
+#pragma unroll
+              for (int ky = 0; ky < 3; ++ky, a_row += row16) {
+#pragma unroll
+                for (int kx = 0; kx < 3; ++kx, b_lo += db_step) {
+                  const uint32_t a_lo = a_row + 4u * kx;
+                  if (ky == 0 && kx == 0 && first) tc_mma_i8_halves<0>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+                  else tc_mma_i8_halves<1>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+                  tc_mma_i8_halves<1>(tmem_d, a_lo + 2u, a_hi, b_lo + 2u, b_hi, p.idesc);
                 }
-                for (int k = 1; k < ksteps; ++k) tc_mma_i8_halves<1>(tmem_d, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, p.idesc);
+              }
+            } else {
+              for (int ky = 0; ky < taps_h; ++ky) {
+                uint32_t a_lo = static_cast<uint32_t>(da0) + static_cast<uint32_t>(ky * p.halo_w) * px16;
+                for (int kx = 0; kx < p.kw; ++kx, a_lo += px16, b_lo += db_step) {
+                  if (first) {
+                    tc_mma_i8_halves<0>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+                    first = false;
+                  } else {
+                    tc_mma_i8_halves<1>(tmem_d, a_lo, a_hi, b_lo, b_hi, p.idesc);
+                  }
+                  for (int k = 1; k < ksteps; ++k) tc_mma_i8_halves<1>(tmem_d, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, p.idesc);
+                }
               }
             }
             tc_commit(smem_u32(&hdr->empty[s]));
