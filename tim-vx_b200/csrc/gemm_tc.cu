@@ -146,7 +146,7 @@ struct GemmParams {
   // TN = 1), and the kh * kw taps are MMAs on shifted views of it: descriptor start = patch + (ky * halo_w + kx) * BK,
   // distance between 8-row groups = halo_w * BK.  The 64-byte swizzle is a function of the absolute shared-memory
   // address on both sides (TMA write, MMA read), so a view may start on any pixel.
-  int halo, halo_w;
+  int halo, halo_w, halo_kh;   // halo_kh: filter rows (kept here so that the issuing thread does not divide)
   uint32_t a_stage_bytes;  // halo mode: bytes of a stage (the patch, rounded up to 1 KB)
   int num_kb_b;            // k-blocks of the weight tile (kh * kw * cblocks; == num_kb unless halo)
   // Pair mode (plain GEMM with a long K loop): a CTA works on two of its M tiles at once, one per accumulator buffer,
@@ -566,7 +566,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             uint32_t b_lo = static_cast<uint32_t>(db0);
             const uint32_t db_step = (static_cast<uint32_t>(p.cblocks) * b_bytes) >> 4;
             const uint32_t px16 = static_cast<uint32_t>(p.BK) >> 4;           // one pixel of the patch, in 16-byte units
-            const int taps_h = p.num_kb_b / (p.cblocks * p.kw);
+            const int taps_h = p.halo_kh;
             bool first = accumulate == 0;
             if (p.kw == 3 && taps_h == 3) {
               // The 3x3 window written out (halo mode always has 64-byte channel blocks: a pixel is four 16-byte units,
@@ -1291,6 +1291,7 @@ GemmTcPlan* gemm_tc_conv_plan_create(const void* X, int x_signed, const int8_t* 
   p.kw = g.kw; p.sx = g.sx; p.sy = g.sy; p.dx = g.dx; p.dy = g.dy; p.pl = g.pl; p.pt = g.pt;
   p.Cp = g.Cp;
   p.cblocks = (g.Cp + p.BK - 1) / p.BK;
+  p.halo_kh = g.kh;
   p.num_kb = p.halo ? p.cblocks : g.kh * g.kw * p.cblocks;   // stages per tile: one patch per channel block, or one box per tap and block
   p.a_tx_bytes = p.halo ? static_cast<uint32_t>(halo_w * halo_h) * p.BK : static_cast<uint32_t>(bw * bh * bn) * p.BK;
   const uint64_t dims[4] = {static_cast<uint64_t>(g.Cp), static_cast<uint64_t>(g.W), static_cast<uint64_t>(g.H), static_cast<uint64_t>(g.N)};
