@@ -546,7 +546,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer loop (profiler captures)")
     ap.add_argument("--no-configs", action="store_true", help="skip the extra configurations (N=1, default workload)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained replay")
-    ap.add_argument("--streams", type=int, default=2,
+    ap.add_argument("--streams", type=int, default=3,
                     help="graph replicas replayed concurrently, each on its own CUDA stream with its own resident batch (the device-resident "
                          "value; 1 = one graph back to back, which the line also reports as single_stream)")
     ap.add_argument("--e2e-threads", type=int, default=4,
