@@ -499,6 +499,10 @@ FUSED_ADD_CASES = {
     "int8_everything": conv_then_add(10, 10, 16, 2, 1, 32, dtype=B.DT_INT8, in_q=(0.05, -3), conv_q=(0.1, 4), res_q=(0.08, -9),
                                      out_q=(0.15, -128)),
     "oc_300_two_tiles": conv_then_add(7, 7, 64, 2, 1, 300),
+    # more than eight tiles per SM with a short K: tiles of 65-128 columns go one per warp group, the residual's pieces
+    # loaded by the epilogue threads themselves
+    "many_tiles_64_96": conv_then_add(448, 400, 64, 1, 1, 96),
+    "many_tiles_32_112_u8w": conv_then_add(448, 360, 32, 1, 1, 112, w_kind="u8", in_q=(0.03, 0)),
 }
 
 
